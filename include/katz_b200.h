@@ -1,0 +1,144 @@
+/*
+ * katz_b200 C ABI: the boundary a host program binds (ctypes / cffi / a TORCH_LIBRARY shim) to run the SDXL UNet
+ * denoising step with adapters on one B200. It stands where the reference's `fast_kernel` torch extension and the
+ * PyTorch library calls around it stand. Citations are file:line inside the reference project.
+ *
+ * Conventions (all entry points):
+ *   - plain pointers and sizes; every pointer is DEVICE memory unless the name starts with `h_`;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream); nothing synchronises, nothing
+ *     allocates unless the comment says so, so calls can be captured into a CUDA graph;
+ *   - return value: 0 = launched; < 0 = argument error (KATZ_E*), nothing launched; > 0 = a cudaError_t;
+ *   - activations are fp16, NHWC / token-major ([B, H*W, C]); weights are fp16 [N, K] row-major; convolution weights
+ *     are [Cout, ky, kx, Cin] (torch's [Cout, Cin, ky, kx] permuted once at load time).
+ */
+#ifndef KATZ_B200_H_
+#define KATZ_B200_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KATZ_ABI_VERSION 1
+
+#define KATZ_E_INVAL (-1)    /* null pointer / bad enum */
+#define KATZ_E_ALIGN (-2)    /* pointer or stride not aligned as the kernel needs */
+#define KATZ_E_SIZE (-3)     /* shape outside what the kernel supports */
+#define KATZ_E_NOTREADY (-4) /* driver entry point or device set-up missing */
+#define KATZ_E_DEVICE (-5)   /* a bounded device-side wait gave up */
+
+#define KATZ_DTYPE_F16 0
+#define KATZ_DTYPE_F32 1
+
+#define KATZ_ACT_NONE 0
+#define KATZ_ACT_SILU 1
+
+int katz_abi_version(void);
+/* Name of the GPU architecture the library was built for ("sm_100a"). */
+const char* katz_build_arch(void);
+
+/* ------------------------------------------------------------------------------------------------ LoRA merge ---- */
+#define KATZ_LORA_MAX_ADAPTERS 4
+
+/* One targeted linear. W is the live weight [out, in]; W0 (optional) the pristine copy it is rebuilt from.
+ * B[i] = lora up [out, rank[i]], A[i] = lora down [rank[i], in], same dtype as W; scale[i] = alpha_i / rank_i * user
+ * scale (the reference hard-codes 20000/64, lora_utils.py:22). */
+typedef struct katz_lora_layer {
+    void* W;
+    const void* W0;
+    const void* B[KATZ_LORA_MAX_ADAPTERS];
+    const void* A[KATZ_LORA_MAX_ADAPTERS];
+    int rank[KATZ_LORA_MAX_ADAPTERS];
+    float scale[KATZ_LORA_MAX_ADAPTERS];
+    int out_features;
+    int in_features;
+    int n_lora;
+    int reserved_;
+} katz_lora_layer;
+
+/* Tile geometry the caller needs to build `d_tile_start`: layer i owns
+ * ceil(out/tile_rows) * ceil(in/tile_cols) consecutive tiles starting at tile_start[i]. */
+int katz_lora_tile_rows(int w_dtype);
+int katz_lora_tile_cols(void);
+/* Host-side validation of one table entry before it is uploaded. */
+int katz_lora_layer_check(const katz_lora_layer* h_layer, int w_dtype);
+/* W = (W0 ? W0 : W) + sign * sum_i scale_i * B_i @ A_i over every layer of the table, one launch.
+ * Replaces lora_utils.patch_on_lora's loop (lora_utils.py:28-33), StableDiffusionXLControlNetPipelineKatz.patch_on_lora
+ * (pipelines/controlnet/pipeline_controlnet_sd_xl_katz.py:1741-1747) and, with n_lora = 0 and W0 set, the restore
+ * `unet.load_state_dict(deepcopy(default_unet_state_dict))` (sdxl_unet_server.py:217). sign = -1 with W0 = NULL is the
+ * subtractive unmerge of LoRACompatibleLinear._unfuse_lora (diffusers/models/lora.py:427-449). */
+int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_tile_start, int n_layers, int total_tiles, int w_dtype,
+                    float sign, void* stream);
+
+/* -------------------------------------------------------------------------------------- fast_kernel drop-ins ---- */
+/* fast_kernel::group_norm_fp16 (fast_kernel/csrc/group_norm.cuh:7-15, group_norm.cu:224-274), channels-last input.
+ * `scratch` holds per-slab partial sums: katz_group_norm_scratch_bytes() bytes, contents undefined on return. */
+long long katz_group_norm_scratch_bytes(int B, int HW, int C, int G);
+int katz_group_norm_nhwc_f16(const void* x, void* y, const void* gamma, const void* beta, int B, int HW, int C, int G,
+                             float eps, int act, void* scratch, long long scratch_bytes, void* stream);
+/* Same op for a channels-first tensor (the `channels_first` branch of group_norm.cu:162-206). */
+int katz_group_norm_nchw_f16(const void* x, void* y, const void* gamma, const void* beta, int B, int HW, int C, int G,
+                             float eps, int act, void* stream);
+/* fast_kernel::fast_gelu_mul_fp16 (fast_kernel/csrc/gelu.cuh:44-59): out = fast_gelu(x) * m, n elements. */
+int katz_fast_gelu_mul_f16(const void* x, const void* m, void* out, long long n, void* stream);
+
+/* --------------------------------------------------------------------------------------------- UNet step ops ---- */
+/* nn.LayerNorm(C, eps, affine) over `rows` rows (diffusers/models/attention.py:195,225,253). */
+int katz_layer_norm_f16(const void* x, void* y, const void* gamma, const void* beta, int rows, int C, float eps,
+                        void* stream);
+/* Unfused GEGLU gating of the torch path (diffusers/models/activations.py:146-149): hg = [M, 2F] (row stride ld),
+ * out[M, F] = hg[:, :F] * gelu_erf(hg[:, F:]). */
+int katz_geglu_erf_f16(const void* hg, void* out, long long M, int F, int ld, void* stream);
+
+/* C[M,N] = A[M,K] @ W[N,K]^T (+bias[N]) (+rowvec[m / rows_per_batch, n]) -> act -> (+residual[M,N]) * out_scale.
+ * nn.Linear as used by Attention / FeedForward / Transformer2DModel (attention_processor.py:1256-1284,
+ * attention.py:649, transformer_2d.py:404-409,479-527) and TimestepEmbedding (embeddings.py:190-235).
+ * `_mma` is the general-shape kernel on the legacy mma.sync path. */
+int katz_linear_f16_mma(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, int K, const void* bias,
+                        const void* rowvec, int ld_rowvec, int rows_per_batch, const void* residual, int ldr, int act,
+                        float out_scale, void* stream);
+
+/* NHWC convolution as implicit GEMM. Input is X[B, Hs, Ws, C1] (optionally channel-concatenated with
+ * X2[B, Hs, Ws, C2], the skip connection of CrossAttnUpBlock2D/UpBlock2D, unet_2d_blocks.py:2473,2608); with
+ * `upsample` the input is read through a nearest-neighbour 2x upsample (Upsample2D, upsampling.py:141-186) and
+ * Hin, Win are the upsampled sizes. Epilogue as katz_linear_f16 with rows_per_batch = Hout*Wout (the time-embedding
+ * add of ResnetBlock2D, resnet.py:381-390, and its shortcut add, resnet.py:410-413). */
+int katz_conv2d_nhwc_f16_mma(const void* X, const void* X2, const void* W, void* Y, int B, int Hin, int Win, int C1,
+                             int C2, int Cout, int ksize, int stride, int pad, int upsample, const void* bias,
+                             const void* rowvec, int ld_rowvec, const void* residual, int act, float out_scale,
+                             void* stream);
+
+/* softmax(Q K^T * scale) V per (batch, head), head_dim 64, no mask (F.scaled_dot_product_attention as called at
+ * attention_processor.py:1276). Q/K/V/O are [B, S, ld*] token-major with head h at columns [64h, 64h+64);
+ * bs* are batch strides in elements. */
+int katz_attention_f16_mma(const void* Q, const void* K, const void* V, void* O, int B, int H, int Sq, int Sk,
+                           int head_dim, int ldq, int ldk, int ldv, int ldo, long long bsq, long long bsk,
+                           long long bsv, long long bso, float scale, void* stream);
+
+/* dst = src + half(sum_i scales[i] * residuals[i]) — ControlNet residual intake (unet_2d_condition.py:1281-1292; the
+ * sum / mean over nets of :1418-1439). `h_residuals` and `h_scales` are HOST arrays of n_res entries (device pointers
+ * inside). */
+int katz_residual_intake_f16(const void* src, void* dst, const void* const* h_residuals, const float* h_scales,
+                             int n_res, long long n, void* stream);
+/* get_timestep_embedding (diffusers/models/embeddings.py:26-66), flip_sin_to_cos, shift 0: out[rows, dim] fp16. */
+int katz_timestep_embedding_f16(const float* t, void* out, int rows, int dim, int ld_out, void* stream);
+int katz_silu_f16(const void* x, void* y, long long n, void* stream);
+int katz_add_f16(const void* a, const void* b, void* y, long long n, void* stream);
+/* y[rows, C1+C2] = x1[rows, C1] ++ x2[rows, C2]: torch.cat([hidden, skip], dim=1) of the up blocks
+ * (diffusers/models/unets/unet_2d_blocks.py:2473,2608) in NHWC. */
+int katz_concat_channels_f16(const void* x1, const void* x2, void* y, long long rows, int C1, int C2, void* stream);
+/* Layout moves at the model boundary: NCHW (C channels) <-> NHWC with Cpad >= C channels (extra channels zero). */
+int katz_nchw_to_nhwc_f16(const void* x, void* y, int B, int C, int HW, int Cpad, void* stream);
+int katz_nhwc_to_nchw_f16(const void* x, void* y, int B, int C, int HW, int Cpad, void* stream);
+
+/* EulerDiscreteScheduler.scale_model_input (schedulers/scheduling_euler_discrete.py:294-295): out = half(x / sqrt(sigma^2+1)),
+ * written `copies` times back to back (the CFG batch). x is the fp16 latent. */
+int katz_euler_scale_input(const void* x, void* out, long long n, float sigma, int copies, void* stream);
+/* CFG combine (pipeline_controlnet_sd_xl_katz.py:1649-1655) + EulerDiscreteScheduler.step (:498-537, epsilon
+ * prediction, s_churn 0) in place on the fp16 latent x. eps_cond may be NULL (no guidance). */
+int katz_euler_cfg_step(void* x, const void* eps_uncond, const void* eps_cond, long long n, float guidance, float sigma,
+                        float sigma_next, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KATZ_B200_H_ */

@@ -1,0 +1,270 @@
+// Small streaming kernels of the UNet step: GEGLU gating, residual intake, embeddings, layout moves, Euler/CFG.
+#include "common.cuh"
+#include "katz_b200.h"
+
+namespace katz {
+
+__device__ __forceinline__ float rh(float v) { return __half2float(__float2half_rn(v)); }
+
+// fast_kernel::fast_gelu_mul_fp16 (fast_kernel/csrc/gelu.cuh:29-42): half arithmetic with one float tanh,
+// out = 0.5*x*(1+tanh(0.79788456*(x+0.044715*x^3)))*m, every intermediate rounded to half as the reference does.
+__device__ __forceinline__ float fast_gelu_mul_one(float x, float m) {
+    const float alpha = rh(0.7978845608028654f), beta = rh(0.044714998453855515f);
+    float t = rh(beta * x);
+    t = rh(t * x);
+    t = rh(t * x);
+    t = rh(x + t);
+    t = rh(alpha * t);
+    float th = rh(tanhf(t));
+    float r = rh(0.5f * x);
+    r = rh(r * rh(1.0f + th));
+    return rh(r * m);
+}
+
+__global__ void fast_gelu_mul_kernel(const __half2* __restrict__ x, const __half2* __restrict__ m, __half2* __restrict__ out,
+                                     long long npairs) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < npairs; i += (long long)gridDim.x * blockDim.x) {
+        float2 xv = __half22float2(x[i]), mv = __half22float2(m[i]);
+        out[i] = __floats2half2_rn(fast_gelu_mul_one(xv.x, mv.x), fast_gelu_mul_one(xv.y, mv.y));
+    }
+}
+
+// Unfused GEGLU of the reference torch path (activations.py:146-149): h, g = chunk(proj(x)); h * gelu(g), erf GELU,
+// gelu result and product each rounded to half as torch's fp16 ops do.
+__global__ void geglu_erf_kernel(const __half* __restrict__ hg, __half* __restrict__ out, long long M, int F, int ld) {
+    const int FP = F >> 1;
+    const long long total = M * FP;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        long long r = i / FP;
+        int c = (int)(i - r * FP) * 2;
+        const __half* row = hg + r * ld;
+        float2 h = __half22float2(*reinterpret_cast<const __half2*>(row + c));
+        float2 g = __half22float2(*reinterpret_cast<const __half2*>(row + F + c));
+        float o0 = rh(gelu_erf_f(g.x)) * h.x, o1 = rh(gelu_erf_f(g.y)) * h.y;
+        *reinterpret_cast<__half2*>(out + r * F + c) = __floats2half2_rn(o0, o1);
+    }
+}
+
+// dst = dst_in + sum_i scale_i * r_i  (ControlNet intake, unet_2d_condition.py:1281-1292,1418-1439)
+struct IntakeArgs {
+    const __half* r[8];
+    float scale[8];
+    int n;
+};
+__global__ void residual_intake_kernel(const __half2* __restrict__ src, __half2* __restrict__ dst, IntakeArgs a,
+                                       long long npairs) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < npairs; i += (long long)gridDim.x * blockDim.x) {
+        float2 acc = make_float2(0.f, 0.f);
+        for (int k = 0; k < a.n; ++k) {
+            float2 v = __half22float2(reinterpret_cast<const __half2*>(a.r[k])[i]);
+            acc.x += v.x * a.scale[k];
+            acc.y += v.y * a.scale[k];
+        }
+        // the reference sums the nets in fp16, then adds to the skip tensor in fp16
+        float2 s = __half22float2(src[i]);
+        dst[i] = __floats2half2_rn(s.x + rh(acc.x), s.y + rh(acc.y));
+    }
+}
+
+// get_timestep_embedding (embeddings.py:26-66) with flip_sin_to_cos=True, downscale_freq_shift=0, scale=1:
+// out[r, 0:half] = cos(t_r * f_i), out[r, half:dim] = sin(t_r * f_i), f_i = exp(-ln(10000) * i / half)
+__global__ void timestep_embedding_kernel(const float* __restrict__ t, __half* __restrict__ out, int rows, int dim,
+                                          int ld_out) {
+    const int half_dim = dim >> 1;
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * half_dim) return;
+    int r = i / half_dim, j = i - r * half_dim;
+    float f = expf(-9.210340371976184f * (float)j / (float)half_dim);
+    float a = t[r] * f;
+    out[(size_t)r * ld_out + j] = __float2half_rn(cosf(a));
+    out[(size_t)r * ld_out + half_dim + j] = __float2half_rn(sinf(a));
+}
+
+__global__ void silu_kernel(const __half2* __restrict__ x, __half2* __restrict__ y, long long npairs) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < npairs; i += (long long)gridDim.x * blockDim.x) {
+        float2 v = __half22float2(x[i]);
+        y[i] = __floats2half2_rn(silu_f(v.x), silu_f(v.y));
+    }
+}
+
+__global__ void add_kernel(const __half2* __restrict__ a, const __half2* __restrict__ b, __half2* __restrict__ y,
+                           long long npairs) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < npairs; i += (long long)gridDim.x * blockDim.x) {
+        float2 u = __half22float2(a[i]), v = __half22float2(b[i]);
+        y[i] = __floats2half2_rn(u.x + v.x, u.y + v.y);
+    }
+}
+
+// NCHW (C real channels) -> NHWC with the channel count padded to Cpad (zeros), and back.
+__global__ void nchw_to_nhwc_kernel(const __half* __restrict__ x, __half* __restrict__ y, int B, int C, int HW, int Cpad) {
+    long long total = (long long)B * HW * Cpad;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        int c = (int)(i % Cpad);
+        long long p = i / Cpad;
+        int hw = (int)(p % HW);
+        int b = (int)(p / HW);
+        y[i] = c < C ? x[((size_t)b * C + c) * HW + hw] : __float2half(0.f);
+    }
+}
+__global__ void nhwc_to_nchw_kernel(const __half* __restrict__ x, __half* __restrict__ y, int B, int C, int HW, int Cpad) {
+    long long total = (long long)B * C * HW;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        int hw = (int)(i % HW);
+        long long p = i / HW;
+        int c = (int)(p % C);
+        int b = (int)(p / C);
+        y[i] = x[((size_t)b * HW + hw) * Cpad + c];
+    }
+}
+
+// scale_model_input (scheduling_euler_discrete.py:294-295): the fp16 latent divided by sqrt(sigma^2 + 1) (sigma is an
+// fp32 scalar, so torch keeps the result in fp16), optionally written twice (batch-2 CFG input).
+__global__ void euler_scale_input_kernel(const __half* __restrict__ x, __half* __restrict__ out, long long n, float sigma,
+                                         int copies) {
+    const float den = sqrtf(sigma * sigma + 1.0f);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        __half h = __float2half_rn(__half2float(x[i]) / den);
+        for (int c = 0; c < copies; ++c) out[(size_t)c * n + i] = h;
+    }
+}
+
+// CFG combine (pipeline_controlnet_sd_xl_katz.py:1649-1655) + EulerDiscreteScheduler.step
+// (scheduling_euler_discrete.py:498-537) with s_churn = 0, epsilon prediction. eps = u + g*(c-u) in fp16; the step
+// upcasts the fp16 latent to fp32: pred_x0 = x - half(sigma*eps); d = (x - pred_x0)/sigma; x' = half(x + d*dt).
+__global__ void euler_cfg_step_kernel(__half* __restrict__ x, const __half* __restrict__ eps_uncond,
+                                      const __half* __restrict__ eps_cond, long long n, float guidance, float sigma,
+                                      float sigma_next) {
+    const float dt = sigma_next - sigma;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        float u = __half2float(eps_uncond[i]);
+        float e = u;
+        if (eps_cond) {
+            float c = __half2float(eps_cond[i]);
+            e = rh(u + rh(guidance * rh(c - u)));
+        }
+        float xv = __half2float(x[i]);
+        float pred = xv - rh(sigma * e);
+        float d = (xv - pred) / sigma;
+        x[i] = __float2half_rn(xv + d * dt);
+    }
+}
+
+// y[r, :] = x1[r, :C1] ++ x2[r, :C2], 16-byte chunks (C1, C2 multiples of 8)
+__global__ void concat_channels_kernel(const uint4* __restrict__ x1, const uint4* __restrict__ x2, uint4* __restrict__ y,
+                                       long long rows, int ch1, int ch2) {
+    const int ch = ch1 + ch2;
+    const long long total = rows * ch;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        long long r = i / ch;
+        int c = (int)(i - r * ch);
+        y[i] = c < ch1 ? x1[r * ch1 + c] : x2[r * ch2 + (c - ch1)];
+    }
+}
+
+static inline int ew_grid(long long n, int threads) {
+    long long g = (n + threads - 1) / threads;
+    long long cap = 148ll * 16;
+    return (int)(g < cap ? (g > 0 ? g : 1) : cap);
+}
+
+}  // namespace katz
+
+using namespace katz;
+
+extern "C" int katz_fast_gelu_mul_f16(const void* x, const void* m, void* out, long long n, void* stream) {
+    KATZ_CHECK_ARG(x && m && out, KATZ_EINVAL);
+    KATZ_CHECK_ARG(n > 0 && n % 2 == 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(((uintptr_t)x & 3) == 0 && ((uintptr_t)m & 3) == 0 && ((uintptr_t)out & 3) == 0, KATZ_EALIGN);
+    fast_gelu_mul_kernel<<<ew_grid(n / 2, 256), 256, 0, (cudaStream_t)stream>>>((const __half2*)x, (const __half2*)m,
+                                                                              (__half2*)out, n / 2);
+    KATZ_LAUNCH_RET();
+}
+
+extern "C" int katz_geglu_erf_f16(const void* hg, void* out, long long M, int F, int ld, void* stream) {
+    KATZ_CHECK_ARG(hg && out, KATZ_EINVAL);
+    KATZ_CHECK_ARG(M > 0 && F > 0 && F % 2 == 0 && ld % 2 == 0 && ld >= 2 * F, KATZ_ESIZE);
+    KATZ_CHECK_ARG(((uintptr_t)hg & 3) == 0 && ((uintptr_t)out & 3) == 0, KATZ_EALIGN);
+    geglu_erf_kernel<<<ew_grid(M * (F / 2), 256), 256, 0, (cudaStream_t)stream>>>((const __half*)hg, (__half*)out, M, F, ld);
+    KATZ_LAUNCH_RET();
+}
+
+extern "C" int katz_residual_intake_f16(const void* src, void* dst, const void* const* residuals, const float* scales,
+                                        int n_res, long long n, void* stream) {
+    KATZ_CHECK_ARG(src && dst && residuals && scales, KATZ_EINVAL);
+    KATZ_CHECK_ARG(n_res >= 1 && n_res <= 8, KATZ_ESIZE);
+    KATZ_CHECK_ARG(n > 0 && n % 2 == 0, KATZ_ESIZE);
+    IntakeArgs a{};
+    a.n = n_res;
+    for (int i = 0; i < n_res; ++i) {
+        KATZ_CHECK_ARG(residuals[i] && ((uintptr_t)residuals[i] & 3) == 0, KATZ_EALIGN);
+        a.r[i] = (const __half*)residuals[i];
+        a.scale[i] = scales[i];
+    }
+    residual_intake_kernel<<<ew_grid(n / 2, 256), 256, 0, (cudaStream_t)stream>>>((const __half2*)src, (__half2*)dst, a, n / 2);
+    KATZ_LAUNCH_RET();
+}
+
+extern "C" int katz_timestep_embedding_f16(const float* t, void* out, int rows, int dim, int ld_out, void* stream) {
+    KATZ_CHECK_ARG(t && out, KATZ_EINVAL);
+    KATZ_CHECK_ARG(rows > 0 && dim > 0 && dim % 2 == 0 && ld_out >= dim, KATZ_ESIZE);
+    int n = rows * (dim / 2);
+    timestep_embedding_kernel<<<ceil_div(n, 128), 128, 0, (cudaStream_t)stream>>>(t, (__half*)out, rows, dim, ld_out);
+    KATZ_LAUNCH_RET();
+}
+
+extern "C" int katz_silu_f16(const void* x, void* y, long long n, void* stream) {
+    KATZ_CHECK_ARG(x && y, KATZ_EINVAL);
+    KATZ_CHECK_ARG(n > 0 && n % 2 == 0, KATZ_ESIZE);
+    silu_kernel<<<ew_grid(n / 2, 256), 256, 0, (cudaStream_t)stream>>>((const __half2*)x, (__half2*)y, n / 2);
+    KATZ_LAUNCH_RET();
+}
+
+extern "C" int katz_add_f16(const void* a, const void* b, void* y, long long n, void* stream) {
+    KATZ_CHECK_ARG(a && b && y, KATZ_EINVAL);
+    KATZ_CHECK_ARG(n > 0 && n % 2 == 0, KATZ_ESIZE);
+    add_kernel<<<ew_grid(n / 2, 256), 256, 0, (cudaStream_t)stream>>>((const __half2*)a, (const __half2*)b, (__half2*)y, n / 2);
+    KATZ_LAUNCH_RET();
+}
+
+extern "C" int katz_concat_channels_f16(const void* x1, const void* x2, void* y, long long rows, int C1, int C2,
+                                        void* stream) {
+    KATZ_CHECK_ARG(x1 && x2 && y, KATZ_EINVAL);
+    KATZ_CHECK_ARG(rows > 0 && C1 > 0 && C2 > 0 && C1 % 8 == 0 && C2 % 8 == 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(aligned16(x1) && aligned16(x2) && aligned16(y), KATZ_EALIGN);
+    long long n = rows * ((C1 + C2) / 8);
+    concat_channels_kernel<<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((const uint4*)x1, (const uint4*)x2, (uint4*)y,
+                                                                            rows, C1 / 8, C2 / 8);
+    KATZ_LAUNCH_RET();
+}
+
+extern "C" int katz_nchw_to_nhwc_f16(const void* x, void* y, int B, int C, int HW, int Cpad, void* stream) {
+    KATZ_CHECK_ARG(x && y, KATZ_EINVAL);
+    KATZ_CHECK_ARG(B > 0 && C > 0 && HW > 0 && Cpad >= C, KATZ_ESIZE);
+    long long n = (long long)B * HW * Cpad;
+    nchw_to_nhwc_kernel<<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((const __half*)x, (__half*)y, B, C, HW, Cpad);
+    KATZ_LAUNCH_RET();
+}
+
+extern "C" int katz_nhwc_to_nchw_f16(const void* x, void* y, int B, int C, int HW, int Cpad, void* stream) {
+    KATZ_CHECK_ARG(x && y, KATZ_EINVAL);
+    KATZ_CHECK_ARG(B > 0 && C > 0 && HW > 0 && Cpad >= C, KATZ_ESIZE);
+    long long n = (long long)B * HW * C;
+    nhwc_to_nchw_kernel<<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((const __half*)x, (__half*)y, B, C, HW, Cpad);
+    KATZ_LAUNCH_RET();
+}
+
+extern "C" int katz_euler_scale_input(const void* x, void* out, long long n, float sigma, int copies, void* stream) {
+    KATZ_CHECK_ARG(x && out, KATZ_EINVAL);
+    KATZ_CHECK_ARG(n > 0 && copies >= 1, KATZ_ESIZE);
+    euler_scale_input_kernel<<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((const __half*)x, (__half*)out, n, sigma, copies);
+    KATZ_LAUNCH_RET();
+}
+
+extern "C" int katz_euler_cfg_step(void* x, const void* eps_uncond, const void* eps_cond, long long n, float guidance,
+                                   float sigma, float sigma_next, void* stream) {
+    KATZ_CHECK_ARG(x && eps_uncond, KATZ_EINVAL);
+    KATZ_CHECK_ARG(n > 0 && sigma != 0.f, KATZ_ESIZE);
+    euler_cfg_step_kernel<<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((__half*)x, (const __half*)eps_uncond,
+                                                                           (const __half*)eps_cond, n, guidance, sigma, sigma_next);
+    KATZ_LAUNCH_RET();
+}

@@ -1,0 +1,296 @@
+// Fused LoRA merge over a whole set of linears in ONE launch:
+//     W_live = (W0 ? W0 : W_live) + sign * sum_i s_i * (B_i @ A_i)        B_i = up [out, r_i], A_i = down [r_i, in]
+//
+// Reference: lora_utils.py:21-33 and pipeline_controlnet_sd_xl_katz.py:1736-1747 (a Python loop of 722 small GEMMs
+// `W[key] += up @ down * scale` followed by a full load_state_dict copy), restore by load_state_dict of a pristine
+// copy (sdxl_unet_server.py:217). With W0 (the pristine weights, resident in HBM) the merge reads W0 and writes
+// W_live, so merge is one pass and restore is a plain copy, which is how the reference keeps the restore bit-exact.
+// With W0 == nullptr the update is in place (sign = -1 gives the subtractive unmerge of
+// diffusers/models/lora.py:427-449, which is not bit-exact in floating point).
+//
+// The work is bound by streaming W through HBM once; the rank-r product runs on tensor cores (mma.sync, fp16 inputs
+// or 3xTF32 for fp32 inputs) from shared-memory tiles while the W tile is in flight. Rounding follows the reference:
+// fp16: delta = half(acc); delta = half(delta * s); W = half(W + delta), per LoRA in order. fp32: W += acc * s.
+#include "common.cuh"
+#include "katz_b200.h"
+
+namespace katz {
+
+constexpr int LM_THREADS = 256;
+constexpr int LM_TN = 128;        // tile columns
+constexpr int LM_MAXR = 64;       // rank processed per pass; larger ranks loop
+
+template <typename T>
+struct LmCfg;
+template <>
+struct LmCfg<__half> {
+    static constexpr int TM = 128;
+    static constexpr int W_BYTES = TM * LM_TN * 2;        // 32 KB, 256 B rows, 16 chunks, swizzled
+    static constexpr int B_BYTES = TM * 128;              // [TM][64 halfs], 128 B rows, swizzled
+    static constexpr int A_BYTES = LM_MAXR * LM_TN * 2;   // [64][128 halfs], 256 B rows, swizzled
+    static constexpr int SMEM = W_BYTES + B_BYTES + A_BYTES;
+};
+template <>
+struct LmCfg<float> {
+    static constexpr int TM = 64;
+    static constexpr int BP = 68;    // B tile pitch in floats (bank-conflict-free fragment reads)
+    static constexpr int AP = 136;   // A tile pitch in floats
+    static constexpr int W_BYTES = TM * LM_TN * 4;        // 32 KB, 512 B rows, 32 chunks, swizzled
+    static constexpr int B_BYTES = TM * BP * 4;
+    static constexpr int A_BYTES = LM_MAXR * AP * 4;
+    static constexpr int SMEM = W_BYTES + B_BYTES + A_BYTES;
+};
+
+__device__ __forceinline__ int find_layer(const int* __restrict__ tile_start, int n_layers, int tile) {
+    int lo = 0, hi = n_layers - 1;
+    while (lo < hi) {
+        int mid = (lo + hi + 1) >> 1;
+        if (tile_start[mid] <= tile) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(LM_THREADS, 2) lora_merge_kernel(const katz_lora_layer* __restrict__ layers,
+                                                                   const int* __restrict__ tile_start, int n_layers,
+                                                                   float sign) {
+    using Cfg = LmCfg<T>;
+    constexpr int TM = Cfg::TM;
+    constexpr int ES = sizeof(T);
+    constexpr int EPC = 16 / ES;                 // elements per 16-byte chunk
+    constexpr int W_CHUNKS_ROW = LM_TN / EPC;    // 16 (fp16) / 32 (fp32)
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned char* sW = smem;
+    unsigned char* sB = smem + Cfg::W_BYTES;
+    unsigned char* sA = sB + Cfg::B_BYTES;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int li = find_layer(tile_start, n_layers, blockIdx.x);
+    const katz_lora_layer L = layers[li];
+    const int t = blockIdx.x - tile_start[li];
+    const int tiles_n = (L.in_features + LM_TN - 1) / LM_TN;
+    const int tm = t / tiles_n, tn = t - tm * tiles_n;
+    const int row0 = tm * TM, col0 = tn * LM_TN;
+    T* Wdst = reinterpret_cast<T*>(L.W);
+    const T* Wsrc = L.W0 ? reinterpret_cast<const T*>(L.W0) : Wdst;
+    const int out_f = L.out_features, in_f = L.in_features;
+
+    auto w_off = [&](int r, int c) -> uint32_t {
+        if constexpr (ES == 2) return r * 256 + ((c ^ (r & 7)) << 4);
+        else return r * 512 + ((c ^ ((r & 3) << 1)) << 4);
+    };
+
+    // ---- W tile in flight
+    for (int idx = tid; idx < TM * W_CHUNKS_ROW; idx += LM_THREADS) {
+        int r = idx / W_CHUNKS_ROW, c = idx - r * W_CHUNKS_ROW;
+        int gr = row0 + r, gc = col0 + c * EPC;
+        bool ok = gr < out_f && gc < in_f;
+        const T* src = ok ? Wsrc + (size_t)gr * in_f + gc : Wsrc;
+        cp_async16(smem_u32(sW + w_off(r, c)), src, ok ? 16 : 0);
+    }
+    cp_async_commit();
+
+    for (int l = 0; l < L.n_lora; ++l) {
+        const T* Bm = reinterpret_cast<const T*>(L.B[l]);
+        const T* Am = reinterpret_cast<const T*>(L.A[l]);
+        const int rank = L.rank[l];
+        const float s = L.scale[l] * sign;
+        float acc[2][ES == 2 ? 8 : 4][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int j = 0; j < (ES == 2 ? 8 : 4); ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+
+        for (int k0 = 0; k0 < rank; k0 += LM_MAXR) {
+            const int kr = min(LM_MAXR, rank - k0);   // multiple of 8 (checked on the host)
+            __syncthreads();                          // previous pass / LoRA done with sA, sB
+            // B tile: TM rows x kr ; A tile: kr rows x 128 cols. Unused k columns/rows are zero-filled up to 16.
+            const int kpad = (kr + 15) & ~15;
+            {
+                const int bchunks = kpad / EPC;
+                for (int idx = tid; idx < TM * bchunks; idx += LM_THREADS) {
+                    int r = idx / bchunks, c = idx - r * bchunks;
+                    int gr = row0 + r, gk = k0 + c * EPC;
+                    bool ok = gr < out_f && (c * EPC) < kr;
+                    const T* src = ok ? Bm + (size_t)gr * rank + gk : Bm;
+                    uint32_t off;
+                    if constexpr (ES == 2) off = r * 128 + ((c ^ (r & 7)) << 4);
+                    else off = (r * Cfg::BP + c * 4) * 4;
+                    cp_async16(smem_u32(sB + off), src, ok ? 16 : 0);
+                }
+                for (int idx = tid; idx < kpad * W_CHUNKS_ROW; idx += LM_THREADS) {
+                    int r = idx / W_CHUNKS_ROW, c = idx - r * W_CHUNKS_ROW;
+                    int gc = col0 + c * EPC;
+                    bool ok = r < kr && gc < in_f;
+                    const T* src = ok ? Am + (size_t)(k0 + r) * in_f + gc : Am;
+                    uint32_t off;
+                    if constexpr (ES == 2) off = r * 256 + ((c ^ (r & 7)) << 4);
+                    else off = (r * Cfg::AP + c * 4) * 4;
+                    cp_async16(smem_u32(sA + off), src, ok ? 16 : 0);
+                }
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncthreads();
+
+            if constexpr (ES == 2) {
+                const int warp_m = warp & 3, warp_n = warp >> 2;   // 4 x 2 warps, warp tile 32 x 64
+                for (int ks = 0; ks < kpad / 16; ++ks) {
+                    uint32_t af[2][4];
+#pragma unroll
+                    for (int mf = 0; mf < 2; ++mf) {
+                        int r = warp_m * 32 + mf * 16 + (lane & 15);
+                        int ch = ks * 2 + (lane >> 4);
+                        ldmatrix_x4(af[mf][0], af[mf][1], af[mf][2], af[mf][3], smem_u32(sB + r * 128 + ((ch ^ (r & 7)) << 4)));
+                    }
+#pragma unroll
+                    for (int np = 0; np < 4; ++np) {
+                        uint32_t bf[4];
+                        int r = ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+                        int ch = warp_n * 8 + np * 2 + (lane >> 4);
+                        ldmatrix_x4_trans(bf[0], bf[1], bf[2], bf[3], smem_u32(sA + r * 256 + ((ch ^ (r & 7)) << 4)));
+#pragma unroll
+                        for (int mf = 0; mf < 2; ++mf) {
+                            mma_f16_16816(acc[mf][np * 2], af[mf], bf);
+                            mma_f16_16816(acc[mf][np * 2 + 1], af[mf], bf + 2);
+                        }
+                    }
+                }
+            } else {
+                const int warp_m = warp & 1, warp_n = warp >> 1;   // 2 x 4 warps, warp tile 32 x 32
+                const float* fB = reinterpret_cast<const float*>(sB);
+                const float* fA = reinterpret_cast<const float*>(sA);
+                const int g = lane >> 2, q = lane & 3;
+                for (int ks = 0; ks < kpad / 8; ++ks) {
+                    uint32_t ahi[2][4], alo[2][4], bhi[4][2], blo[4][2];
+#pragma unroll
+                    for (int mf = 0; mf < 2; ++mf) {
+                        int r = warp_m * 32 + mf * 16 + g;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float v = fB[(r + (e & 1) * 8) * Cfg::BP + ks * 8 + q + (e >> 1) * 4];
+                            ahi[mf][e] = f32_to_tf32(v);
+                            alo[mf][e] = f32_to_tf32(v - __uint_as_float(ahi[mf][e]));
+                        }
+                    }
+#pragma unroll
+                    for (int nf = 0; nf < 4; ++nf) {
+                        int n = warp_n * 32 + nf * 8 + g;
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            float v = fA[(ks * 8 + q + e * 4) * Cfg::AP + n];
+                            bhi[nf][e] = f32_to_tf32(v);
+                            blo[nf][e] = f32_to_tf32(v - __uint_as_float(bhi[nf][e]));
+                        }
+                    }
+#pragma unroll
+                    for (int mf = 0; mf < 2; ++mf)
+#pragma unroll
+                        for (int nf = 0; nf < 4; ++nf) {
+                            mma_tf32_1688(acc[mf][nf], alo[mf], bhi[nf]);
+                            mma_tf32_1688(acc[mf][nf], ahi[mf], blo[nf]);
+                            mma_tf32_1688(acc[mf][nf], ahi[mf], bhi[nf]);
+                        }
+                }
+            }
+        }
+
+        // ---- fold this LoRA's delta into the W tile held in shared memory (each element has one owner thread)
+        if constexpr (ES == 2) {
+            const int warp_m = warp & 3, warp_n = warp >> 2;
+#pragma unroll
+            for (int mf = 0; mf < 2; ++mf)
+#pragma unroll
+                for (int hr = 0; hr < 2; ++hr) {
+                    int r = warp_m * 32 + mf * 16 + (lane >> 2) + hr * 8;
+#pragma unroll
+                    for (int nf = 0; nf < 8; ++nf) {
+                        int c = warp_n * 64 + nf * 8 + (lane & 3) * 2;
+                        __half2* wp = reinterpret_cast<__half2*>(sW + r * 256 + (((c >> 3) ^ (r & 7)) << 4) + (c & 7) * 2);
+                        float2 w = __half22float2(*wp);
+                        float d0 = __half2float(__float2half_rn(acc[mf][nf][hr * 2]));
+                        float d1 = __half2float(__float2half_rn(acc[mf][nf][hr * 2 + 1]));
+                        d0 = __half2float(__float2half_rn(d0 * s));
+                        d1 = __half2float(__float2half_rn(d1 * s));
+                        *wp = __floats2half2_rn(w.x + d0, w.y + d1);
+                    }
+                }
+        } else {
+            const int warp_m = warp & 1, warp_n = warp >> 1;
+#pragma unroll
+            for (int mf = 0; mf < 2; ++mf)
+#pragma unroll
+                for (int hr = 0; hr < 2; ++hr) {
+                    int r = warp_m * 32 + mf * 16 + (lane >> 2) + hr * 8;
+#pragma unroll
+                    for (int nf = 0; nf < 4; ++nf) {
+                        int c = warp_n * 32 + nf * 8 + (lane & 3) * 2;
+                        float2* wp = reinterpret_cast<float2*>(sW + r * 512 + (((c >> 2) ^ ((r & 3) << 1)) << 4) + (c & 3) * 4);
+                        float2 w = *wp;
+                        w.x = w.x + acc[mf][nf][hr * 2] * s;
+                        w.y = w.y + acc[mf][nf][hr * 2 + 1] * s;
+                        *wp = w;
+                    }
+                }
+        }
+    }
+    cp_async_wait<0>();   // covers n_lora == 0 (plain restore copy)
+    __syncthreads();
+
+    // ---- coalesced write-back
+    for (int idx = tid; idx < TM * W_CHUNKS_ROW; idx += LM_THREADS) {
+        int r = idx / W_CHUNKS_ROW, c = idx - r * W_CHUNKS_ROW;
+        int gr = row0 + r, gc = col0 + c * EPC;
+        if (gr < out_f && gc < in_f) {
+            uint4 v = *reinterpret_cast<const uint4*>(sW + w_off(r, c));
+            *reinterpret_cast<uint4*>(Wdst + (size_t)gr * in_f + gc) = v;
+        }
+    }
+}
+
+}  // namespace katz
+
+using namespace katz;
+
+extern "C" int katz_lora_tile_rows(int w_dtype) { return w_dtype == KATZ_DTYPE_F16 ? LmCfg<__half>::TM : LmCfg<float>::TM; }
+extern "C" int katz_lora_tile_cols(void) { return LM_TN; }
+
+extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_tile_start, int n_layers, int total_tiles,
+                               int w_dtype, float sign, void* stream) {
+    KATZ_CHECK_ARG(d_layers && d_tile_start, KATZ_EINVAL);
+    KATZ_CHECK_ARG(n_layers > 0 && total_tiles > 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(w_dtype == KATZ_DTYPE_F16 || w_dtype == KATZ_DTYPE_F32, KATZ_EINVAL);
+    KATZ_CHECK_ARG(sign == 1.0f || sign == -1.0f, KATZ_EINVAL);
+    cudaStream_t st = (cudaStream_t)stream;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(lora_merge_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, LmCfg<__half>::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(lora_merge_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, LmCfg<float>::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    if (w_dtype == KATZ_DTYPE_F16)
+        lora_merge_kernel<__half><<<total_tiles, LM_THREADS, LmCfg<__half>::SMEM, st>>>(d_layers, d_tile_start, n_layers, sign);
+    else
+        lora_merge_kernel<float><<<total_tiles, LM_THREADS, LmCfg<float>::SMEM, st>>>(d_layers, d_tile_start, n_layers, sign);
+    KATZ_LAUNCH_RET();
+}
+
+// Host-side validation of one table entry (the table itself lives in device memory, so the caller validates before
+// uploading). Returns 0 or a negative argument error.
+extern "C" int katz_lora_layer_check(const katz_lora_layer* h, int w_dtype) {
+    KATZ_CHECK_ARG(h, KATZ_EINVAL);
+    KATZ_CHECK_ARG(w_dtype == KATZ_DTYPE_F16 || w_dtype == KATZ_DTYPE_F32, KATZ_EINVAL);
+    const int epc = w_dtype == KATZ_DTYPE_F16 ? 8 : 4;
+    KATZ_CHECK_ARG(h->W && aligned16(h->W) && (!h->W0 || aligned16(h->W0)), KATZ_EALIGN);
+    KATZ_CHECK_ARG(h->out_features > 0 && h->in_features > 0 && h->in_features % epc == 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(h->n_lora >= 0 && h->n_lora <= KATZ_LORA_MAX_ADAPTERS, KATZ_ESIZE);
+    for (int i = 0; i < h->n_lora; ++i) {
+        KATZ_CHECK_ARG(h->A[i] && h->B[i] && aligned16(h->A[i]) && aligned16(h->B[i]), KATZ_EALIGN);
+        KATZ_CHECK_ARG(h->rank[i] > 0 && h->rank[i] % 8 == 0, KATZ_ESIZE);
+    }
+    return KATZ_OK;
+}

@@ -1,0 +1,294 @@
+// GroupNorm (+ optional SiLU) and LayerNorm, fp16 in/out, fp32 statistics.
+//
+// GroupNorm replaces fast_kernel::group_norm_fp16 (fast_kernel/csrc/group_norm.cu:155-274, which lowers to the
+// LayerNorm kernels of normalize.cuh:558-834 with one CTA per (batch, group) row: 64 CTAs at SDXL shapes) and
+// torch's nn.GroupNorm in Transformer2DModel (transformer_2d.py:173-175). Here the NHWC tensor is cut into row
+// slabs so the grid covers every SM: a statistics pass writes one (sum, sum of squares) partial per
+// (batch, slab, group) into caller-provided scratch, and the apply pass folds the partials in fp64 and normalises.
+//
+// LayerNorm replaces nn.LayerNorm(C, eps=1e-5, affine) of BasicTransformerBlock (attention.py:195,225,253).
+#include "common.cuh"
+#include "katz_b200.h"
+
+namespace katz {
+
+constexpr int GN_THREADS = 256;
+constexpr int GN_MAXP = 8;      // channel pairs per thread: C <= 2 * 256 * 8 = 4096
+constexpr int GN_MAXG = 64;
+
+__global__ void __launch_bounds__(GN_THREADS) gn_stats_nhwc_kernel(const __half* __restrict__ x, float* __restrict__ partial,
+                                                                   int HW, int C, int G, int rows_per_slab) {
+    __shared__ float s_sum[GN_MAXG], s_sq[GN_MAXG];
+    const int slab = blockIdx.x, b = blockIdx.y, nslab = gridDim.x;
+    const int tid = threadIdx.x;
+    if (tid < G) {
+        s_sum[tid] = 0.f;
+        s_sq[tid] = 0.f;
+    }
+    __syncthreads();
+    const int CP = C >> 1, cpg = C / G;
+    const int r0 = slab * rows_per_slab;
+    const int r1 = min(HW, r0 + rows_per_slab);
+    float sum[GN_MAXP], sq[GN_MAXP];
+#pragma unroll
+    for (int i = 0; i < GN_MAXP; ++i) sum[i] = sq[i] = 0.f;
+    const __half2* xb = reinterpret_cast<const __half2*>(x) + (size_t)b * HW * CP;
+    for (int r = r0; r < r1; ++r) {
+        const __half2* xr = xb + (size_t)r * CP;
+#pragma unroll
+        for (int i = 0; i < GN_MAXP; ++i) {
+            int cp = tid + i * GN_THREADS;
+            if (cp < CP) {
+                float2 v = __half22float2(xr[cp]);
+                sum[i] += v.x + v.y;
+                sq[i] += v.x * v.x + v.y * v.y;
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < GN_MAXP; ++i) {
+        int cp = tid + i * GN_THREADS;
+        if (cp < CP) {
+            int g = (cp * 2) / cpg;
+            atomicAdd(&s_sum[g], sum[i]);
+            atomicAdd(&s_sq[g], sq[i]);
+        }
+    }
+    __syncthreads();
+    if (tid < G) {
+        float* o = partial + (((size_t)b * nslab + slab) * G + tid) * 2;
+        o[0] = s_sum[tid];
+        o[1] = s_sq[tid];
+    }
+}
+
+__global__ void __launch_bounds__(GN_THREADS) gn_apply_nhwc_kernel(const __half* __restrict__ x, __half* __restrict__ y,
+                                                                   const float* __restrict__ partial, int nslab_stats,
+                                                                   const __half* __restrict__ gamma,
+                                                                   const __half* __restrict__ beta, int HW, int C, int G,
+                                                                   int rows_per_slab, float eps, int act) {
+    __shared__ float s_mean[GN_MAXG], s_rstd[GN_MAXG];
+    const int slab = blockIdx.x, b = blockIdx.y;
+    const int tid = threadIdx.x;
+    const int CP = C >> 1, cpg = C / G;
+    if (tid < G) {
+        double s = 0.0, q = 0.0;
+        const float* pp = partial + ((size_t)b * nslab_stats * G + tid) * 2;
+        for (int i = 0; i < nslab_stats; ++i) {
+            s += (double)pp[(size_t)i * G * 2];
+            q += (double)pp[(size_t)i * G * 2 + 1];
+        }
+        double n = (double)HW * cpg;
+        double mean = s / n;
+        double var = q / n - mean * mean;
+        if (var < 0.0) var = 0.0;
+        s_mean[tid] = (float)mean;
+        s_rstd[tid] = (float)(1.0 / sqrt(var + (double)eps));
+    }
+    __syncthreads();
+    float sc[GN_MAXP][2], sh[GN_MAXP][2];
+#pragma unroll
+    for (int i = 0; i < GN_MAXP; ++i) {
+        int cp = tid + i * GN_THREADS;
+        if (cp < CP) {
+            int g = (cp * 2) / cpg;
+            float ga0 = gamma ? __half2float(gamma[cp * 2]) : 1.f, ga1 = gamma ? __half2float(gamma[cp * 2 + 1]) : 1.f;
+            float be0 = beta ? __half2float(beta[cp * 2]) : 0.f, be1 = beta ? __half2float(beta[cp * 2 + 1]) : 0.f;
+            sc[i][0] = s_rstd[g] * ga0;
+            sc[i][1] = s_rstd[g] * ga1;
+            sh[i][0] = be0 - s_mean[g] * sc[i][0];
+            sh[i][1] = be1 - s_mean[g] * sc[i][1];
+        }
+    }
+    const int r0 = slab * rows_per_slab;
+    const int r1 = min(HW, r0 + rows_per_slab);
+    const __half2* xb = reinterpret_cast<const __half2*>(x) + (size_t)b * HW * CP;
+    __half2* yb = reinterpret_cast<__half2*>(y) + (size_t)b * HW * CP;
+    for (int r = r0; r < r1; ++r) {
+#pragma unroll
+        for (int i = 0; i < GN_MAXP; ++i) {
+            int cp = tid + i * GN_THREADS;
+            if (cp < CP) {
+                float2 v = __half22float2(xb[(size_t)r * CP + cp]);
+                float a0 = v.x * sc[i][0] + sh[i][0];
+                float a1 = v.y * sc[i][1] + sh[i][1];
+                if (act == 1) {
+                    a0 = silu_f(a0);
+                    a1 = silu_f(a1);
+                }
+                yb[(size_t)r * CP + cp] = __floats2half2_rn(a0, a1);
+            }
+        }
+    }
+}
+
+// Channels-first variant: each (batch, group) is one contiguous run of (C/G)*HW values.
+__global__ void __launch_bounds__(1024) gn_nchw_kernel(const __half* __restrict__ x, __half* __restrict__ y,
+                                                       const __half* __restrict__ gamma, const __half* __restrict__ beta,
+                                                       int HW, int C, int G, float eps, int act) {
+    __shared__ double s_a[32], s_b[32];
+    __shared__ float s_mean, s_rstd;
+    const int g = blockIdx.x, b = blockIdx.y, cpg = C / G;
+    const size_t base = ((size_t)b * C + (size_t)g * cpg) * HW;
+    const long long n = (long long)cpg * HW;
+    double s = 0.0, q = 0.0;
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+        float v = __half2float(x[base + i]);
+        s += v;
+        q += (double)v * v;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        s += __shfl_xor_sync(0xffffffffu, s, o);
+        q += __shfl_xor_sync(0xffffffffu, q, o);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        s_a[threadIdx.x >> 5] = s;
+        s_b[threadIdx.x >> 5] = q;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double ts = 0, tq = 0;
+        for (int i = 0; i < (int)(blockDim.x >> 5); ++i) {
+            ts += s_a[i];
+            tq += s_b[i];
+        }
+        double mean = ts / (double)n, var = tq / (double)n - mean * mean;
+        if (var < 0) var = 0;
+        s_mean = (float)mean;
+        s_rstd = (float)(1.0 / sqrt(var + (double)eps));
+    }
+    __syncthreads();
+    const float mean = s_mean, rstd = s_rstd;
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+        int c = g * cpg + (int)(i / HW);
+        float ga = gamma ? __half2float(gamma[c]) : 1.f, be = beta ? __half2float(beta[c]) : 0.f;
+        float a = (__half2float(x[base + i]) - mean) * rstd * ga + be;
+        if (act == 1) a = silu_f(a);
+        y[base + i] = __float2half_rn(a);
+    }
+}
+
+constexpr int LN_MAXCH = 10;  // 16-byte chunks per lane: C <= 32 * 10 * 8 = 2560
+
+__global__ void __launch_bounds__(256) layer_norm_kernel(const __half* __restrict__ x, __half* __restrict__ y,
+                                                         const __half* __restrict__ gamma, const __half* __restrict__ beta,
+                                                         int rows, int C, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int nch = C >> 3;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * C);
+    float v[LN_MAXCH][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < LN_MAXCH; ++i) {
+        int ch = lane + i * 32;
+        if (ch < nch) {
+            uint4 u = xr[ch];
+            float2 a = unpack_half2(u.x), b2 = unpack_half2(u.y), c = unpack_half2(u.z), d = unpack_half2(u.w);
+            v[i][0] = a.x; v[i][1] = a.y; v[i][2] = b2.x; v[i][3] = b2.y;
+            v[i][4] = c.x; v[i][5] = c.y; v[i][6] = d.x; v[i][7] = d.y;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s += v[i][e];
+        }
+    }
+    const float mean = warp_sum(s) / (float)C;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < LN_MAXCH; ++i) {
+        int ch = lane + i * 32;
+        if (ch < nch) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float d = v[i][e] - mean;
+                q += d * d;
+            }
+        }
+    }
+    const float rstd = rsqrtf(warp_sum(q) / (float)C + eps);
+    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * C);
+#pragma unroll
+    for (int i = 0; i < LN_MAXCH; ++i) {
+        int ch = lane + i * 32;
+        if (ch < nch) {
+            float o[8];
+            uint4 g4 = reinterpret_cast<const uint4*>(gamma)[ch];
+            uint4 b4 = reinterpret_cast<const uint4*>(beta)[ch];
+            float2 g0 = unpack_half2(g4.x), g1 = unpack_half2(g4.y), g2 = unpack_half2(g4.z), g3 = unpack_half2(g4.w);
+            float2 b0 = unpack_half2(b4.x), b1 = unpack_half2(b4.y), b2 = unpack_half2(b4.z), b3 = unpack_half2(b4.w);
+            float gg[8] = {g0.x, g0.y, g1.x, g1.y, g2.x, g2.y, g3.x, g3.y};
+            float bb[8] = {b0.x, b0.y, b1.x, b1.y, b2.x, b2.y, b3.x, b3.y};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = (v[i][e] - mean) * rstd * gg[e] + bb[e];
+            uint4 u;
+            u.x = pack_half2(o[0], o[1]);
+            u.y = pack_half2(o[2], o[3]);
+            u.z = pack_half2(o[4], o[5]);
+            u.w = pack_half2(o[6], o[7]);
+            yr[ch] = u;
+        }
+    }
+}
+
+static int gn_rows_per_slab(int HW, int B) {
+    // aim at >= 4 CTAs per SM over the whole grid, slabs of at least 8 rows
+    int target = (148 * 4 + B - 1) / B;
+    int rows = (HW + target - 1) / target;
+    if (rows < 8) rows = 8;
+    return rows;
+}
+
+}  // namespace katz
+
+using namespace katz;
+
+extern "C" long long katz_group_norm_scratch_bytes(int B, int HW, int C, int G) {
+    if (B <= 0 || HW <= 0 || G <= 0) return -1;
+    int rows = gn_rows_per_slab(HW, B);
+    long long nslab = ceil_div(HW, rows);
+    return (long long)B * nslab * G * 2 * (long long)sizeof(float);
+}
+
+extern "C" int katz_group_norm_nhwc_f16(const void* x, void* y, const void* gamma, const void* beta, int B, int HW, int C,
+                                        int G, float eps, int act, void* scratch, long long scratch_bytes,
+                                        void* stream) {
+    KATZ_CHECK_ARG(x && y && scratch, KATZ_EINVAL);
+    KATZ_CHECK_ARG(B > 0 && HW > 0 && C > 0 && G > 0 && G <= GN_MAXG, KATZ_ESIZE);
+    KATZ_CHECK_ARG(B <= 65535, KATZ_ESIZE);
+    KATZ_CHECK_ARG(C % G == 0 && (C / G) % 2 == 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(C <= 2 * GN_THREADS * GN_MAXP, KATZ_ESIZE);
+    KATZ_CHECK_ARG(act == 0 || act == 1, KATZ_EINVAL);
+    KATZ_CHECK_ARG(((uintptr_t)x & 3) == 0 && ((uintptr_t)y & 3) == 0 && ((uintptr_t)scratch & 3) == 0, KATZ_EALIGN);
+    KATZ_CHECK_ARG(scratch_bytes >= katz_group_norm_scratch_bytes(B, HW, C, G), KATZ_ESIZE);
+    const int rows = gn_rows_per_slab(HW, B);
+    const int nslab = ceil_div(HW, rows);
+    dim3 grid(nslab, B);
+    cudaStream_t st = (cudaStream_t)stream;
+    gn_stats_nhwc_kernel<<<grid, GN_THREADS, 0, st>>>((const __half*)x, (float*)scratch, HW, C, G, rows);
+    gn_apply_nhwc_kernel<<<grid, GN_THREADS, 0, st>>>((const __half*)x, (__half*)y, (const float*)scratch, nslab,
+                                                      (const __half*)gamma, (const __half*)beta, HW, C, G, rows, eps, act);
+    KATZ_LAUNCH_RET();
+}
+
+extern "C" int katz_group_norm_nchw_f16(const void* x, void* y, const void* gamma, const void* beta, int B, int HW, int C,
+                                        int G, float eps, int act, void* stream) {
+    KATZ_CHECK_ARG(x && y, KATZ_EINVAL);
+    KATZ_CHECK_ARG(B > 0 && HW > 0 && C > 0 && G > 0 && C % G == 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(B <= 65535, KATZ_ESIZE);
+    KATZ_CHECK_ARG(act == 0 || act == 1, KATZ_EINVAL);
+    gn_nchw_kernel<<<dim3(G, B), 1024, 0, (cudaStream_t)stream>>>((const __half*)x, (__half*)y, (const __half*)gamma,
+                                                                  (const __half*)beta, HW, C, G, eps, act);
+    KATZ_LAUNCH_RET();
+}
+
+extern "C" int katz_layer_norm_f16(const void* x, void* y, const void* gamma, const void* beta, int rows, int C, float eps,
+                                   void* stream) {
+    KATZ_CHECK_ARG(x && y && gamma && beta, KATZ_EINVAL);
+    KATZ_CHECK_ARG(rows > 0 && C > 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(C % 8 == 0 && C <= 32 * LN_MAXCH * 8, KATZ_ESIZE);
+    KATZ_CHECK_ARG(aligned16(x) && aligned16(y) && aligned16(gamma) && aligned16(beta), KATZ_EALIGN);
+    const int rows_per_cta = 8;
+    layer_norm_kernel<<<ceil_div(rows, rows_per_cta), rows_per_cta * 32, 0, (cudaStream_t)stream>>>(
+        (const __half*)x, (__half*)y, (const __half*)gamma, (const __half*)beta, rows, C, eps);
+    KATZ_LAUNCH_RET();
+}

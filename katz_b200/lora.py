@@ -1,0 +1,202 @@
+"""LoRA merge / restore / unmerge over a set of device-resident linears, one kernel launch per operation.
+
+Entry points mirror the reference's:
+  * `patch_on_lora(pipe, lora_state_dicts, ...)` — lora_utils.patch_on_lora (lora_utils.py:9-33): for every key of the
+    key map, `W[key] += up @ down * scale` with scale = fp16(20000/64).
+  * `KatzLoraPipelineMixin.patch_on_lora(lora_state_dict, lora_model_repos, default_unet_state_dict)` —
+    StableDiffusionXLControlNetPipelineKatz.patch_on_lora (pipeline_controlnet_sd_xl_katz.py:1730-1747): merge into a
+    pristine copy, then load.
+  * `LoraMerger.restore()` — `unet.load_state_dict(deepcopy(default_unet_state_dict))` (sdxl_unet_server.py:217).
+
+The merger keeps the pristine weights W0 resident in HBM next to the live weights, so `merge` is a single streaming
+pass W_live = W0 + sum_i s_i * B_i A_i and `restore` is a bit-exact copy — the reference's copy semantics, without its
+three full-model copies per request. `merge_in_place` / `unmerge_in_place` give the +/- arithmetic of
+LoRACompatibleLinear._fuse_lora/_unfuse_lora (diffusers/models/lora.py:403-449), which floating point does not undo
+exactly.
+"""
+import ctypes
+import json
+from collections import OrderedDict
+
+import torch
+
+from . import _lib
+from ._lib import KATZ_DTYPE_F16, KATZ_DTYPE_F32, KatzError, LoraLayer, LORA_MAX_ADAPTERS
+
+REFERENCE_UNET_SCALE = float(torch.tensor(20000.0 / 64.0, dtype=torch.float16))  # lora_utils.py:22
+
+
+def _dtype_code(dt):
+    if dt == torch.float16:
+        return KATZ_DTYPE_F16
+    if dt == torch.float32:
+        return KATZ_DTYPE_F32
+    raise KatzError("LoRA merge supports fp16 or fp32 weights, not %s" % dt)
+
+
+class LoraMerger:
+    """Owns the layer table for a fixed set of target weights.
+
+    weights: OrderedDict key -> CUDA tensor [out, in] (contiguous rows; views into fused buffers are fine).
+    keep_pristine: clone every target weight once (W0) so restore is a copy and merge never accumulates error.
+    """
+
+    def __init__(self, weights, keep_pristine=True):
+        if not weights:
+            raise KatzError("no target weights")
+        self.keys = list(weights.keys())
+        self.weights = OrderedDict(weights)
+        first = next(iter(weights.values()))
+        self.device = first.device
+        self.dtype = first.dtype
+        self.code = _dtype_code(self.dtype)
+        for k, w in weights.items():
+            if w.dim() != 2 or not w.is_contiguous() or w.dtype != self.dtype or w.device != self.device:
+                raise KatzError("target %s must be a contiguous 2-D %s tensor on %s" % (k, self.dtype, self.device))
+        lib = _lib.load()
+        self.tile_rows = lib.katz_lora_tile_rows(self.code)
+        self.tile_cols = lib.katz_lora_tile_cols()
+        starts, total = [], 0
+        for w in self.weights.values():
+            starts.append(total)
+            total += -(-w.shape[0] // self.tile_rows) * -(-w.shape[1] // self.tile_cols)
+        self.total_tiles = total
+        self.d_tile_start = torch.tensor(starts, dtype=torch.int32, device=self.device)
+        self.pristine = None
+        if keep_pristine:
+            self.snapshot_pristine()
+        n = len(self.keys)
+        self._h_table = (LoraLayer * n)()
+        self._h_pinned = torch.empty(ctypes.sizeof(self._h_table), dtype=torch.uint8).pin_memory()
+        self._d_table = torch.empty(ctypes.sizeof(self._h_table), dtype=torch.uint8, device=self.device)
+        self._keepalive = []
+        self._upload_done = None   # event after the last table upload: the pinned staging buffer is reused
+        self.merged = []   # description of what is currently merged
+
+    # -- pristine copy ------------------------------------------------------------------------------------------
+    def snapshot_pristine(self):
+        """Record the current live weights as W0 (gen_unet_state_dict.py:54-58 plays this role in the reference)."""
+        self.pristine = OrderedDict((k, w.clone()) for k, w in self.weights.items())
+
+    def algorithmic_bytes(self, ranks):
+        """Bytes one merge pass must move: read + write of every W, plus each adapter's A and B once."""
+        es = 2 if self.dtype == torch.float16 else 4
+        wb = sum(w.numel() for w in self.weights.values()) * es
+        ab = sum(r * (w.shape[0] + w.shape[1]) for w in self.weights.values() for r in ranks) * es
+        return 2 * wb + ab
+
+    # -- table --------------------------------------------------------------------------------------------------
+    def _fill(self, adapters, scales, use_pristine):
+        """adapters: list of dict key -> (up [out,r], down [r,in]) on this device, same dtype as W."""
+        if len(adapters) > LORA_MAX_ADAPTERS:
+            raise KatzError("at most %d adapters per merge" % LORA_MAX_ADAPTERS)
+        if use_pristine and self.pristine is None:
+            raise KatzError("no pristine copy: construct with keep_pristine=True or call snapshot_pristine()")
+        lib = _lib.load()
+        if self._upload_done is not None:
+            self._upload_done.synchronize()
+        keep = []
+        for i, k in enumerate(self.keys):
+            w = self.weights[k]
+            e = self._h_table[i]
+            e.W = w.data_ptr()
+            e.W0 = self.pristine[k].data_ptr() if use_pristine else None
+            e.out_features, e.in_features = w.shape
+            n = 0
+            for ad, s in zip(adapters, scales):
+                if k not in ad:
+                    continue
+                up, down = ad[k]
+                if up.dtype != self.dtype or down.dtype != self.dtype or up.device != self.device or down.device != self.device:
+                    raise KatzError("adapter tensors for %s must be %s on %s" % (k, self.dtype, self.device))
+                if not up.is_contiguous() or not down.is_contiguous():
+                    raise KatzError("adapter tensors for %s must be contiguous" % k)
+                r = down.shape[0]
+                if up.shape != (w.shape[0], r) or down.shape != (r, w.shape[1]):
+                    raise KatzError("adapter shapes for %s do not match W%s: up%s down%s" % (k, tuple(w.shape), tuple(up.shape), tuple(down.shape)))
+                e.B[n] = up.data_ptr()
+                e.A[n] = down.data_ptr()
+                e.rank[n] = r
+                e.scale[n] = float(s[k]) if isinstance(s, dict) else float(s)
+                keep.append((up, down))
+                n += 1
+            e.n_lora = n
+            _lib.check(lib.katz_lora_layer_check(ctypes.byref(e), self.code), "katz_lora_layer_check(%s)" % k)
+        self._keepalive = keep
+        ctypes.memmove(self._h_pinned.data_ptr(), ctypes.addressof(self._h_table), ctypes.sizeof(self._h_table))
+        self._d_table.copy_(self._h_pinned, non_blocking=True)
+        self._upload_done = torch.cuda.Event()
+        self._upload_done.record(torch.cuda.current_stream(self.device))
+
+    def _launch(self, sign):
+        lib = _lib.load()
+        st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        _lib.check(lib.katz_lora_merge(ctypes.c_void_p(self._d_table.data_ptr()), ctypes.c_void_p(self.d_tile_start.data_ptr()),
+                                       len(self.keys), self.total_tiles, self.code, float(sign), st), "katz_lora_merge")
+
+    # -- operations ---------------------------------------------------------------------------------------------
+    def merge(self, adapters, scales):
+        """W_live = W0 + sum_i scale_i * up_i @ down_i (one pass; whatever was merged before is replaced)."""
+        adapters = adapters if isinstance(adapters, (list, tuple)) else [adapters]
+        scales = scales if isinstance(scales, (list, tuple)) else [scales] * len(adapters)
+        self._fill(adapters, scales, use_pristine=True)
+        self._launch(1.0)
+        self.merged = list(zip(adapters, scales))
+
+    def restore(self):
+        """W_live = W0, bit-exact."""
+        self._fill([], [], use_pristine=True)
+        self._launch(1.0)
+        self.merged = []
+
+    def merge_in_place(self, adapters, scales):
+        """W_live += sum_i scale_i * up_i @ down_i (no pristine copy involved)."""
+        adapters = adapters if isinstance(adapters, (list, tuple)) else [adapters]
+        scales = scales if isinstance(scales, (list, tuple)) else [scales] * len(adapters)
+        self._fill(adapters, scales, use_pristine=False)
+        self._launch(1.0)
+        self.merged = self.merged + list(zip(adapters, scales))
+
+    def unmerge_in_place(self, adapters, scales):
+        """W_live -= sum_i scale_i * up_i @ down_i: the subtractive unmerge; NOT guaranteed to restore W bit-exactly."""
+        adapters = adapters if isinstance(adapters, (list, tuple)) else [adapters]
+        scales = scales if isinstance(scales, (list, tuple)) else [scales] * len(adapters)
+        self._fill(adapters, scales, use_pristine=False)
+        self._launch(-1.0)
+
+
+def adapter_from_lora_state_dict(lora_state_dict, key_map, device, dtype):
+    """Gather (up, down) per UNet key from a LoRA state dict using the reference's key-map format
+    (lora_info_shm/*_key_match_unet.json: {unet_key: {"lora_down_key", "lora_up_key"}})."""
+    out = OrderedDict()
+    for k, m in key_map.items():
+        down = lora_state_dict[m["lora_down_key"]].to(device=device, dtype=dtype, non_blocking=True).contiguous()
+        up = lora_state_dict[m["lora_up_key"]].to(device=device, dtype=dtype, non_blocking=True).contiguous()
+        out[k] = (up, down)
+    return out
+
+
+def synthetic_key_map(keys):
+    """A key map in the reference's JSON format for a list of UNet weight keys."""
+    km = OrderedDict()
+    for k in keys:
+        stem = "unet." + k[: -len(".weight")]
+        km[k] = {"lora_down_key": stem + ".lora.down.weight", "lora_up_key": stem + ".lora.up.weight"}
+    return km
+
+
+def load_key_map(path):
+    with open(path, "r") as fr:
+        return json.load(fr, object_pairs_hook=OrderedDict)
+
+
+def patch_on_lora(unet, merger, lora_state_dicts, key_maps, scale=REFERENCE_UNET_SCALE):
+    """lora_utils.patch_on_lora (lora_utils.py:9-33) for the UNet: every adapter's `up @ down * scale` is added to the
+    matching UNet linear. `lora_state_dicts` / `key_maps` are per-adapter lists (the reference reads them from the hub
+    and from ./lora_info_shm). Returns the adapters gathered on the device."""
+    if not isinstance(lora_state_dicts, (list, tuple)):
+        lora_state_dicts, key_maps = [lora_state_dicts], [key_maps]
+    adapters = [adapter_from_lora_state_dict(sd, km, merger.device, merger.dtype) for sd, km in zip(lora_state_dicts, key_maps)]
+    merger.merge(adapters, [scale] * len(adapters))
+    unet.invalidate_caches()
+    return adapters

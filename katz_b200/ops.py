@@ -1,0 +1,283 @@
+"""Tensor-level wrappers over the C ABI: each takes torch CUDA tensors, checks layout, and launches on the current
+torch stream. No op here computes anything in torch; a missing library or a failing launch raises KatzError."""
+import ctypes
+import os
+
+import torch
+
+from . import _lib
+from ._lib import ACT_NONE, ACT_SILU, KatzError, call  # noqa: F401
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _f16(t, name):
+    if t.dtype != torch.float16 or not t.is_cuda:
+        raise KatzError("%s must be a CUDA fp16 tensor (got %s on %s)" % (name, t.dtype, t.device))
+    return t
+
+
+def _use_tc05():
+    return os.environ.get("KATZ_GEMM", "tc05") != "mma"
+
+
+_tc05_linear = None
+_tc05_conv = None
+
+
+def register_tc05(linear_fn, conv_fn):
+    """Installed by katz_b200.tc05 when the tcgen05 entry points are present in the library."""
+    global _tc05_linear, _tc05_conv
+    _tc05_linear, _tc05_conv = linear_fn, conv_fn
+
+
+def linear(x, w, bias=None, residual=None, act=ACT_NONE, rowvec=None, rows_per_batch=0, out=None, out_scale=1.0):
+    """out[M,N] = x[M,K] @ w[N,K]^T (+bias) (+rowvec[m // rows_per_batch]) -> act -> (+residual) * out_scale.
+    `x`, `residual`, `out` may be row-strided 2-D views (unit column stride)."""
+    _f16(x, "x"), _f16(w, "w")
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
+        raise KatzError("linear: shape mismatch x%s w%s" % (tuple(x.shape), tuple(w.shape)))
+    if x.stride(1) != 1 or not w.is_contiguous():
+        raise KatzError("linear: x must have unit column stride and w must be contiguous")
+    M, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float16, device=x.device)
+    if out.stride(1) != 1 or out.shape != (M, N):
+        raise KatzError("linear: bad out")
+    if residual is not None and (residual.shape != (M, N) or residual.stride(1) != 1):
+        raise KatzError("linear: bad residual")
+    if _use_tc05() and _tc05_linear is not None:
+        if _tc05_linear(x, w, bias, residual, act, rowvec, rows_per_batch, out, out_scale):
+            return out
+    call("katz_linear_f16_mma", _p(x), x.stride(0), _p(w), _p(out), out.stride(0), M, N, K, _p(bias), _p(rowvec),
+         rowvec.stride(0) if rowvec is not None else 0, rows_per_batch, _p(residual),
+         residual.stride(0) if residual is not None else 0, act, float(out_scale), _stream())
+    return out
+
+
+def conv2d(x, w, bias=None, ksize=3, stride=1, pad=1, upsample=False, x2=None, rowvec=None, residual=None,
+           act=ACT_NONE, out=None, out_scale=1.0):
+    """NHWC convolution. x: [B,Hs,Ws,C1] (+ optional x2 [B,Hs,Ws,C2] concatenated along channels); w: [Cout,k,k,C1+C2].
+    With upsample=True the input is read through a nearest 2x upsample. rowvec: [B, >=Cout] row-strided view added per
+    batch element; residual: [B,Hout,Wout,Cout]."""
+    _f16(x, "x"), _f16(w, "w")
+    if not x.is_contiguous() or not w.is_contiguous():
+        raise KatzError("conv2d: x and w must be contiguous")
+    B, Hs, Ws, C1 = x.shape
+    C2 = 0
+    if x2 is not None:
+        if not x2.is_contiguous() or x2.shape[:3] != x.shape[:3]:
+            raise KatzError("conv2d: bad x2")
+        C2 = x2.shape[3]
+    Cout = w.shape[0]
+    if w.numel() != Cout * ksize * ksize * (C1 + C2):
+        raise KatzError("conv2d: weight does not match [Cout,k,k,Cin]")
+    Hin, Win = (Hs * 2, Ws * 2) if upsample else (Hs, Ws)
+    Hout = (Hin + 2 * pad - ksize) // stride + 1
+    Wout = (Win + 2 * pad - ksize) // stride + 1
+    if out is None:
+        out = torch.empty((B, Hout, Wout, Cout), dtype=torch.float16, device=x.device)
+    if residual is not None and (tuple(residual.shape) != (B, Hout, Wout, Cout) or not residual.is_contiguous()):
+        raise KatzError("conv2d: bad residual")
+    if _use_tc05() and _tc05_conv is not None:
+        if _tc05_conv(x, x2, w, bias, ksize, stride, pad, upsample, rowvec, residual, act, out, out_scale):
+            return out
+    call("katz_conv2d_nhwc_f16_mma", _p(x), _p(x2), _p(w), _p(out), B, Hin, Win, C1, C2, Cout, ksize, stride, pad,
+         1 if upsample else 0, _p(bias), _p(rowvec), rowvec.stride(0) if rowvec is not None else 0, _p(residual), act,
+         float(out_scale), _stream())
+    return out
+
+
+_gn_scratch = {}
+
+
+def _scratch(device, nbytes):
+    buf = _gn_scratch.get(device)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _gn_scratch[device] = buf
+    return buf
+
+
+def group_norm_nhwc(x, gamma, beta, groups, eps, act=ACT_NONE, out=None):
+    """GroupNorm (+SiLU) over an NHWC tensor [B,H,W,C] (or [B,HW,C])."""
+    _f16(x, "x")
+    if not x.is_contiguous():
+        raise KatzError("group_norm: x must be contiguous")
+    B, C = x.shape[0], x.shape[-1]
+    HW = x.numel() // (B * C)
+    if out is None:
+        out = torch.empty_like(x)
+    lib = _lib.load()
+    need = lib.katz_group_norm_scratch_bytes(B, HW, C, groups)
+    if need < 0:
+        raise KatzError("group_norm: bad shape")
+    # The scratch buffer is shared by every GroupNorm call on this device: calls are ordered on one stream.
+    scratch = _scratch(x.device, need)
+    call("katz_group_norm_nhwc_f16", _p(x), _p(out), _p(gamma), _p(beta), B, HW, C, groups, float(eps), act,
+         _p(scratch), scratch.numel(), _stream())
+    return out
+
+
+def group_norm_nchw(x, gamma, beta, groups, eps, act=ACT_NONE, out=None):
+    _f16(x, "x")
+    if not x.is_contiguous():
+        raise KatzError("group_norm: x must be contiguous")
+    B, C = x.shape[0], x.shape[1]
+    HW = x.numel() // (B * C)
+    if out is None:
+        out = torch.empty_like(x)
+    call("katz_group_norm_nchw_f16", _p(x), _p(out), _p(gamma), _p(beta), B, HW, C, groups, float(eps), act, _stream())
+    return out
+
+
+def layer_norm(x, gamma, beta, eps=1e-5, out=None):
+    _f16(x, "x")
+    if not x.is_contiguous():
+        raise KatzError("layer_norm: x must be contiguous")
+    C = x.shape[-1]
+    rows = x.numel() // C
+    if out is None:
+        out = torch.empty_like(x)
+    call("katz_layer_norm_f16", _p(x), _p(out), _p(gamma), _p(beta), rows, C, float(eps), _stream())
+    return out
+
+
+def geglu_erf(hg, out=None):
+    """hg: [M, 2F] contiguous -> [M, F] = hg[:, :F] * gelu(hg[:, F:])."""
+    _f16(hg, "hg")
+    M, F2 = hg.shape
+    F = F2 // 2
+    if out is None:
+        out = torch.empty((M, F), dtype=torch.float16, device=hg.device)
+    call("katz_geglu_erf_f16", _p(hg), _p(out), M, F, hg.stride(0), _stream())
+    return out
+
+
+def fast_gelu_mul(x, m, out=None):
+    _f16(x, "x"), _f16(m, "m")
+    if x.shape != m.shape:
+        raise KatzError("Input tensors x and m must have the same shape.")
+    if not x.is_contiguous():
+        raise KatzError("Input tensor x must be contiguous.")
+    if not m.is_contiguous():
+        raise KatzError("Input tensor m must be contiguous.")
+    if out is None:
+        out = torch.empty_like(x)
+    call("katz_fast_gelu_mul_f16", _p(x), _p(m), _p(out), x.numel(), _stream())
+    return out
+
+
+def attention(q, k, v, heads, out=None, scale=None):
+    """q: [B,Sq,>=H*64] view, k/v: [B,Sk,...] views (unit last stride, any row/batch stride); returns [B,Sq,H*64]."""
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _f16(t, n)
+        if t.dim() != 3 or t.stride(2) != 1:
+            raise KatzError("attention: %s must be [B,S,C] with unit last stride" % n)
+    B, Sq, _ = q.shape
+    Sk = k.shape[1]
+    D = 64
+    if out is None:
+        out = torch.empty((B, Sq, heads * D), dtype=torch.float16, device=q.device)
+    if scale is None:
+        scale = D ** -0.5
+    call("katz_attention_f16_mma", _p(q), _p(k), _p(v), _p(out), B, heads, Sq, Sk, D, q.stride(1), k.stride(1),
+         v.stride(1), out.stride(1), q.stride(0), k.stride(0), v.stride(0), out.stride(0), float(scale), _stream())
+    return out
+
+
+def residual_intake(src, residuals, scales, out=None):
+    """out = src + half(sum_i scales[i] * residuals[i])."""
+    _f16(src, "src")
+    n = len(residuals)
+    if out is None:
+        out = torch.empty_like(src)
+    ptrs = (ctypes.c_void_p * n)(*[r.data_ptr() for r in residuals])
+    for r in residuals:
+        _f16(r, "residual")
+        if r.numel() != src.numel() or not r.is_contiguous():
+            raise KatzError("residual_intake: residual shape/layout mismatch")
+    sc = (ctypes.c_float * n)(*[float(s) for s in scales])
+    call("katz_residual_intake_f16", _p(src), _p(out), ptrs, sc, n, src.numel(), _stream())
+    return out
+
+
+def timestep_embedding(t, dim, out=None):
+    """t: fp32 CUDA tensor [rows] -> fp16 [rows, dim]."""
+    if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous():
+        raise KatzError("timestep_embedding: t must be a contiguous CUDA fp32 tensor")
+    rows = t.numel()
+    if out is None:
+        out = torch.empty((rows, dim), dtype=torch.float16, device=t.device)
+    call("katz_timestep_embedding_f16", _p(t), _p(out), rows, dim, out.stride(0), _stream())
+    return out
+
+
+def silu(x, out=None):
+    _f16(x, "x")
+    if out is None:
+        out = torch.empty_like(x)
+    call("katz_silu_f16", _p(x), _p(out), x.numel(), _stream())
+    return out
+
+
+def add(a, b, out=None):
+    _f16(a, "a"), _f16(b, "b")
+    if out is None:
+        out = torch.empty_like(a)
+    call("katz_add_f16", _p(a), _p(b), _p(out), a.numel(), _stream())
+    return out
+
+
+def concat_channels(a, b, out=None):
+    """[..., C1] ++ [..., C2] -> [..., C1+C2] (skip-connection concat of the up blocks)."""
+    _f16(a, "a"), _f16(b, "b")
+    C1, C2 = a.shape[-1], b.shape[-1]
+    rows = a.numel() // C1
+    if out is None:
+        out = torch.empty(tuple(a.shape[:-1]) + (C1 + C2,), dtype=torch.float16, device=a.device)
+    call("katz_concat_channels_f16", _p(a), _p(b), _p(out), rows, C1, C2, _stream())
+    return out
+
+
+def nchw_to_nhwc(x, cpad=None, out=None):
+    _f16(x, "x")
+    B, C, H, W = x.shape
+    cpad = cpad or C
+    if out is None:
+        out = torch.empty((B, H, W, cpad), dtype=torch.float16, device=x.device)
+    call("katz_nchw_to_nhwc_f16", _p(x.contiguous()), _p(out), B, C, H * W, cpad, _stream())
+    return out
+
+
+def nhwc_to_nchw(x, c=None, out=None):
+    _f16(x, "x")
+    B, H, W, cpad = x.shape
+    c = c or cpad
+    if out is None:
+        out = torch.empty((B, c, H, W), dtype=torch.float16, device=x.device)
+    call("katz_nhwc_to_nchw_f16", _p(x), _p(out), B, c, H * W, cpad, _stream())
+    return out
+
+
+def euler_scale_input(x, sigma, copies=1, out=None):
+    _f16(x, "x")
+    if out is None:
+        out = torch.empty((copies * x.shape[0],) + tuple(x.shape[1:]), dtype=torch.float16, device=x.device)
+    call("katz_euler_scale_input", _p(x), _p(out), x.numel(), float(sigma), copies, _stream())
+    return out
+
+
+def euler_cfg_step(x, eps_uncond, eps_cond, guidance, sigma, sigma_next):
+    """In-place Euler step on the fp16 latent x with classifier-free guidance."""
+    _f16(x, "x"), _f16(eps_uncond, "eps_uncond")
+    call("katz_euler_cfg_step", _p(x), _p(eps_uncond), _p(eps_cond), x.numel(), float(guidance), float(sigma),
+         float(sigma_next), _stream())
+    return x

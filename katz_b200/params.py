@@ -1,0 +1,230 @@
+"""Parameter inventory of the SDXL UNet / ControlNet (names and shapes as in the reference's state dicts) and a
+deterministic random initialiser for them.
+
+Names follow `UNet2DConditionModel.state_dict()` / `ControlNetModel.state_dict()` of the reference fork
+(diffusers/models/unets/unet_2d_condition.py:264-562, diffusers/models/controlnet.py:188-430): resnet norms are
+`norm_silu1.0` / `norm_silu2.0`, the output norm is `conv_norm_silu.0`, GEGLU is the unsplit `proj`.
+"""
+from collections import OrderedDict
+
+import numpy as np
+import torch
+
+SDXL_UNET_CONFIG = dict(
+    in_channels=4, out_channels=4, block_out_channels=(320, 640, 1280),
+    down_block_types=("DownBlock2D", "CrossAttnDownBlock2D", "CrossAttnDownBlock2D"),
+    up_block_types=("CrossAttnUpBlock2D", "CrossAttnUpBlock2D", "UpBlock2D"),
+    layers_per_block=2, transformer_layers_per_block=(1, 2, 10), attention_head_dim=(5, 10, 20),
+    cross_attention_dim=2048, addition_time_embed_dim=256, projection_class_embeddings_input_dim=2816,
+    norm_num_groups=32, norm_eps=1e-5, sample_size=128,
+)
+
+TINY_UNET_CONFIG = dict(
+    in_channels=4, out_channels=4, block_out_channels=(64, 128, 256),
+    down_block_types=("DownBlock2D", "CrossAttnDownBlock2D", "CrossAttnDownBlock2D"),
+    up_block_types=("CrossAttnUpBlock2D", "CrossAttnUpBlock2D", "UpBlock2D"),
+    layers_per_block=2, transformer_layers_per_block=(1, 1, 2), attention_head_dim=(1, 2, 4),
+    cross_attention_dim=128, addition_time_embed_dim=32, projection_class_embeddings_input_dim=32 * 6 + 64,
+    norm_num_groups=32, norm_eps=1e-5, sample_size=16,
+)
+
+CONTROLNET_COND_CHANNELS = (16, 32, 96, 256)
+
+
+def _resnet(out, p, cin, cout, temb):
+    out[p + ".norm_silu1.0.weight"] = (cin,)
+    out[p + ".norm_silu1.0.bias"] = (cin,)
+    out[p + ".conv1.weight"] = (cout, cin, 3, 3)
+    out[p + ".conv1.bias"] = (cout,)
+    out[p + ".time_emb_proj.weight"] = (cout, temb)
+    out[p + ".time_emb_proj.bias"] = (cout,)
+    out[p + ".norm_silu2.0.weight"] = (cout,)
+    out[p + ".norm_silu2.0.bias"] = (cout,)
+    out[p + ".conv2.weight"] = (cout, cout, 3, 3)
+    out[p + ".conv2.bias"] = (cout,)
+    if cin != cout:
+        out[p + ".conv_shortcut.weight"] = (cout, cin, 1, 1)
+        out[p + ".conv_shortcut.bias"] = (cout,)
+
+
+def _transformer(out, p, c, layers, cross):
+    out[p + ".norm.weight"] = (c,)
+    out[p + ".norm.bias"] = (c,)
+    out[p + ".proj_in.weight"] = (c, c)
+    out[p + ".proj_in.bias"] = (c,)
+    for i in range(layers):
+        b = "%s.transformer_blocks.%d" % (p, i)
+        out[b + ".norm1.weight"] = (c,)
+        out[b + ".norm1.bias"] = (c,)
+        for n in ("to_q", "to_k", "to_v"):
+            out["%s.attn1.%s.weight" % (b, n)] = (c, c)
+        out[b + ".attn1.to_out.0.weight"] = (c, c)
+        out[b + ".attn1.to_out.0.bias"] = (c,)
+        out[b + ".norm2.weight"] = (c,)
+        out[b + ".norm2.bias"] = (c,)
+        out[b + ".attn2.to_q.weight"] = (c, c)
+        out[b + ".attn2.to_k.weight"] = (c, cross)
+        out[b + ".attn2.to_v.weight"] = (c, cross)
+        out[b + ".attn2.to_out.0.weight"] = (c, c)
+        out[b + ".attn2.to_out.0.bias"] = (c,)
+        out[b + ".norm3.weight"] = (c,)
+        out[b + ".norm3.bias"] = (c,)
+        out[b + ".ff.net.0.proj.weight"] = (8 * c, c)
+        out[b + ".ff.net.0.proj.bias"] = (8 * c,)
+        out[b + ".ff.net.2.weight"] = (c, 4 * c)
+        out[b + ".ff.net.2.bias"] = (c,)
+    out[p + ".proj_out.weight"] = (c, c)
+    out[p + ".proj_out.bias"] = (c,)
+
+
+def _encoder(out, cfg):
+    """conv_in, embeddings, down blocks, mid block: shared by the UNet and the ControlNet."""
+    boc = cfg["block_out_channels"]
+    temb = boc[0] * 4
+    out["conv_in.weight"] = (boc[0], cfg["in_channels"], 3, 3)
+    out["conv_in.bias"] = (boc[0],)
+    out["time_embedding.linear_1.weight"] = (temb, boc[0])
+    out["time_embedding.linear_1.bias"] = (temb,)
+    out["time_embedding.linear_2.weight"] = (temb, temb)
+    out["time_embedding.linear_2.bias"] = (temb,)
+    out["add_embedding.linear_1.weight"] = (temb, cfg["projection_class_embeddings_input_dim"])
+    out["add_embedding.linear_1.bias"] = (temb,)
+    out["add_embedding.linear_2.weight"] = (temb, temb)
+    out["add_embedding.linear_2.bias"] = (temb,)
+    cin = boc[0]
+    for bi, btype in enumerate(cfg["down_block_types"]):
+        cout = boc[bi]
+        p = "down_blocks.%d" % bi
+        if btype == "CrossAttnDownBlock2D":
+            for li in range(cfg["layers_per_block"]):
+                _transformer(out, "%s.attentions.%d" % (p, li), cout, cfg["transformer_layers_per_block"][bi],
+                             cfg["cross_attention_dim"])
+        for li in range(cfg["layers_per_block"]):
+            _resnet(out, "%s.resnets.%d" % (p, li), cin if li == 0 else cout, cout, temb)
+        if bi != len(boc) - 1:
+            out[p + ".downsamplers.0.conv.weight"] = (cout, cout, 3, 3)
+            out[p + ".downsamplers.0.conv.bias"] = (cout,)
+        cin = cout
+    c = boc[-1]
+    _transformer(out, "mid_block.attentions.0", c, cfg["transformer_layers_per_block"][-1], cfg["cross_attention_dim"])
+    _resnet(out, "mid_block.resnets.0", c, c, temb)
+    _resnet(out, "mid_block.resnets.1", c, c, temb)
+
+
+def unet_param_shapes(cfg):
+    """OrderedDict name -> shape of UNet2DConditionModel for `cfg` (SDXL structure)."""
+    out = OrderedDict()
+    _encoder(out, cfg)
+    boc = cfg["block_out_channels"]
+    temb = boc[0] * 4
+    # up blocks are appended to the module after the mid block but state_dict order follows registration order:
+    # conv_in, embeddings, down_blocks, up_blocks, mid_block, conv_norm, conv_out. Order is irrelevant to users of this
+    # dict; keys and shapes are what matters.
+    rev = tuple(reversed(boc))
+    rev_layers = tuple(reversed(cfg["transformer_layers_per_block"]))
+    prev = rev[0]
+    for bi, btype in enumerate(cfg["up_block_types"]):
+        cout = rev[bi]
+        cin_skip = rev[min(bi + 1, len(boc) - 1)]
+        p = "up_blocks.%d" % bi
+        n = cfg["layers_per_block"] + 1
+        if btype == "CrossAttnUpBlock2D":
+            for li in range(n):
+                _transformer(out, "%s.attentions.%d" % (p, li), cout, rev_layers[bi], cfg["cross_attention_dim"])
+        for li in range(n):
+            skip = cin_skip if li == n - 1 else cout
+            rin = prev if li == 0 else cout
+            _resnet(out, "%s.resnets.%d" % (p, li), rin + skip, cout, temb)
+        if bi != len(boc) - 1:
+            out[p + ".upsamplers.0.conv.weight"] = (cout, cout, 3, 3)
+            out[p + ".upsamplers.0.conv.bias"] = (cout,)
+        prev = cout
+    out["conv_norm_silu.0.weight"] = (boc[0],)
+    out["conv_norm_silu.0.bias"] = (boc[0],)
+    out["conv_out.weight"] = (cfg["out_channels"], boc[0], 3, 3)
+    out["conv_out.bias"] = (cfg["out_channels"],)
+    return out
+
+
+def controlnet_param_shapes(cfg, cond_channels=3):
+    """OrderedDict name -> shape of ControlNetModel.from_unet(unet) for `cfg`."""
+    out = OrderedDict()
+    _encoder(out, cfg)
+    boc = cfg["block_out_channels"]
+    ch = CONTROLNET_COND_CHANNELS
+    p = "controlnet_cond_embedding"
+    out[p + ".conv_in.weight"] = (ch[0], cond_channels, 3, 3)
+    out[p + ".conv_in.bias"] = (ch[0],)
+    for i in range(len(ch) - 1):
+        out["%s.blocks.%d.weight" % (p, 2 * i)] = (ch[i], ch[i], 3, 3)
+        out["%s.blocks.%d.bias" % (p, 2 * i)] = (ch[i],)
+        out["%s.blocks.%d.weight" % (p, 2 * i + 1)] = (ch[i + 1], ch[i], 3, 3)
+        out["%s.blocks.%d.bias" % (p, 2 * i + 1)] = (ch[i + 1],)
+    out[p + ".conv_out.weight"] = (boc[0], ch[-1], 3, 3)
+    out[p + ".conv_out.bias"] = (boc[0],)
+    # zero-convs: one for conv_in's output, one per resnet output, one per downsampler output
+    idx = 0
+    chans = [boc[0]]
+    for bi in range(len(boc)):
+        chans += [boc[bi]] * cfg["layers_per_block"]
+        if bi != len(boc) - 1:
+            chans.append(boc[bi])
+    for c in chans:
+        out["controlnet_down_blocks.%d.weight" % idx] = (c, c, 1, 1)
+        out["controlnet_down_blocks.%d.bias" % idx] = (c,)
+        idx += 1
+    out["controlnet_mid_block.weight"] = (boc[-1], boc[-1], 1, 1)
+    out["controlnet_mid_block.bias"] = (boc[-1],)
+    return out
+
+
+def lora_target_keys(cfg, include_proj=False):
+    """UNet linears a LoRA targets, in module order: per transformer block attn1 q/k/v/out, attn2 q/k/v/out, ff proj,
+    ff out (700 layers for SDXL); with `include_proj` also each Transformer2DModel's proj_in/proj_out, which is the
+    722-entry set of the reference's key-map fixtures (lora_info_shm/*_key_match_unet.json)."""
+    keys = []
+    for name in unet_param_shapes(cfg):
+        if not name.endswith(".weight"):
+            continue
+        if ".transformer_blocks." in name and (".attn1.to_" in name or ".attn2.to_" in name or ".ff.net.0.proj." in name
+                                               or ".ff.net.2." in name):
+            keys.append(name)
+        elif include_proj and (name.endswith(".proj_in.weight") or name.endswith(".proj_out.weight")):
+            keys.append(name)
+    return keys
+
+
+def init_state_dict(shapes, seed=0, dtype=torch.float16, device="cpu", generator_device=None):
+    """Deterministic random initialisation: weights and biases U(-1/sqrt(fan_in), 1/sqrt(fan_in)) (torch's default for
+    Linear/Conv2d), norm scales 1 + 0.1*U(-1,1), norm shifts 0.1*U(-1,1). With device='cpu' numbers come from numpy's
+    PCG64 stream (identical on every machine); with `generator_device='cuda'` they are drawn on the GPU (fast, used by
+    the benchmark, not reproducible across devices)."""
+    sd = OrderedDict()
+    if generator_device is None:
+        rng = np.random.default_rng(seed)
+        for name, shape in shapes.items():
+            n = int(np.prod(shape))
+            u = rng.random(n, dtype=np.float32) * 2.0 - 1.0
+            t = torch.from_numpy(u).reshape(shape)
+            sd[name] = _scale_param(name, shape, t).to(dtype).to(device)
+    else:
+        g = torch.Generator(device=generator_device)
+        g.manual_seed(seed)
+        for name, shape in shapes.items():
+            t = torch.rand(shape, generator=g, device=generator_device, dtype=torch.float32) * 2.0 - 1.0
+            sd[name] = _scale_param(name, shape, t).to(dtype).to(device)
+    return sd
+
+
+def _scale_param(name, shape, t):
+    is_norm = (".norm" in name or name.startswith("conv_norm")) and len(shape) == 1
+    if is_norm:
+        return 1.0 + 0.1 * t if name.endswith(".weight") else 0.1 * t
+    if name.endswith(".weight"):
+        fan_in = int(np.prod(shape[1:]))
+    else:
+        fan_in = _bias_fan_in.get(name, None) or shape[0]
+    return t * (1.0 / float(np.sqrt(fan_in)))
+
+
+_bias_fan_in = {}

@@ -1,0 +1,447 @@
+"""Host-side mirror of the reference's SDXL UNet / ControlNet step over the katz_b200 kernels.
+
+Keeps the reference's call surface for this path — `unet(sample, timestep, encoder_hidden_states=...,
+added_cond_kwargs={"text_embeds","time_ids"}, down_block_additional_residuals=..., mid_block_additional_residual=...,
+return_dict=False)` as used by sdxl_unet_server.py:199-213, and `controlnet(sample, t, encoder_hidden_states=...,
+controlnet_cond=..., added_cond_kwargs=..., conditioning_scale=0.5)` as used by sdxl_controlnet_server.py:94-100 — and
+the state-dict key names of the reference fork, so weights, LoRA key maps and the pristine-state restore carry over.
+
+The computation follows `_down_forward` -> ControlNet residual add -> `_up_forward`
+(diffusers/models/unets/unet_2d_condition.py:1127-1341), i.e. the reference's CUDA-graph path that adds all nine down
+residuals and the mid residual. Activations are NHWC fp16 end to end ([B, H, W, C] is also the [B, H*W, C] token
+layout, so Transformer2DModel's permutes disappear); NCHW appears only at the model boundary.
+"""
+from collections import OrderedDict
+
+import torch
+
+from . import ops
+from .ops import ACT_NONE, ACT_SILU, KatzError
+from .params import CONTROLNET_COND_CHANNELS, controlnet_param_shapes, unet_param_shapes
+
+_ALT_NAMES = (
+    (".norm1.", ".norm_silu1.0."),
+    (".norm2.", ".norm_silu2.0."),
+)
+
+
+def _canonical_key(k):
+    """Map upstream-diffusers key spellings onto the fork's (resnet.py:336-350, unet_2d_condition.py:521-529)."""
+    if ".resnets." in k:
+        for a, b in _ALT_NAMES:
+            if a in k and ".transformer_blocks." not in k:
+                k = k.replace(a, b)
+    if k.startswith("conv_norm_out."):
+        k = "conv_norm_silu.0." + k[len("conv_norm_out."):]
+    return k
+
+
+class _Weights:
+    """Device-resident fp16 parameters in the layouts the kernels read, addressable by reference key.
+
+    Linear weights are stored as-is ([N, K]); the three self-attention projections of a block live in one [3C, C]
+    buffer, every block's cross-attention to_k/to_v in one [sum 2C, cross_dim] buffer, and every resnet's
+    time_emb_proj in one [sum Cout, temb] buffer — each reference key is a row-range VIEW of those buffers, so a LoRA
+    merge through the key writes the storage the fused GEMMs read. Convolution weights are stored [Cout, ky, kx, Cin].
+    """
+
+    def __init__(self, shapes, device):
+        self.shapes = shapes
+        self.device = device
+        self.t = {}          # key -> tensor in kernel layout (views for fused groups)
+        self.fused = {}      # name -> fused buffer
+        self.conv_cin_pad = {}
+
+    def alloc(self):
+        dev = self.device
+        shapes = self.shapes
+        # --- fused groups
+        qkv_blocks = sorted({k[: -len(".attn1.to_q.weight")] for k in shapes if k.endswith(".attn1.to_q.weight")})
+        for b in qkv_blocks:
+            c = shapes[b + ".attn1.to_q.weight"][0]
+            buf = torch.zeros((3 * c, c), dtype=torch.float16, device=dev)
+            self.fused[b + ".attn1.qkv"] = buf
+            for i, n in enumerate(("to_q", "to_k", "to_v")):
+                self.t["%s.attn1.%s.weight" % (b, n)] = buf[i * c:(i + 1) * c]
+        kv_keys = [k for k in shapes if k.endswith(".attn2.to_k.weight")]
+        if kv_keys:
+            cross = shapes[kv_keys[0]][1]
+            total = sum(2 * shapes[k][0] for k in kv_keys)
+            buf = torch.zeros((total, cross), dtype=torch.float16, device=dev)
+            self.fused["cross_kv"] = buf
+            self.cross_kv_offset = {}
+            off = 0
+            for k in kv_keys:
+                c = shapes[k][0]
+                b = k[: -len(".attn2.to_k.weight")]
+                self.t[b + ".attn2.to_k.weight"] = buf[off:off + c]
+                self.t[b + ".attn2.to_v.weight"] = buf[off + c:off + 2 * c]
+                self.cross_kv_offset[b] = off
+                off += 2 * c
+        te_keys = [k for k in shapes if k.endswith(".time_emb_proj.weight")]
+        temb = shapes[te_keys[0]][1]
+        total = sum(shapes[k][0] for k in te_keys)
+        wbuf = torch.zeros((total, temb), dtype=torch.float16, device=dev)
+        bbuf = torch.zeros((total,), dtype=torch.float16, device=dev)
+        self.fused["temb_w"], self.fused["temb_b"] = wbuf, bbuf
+        self.temb_offset = {}
+        off = 0
+        for k in te_keys:
+            c = shapes[k][0]
+            b = k[: -len(".time_emb_proj.weight")]
+            self.t[k] = wbuf[off:off + c]
+            self.t[b + ".time_emb_proj.bias"] = bbuf[off:off + c]
+            self.temb_offset[b] = (off, c)
+            off += c
+        # --- everything else
+        for k, shp in shapes.items():
+            if k in self.t:
+                continue
+            if len(shp) == 4:
+                cout, cin, kh, kw = shp
+                cin_pad = (cin + 7) // 8 * 8
+                self.conv_cin_pad[k] = cin_pad
+                self.t[k] = torch.zeros((cout, kh, kw, cin_pad), dtype=torch.float16, device=dev)
+            else:
+                self.t[k] = torch.zeros(shp, dtype=torch.float16, device=dev)
+
+    def load(self, sd, strict=True):
+        missing = []
+        seen = set()
+        for k, v in sd.items():
+            ck = _canonical_key(k)
+            if ck.endswith(".proj_1.weight") or ck.endswith(".proj_2.weight") or ck.endswith(".proj_1.bias") or ck.endswith(".proj_2.bias"):
+                # the fork's split GEGLU (activations.py:151-170): proj_1 = first half, proj_2 = second half
+                base, which, kind = ck.rsplit(".", 2)[0], ck.rsplit(".", 2)[1], ck.rsplit(".", 2)[2]
+                dst = self.t[base + ".proj." + kind]
+                half = dst.shape[0] // 2
+                sl = slice(0, half) if which == "proj_1" else slice(half, 2 * half)
+                dst[sl].copy_(v.to(device=self.device, dtype=torch.float16))
+                seen.add(base + ".proj." + kind)
+                continue
+            if ck not in self.t:
+                if strict:
+                    raise KatzError("unexpected key in state dict: %s" % k)
+                continue
+            dst = self.t[ck]
+            src = v.to(device=self.device, dtype=torch.float16)
+            if len(self.shapes[ck]) == 4:
+                cin = self.shapes[ck][1]
+                if tuple(src.shape) != tuple(self.shapes[ck]):
+                    raise KatzError("shape mismatch for %s: %s vs %s" % (k, tuple(src.shape), self.shapes[ck]))
+                dst[..., :cin].copy_(src.permute(0, 2, 3, 1))
+            else:
+                if tuple(src.shape) != tuple(dst.shape):
+                    raise KatzError("shape mismatch for %s: %s vs %s" % (k, tuple(src.shape), tuple(dst.shape)))
+                dst.copy_(src)
+            seen.add(ck)
+        if strict:
+            missing = [k for k in self.shapes if k not in seen]
+            if missing:
+                raise KatzError("missing keys in state dict: %s ..." % missing[:5])
+        return missing
+
+    def export(self):
+        """Reference-layout state dict (fresh tensors, torch conv layout)."""
+        out = OrderedDict()
+        for k, shp in self.shapes.items():
+            t = self.t[k]
+            if len(shp) == 4:
+                out[k] = t[..., :shp[1]].permute(0, 3, 1, 2).contiguous()
+            else:
+                out[k] = t.clone()
+        return out
+
+
+class _Net:
+    """Shared machinery of the UNet and the ControlNet: embeddings, down blocks, mid block."""
+
+    def __init__(self, cfg, shapes, device):
+        self.cfg = dict(cfg)
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise KatzError("katz_b200 models run on a CUDA device only (no CPU fallback)")
+        self.w = _Weights(shapes, self.device)
+        self.w.alloc()
+        self.dtype = torch.float16
+        self.cache_text_kv = False     # optional hoist of the step-invariant cross-attention K/V (off: reference semantics)
+        self._kv_cache_key = None
+        self._kv_cache = None
+
+    # ---- state-dict surface (reference names)
+    def load_state_dict(self, sd, strict=True):
+        self._kv_cache_key = None
+        return self.w.load(sd, strict=strict)
+
+    def state_dict(self):
+        return self.w.export()
+
+    def lora_targets(self, keys):
+        """key -> live weight view [out, in] for LoRA merging."""
+        out = OrderedDict()
+        for k in keys:
+            if k not in self.w.t or len(self.w.shapes[k]) != 2:
+                raise KatzError("not a linear weight of this model: %s" % k)
+            out[k] = self.w.t[k]
+        return out
+
+    def invalidate_caches(self):
+        self._kv_cache_key = None
+
+    # ---- pieces
+    def _P(self, k):
+        return self.w.t[k]
+
+    def _embeddings(self, timestep, text_embeds, time_ids, B):
+        cfg, P = self.cfg, self._P
+        if not torch.is_tensor(timestep):
+            timestep = torch.tensor([float(timestep)], dtype=torch.float32, device=self.device)
+        t = timestep.to(device=self.device, dtype=torch.float32).reshape(-1)
+        if t.numel() == 1:
+            t = t.expand(B)
+        t = t.contiguous()
+        c0 = cfg["block_out_channels"][0]
+        t_emb = ops.timestep_embedding(t, c0)
+        h = ops.linear(t_emb, P("time_embedding.linear_1.weight"), P("time_embedding.linear_1.bias"), act=ACT_SILU)
+        emb = ops.linear(h, P("time_embedding.linear_2.weight"), P("time_embedding.linear_2.bias"))
+        ad = cfg["addition_time_embed_dim"]
+        n_ids = time_ids.shape[1]
+        add_in = torch.empty((B, text_embeds.shape[1] + n_ids * ad), dtype=torch.float16, device=self.device)
+        add_in[:, :text_embeds.shape[1]].copy_(text_embeds)
+        tid = ops.timestep_embedding(time_ids.to(device=self.device, dtype=torch.float32).reshape(-1).contiguous(), ad)
+        add_in[:, text_embeds.shape[1]:].copy_(tid.reshape(B, n_ids * ad))
+        h = ops.linear(add_in, P("add_embedding.linear_1.weight"), P("add_embedding.linear_1.bias"), act=ACT_SILU)
+        # emb = time_emb + aug_emb: the second MLP's output lands on emb through the residual epilogue
+        emb = ops.linear(h, P("add_embedding.linear_2.weight"), P("add_embedding.linear_2.bias"), residual=emb)
+        # every resnet's time_emb_proj(silu(emb)) in one GEMM
+        semb = ops.silu(emb)
+        temb_all = ops.linear(semb, self.w.fused["temb_w"], self.w.fused["temb_b"])
+        return emb, temb_all
+
+    def _cross_kv(self, ctx):
+        """K/V projections of the text context for every transformer block at once: [B*S, sum 2C]."""
+        if "cross_kv" not in self.w.fused:
+            return None
+        if self.cache_text_kv:
+            key = (ctx.data_ptr(), tuple(ctx.shape), ctx._version)
+            if self._kv_cache_key == key:
+                return self._kv_cache
+        B, S, D = ctx.shape
+        kv = ops.linear(ctx.reshape(B * S, D), self.w.fused["cross_kv"])
+        kv = kv.view(B, S, -1)
+        if self.cache_text_kv:
+            self._kv_cache_key, self._kv_cache = key, kv
+        return kv
+
+    def _resnet(self, p, x, temb_all):
+        cfg, P = self.cfg, self._P
+        g, eps = cfg["norm_num_groups"], cfg["norm_eps"]
+        B, H, W, Cin = x.shape
+        off, cout = self.w.temb_offset[p]
+        h = ops.group_norm_nhwc(x, P(p + ".norm_silu1.0.weight"), P(p + ".norm_silu1.0.bias"), g, eps, ACT_SILU)
+        h = ops.conv2d(h, P(p + ".conv1.weight"), P(p + ".conv1.bias"), rowvec=temb_all[:, off:off + cout])
+        h = ops.group_norm_nhwc(h, P(p + ".norm_silu2.0.weight"), P(p + ".norm_silu2.0.bias"), g, eps, ACT_SILU)
+        if (p + ".conv_shortcut.weight") in self.w.t:
+            sc = ops.linear(x.view(B * H * W, Cin), P(p + ".conv_shortcut.weight").view(cout, Cin),
+                            P(p + ".conv_shortcut.bias")).view(B, H, W, cout)
+        else:
+            sc = x
+        return ops.conv2d(h, P(p + ".conv2.weight"), P(p + ".conv2.bias"), residual=sc)
+
+    def _transformer(self, p, x, kv, heads, n_layers):
+        cfg, P = self.cfg, self._P
+        B, H, W, C = x.shape
+        M = B * H * W
+        h = ops.group_norm_nhwc(x, P(p + ".norm.weight"), P(p + ".norm.bias"), cfg["norm_num_groups"], 1e-6, ACT_NONE)
+        h = ops.linear(h.view(M, C), P(p + ".proj_in.weight"), P(p + ".proj_in.bias"))
+        for i in range(n_layers):
+            b = "%s.transformer_blocks.%d" % (p, i)
+            n = ops.layer_norm(h, P(b + ".norm1.weight"), P(b + ".norm1.bias"))
+            qkv = ops.linear(n, self.w.fused[b + ".attn1.qkv"]).view(B, H * W, 3 * C)
+            a = ops.attention(qkv[:, :, :C], qkv[:, :, C:2 * C], qkv[:, :, 2 * C:], heads)
+            h = ops.linear(a.view(M, C), P(b + ".attn1.to_out.0.weight"), P(b + ".attn1.to_out.0.bias"), residual=h)
+            n = ops.layer_norm(h, P(b + ".norm2.weight"), P(b + ".norm2.bias"))
+            q = ops.linear(n, P(b + ".attn2.to_q.weight")).view(B, H * W, C)
+            off = self.w.cross_kv_offset[b]
+            a = ops.attention(q, kv[:, :, off:off + C], kv[:, :, off + C:off + 2 * C], heads)
+            h = ops.linear(a.view(M, C), P(b + ".attn2.to_out.0.weight"), P(b + ".attn2.to_out.0.bias"), residual=h)
+            n = ops.layer_norm(h, P(b + ".norm3.weight"), P(b + ".norm3.bias"))
+            hg = ops.linear(n, P(b + ".ff.net.0.proj.weight"), P(b + ".ff.net.0.proj.bias"))
+            f = ops.geglu_erf(hg)
+            h = ops.linear(f, P(b + ".ff.net.2.weight"), P(b + ".ff.net.2.bias"), residual=h)
+        out = ops.linear(h, P(p + ".proj_out.weight"), P(p + ".proj_out.bias"), residual=x.view(M, C))
+        return out.view(B, H, W, C)
+
+    def _down_and_mid(self, sample, temb_all, kv):
+        cfg, P = self.cfg, self._P
+        res = [sample]
+        nb = len(cfg["block_out_channels"])
+        for bi, btype in enumerate(cfg["down_block_types"]):
+            heads = cfg["attention_head_dim"][bi]
+            for li in range(cfg["layers_per_block"]):
+                sample = self._resnet("down_blocks.%d.resnets.%d" % (bi, li), sample, temb_all)
+                if btype == "CrossAttnDownBlock2D":
+                    sample = self._transformer("down_blocks.%d.attentions.%d" % (bi, li), sample, kv, heads,
+                                               cfg["transformer_layers_per_block"][bi])
+                res.append(sample)
+            if bi != nb - 1:
+                p = "down_blocks.%d.downsamplers.0.conv" % bi
+                sample = ops.conv2d(sample, P(p + ".weight"), P(p + ".bias"), stride=2, pad=1)
+                res.append(sample)
+        heads = cfg["attention_head_dim"][-1]
+        sample = self._resnet("mid_block.resnets.0", sample, temb_all)
+        sample = self._transformer("mid_block.attentions.0", sample, kv, heads, cfg["transformer_layers_per_block"][-1])
+        sample = self._resnet("mid_block.resnets.1", sample, temb_all)
+        return sample, res
+
+    def _prep_inputs(self, sample, encoder_hidden_states, added_cond_kwargs):
+        if added_cond_kwargs is None or "text_embeds" not in added_cond_kwargs or "time_ids" not in added_cond_kwargs:
+            raise ValueError("addition_embed_type 'text_time' requires `text_embeds` and `time_ids` in added_cond_kwargs")
+        x = sample.to(device=self.device, dtype=torch.float16)
+        ctx = encoder_hidden_states.to(device=self.device, dtype=torch.float16).contiguous()
+        te = added_cond_kwargs["text_embeds"].to(device=self.device, dtype=torch.float16)
+        ti = added_cond_kwargs["time_ids"].to(device=self.device)
+        return x, ctx, te, ti
+
+
+def _to_nhwc_residual(r, device):
+    """ControlNet residuals arrive NCHW (reference layout) or NHWC-tagged; return a contiguous NHWC fp16 tensor."""
+    if isinstance(r, NHWC):
+        return r.t
+    r = r.to(device=device, dtype=torch.float16)
+    return ops.nchw_to_nhwc(r)
+
+
+class NHWC:
+    """Marks a tensor that is already [B, H, W, C]; lets an in-process ControlNet hand residuals to the UNet without
+    two layout moves."""
+
+    def __init__(self, t):
+        self.t = t
+
+
+class KatzUNet(_Net):
+    """UNet2DConditionModel of the reference, SDXL structure."""
+
+    def __init__(self, cfg, device="cuda", state_dict=None):
+        super().__init__(cfg, unet_param_shapes(cfg), device)
+        if state_dict is not None:
+            self.load_state_dict(state_dict)
+
+    def down_forward(self, x, timestep, ctx, te, ti):
+        """`_down_forward` (unet_2d_condition.py:1127-1252) on NHWC tensors."""
+        B = x.shape[0]
+        emb, temb_all = self._embeddings(timestep, te, ti, B)
+        kv = self._cross_kv(ctx)
+        h = ops.nchw_to_nhwc(x, cpad=self.w.conv_cin_pad["conv_in.weight"])
+        h = ops.conv2d(h, self._P("conv_in.weight"), self._P("conv_in.bias"))
+        mid, res = self._down_and_mid(h, temb_all, kv)
+        return mid, temb_all, res, kv
+
+    def up_forward(self, sample, temb_all, res, kv, down_residuals=None, mid_residual=None, combine_scales=None):
+        """`_up_forward` (unet_2d_condition.py:1254-1341). `down_residuals` is a list of 9 tensors, or a list of such
+        lists (one per ControlNet) combined with `combine_scales` (sum: 1.0 each; the service path's mean: 1/N each,
+        unet_2d_condition.py:1418-1439)."""
+        cfg, P = self.cfg, self._P
+        if down_residuals is not None:
+            nets = down_residuals if isinstance(down_residuals[0], (list, tuple)) else [down_residuals]
+            mids = mid_residual if isinstance(mid_residual, (list, tuple)) else [mid_residual]
+            scales = combine_scales or [1.0] * len(nets)
+            if any(len(n) != len(res) for n in nets):
+                raise KatzError("expected %d down residuals per ControlNet" % len(res))
+            res = [ops.residual_intake(r, [_to_nhwc_residual(n[j], self.device) for n in nets], scales)
+                   for j, r in enumerate(res)]
+            sample = ops.residual_intake(sample, [_to_nhwc_residual(m, self.device) for m in mids], scales)
+        nb = len(cfg["block_out_channels"])
+        rev_heads = tuple(reversed(cfg["attention_head_dim"]))
+        rev_layers = tuple(reversed(cfg["transformer_layers_per_block"]))
+        res = list(res)
+        for bi, btype in enumerate(cfg["up_block_types"]):
+            n_res = cfg["layers_per_block"] + 1
+            for li in range(n_res):
+                skip = res.pop()
+                sample = ops.concat_channels(sample, skip)
+                sample = self._resnet("up_blocks.%d.resnets.%d" % (bi, li), sample, temb_all)
+                if btype == "CrossAttnUpBlock2D":
+                    sample = self._transformer("up_blocks.%d.attentions.%d" % (bi, li), sample, kv, rev_heads[bi],
+                                               rev_layers[bi])
+            if bi != nb - 1:
+                p = "up_blocks.%d.upsamplers.0.conv" % bi
+                sample = ops.conv2d(sample, P(p + ".weight"), P(p + ".bias"), upsample=True)
+        h = ops.group_norm_nhwc(sample, P("conv_norm_silu.0.weight"), P("conv_norm_silu.0.bias"), cfg["norm_num_groups"],
+                                cfg["norm_eps"], ACT_SILU)
+        out = ops.conv2d(h, P("conv_out.weight"), P("conv_out.bias"))
+        return ops.nhwc_to_nchw(out, c=cfg["out_channels"])
+
+    def __call__(self, sample, timestep, encoder_hidden_states, timestep_cond=None, cross_attention_kwargs=None,
+                 added_cond_kwargs=None, down_block_additional_residuals=None, mid_block_additional_residual=None,
+                 return_dict=False, combine_scales=None, **_ignored):
+        """One denoising step; returns `(noise_pred,)` (NCHW fp16) like the reference with return_dict=False."""
+        x, ctx, te, ti = self._prep_inputs(sample, encoder_hidden_states, added_cond_kwargs)
+        mid, temb_all, res, kv = self.down_forward(x, timestep, ctx, te, ti)
+        out = self.up_forward(mid, temb_all, res, kv, down_block_additional_residuals, mid_block_additional_residual,
+                              combine_scales)
+        return (out,)
+
+    forward = __call__
+
+
+class KatzControlNet(_Net):
+    """ControlNetModel of the reference (encoder + mid copy of the UNet, conditioning embedding, zero-convs)."""
+
+    def __init__(self, cfg, device="cuda", state_dict=None, conditioning_channels=3):
+        super().__init__(cfg, controlnet_param_shapes(cfg, conditioning_channels), device)
+        self.cache_cond_embedding = False   # optional hoist of the step-invariant conditioning embedding
+        self._cond_key = None
+        self._cond_emb = None
+        if state_dict is not None:
+            self.load_state_dict(state_dict)
+
+    def _cond_embedding(self, cond):
+        """ControlNetConditioningEmbedding.forward (controlnet.py:113-127)."""
+        if self.cache_cond_embedding:
+            key = (cond.data_ptr(), tuple(cond.shape), cond._version)
+            if key == self._cond_key:
+                return self._cond_emb
+        P = self._P
+        p = "controlnet_cond_embedding"
+        h = ops.nchw_to_nhwc(cond.to(device=self.device, dtype=torch.float16), cpad=self.w.conv_cin_pad[p + ".conv_in.weight"])
+        h = ops.conv2d(h, P(p + ".conv_in.weight"), P(p + ".conv_in.bias"), act=ACT_SILU)
+        for i in range(2 * (len(CONTROLNET_COND_CHANNELS) - 1)):
+            h = ops.conv2d(h, P("%s.blocks.%d.weight" % (p, i)), P("%s.blocks.%d.bias" % (p, i)),
+                           stride=2 if i % 2 == 1 else 1, act=ACT_SILU)
+        if self.cache_cond_embedding:
+            self._cond_key, self._cond_emb = key, h
+        return h
+
+    def __call__(self, sample, timestep, encoder_hidden_states, controlnet_cond, conditioning_scale=0.5,
+                 added_cond_kwargs=None, return_dict=False, nhwc_out=False, **_ignored):
+        """`_controlnet_forward` (controlnet.py:687-847): returns (list of 9 down residuals, mid residual), each already
+        multiplied by `conditioning_scale`; NCHW like the reference unless `nhwc_out`."""
+        P = self._P
+        x, ctx, te, ti = self._prep_inputs(sample, encoder_hidden_states, added_cond_kwargs)
+        B = x.shape[0]
+        emb, temb_all = self._embeddings(timestep, te, ti, B)
+        kv = self._cross_kv(ctx)
+        p = "controlnet_cond_embedding"
+        ce = self._cond_embedding(controlnet_cond)
+        h = ops.nchw_to_nhwc(x, cpad=self.w.conv_cin_pad["conv_in.weight"])
+        h = ops.conv2d(h, P("conv_in.weight"), P("conv_in.bias"))
+        # sample = conv_in(sample) + cond_embedding.conv_out(...): the add rides on the second conv's residual epilogue
+        h = ops.conv2d(ce, P(p + ".conv_out.weight"), P(p + ".conv_out.bias"), residual=h)
+        mid, res = self._down_and_mid(h, temb_all, kv)
+        outs = []
+        s = float(conditioning_scale)
+        for i, r in enumerate(res):
+            Bq, H, W, C = r.shape
+            o = ops.linear(r.view(Bq * H * W, C), P("controlnet_down_blocks.%d.weight" % i).view(C, C),
+                           P("controlnet_down_blocks.%d.bias" % i), out_scale=s).view(Bq, H, W, C)
+            outs.append(o)
+        Bq, H, W, C = mid.shape
+        m = ops.linear(mid.view(Bq * H * W, C), P("controlnet_mid_block.weight").view(C, C), P("controlnet_mid_block.bias"),
+                       out_scale=s).view(Bq, H, W, C)
+        if nhwc_out:
+            return [NHWC(o) for o in outs], NHWC(m)
+        return [ops.nhwc_to_nchw(o) for o in outs], ops.nhwc_to_nchw(m)
+
+    forward = __call__
