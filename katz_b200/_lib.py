@@ -107,6 +107,23 @@ def check(code, what):
     raise KatzError("%s: CUDA error %d" % (what, code))
 
 
+# kernels launched per successful entry-point call (everything else launches one)
+_KERNELS_PER_CALL = {"katz_group_norm_nhwc_f16": 2}
+_launches = 0
+
+
+def launch_count():
+    """Kernels this process has launched through the library so far."""
+    return _launches
+
+
+def note_launches(n):
+    global _launches
+    _launches += n
+
+
 def call(name, *args):
+    global _launches
     lib = load()
     check(getattr(lib, name)(*args), name)
+    _launches += _KERNELS_PER_CALL.get(name, 1)

@@ -133,6 +133,7 @@ class LoraMerger:
         st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
         _lib.check(lib.katz_lora_merge(ctypes.c_void_p(self._d_table.data_ptr()), ctypes.c_void_p(self.d_tile_start.data_ptr()),
                                        len(self.keys), self.total_tiles, self.code, float(sign), st), "katz_lora_merge")
+        _lib.note_launches(1)
 
     # -- operations ---------------------------------------------------------------------------------------------
     def merge(self, adapters, scales):

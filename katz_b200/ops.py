@@ -37,6 +37,11 @@ def register_tc05(linear_fn, conv_fn):
     _tc05_linear, _tc05_conv = linear_fn, conv_fn
 
 
+def gemm_kernel_name():
+    """Which GEMM family `linear` dispatches large aligned shapes to."""
+    return "tcgen05" if (_use_tc05() and _tc05_linear is not None) else "mma.sync"
+
+
 def linear(x, w, bias=None, residual=None, act=ACT_NONE, rowvec=None, rows_per_batch=0, out=None, out_scale=1.0):
     """out[M,N] = x[M,K] @ w[N,K]^T (+bias) (+rowvec[m // rows_per_batch]) -> act -> (+residual) * out_scale.
     `x`, `residual`, `out` may be row-strided 2-D views (unit column stride)."""

@@ -178,6 +178,87 @@ def controlnet_param_shapes(cfg, cond_channels=3):
     return out
 
 
+def unet_step_flops(cfg, batch, height, width, text_len=77, controlnet=False):
+    """Algorithmic FLOPs of one step: 2*M*N*K per linear / convolution-as-GEMM, 4*B*H*Sq*Sk*D per attention.
+    Returns a dict by operator class plus 'total'. (height, width) is the latent size."""
+    f = dict(linear=0.0, conv3x3=0.0, conv1x1=0.0, self_attn=0.0, cross_attn=0.0)
+    boc = cfg["block_out_channels"]
+    temb = boc[0] * 4
+    cross = cfg["cross_attention_dim"]
+
+    def resnet(cin, cout, h, w):
+        m = batch * h * w
+        f["conv3x3"] += 2.0 * m * cout * 9 * cin + 2.0 * m * cout * 9 * cout
+        f["linear"] += 2.0 * batch * cout * temb
+        if cin != cout:
+            f["conv1x1"] += 2.0 * m * cout * cin
+
+    def transformer(c, layers, h, w):
+        m = batch * h * w
+        s = h * w
+        f["linear"] += 2 * (2.0 * m * c * c)                       # proj_in, proj_out
+        for _ in range(layers):
+            f["linear"] += 4 * (2.0 * m * c * c)                   # attn1 q,k,v,out
+            f["linear"] += 2 * (2.0 * m * c * c)                   # attn2 q,out
+            f["linear"] += 2 * (2.0 * batch * text_len * c * cross)  # attn2 k,v
+            f["linear"] += 2.0 * m * 8 * c * c + 2.0 * m * c * 4 * c  # ff
+            f["self_attn"] += 4.0 * batch * s * s * c
+            f["cross_attn"] += 4.0 * batch * s * text_len * c
+
+    h, w = height, width
+    f["conv3x3"] += 2.0 * batch * h * w * boc[0] * 9 * cfg["in_channels"]
+    f["linear"] += 2.0 * batch * (temb * boc[0] + temb * temb + temb * cfg["projection_class_embeddings_input_dim"] + temb * temb)
+    cin = boc[0]
+    skips = [(boc[0], h, w)]
+    for bi, btype in enumerate(cfg["down_block_types"]):
+        cout = boc[bi]
+        for li in range(cfg["layers_per_block"]):
+            resnet(cin if li == 0 else cout, cout, h, w)
+            if btype == "CrossAttnDownBlock2D":
+                transformer(cout, cfg["transformer_layers_per_block"][bi], h, w)
+            skips.append((cout, h, w))
+        if bi != len(boc) - 1:
+            h, w = h // 2, w // 2
+            f["conv3x3"] += 2.0 * batch * h * w * cout * 9 * cout
+            skips.append((cout, h, w))
+        cin = cout
+    c = boc[-1]
+    resnet(c, c, h, w)
+    transformer(c, cfg["transformer_layers_per_block"][-1], h, w)
+    resnet(c, c, h, w)
+    if controlnet:
+        for (sc, sh, sw) in skips:
+            f["conv1x1"] += 2.0 * batch * sh * sw * sc * sc
+        f["conv1x1"] += 2.0 * batch * h * w * c * c
+        ch = CONTROLNET_COND_CHANNELS
+        ih, iw = height * 8, width * 8
+        f["conv3x3"] += 2.0 * batch * ih * iw * ch[0] * 9 * 3
+        for i in range(len(ch) - 1):
+            f["conv3x3"] += 2.0 * batch * ih * iw * ch[i] * 9 * ch[i]
+            ih, iw = ih // 2, iw // 2
+            f["conv3x3"] += 2.0 * batch * ih * iw * ch[i + 1] * 9 * ch[i]
+        f["conv3x3"] += 2.0 * batch * ih * iw * boc[0] * 9 * ch[-1]
+    else:
+        rev = tuple(reversed(boc))
+        rev_layers = tuple(reversed(cfg["transformer_layers_per_block"]))
+        prev = rev[0]
+        for bi, btype in enumerate(cfg["up_block_types"]):
+            cout = rev[bi]
+            n = cfg["layers_per_block"] + 1
+            for li in range(n):
+                sc, sh, sw = skips.pop()
+                resnet((prev if li == 0 else cout) + sc, cout, h, w)
+                if btype == "CrossAttnUpBlock2D":
+                    transformer(cout, rev_layers[bi], h, w)
+            if bi != len(boc) - 1:
+                h, w = h * 2, w * 2
+                f["conv3x3"] += 2.0 * batch * h * w * cout * 9 * cout
+            prev = cout
+        f["conv3x3"] += 2.0 * batch * h * w * cfg["out_channels"] * 9 * boc[0]
+    f["total"] = sum(f.values())
+    return f
+
+
 def lora_target_keys(cfg, include_proj=False):
     """UNet linears a LoRA targets, in module order: per transformer block attn1 q/k/v/out, attn2 q/k/v/out, ff proj,
     ff out (700 layers for SDXL); with `include_proj` also each Transformer2DModel's proj_in/proj_out, which is the

@@ -325,6 +325,8 @@ class KatzUNet(_Net):
 
     def __init__(self, cfg, device="cuda", state_dict=None):
         super().__init__(cfg, unet_param_shapes(cfg), device)
+        self.use_cuda_graph = False
+        self._graphs = {}
         if state_dict is not None:
             self.load_state_dict(state_dict)
 
@@ -376,7 +378,13 @@ class KatzUNet(_Net):
     def __call__(self, sample, timestep, encoder_hidden_states, timestep_cond=None, cross_attention_kwargs=None,
                  added_cond_kwargs=None, down_block_additional_residuals=None, mid_block_additional_residual=None,
                  return_dict=False, combine_scales=None, **_ignored):
-        """One denoising step; returns `(noise_pred,)` (NCHW fp16) like the reference with return_dict=False."""
+        """One denoising step; returns `(noise_pred,)` (NCHW fp16) like the reference with return_dict=False.
+        With `use_cuda_graph` (the reference's ENABLE_CUDA_GRAPH=1) the step is captured once per input signature and
+        replayed with the inputs copied into static buffers, as `_forward_w_separate_cuda_graph` does."""
+        if self.use_cuda_graph and not torch.cuda.is_current_stream_capturing():
+            from .engine import graphed_unet_call
+            return (graphed_unet_call(self, sample, timestep, encoder_hidden_states, added_cond_kwargs,
+                                      down_block_additional_residuals, mid_block_additional_residual, combine_scales),)
         x, ctx, te, ti = self._prep_inputs(sample, encoder_hidden_states, added_cond_kwargs)
         mid, temb_all, res, kv = self.down_forward(x, timestep, ctx, te, ti)
         out = self.up_forward(mid, temb_all, res, kv, down_block_additional_residuals, mid_block_additional_residual,

@@ -1,0 +1,196 @@
+"""GPU parity of each kernel against the CPU oracle (torch fp32 / numpy half arithmetic), through the C ABI.
+Tolerances: byte/layout ops bit-exact; fp16 GEMM-like ops 2e-3 relative to the output scale (fp32 accumulation, one
+rounding); normalisations 2e-3 absolute on unit-scale outputs."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return float((a - b).abs().max() / (b.abs().max() + 1e-12))
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 320, 640), (154, 640, 2048), (2, 1280, 320), (2048, 1280, 1280), (300, 72, 40)])
+def test_linear_mma(cuda_device, M, N, K, monkeypatch):
+    monkeypatch.setenv("KATZ_GEMM", "mma")
+    from katz_b200 import ops
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(M, K, generator=g).half()
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).half()
+    b = torch.randn(N, generator=g).half()
+    r = torch.randn(M, N, generator=g).half()
+    ref = F.linear(x.float(), w.float(), b.float()) + r.float()
+    out = ops.linear(x.cuda(), w.cuda(), b.cuda(), residual=r.cuda())
+    assert _rel(out, ref) < 2e-3
+    ref2 = F.silu(F.linear(x.float(), w.float(), b.float())) * 0.5
+    out2 = ops.linear(x.cuda(), w.cuda(), b.cuda(), act=ops.ACT_SILU, out_scale=0.5)
+    assert _rel(out2, ref2) < 2e-3
+
+
+def test_linear_rowvec_and_strided(cuda_device, monkeypatch):
+    monkeypatch.setenv("KATZ_GEMM", "mma")
+    from katz_b200 import ops
+    g = torch.Generator().manual_seed(1)
+    B, S, K, N = 2, 96, 64, 128
+    x = torch.randn(B * S, 3 * K, generator=g).half().cuda()
+    w = (torch.randn(N, K, generator=g) / 8).half().cuda()
+    rv = torch.randn(B, 4 * N, generator=g).half().cuda()
+    out = ops.linear(x[:, K:2 * K], w, rowvec=rv[:, N:2 * N], rows_per_batch=S)
+    ref = F.linear(x[:, K:2 * K].float(), w.float()).view(B, S, N) + rv[:, N:2 * N].float()[:, None, :]
+    assert _rel(out.view(B, S, N), ref) < 2e-3
+
+
+@pytest.mark.parametrize("B,H,W,C1,C2,Cout,ks,stride,up", [
+    (2, 16, 16, 64, 0, 128, 3, 1, False),
+    (2, 16, 16, 64, 0, 64, 3, 2, False),
+    (1, 8, 8, 128, 0, 128, 3, 1, True),
+    (2, 12, 20, 64, 32, 96, 3, 1, False),
+    (2, 32, 32, 8, 0, 64, 3, 1, False),
+    (2, 16, 16, 320, 0, 4, 3, 1, False),
+    (1, 16, 16, 64, 0, 64, 1, 1, False),
+])
+def test_conv2d_mma(cuda_device, B, H, W, C1, C2, Cout, ks, stride, up, monkeypatch):
+    monkeypatch.setenv("KATZ_GEMM", "mma")
+    from katz_b200 import ops
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(B, C1 + C2, H, W, generator=g).half()
+    w = (torch.randn(Cout, C1 + C2, ks, ks, generator=g) / (ks * ks * (C1 + C2)) ** 0.5).half()
+    bias = torch.randn(Cout, generator=g).half()
+    xin = F.interpolate(x.float(), scale_factor=2.0, mode="nearest") if up else x.float()
+    ref = F.conv2d(xin, w.float(), bias.float(), stride=stride, padding=ks // 2)
+    temb = torch.randn(B, Cout, generator=g).half()
+    res = torch.randn_like(ref).half()
+    ref = ref + temb.float()[:, :, None, None] + res.float()
+    xn = x.permute(0, 2, 3, 1).contiguous().cuda()
+    x1 = xn[..., :C1].contiguous()
+    x2 = xn[..., C1:].contiguous() if C2 else None
+    wn = w.permute(0, 2, 3, 1).contiguous().cuda()
+    out = ops.conv2d(x1, wn, bias.cuda(), ksize=ks, stride=stride, pad=ks // 2, upsample=up, x2=x2, rowvec=temb.cuda(),
+                     residual=res.permute(0, 2, 3, 1).contiguous().cuda())
+    assert _rel(out.permute(0, 3, 1, 2), ref) < 2e-3
+
+
+@pytest.mark.parametrize("B,H,Sq,Sk", [(2, 2, 256, 256), (2, 5, 1024, 77), (1, 3, 200, 130), (2, 10, 4096, 4096)])
+def test_attention_mma(cuda_device, B, H, Sq, Sk):
+    from katz_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    C = H * 64
+    qkv = torch.randn(B, Sq, 3 * C, generator=g).half()
+    kv = torch.randn(B, Sk, 2 * C, generator=g).half()
+    q = qkv[:, :, :C]
+    k, v = (kv[:, :, :C], kv[:, :, C:]) if Sk != Sq else (qkv[:, :, C:2 * C], qkv[:, :, 2 * C:])
+
+    def heads(t):
+        return t.float().reshape(B, -1, H, 64).transpose(1, 2)
+    dev = "cuda" if Sq * Sk > 1 << 22 else "cpu"   # the largest case takes the fp32 reference on the GPU
+    ref = F.scaled_dot_product_attention(heads(q).to(dev), heads(k).to(dev), heads(v).to(dev)).transpose(1, 2).reshape(B, Sq, C)
+    qg, kvg = qkv.cuda(), kv.cuda()
+    if Sk != Sq:
+        out = ops.attention(qg[:, :, :C], kvg[:, :, :C], kvg[:, :, C:], H)
+    else:
+        out = ops.attention(qg[:, :, :C], qg[:, :, C:2 * C], qg[:, :, 2 * C:], H)
+    assert float((out.float().cpu() - ref.cpu()).abs().max()) < 4e-3
+
+
+@pytest.mark.parametrize("B,HW,C,act,shift", [(2, 256, 64, 1, 0.0), (2, 4096, 320, 1, 3.0), (2, 1024, 1920, 0, 0.0), (1, 100, 2560, 1, -2.0)])
+def test_group_norm_nhwc(cuda_device, B, HW, C, act, shift):
+    from katz_b200 import ops
+    from oracle import kernels_oracle
+    g = torch.Generator().manual_seed(4)
+    x = (torch.randn(B, HW, C, generator=g) + shift).half()
+    gamma = (1 + 0.1 * torch.randn(C, generator=g)).half()
+    beta = (0.1 * torch.randn(C, generator=g)).half()
+    ref = kernels_oracle.group_norm(x.permute(0, 2, 1).reshape(B, C, HW, 1), 32, gamma, beta, 1e-5, act == 1)
+    out = ops.group_norm_nhwc(x.cuda(), gamma.cuda(), beta.cuda(), 32, 1e-5, act)
+    assert float((out.cpu().float() - ref.reshape(B, C, HW).permute(0, 2, 1).float()).abs().max()) < 4e-3
+
+
+def test_group_norm_fast_kernel_op(cuda_device):
+    """The drop-in op with the reference's schema and calling convention (normalization.py:90-91)."""
+    import fast_kernel  # noqa: F401
+    from oracle import kernels_oracle
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(2, 320, 32, 32, generator=g).half()
+    w, b = torch.randn(320, generator=g).half(), torch.randn(320, generator=g).half()
+    xc = x.cuda().contiguous(memory_format=torch.channels_last)
+    y = torch.empty_like(xc)
+    torch.ops.fast_kernel.group_norm_fp16(xc, y, 1e-5, 32, "silu", w.cuda(), b.cuda(), True, False)
+    ref = kernels_oracle.group_norm(x, 32, w, b, 1e-5, True)
+    assert float((y.cpu().float() - ref.float()).abs().max()) < 8e-3
+    # channels-first branch
+    y2 = torch.empty_like(x.cuda())
+    torch.ops.fast_kernel.group_norm_fp16(x.cuda(), y2, 1e-5, 32, "none", w.cuda(), b.cuda(), True, True)
+    ref2 = kernels_oracle.group_norm(x, 32, w, b, 1e-5, False)
+    assert float((y2.cpu().float() - ref2.float()).abs().max()) < 8e-3
+    # error behaviour: shape mismatch raises RuntimeError like TORCH_CHECK
+    with pytest.raises(RuntimeError):
+        torch.ops.fast_kernel.fast_gelu_mul_fp16(x.cuda(), x.cuda()[:1])
+
+
+def test_fast_gelu_mul(cuda_device):
+    import fast_kernel  # noqa: F401
+    from oracle import kernels_oracle
+    g = torch.Generator().manual_seed(6)
+    x = (torch.randn(2, 1024, 2560, generator=g) * 2).half()
+    m = torch.randn(2, 1024, 2560, generator=g).half()
+    out = torch.ops.fast_kernel.fast_gelu_mul_fp16(x.cuda(), m.cuda()).cpu()
+    ref = torch.from_numpy(kernels_oracle.fast_gelu_mul(x.numpy(), m.numpy()))
+    diff = (out.float() - ref.float()).abs()
+    # same rounding sequence; the only freedom is tanh's last bit
+    assert float(diff.max()) <= 4e-3 and float((diff > 0).float().mean()) < 0.02
+
+
+def test_layer_norm_and_geglu(cuda_device):
+    from katz_b200 import ops
+    from oracle import kernels_oracle
+    g = torch.Generator().manual_seed(7)
+    for C in (640, 1280, 64):
+        x = (torch.randn(513, C, generator=g) * 2 + 0.5).half()
+        w, b = torch.randn(C, generator=g).half(), torch.randn(C, generator=g).half()
+        ref = F.layer_norm(x.float(), (C,), w.float(), b.float(), 1e-5)
+        out = ops.layer_norm(x.cuda(), w.cuda(), b.cuda())
+        assert float((out.cpu().float() - ref).abs().max()) < 8e-3
+    hg = torch.randn(300, 2 * 2560, generator=g).half()
+    out = ops.geglu_erf(hg.cuda()).cpu()
+    ref = kernels_oracle.geglu_erf(hg)
+    assert float((out.float() - ref.float()).abs().max()) <= 2e-3
+
+
+def test_small_kernels(cuda_device, golden_dir):
+    import os
+    from katz_b200 import ops
+    from oracle import unet_oracle
+    g = torch.Generator().manual_seed(8)
+    # layout moves are bit-exact
+    x = torch.randn(2, 4, 16, 16, generator=g).half()
+    n = ops.nchw_to_nhwc(x.cuda(), cpad=8)
+    assert torch.equal(n[..., :4].cpu(), x.permute(0, 2, 3, 1)) and float(n[..., 4:].abs().max()) == 0
+    assert torch.equal(ops.nhwc_to_nchw(n, c=4).cpu(), x)
+    a, b = torch.randn(2, 8, 8, 64, generator=g).half(), torch.randn(2, 8, 8, 32, generator=g).half()
+    assert torch.equal(ops.concat_channels(a.cuda(), b.cuda()).cpu(), torch.cat([a, b], dim=-1))
+    # timestep embedding
+    t = torch.tensor([500.0, 981.0, 1.0])
+    ref = unet_oracle.timestep_embedding(t, 320)
+    out = ops.timestep_embedding(t.cuda(), 320)
+    assert float((out.cpu().float() - ref).abs().max()) < 2e-3
+    # residual intake: sum and mean
+    src = torch.randn(2, 8, 8, 64, generator=g).half()
+    r1, r2 = torch.randn_like(src), torch.randn_like(src)
+    out = ops.residual_intake(src.cuda(), [r1.cuda(), r2.cuda()], [0.5, 0.5]).cpu()
+    ref = (src.float() + ((r1.float() + r2.float()) * 0.5).half().float()).half()
+    assert float((out.float() - ref.float()).abs().max()) <= 2e-3
+    # Euler / CFG arithmetic: bit-exact against what the reference scheduler produced
+    gz = np.load(os.path.join(golden_dir, "euler_sdxl.npz"))
+    sig = gz["sigmas"]
+    lat = torch.from_numpy(gz["latent0"]).cuda()
+    for i in range(4):
+        inp = ops.euler_scale_input(lat, sig[i], copies=2)
+        assert torch.equal(inp[0].cpu(), torch.from_numpy(gz["scaled_%d" % i])[0])
+        assert torch.equal(inp[1].cpu(), torch.from_numpy(gz["scaled_%d" % i])[0])
+        ops.euler_cfg_step(lat, torch.from_numpy(gz["eps_u_%d" % i]).cuda(), torch.from_numpy(gz["eps_c_%d" % i]).cuda(),
+                           5.0, sig[i], sig[i + 1])
+        assert torch.equal(lat.cpu(), torch.from_numpy(gz["latent_%d" % (i + 1)]))
