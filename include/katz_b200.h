@@ -97,6 +97,25 @@ int katz_linear_f16_mma(const void* A, int lda, const void* W, void* C, int ldc,
                         const void* rowvec, int ld_rowvec, int rows_per_batch, const void* residual, int ldr, int act,
                         float out_scale, void* stream);
 
+/* Same contract as katz_linear_f16_mma on the tcgen05 path (TMA operands, TMEM accumulator). Needs K % 64 == 0,
+ * N % 8 == 0, 16-byte aligned pointers and lda/ldc/ldr/ld_rowvec multiples of 8; other shapes return KATZ_E_SIZE /
+ * KATZ_E_ALIGN and belong to the _mma entry point. */
+int katz_linear_f16(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, int K, const void* bias,
+                    const void* rowvec, int ld_rowvec, int rows_per_batch, const void* residual, int ldr, int act,
+                    float out_scale, void* stream);
+/* 3x3, stride 1, padding 1 NHWC convolution on the tcgen05 path (nn.Conv2d of ResnetBlock2D, resnet.py:378,408).
+ * X[B,H,W,Cin], W[Cout,3,3,Cin], Y[B,H,W,Cout]; needs Cin % 64 == 0, Cout % 8 == 0 and W a power of two >= 8 or a
+ * multiple of 128. Epilogue as katz_conv2d_nhwc_f16_mma. */
+int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int B, int H, int Wd, int Cin, int Cout,
+                          const void* bias, const void* rowvec, int ld_rowvec, const void* residual, int act,
+                          float out_scale, void* stream);
+/* Status word of the tcgen05 kernels: 0, or which bounded device-side wait gave up (1 producer, 2 MMA issuer,
+ * 3 epilogue). Reading it synchronises the device; clear it before the next launch. */
+int katz_tc05_status(void);
+int katz_tc05_clear_status(void);
+/* Nearest-neighbour 2x upsample, NHWC (Upsample2D.forward, diffusers/models/upsampling.py:165-172). */
+int katz_upsample_nearest2x_nhwc_f16(const void* x, void* y, int B, int H, int W, int C, void* stream);
+
 /* NHWC convolution as implicit GEMM. Input is X[B, Hs, Ws, C1] (optionally channel-concatenated with
  * X2[B, Hs, Ws, C2], the skip connection of CrossAttnUpBlock2D/UpBlock2D, unet_2d_blocks.py:2473,2608); with
  * `upsample` the input is read through a nearest-neighbour 2x upsample (Upsample2D, upsampling.py:141-186) and
@@ -134,9 +153,11 @@ int katz_nhwc_to_nchw_f16(const void* x, void* y, int B, int C, int HW, int Cpad
  * written `copies` times back to back (the CFG batch). x is the fp16 latent. */
 int katz_euler_scale_input(const void* x, void* out, long long n, float sigma, int copies, void* stream);
 /* CFG combine (pipeline_controlnet_sd_xl_katz.py:1649-1655) + EulerDiscreteScheduler.step (:498-537, epsilon
- * prediction, s_churn 0) in place on the fp16 latent x. eps_cond may be NULL (no guidance). */
+ * prediction, s_churn 0) in place on the fp16 latent x. eps_cond may be NULL (no guidance). `sigma_mul` is the value
+ * that multiplies the fp16 noise prediction (`sigma_hat * model_output`, :516): torch on CUDA keeps the fp32 sigma
+ * there (pass sigma), torch on CPU rounds it to fp16 first (pass half(sigma)); both are reproduced bit for bit. */
 int katz_euler_cfg_step(void* x, const void* eps_uncond, const void* eps_cond, long long n, float guidance, float sigma,
-                        float sigma_next, void* stream);
+                        float sigma_next, float sigma_mul, void* stream);
 
 #ifdef __cplusplus
 }

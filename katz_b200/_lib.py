@@ -61,6 +61,11 @@ SIGNATURES = {
     "katz_layer_norm_f16": (_I, [_V, _V, _V, _V, _I, _I, _F, _V]),
     "katz_geglu_erf_f16": (_I, [_V, _V, _L, _I, _I, _V]),
     "katz_linear_f16_mma": (_I, [_V, _I, _V, _V, _I, _I, _I, _I, _V, _V, _I, _I, _V, _I, _I, _F, _V]),
+    "katz_linear_f16": (_I, [_V, _I, _V, _V, _I, _I, _I, _I, _V, _V, _I, _I, _V, _I, _I, _F, _V]),
+    "katz_conv3x3_nhwc_f16": (_I, [_V, _V, _V, _I, _I, _I, _I, _I, _V, _V, _I, _V, _I, _F, _V]),
+    "katz_tc05_status": (_I, []),
+    "katz_tc05_clear_status": (_I, []),
+    "katz_upsample_nearest2x_nhwc_f16": (_I, [_V, _V, _I, _I, _I, _I, _V]),
     "katz_conv2d_nhwc_f16_mma": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _V, _V, _I, _V, _I, _F, _V]),
     "katz_attention_f16_mma": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _V]),
     "katz_residual_intake_f16": (_I, [_V, _V, POINTER(c_void_p), POINTER(c_float), _I, _L, _V]),
@@ -71,7 +76,7 @@ SIGNATURES = {
     "katz_nchw_to_nhwc_f16": (_I, [_V, _V, _I, _I, _I, _I, _V]),
     "katz_nhwc_to_nchw_f16": (_I, [_V, _V, _I, _I, _I, _I, _V]),
     "katz_euler_scale_input": (_I, [_V, _V, _L, _F, _I, _V]),
-    "katz_euler_cfg_step": (_I, [_V, _V, _V, _L, _F, _F, _F, _V]),
+    "katz_euler_cfg_step": (_I, [_V, _V, _V, _L, _F, _F, _F, _F, _V]),
 }
 
 _lib = None

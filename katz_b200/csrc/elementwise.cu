@@ -133,7 +133,7 @@ __global__ void euler_scale_input_kernel(const __half* __restrict__ x, __half* _
 // upcasts the fp16 latent to fp32: pred_x0 = x - half(sigma*eps); d = (x - pred_x0)/sigma; x' = half(x + d*dt).
 __global__ void euler_cfg_step_kernel(__half* __restrict__ x, const __half* __restrict__ eps_uncond,
                                       const __half* __restrict__ eps_cond, long long n, float guidance, float sigma,
-                                      float sigma_next) {
+                                      float sigma_next, float sigma_mul) {
     const float dt = sigma_next - sigma;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         float u = __half2float(eps_uncond[i]);
@@ -143,7 +143,7 @@ __global__ void euler_cfg_step_kernel(__half* __restrict__ x, const __half* __re
             e = rh(u + rh(guidance * rh(c - u)));
         }
         float xv = __half2float(x[i]);
-        float pred = xv - rh(sigma * e);
+        float pred = xv - rh(sigma_mul * e);
         float d = (xv - pred) / sigma;
         x[i] = __float2half_rn(xv + d * dt);
     }
@@ -158,6 +158,20 @@ __global__ void concat_channels_kernel(const uint4* __restrict__ x1, const uint4
         long long r = i / ch;
         int c = (int)(i - r * ch);
         y[i] = c < ch1 ? x1[r * ch1 + c] : x2[r * ch2 + (c - ch1)];
+    }
+}
+
+// Nearest-neighbour 2x upsample of an NHWC tensor (Upsample2D's F.interpolate, upsampling.py:165-172), 16-byte chunks.
+__global__ void upsample2x_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int B, int H, int W, int ch) {
+    const long long total = (long long)B * (2 * H) * (2 * W) * ch;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        int c = (int)(i % ch);
+        long long p = i / ch;
+        int ox = (int)(p % (2 * W));
+        p /= (2 * W);
+        int oy = (int)(p % (2 * H));
+        int b = (int)(p / (2 * H));
+        y[i] = x[(((size_t)b * H + (oy >> 1)) * W + (ox >> 1)) * ch + c];
     }
 }
 
@@ -237,6 +251,15 @@ extern "C" int katz_concat_channels_f16(const void* x1, const void* x2, void* y,
     KATZ_LAUNCH_RET();
 }
 
+extern "C" int katz_upsample_nearest2x_nhwc_f16(const void* x, void* y, int B, int H, int W, int C, void* stream) {
+    KATZ_CHECK_ARG(x && y, KATZ_EINVAL);
+    KATZ_CHECK_ARG(B > 0 && H > 0 && W > 0 && C > 0 && C % 8 == 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(aligned16(x) && aligned16(y), KATZ_EALIGN);
+    long long n = (long long)B * 4 * H * W * (C / 8);
+    upsample2x_kernel<<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((const uint4*)x, (uint4*)y, B, H, W, C / 8);
+    KATZ_LAUNCH_RET();
+}
+
 extern "C" int katz_nchw_to_nhwc_f16(const void* x, void* y, int B, int C, int HW, int Cpad, void* stream) {
     KATZ_CHECK_ARG(x && y, KATZ_EINVAL);
     KATZ_CHECK_ARG(B > 0 && C > 0 && HW > 0 && Cpad >= C, KATZ_ESIZE);
@@ -261,10 +284,10 @@ extern "C" int katz_euler_scale_input(const void* x, void* out, long long n, flo
 }
 
 extern "C" int katz_euler_cfg_step(void* x, const void* eps_uncond, const void* eps_cond, long long n, float guidance,
-                                   float sigma, float sigma_next, void* stream) {
+                                   float sigma, float sigma_next, float sigma_mul, void* stream) {
     KATZ_CHECK_ARG(x && eps_uncond, KATZ_EINVAL);
     KATZ_CHECK_ARG(n > 0 && sigma != 0.f, KATZ_ESIZE);
     euler_cfg_step_kernel<<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((__half*)x, (const __half*)eps_uncond,
-                                                                           (const __half*)eps_cond, n, guidance, sigma, sigma_next);
+                                                                           (const __half*)eps_cond, n, guidance, sigma, sigma_next, sigma_mul);
     KATZ_LAUNCH_RET();
 }

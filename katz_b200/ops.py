@@ -27,19 +27,42 @@ def _use_tc05():
     return os.environ.get("KATZ_GEMM", "tc05") != "mma"
 
 
-_tc05_linear = None
-_tc05_conv = None
+def _al16(t):
+    return t is None or t.data_ptr() % 16 == 0
 
 
-def register_tc05(linear_fn, conv_fn):
-    """Installed by katz_b200.tc05 when the tcgen05 entry points are present in the library."""
-    global _tc05_linear, _tc05_conv
-    _tc05_linear, _tc05_conv = linear_fn, conv_fn
+def _tc05_linear_ok(x, w, bias, residual, rowvec, out):
+    """Shapes/alignments the tcgen05 GEMM takes; anything else goes to the mma.sync kernel."""
+    M, K = x.shape
+    N = w.shape[0]
+    if K % 64 or N % 8 or x.stride(0) % 8 or out.stride(0) % 8:
+        return False
+    if not (_al16(x) and _al16(w) and _al16(out) and _al16(bias) and _al16(residual) and _al16(rowvec)):
+        return False
+    if residual is not None and residual.stride(0) % 8:
+        return False
+    if rowvec is not None and rowvec.stride(0) % 8:
+        return False
+    return True
 
 
 def gemm_kernel_name():
     """Which GEMM family `linear` dispatches large aligned shapes to."""
-    return "tcgen05" if (_use_tc05() and _tc05_linear is not None) else "mma.sync"
+    return "tcgen05" if _use_tc05() else "mma.sync"
+
+
+def tc05_status():
+    """Status word of the tcgen05 kernels (0 = no bounded wait ever gave up). Synchronises the device."""
+    return _lib.load().katz_tc05_status()
+
+
+def upsample_nearest2x(x, out=None):
+    _f16(x, "x")
+    B, H, W, C = x.shape
+    if out is None:
+        out = torch.empty((B, 2 * H, 2 * W, C), dtype=torch.float16, device=x.device)
+    call("katz_upsample_nearest2x_nhwc_f16", _p(x), _p(out), B, H, W, C, _stream())
+    return out
 
 
 def linear(x, w, bias=None, residual=None, act=ACT_NONE, rowvec=None, rows_per_batch=0, out=None, out_scale=1.0):
@@ -58,10 +81,8 @@ def linear(x, w, bias=None, residual=None, act=ACT_NONE, rowvec=None, rows_per_b
         raise KatzError("linear: bad out")
     if residual is not None and (residual.shape != (M, N) or residual.stride(1) != 1):
         raise KatzError("linear: bad residual")
-    if _use_tc05() and _tc05_linear is not None:
-        if _tc05_linear(x, w, bias, residual, act, rowvec, rows_per_batch, out, out_scale):
-            return out
-    call("katz_linear_f16_mma", _p(x), x.stride(0), _p(w), _p(out), out.stride(0), M, N, K, _p(bias), _p(rowvec),
+    name = "katz_linear_f16" if (_use_tc05() and _tc05_linear_ok(x, w, bias, residual, rowvec, out)) else "katz_linear_f16_mma"
+    call(name, _p(x), x.stride(0), _p(w), _p(out), out.stride(0), M, N, K, _p(bias), _p(rowvec),
          rowvec.stride(0) if rowvec is not None else 0, rows_per_batch, _p(residual),
          residual.stride(0) if residual is not None else 0, act, float(out_scale), _stream())
     return out
@@ -91,9 +112,14 @@ def conv2d(x, w, bias=None, ksize=3, stride=1, pad=1, upsample=False, x2=None, r
         out = torch.empty((B, Hout, Wout, Cout), dtype=torch.float16, device=x.device)
     if residual is not None and (tuple(residual.shape) != (B, Hout, Wout, Cout) or not residual.is_contiguous()):
         raise KatzError("conv2d: bad residual")
-    if _use_tc05() and _tc05_conv is not None:
-        if _tc05_conv(x, x2, w, bias, ksize, stride, pad, upsample, rowvec, residual, act, out, out_scale):
-            return out
+    tw = min(Ws * (2 if upsample else 1), 128)
+    if (_use_tc05() and ksize == 3 and stride == 1 and pad == 1 and x2 is None and C1 % 64 == 0 and Cout % 8 == 0
+            and tw >= 8 and (tw & (tw - 1)) == 0 and Win % tw == 0 and _al16(x) and _al16(w) and _al16(out) and _al16(bias)
+            and _al16(residual) and (rowvec is None or (_al16(rowvec) and rowvec.stride(0) % 8 == 0))):
+        src = upsample_nearest2x(x) if upsample else x
+        call("katz_conv3x3_nhwc_f16", _p(src), _p(w), _p(out), B, Hin, Win, C1, Cout, _p(bias), _p(rowvec),
+             rowvec.stride(0) if rowvec is not None else 0, _p(residual), act, float(out_scale), _stream())
+        return out
     call("katz_conv2d_nhwc_f16_mma", _p(x), _p(x2), _p(w), _p(out), B, Hin, Win, C1, C2, Cout, ksize, stride, pad,
          1 if upsample else 0, _p(bias), _p(rowvec), rowvec.stride(0) if rowvec is not None else 0, _p(residual), act,
          float(out_scale), _stream())
@@ -280,9 +306,12 @@ def euler_scale_input(x, sigma, copies=1, out=None):
     return out
 
 
-def euler_cfg_step(x, eps_uncond, eps_cond, guidance, sigma, sigma_next):
-    """In-place Euler step on the fp16 latent x with classifier-free guidance."""
+def euler_cfg_step(x, eps_uncond, eps_cond, guidance, sigma, sigma_next, cpu_torch_rounding=False):
+    """In-place Euler step on the fp16 latent x with classifier-free guidance. `cpu_torch_rounding` reproduces torch's
+    CPU kernels, which round sigma to fp16 before `sigma * eps`; the default is what torch does on CUDA."""
     _f16(x, "x"), _f16(eps_uncond, "eps_uncond")
-    call("katz_euler_cfg_step", _p(x), _p(eps_uncond), _p(eps_cond), x.numel(), float(guidance), float(sigma),
-         float(sigma_next), _stream())
+    sigma = float(sigma)
+    smul = float(torch.tensor(sigma, dtype=torch.float32).half()) if cpu_torch_rounding else sigma
+    call("katz_euler_cfg_step", _p(x), _p(eps_uncond), _p(eps_cond), x.numel(), float(guidance), sigma,
+         float(sigma_next), smul, _stream())
     return x

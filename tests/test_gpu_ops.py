@@ -192,5 +192,76 @@ def test_small_kernels(cuda_device, golden_dir):
         assert torch.equal(inp[0].cpu(), torch.from_numpy(gz["scaled_%d" % i])[0])
         assert torch.equal(inp[1].cpu(), torch.from_numpy(gz["scaled_%d" % i])[0])
         ops.euler_cfg_step(lat, torch.from_numpy(gz["eps_u_%d" % i]).cuda(), torch.from_numpy(gz["eps_c_%d" % i]).cuda(),
-                           5.0, sig[i], sig[i + 1])
+                           5.0, sig[i], sig[i + 1], cpu_torch_rounding=True)
         assert torch.equal(lat.cpu(), torch.from_numpy(gz["latent_%d" % (i + 1)]))
+    # default rounding = torch's CUDA kernels: the oracle's torch ops run on the device are the reference here
+    lat = torch.from_numpy(gz["latent0"]).cuda()
+    ref = lat.clone()
+    for i in range(4):
+        u, c = torch.from_numpy(gz["eps_u_%d" % i]).cuda(), torch.from_numpy(gz["eps_c_%d" % i]).cuda()
+        ops.euler_cfg_step(lat, u, c, 5.0, sig[i], sig[i + 1])
+        ref = unet_oracle.euler_step(ref, unet_oracle.cfg_combine(u, c, 5.0), float(sig[i]), float(sig[i + 1]))
+        assert torch.equal(lat, ref)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 320, 640), (154, 640, 2048), (2, 1280, 320), (2048, 1280, 1280),
+                                   (8192, 5120, 640), (300, 72, 64), (4096, 640, 2560)])
+def test_linear_tcgen05(cuda_device, M, N, K, monkeypatch):
+    monkeypatch.setenv("KATZ_GEMM", "tc05")
+    from katz_b200 import ops
+    g = torch.Generator().manual_seed(10)
+    x = torch.randn(M, K, generator=g).half()
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).half()
+    b = torch.randn(N, generator=g).half()
+    r = torch.randn(M, N, generator=g).half()
+    assert ops._tc05_linear_ok(x.cuda(), w.cuda(), b.cuda(), r.cuda(), None, torch.empty(M, N, dtype=torch.float16, device="cuda"))
+    xg, wg, bg, rg = x.cuda(), w.cuda(), b.cuda(), r.cuda()
+    ref = (xg.float() @ wg.float().t() + bg.float() + rg.float()).cpu()
+    out = ops.linear(xg, wg, bg, residual=rg)
+    assert ops.tc05_status() == 0
+    assert _rel(out, ref) < 2e-3
+    ref2 = (F.silu(xg.float() @ wg.float().t() + bg.float()) * 0.5).cpu()
+    out2 = ops.linear(xg, wg, bg, act=ops.ACT_SILU, out_scale=0.5)
+    assert _rel(out2, ref2) < 2e-3
+    # same answer as the mma.sync kernel up to accumulation order
+    monkeypatch.setenv("KATZ_GEMM", "mma")
+    out3 = ops.linear(xg, wg, bg, residual=rg)
+    assert _rel(out, out3.cpu()) < 1e-3
+
+
+def test_linear_tcgen05_strided_views(cuda_device, monkeypatch):
+    monkeypatch.setenv("KATZ_GEMM", "tc05")
+    from katz_b200 import ops
+    g = torch.Generator().manual_seed(11)
+    B, S, K, N = 2, 160, 128, 256
+    x = torch.randn(B * S, 3 * K, generator=g).half().cuda()
+    w = (torch.randn(N, K, generator=g) / 11).half().cuda()
+    rv = torch.randn(B, 4 * N, generator=g).half().cuda()
+    big = torch.zeros(B * S, 2 * N, dtype=torch.float16, device="cuda")
+    out = ops.linear(x[:, K:2 * K], w, rowvec=rv[:, N:2 * N], rows_per_batch=S, out=big[:, N:])
+    ref = (x[:, K:2 * K].float() @ w.float().t()).view(B, S, N) + rv[:, N:2 * N].float()[:, None, :]
+    assert ops.tc05_status() == 0
+    assert _rel(out.reshape(B, S, N), ref) < 2e-3
+    assert float(big[:, :N].abs().max()) == 0
+
+
+@pytest.mark.parametrize("B,H,W,Cin,Cout,up", [(2, 16, 16, 64, 128, False), (2, 32, 32, 128, 320, False),
+                                               (1, 128, 128, 64, 64, False), (2, 64, 64, 320, 640, False),
+                                               (1, 6, 16, 64, 64, False), (1, 16, 16, 128, 128, True),
+                                               (1, 8, 256, 64, 64, False)])
+def test_conv3x3_tcgen05(cuda_device, B, H, W, Cin, Cout, up, monkeypatch):
+    monkeypatch.setenv("KATZ_GEMM", "tc05")
+    from katz_b200 import ops
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(B, Cin, H, W, generator=g).half().cuda()
+    w = (torch.randn(Cout, Cin, 3, 3, generator=g) / (9 * Cin) ** 0.5).half().cuda()
+    bias = torch.randn(Cout, generator=g).half().cuda()
+    xin = F.interpolate(x.float(), scale_factor=2.0, mode="nearest") if up else x.float()
+    ref = F.conv2d(xin, w.float(), bias.float(), padding=1)
+    temb = torch.randn(B, Cout, generator=g).half().cuda()
+    res = torch.randn(ref.shape, generator=g).half().cuda()
+    ref = ref + temb.float()[:, :, None, None] + res.float()
+    out = ops.conv2d(x.permute(0, 2, 3, 1).contiguous(), w.permute(0, 2, 3, 1).contiguous(), bias, upsample=up,
+                     rowvec=temb, residual=res.permute(0, 2, 3, 1).contiguous())
+    assert ops.tc05_status() == 0
+    assert _rel(out.permute(0, 3, 1, 2), ref) < 2e-3
