@@ -178,6 +178,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="katz", choices=["katz", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-step", action="store_true",
+                    help="run ONE eager UNet step between cudaProfilerStart/Stop and exit (for `ncu --profile-from-start off`)")
+    ap.add_argument("--profile-merge", action="store_true",
+                    help="run ONE LoRA merge over a reduced layer set between cudaProfilerStart/Stop and exit")
     ap.add_argument("--latent", type=int, default=128, help="latent height = width (128 = 1024^2 images)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "katz" else max(args.warmup, 0)
@@ -212,6 +216,35 @@ def main():
     unet = KatzUNet(cfg, dev, sd)
     del sd
     keys = lora_target_keys(cfg, include_proj=True)     # the reference's 722-entry target set
+    if args.profile_step:
+        g = torch.Generator().manual_seed(0)
+        x = torch.randn(B, 4, HW, HW, generator=g).half().to(dev)
+        ctx = torch.randn(B, 77, 2048, generator=g).half().to(dev)
+        added = {"text_embeds": torch.randn(B, 1280, generator=g).half().to(dev),
+                 "time_ids": torch.tensor([[1024., 1024., 0., 0., 1024., 1024.]] * B).half().to(dev)}
+        t = torch.tensor([500.0], device=dev)
+        for _ in range(2):
+            unet(x, t, encoder_hidden_states=ctx, added_cond_kwargs=added)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        unet(x, t, encoder_hidden_states=ctx, added_cond_kwargs=added)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"profiled": "one eager UNet step", "launches": _lib.launch_count() // 3}))
+        return
+    if args.profile_merge:
+        keys = [k for k in keys if k.startswith("down_blocks.2.attentions.0.")]     # 102 layers, 0.7 GB of weights
+        merger = LoraMerger(unet.lora_targets(keys))
+        lora = make_lora(unet, keys, 64, 100, dev)
+        for _ in range(2):
+            merger.merge(lora, 1.0)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        merger.merge(lora, 1.0)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"profiled": "one LoRA merge", "layers": len(keys), "bytes": merger.algorithmic_bytes([64])}))
+        return
     merger = LoraMerger(unet.lora_targets(keys))
     lora = make_lora(unet, keys, 64, 100, dev)
 

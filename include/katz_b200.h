@@ -103,6 +103,12 @@ int katz_linear_f16_mma(const void* A, int lda, const void* W, void* C, int ldc,
 int katz_linear_f16(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, int K, const void* bias,
                     const void* rowvec, int ld_rowvec, int rows_per_batch, const void* residual, int ldr, int act,
                     float out_scale, void* stream);
+/* Feed-forward projection with the GEGLU gate fused into the epilogue (FeedForward / GEGLU,
+ * diffusers/models/attention.py:608-664, activations.py:146-149): W is the unsplit `proj` weight [2F, K], bias [2F];
+ * C[M, F] = half(A W[:F]^T + b[:F]) * half(gelu_erf(half(A W[F:]^T + b[F:]))), rounded to half where the reference's
+ * fp16 tensors round. Same shape rules as katz_linear_f16, F % 16 == 0. */
+int katz_linear_geglu_f16(const void* A, int lda, const void* W, void* C, int ldc, int M, int F, int K, const void* bias,
+                          void* stream);
 /* 3x3, stride 1, padding 1 NHWC convolution on the tcgen05 path (nn.Conv2d of ResnetBlock2D, resnet.py:378,408).
  * X[B,H,W,Cin], W[Cout,3,3,Cin], Y[B,H,W,Cout]; needs Cin % 64 == 0, Cout % 8 == 0 and W a power of two >= 8 or a
  * multiple of 128. Epilogue as katz_conv2d_nhwc_f16_mma. */
@@ -149,15 +155,18 @@ int katz_concat_channels_f16(const void* x1, const void* x2, void* y, long long 
 int katz_nchw_to_nhwc_f16(const void* x, void* y, int B, int C, int HW, int Cpad, void* stream);
 int katz_nhwc_to_nchw_f16(const void* x, void* y, int B, int C, int HW, int Cpad, void* stream);
 
+/* torch evaluates `tensor / host_scalar` and `host_scalar * half_tensor` differently on its two devices; `mode` picks
+ * which one is reproduced bit for bit: 0 = torch on CUDA (the reference's serving path: multiply by the fp32
+ * reciprocal; fp32 sigma times the fp16 prediction), 1 = torch on CPU (true division; sigma rounded to fp16 first). */
+#define KATZ_ROUNDING_TORCH_CUDA 0
+#define KATZ_ROUNDING_TORCH_CPU 1
 /* EulerDiscreteScheduler.scale_model_input (schedulers/scheduling_euler_discrete.py:294-295): out = half(x / sqrt(sigma^2+1)),
  * written `copies` times back to back (the CFG batch). x is the fp16 latent. */
-int katz_euler_scale_input(const void* x, void* out, long long n, float sigma, int copies, void* stream);
+int katz_euler_scale_input(const void* x, void* out, long long n, float sigma, int copies, int mode, void* stream);
 /* CFG combine (pipeline_controlnet_sd_xl_katz.py:1649-1655) + EulerDiscreteScheduler.step (:498-537, epsilon
- * prediction, s_churn 0) in place on the fp16 latent x. eps_cond may be NULL (no guidance). `sigma_mul` is the value
- * that multiplies the fp16 noise prediction (`sigma_hat * model_output`, :516): torch on CUDA keeps the fp32 sigma
- * there (pass sigma), torch on CPU rounds it to fp16 first (pass half(sigma)); both are reproduced bit for bit. */
+ * prediction, s_churn 0) in place on the fp16 latent x. eps_cond may be NULL (no guidance). */
 int katz_euler_cfg_step(void* x, const void* eps_uncond, const void* eps_cond, long long n, float guidance, float sigma,
-                        float sigma_next, float sigma_mul, void* stream);
+                        float sigma_next, int mode, void* stream);
 
 #ifdef __cplusplus
 }

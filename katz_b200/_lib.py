@@ -62,6 +62,7 @@ SIGNATURES = {
     "katz_geglu_erf_f16": (_I, [_V, _V, _L, _I, _I, _V]),
     "katz_linear_f16_mma": (_I, [_V, _I, _V, _V, _I, _I, _I, _I, _V, _V, _I, _I, _V, _I, _I, _F, _V]),
     "katz_linear_f16": (_I, [_V, _I, _V, _V, _I, _I, _I, _I, _V, _V, _I, _I, _V, _I, _I, _F, _V]),
+    "katz_linear_geglu_f16": (_I, [_V, _I, _V, _V, _I, _I, _I, _I, _V, _V]),
     "katz_conv3x3_nhwc_f16": (_I, [_V, _V, _V, _I, _I, _I, _I, _I, _V, _V, _I, _V, _I, _F, _V]),
     "katz_tc05_status": (_I, []),
     "katz_tc05_clear_status": (_I, []),
@@ -75,8 +76,8 @@ SIGNATURES = {
     "katz_concat_channels_f16": (_I, [_V, _V, _V, _L, _I, _I, _V]),
     "katz_nchw_to_nhwc_f16": (_I, [_V, _V, _I, _I, _I, _I, _V]),
     "katz_nhwc_to_nchw_f16": (_I, [_V, _V, _I, _I, _I, _I, _V]),
-    "katz_euler_scale_input": (_I, [_V, _V, _L, _F, _I, _V]),
-    "katz_euler_cfg_step": (_I, [_V, _V, _V, _L, _F, _F, _F, _F, _V]),
+    "katz_euler_scale_input": (_I, [_V, _V, _L, _F, _I, _I, _V]),
+    "katz_euler_cfg_step": (_I, [_V, _V, _V, _L, _F, _F, _F, _I, _V]),
 }
 
 _lib = None

@@ -117,13 +117,22 @@ __global__ void nhwc_to_nchw_kernel(const __half* __restrict__ x, __half* __rest
     }
 }
 
+// torch evaluates `tensor / cpu_scalar` and `cpu_scalar * half_tensor` differently on the two devices the reference
+// can run on; both are reproduced bit for bit:
+//   mode 0 (torch on CUDA, the reference's serving path): division by a host scalar is a multiplication by its fp32
+//          reciprocal, and the fp32 sigma multiplies the fp16 prediction at full precision;
+//   mode 1 (torch on CPU): true division, and sigma is rounded to fp16 before `sigma * model_output`.
+//
 // scale_model_input (scheduling_euler_discrete.py:294-295): the fp16 latent divided by sqrt(sigma^2 + 1) (sigma is an
 // fp32 scalar, so torch keeps the result in fp16), optionally written twice (batch-2 CFG input).
 __global__ void euler_scale_input_kernel(const __half* __restrict__ x, __half* __restrict__ out, long long n, float sigma,
-                                         int copies) {
-    const float den = sqrtf(sigma * sigma + 1.0f);
+                                         int copies, int mode) {
+    // sigma**2, + 1, ** 0.5 are three separately rounded fp32 operations in the reference: no fused multiply-add
+    const float den = __fsqrt_rn(__fadd_rn(__fmul_rn(sigma, sigma), 1.0f));
+    const float inv = __fdiv_rn(1.0f, den);
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-        __half h = __float2half_rn(__half2float(x[i]) / den);
+        const float xv = __half2float(x[i]);
+        __half h = __float2half_rn(mode == 0 ? __fmul_rn(xv, inv) : __fdiv_rn(xv, den));
         for (int c = 0; c < copies; ++c) out[(size_t)c * n + i] = h;
     }
 }
@@ -133,8 +142,10 @@ __global__ void euler_scale_input_kernel(const __half* __restrict__ x, __half* _
 // upcasts the fp16 latent to fp32: pred_x0 = x - half(sigma*eps); d = (x - pred_x0)/sigma; x' = half(x + d*dt).
 __global__ void euler_cfg_step_kernel(__half* __restrict__ x, const __half* __restrict__ eps_uncond,
                                       const __half* __restrict__ eps_cond, long long n, float guidance, float sigma,
-                                      float sigma_next, float sigma_mul) {
-    const float dt = sigma_next - sigma;
+                                      float sigma_next, int mode) {
+    const float dt = __fsub_rn(sigma_next, sigma);
+    const float sigma_mul = mode == 0 ? sigma : rh(sigma);
+    const float inv_sigma = __fdiv_rn(1.0f, sigma);
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         float u = __half2float(eps_uncond[i]);
         float e = u;
@@ -143,9 +154,11 @@ __global__ void euler_cfg_step_kernel(__half* __restrict__ x, const __half* __re
             e = rh(u + rh(guidance * rh(c - u)));
         }
         float xv = __half2float(x[i]);
-        float pred = xv - rh(sigma_mul * e);
-        float d = (xv - pred) / sigma;
-        x[i] = __float2half_rn(xv + d * dt);
+        // each torch op rounds on its own: keep the compiler from contracting them into fused multiply-adds
+        float pred = __fsub_rn(xv, rh(__fmul_rn(sigma_mul, e)));
+        float num = __fsub_rn(xv, pred);
+        float d = mode == 0 ? __fmul_rn(num, inv_sigma) : __fdiv_rn(num, sigma);
+        x[i] = __float2half_rn(__fadd_rn(xv, __fmul_rn(d, dt)));
     }
 }
 
@@ -276,18 +289,19 @@ extern "C" int katz_nhwc_to_nchw_f16(const void* x, void* y, int B, int C, int H
     KATZ_LAUNCH_RET();
 }
 
-extern "C" int katz_euler_scale_input(const void* x, void* out, long long n, float sigma, int copies, void* stream) {
+extern "C" int katz_euler_scale_input(const void* x, void* out, long long n, float sigma, int copies, int mode,
+                                      void* stream) {
     KATZ_CHECK_ARG(x && out, KATZ_EINVAL);
     KATZ_CHECK_ARG(n > 0 && copies >= 1, KATZ_ESIZE);
-    euler_scale_input_kernel<<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((const __half*)x, (__half*)out, n, sigma, copies);
+    euler_scale_input_kernel<<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((const __half*)x, (__half*)out, n, sigma, copies, mode);
     KATZ_LAUNCH_RET();
 }
 
 extern "C" int katz_euler_cfg_step(void* x, const void* eps_uncond, const void* eps_cond, long long n, float guidance,
-                                   float sigma, float sigma_next, float sigma_mul, void* stream) {
+                                   float sigma, float sigma_next, int mode, void* stream) {
     KATZ_CHECK_ARG(x && eps_uncond, KATZ_EINVAL);
     KATZ_CHECK_ARG(n > 0 && sigma != 0.f, KATZ_ESIZE);
     euler_cfg_step_kernel<<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((__half*)x, (const __half*)eps_uncond,
-                                                                           (const __half*)eps_cond, n, guidance, sigma, sigma_next, sigma_mul);
+                                                                           (const __half*)eps_cond, n, guidance, sigma, sigma_next, mode);
     KATZ_LAUNCH_RET();
 }

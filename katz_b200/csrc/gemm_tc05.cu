@@ -1,15 +1,20 @@
 // tcgen05 GEMM / implicit-GEMM 3x3 convolution: C[M,N] = A[M,K] * W[N,K]^T with a fused epilogue.
 //
-//   * operands: TMA tile loads (128-byte swizzle) into a multi-stage shared-memory ring, one elected thread;
-//   * math: tcgen05.mma kind::f16, 128 x BN x 16 per instruction, fp32 accumulator in TMEM, one elected thread;
-//   * epilogue: four warps read TMEM with tcgen05.ld, add bias / per-batch row vector / residual, apply SiLU and
-//     write fp16 with 16-byte stores.
-// Linear layers read A through a 2-D tensor map; the 3x3 stride-1 convolution reads the NHWC activation through a
-// 4-D tensor map as nine shifted tile loads per channel chunk (out-of-image pixels arrive as zeros), so no im2col
-// buffer exists. One CTA computes one 128 x BN output tile; with BN = 128 two CTAs share an SM so one tile's epilogue
-// overlaps the other's main loop.
+// One persistent CTA per SM walks output tiles of 128 x BN (BN = 128, 160 or 256; 160 divides every channel count of
+// the SDXL UNet and puts the 2048-token GEMMs on 128 of the 148 SMs in a single wave):
+//   * warp 0, one elected thread: TMA tile loads (128-byte swizzle) into a multi-stage shared-memory ring, running
+//     ahead across tile boundaries;
+//   * warp 1, one elected thread: tcgen05.mma kind::f16 (128 x BN x 16 per instruction), fp32 accumulators in TMEM,
+//     two accumulator buffers so tile i+1's main loop overlaps tile i's epilogue;
+//   * warps 2-5: epilogue. tcgen05.ld brings a 32-row x 32-column block per warp into registers, the block is
+//     transposed through swizzled shared memory, and bias / per-batch row vector / SiLU / residual / scale are applied
+//     on the way out with every global access covering whole 32-byte sectors of a row.
+// Linear layers read A through a 2-D tensor map. The 3x3 stride-1 convolution reads the NHWC activation through a 4-D
+// tensor map as nine shifted tile loads per channel chunk (out-of-image pixels arrive as zeros): no im2col buffer.
+// GEGLU mode loads the two halves of the projection weight into one B tile (rows n..n+BN/2 and F+n..F+n+BN/2), so
+// the value and gate columns of an output element sit in the same thread and `h * gelu(g)` is the epilogue.
 //
-// Every mbarrier wait is bounded (tc05.cuh): on a time-out the CTA records a status word, skips its stores, frees its
+// Every mbarrier wait is bounded (tc05.cuh): on a time-out the CTA records a status word, stops storing, frees its
 // TMEM and returns; the host reads the word with katz_tc05_status().
 //
 // Replaces the cuBLAS / cuDNN calls behind nn.Linear and nn.Conv2d in the reference's UNet
@@ -23,16 +28,20 @@ using namespace tc05;
 
 constexpr int TBM = 128, TBK = 64;
 constexpr int TC_THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int TMEM_COLS = 512;    // two accumulator buffers at columns 0 and 256
+constexpr int STG_FLOATS = 32 * 32;
 
 struct Tc05Params {
     __half* C;
     const __half* bias;
     const __half* rowvec;
     const __half* residual;
-    int M, N, K;
+    int M, N, K;            // N = output columns (GEGLU: F, the gated width)
     int ldc, ldr, ld_rowvec, rows_per_batch;
     int act;
     float out_scale;
+    int m_tiles, n_tiles;
+    int geglu_F;            // > 0: GEGLU mode, weight has 2F rows
     // convolution geometry (stride 1, output size = input size)
     int conv, H, W, TW, TH, tiles_w, tiles_h, cin_chunks, ksize, pad;
     int* status;
@@ -40,34 +49,39 @@ struct Tc05Params {
 
 __device__ int g_tc05_status = 0;
 
-template <int BN, int STAGES>
-__global__ void __launch_bounds__(TC_THREADS) tc05_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
-                                                               const __grid_constant__ CUtensorMap tmB, const Tc05Params p) {
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ float rhalf(float v) { return __half2float(__float2half_rn(v)); }
+
+template <int BN, int STAGES, bool GEGLU>
+__global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                                  const __grid_constant__ CUtensorMap tmB,
+                                                                  const Tc05Params p) {
     constexpr int A_BYTES = TBM * TBK * 2;
     constexpr int B_BYTES = BN * TBK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int BN_OUT = GEGLU ? BN / 2 : BN;      // output columns per tile
+    constexpr int NSTG = GEGLU ? 2 : 1;              // staging blocks per epilogue warp
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte alignment: the swizzle pattern and the UMMA descriptors assume it
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    float* staging = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + 4 * NSTG * STG_FLOATS * 4);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     const uint32_t smem_base = smem_u32(smem);
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), tfull = smem_u32(bars + 2 * STAGES);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+    const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BN;
-    int m0 = 0, cb = 0, ch0 = 0, cw0 = 0;
-    if (p.conv) {
-        const int tpi = p.tiles_w * p.tiles_h;
-        cb = blockIdx.y / tpi;
-        const int r = blockIdx.y - cb * tpi;
-        const int ty = r / p.tiles_w;
-        ch0 = ty * p.TH;
-        cw0 = (r - ty * p.tiles_w) * p.TW;
-    } else {
-        m0 = blockIdx.y * TBM;
-    }
     const int KT = p.K / TBK;
+    const int total_tiles = p.m_tiles * p.n_tiles;
 
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmA);
@@ -76,11 +90,14 @@ __global__ void __launch_bounds__(TC_THREADS) tc05_gemm_kernel(const __grid_cons
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
-        mbar_init(tfull, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tfull0 + 8 * b, 1);
+            mbar_init(tempty0 + 8 * b, 4);    // one arrival per epilogue warp
+        }
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), BN);
+        tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
         tmem_relinquish();
     }
     fence_before_sync();
@@ -88,136 +105,207 @@ __global__ void __launch_bounds__(TC_THREADS) tc05_gemm_kernel(const __grid_cons
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    bool ok = true;
     if (warp == 0) {
         // ------------------------------------------------------------------------------------ TMA producer
         if (elect_one()) {
-            int issued = 0;
-            for (int kt = 0; kt < KT; ++kt) {
-                const int s = kt % STAGES;
-                const uint32_t ph = (kt / STAGES) & 1;
-                if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { ok = false; break; }
-                const uint32_t fb = full0 + 8 * s;
-                mbar_expect_tx(fb, STAGE_BYTES);
-                const uint32_t sa = smem_base + s * STAGE_BYTES;
+            bool ok = true;
+            uint32_t it = 0, issued = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
+                int m0 = mt * TBM, cb = 0, ch0 = 0, cw0 = 0;
                 if (p.conv) {
-                    const int tap = kt / p.cin_chunks;
-                    const int cc = kt - tap * p.cin_chunks;
-                    const int ky = tap / p.ksize, kx = tap - ky * p.ksize;
-                    tma_load_4d(sa, &tmA, cc * TBK, cw0 + kx - p.pad, ch0 + ky - p.pad, cb, fb);
-                } else {
-                    tma_load_2d(sa, &tmA, kt * TBK, m0, fb);
+                    const int tpi = p.tiles_w * p.tiles_h;
+                    cb = mt / tpi;
+                    const int r = mt - cb * tpi;
+                    const int ty = r / p.tiles_w;
+                    ch0 = ty * p.TH;
+                    cw0 = (r - ty * p.tiles_w) * p.TW;
                 }
-                tma_load_2d(sa + A_BYTES, &tmB, kt * TBK, n0, fb);
-                issued = kt + 1;
+                const int n0 = nt * BN_OUT;
+                for (int kt = 0; kt < KT; ++kt, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { ok = false; break; }
+                    const uint32_t fb = full0 + 8 * s;
+                    mbar_expect_tx(fb, STAGE_BYTES);
+                    const uint32_t sa = smem_base + s * STAGE_BYTES;
+                    if (p.conv) {
+                        const int tap = kt / p.cin_chunks;
+                        const int cc = kt - tap * p.cin_chunks;
+                        const int ky = tap / p.ksize, kx = tap - ky * p.ksize;
+                        tma_load_4d(sa, &tmA, cc * TBK, cw0 + kx - p.pad, ch0 + ky - p.pad, cb, fb);
+                    } else {
+                        tma_load_2d(sa, &tmA, kt * TBK, m0, fb);
+                    }
+                    if (GEGLU) {
+                        tma_load_2d(sa + A_BYTES, &tmB, kt * TBK, n0, fb);
+                        tma_load_2d(sa + A_BYTES + B_BYTES / 2, &tmB, kt * TBK, p.geglu_F + n0, fb);
+                    } else {
+                        tma_load_2d(sa + A_BYTES, &tmB, kt * TBK, n0, fb);
+                    }
+                    issued = it + 1;
+                }
             }
             if (!ok) {
                 atomicExch(p.status, 1);
                 // let copies already in flight land before the CTA's shared memory is released
-                for (int kt = max(0, issued - STAGES); kt < issued; ++kt)
-                    mbar_wait(full0 + 8 * (kt % STAGES), (kt / STAGES) & 1);
+                const uint32_t first = issued > (uint32_t)STAGES ? issued - STAGES : 0;
+                for (uint32_t j = first; j < issued; ++j) mbar_wait(full0 + 8 * (j % STAGES), (j / STAGES) & 1);
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------------------------ MMA issuer
         if (elect_one()) {
             constexpr uint32_t idesc = idesc_f16(TBM, BN);
-            for (int kt = 0; kt < KT; ++kt) {
-                const int s = kt % STAGES;
-                const uint32_t ph = (kt / STAGES) & 1;
-                if (!mbar_wait(full0 + 8 * s, ph)) { ok = false; break; }
+            bool ok = true;
+            uint32_t it = 0, t = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+                const uint32_t buf = t & 1;
+                if (!mbar_wait(tempty0 + 8 * buf, ((t >> 1) & 1) ^ 1)) { ok = false; break; }
                 fence_after_sync();
-                const uint32_t sa = smem_base + s * STAGE_BYTES;
-                const uint64_t ad = smem_desc_sw128(sa), bd = smem_desc_sw128(sa + A_BYTES);
+                const uint32_t tacc = tmem_base + buf * 256;
+                for (int kt = 0; kt < KT; ++kt, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(full0 + 8 * s, ph)) { ok = false; break; }
+                    fence_after_sync();
+                    const uint32_t sa = smem_base + s * STAGE_BYTES;
+                    const uint64_t ad = smem_desc_sw128(sa), bd = smem_desc_sw128(sa + A_BYTES);
 #pragma unroll
-                for (int k = 0; k < TBK / 16; ++k) {
-                    // +32 bytes per 16-element K step inside the 128-byte swizzle row (encoded >> 4)
-                    umma_f16(tmem_base, ad + 2 * k, bd + 2 * k, idesc, (kt | k) != 0);
+                    for (int k = 0; k < TBK / 16; ++k) {
+                        // +32 bytes per 16-element K step inside the 128-byte swizzle row (encoded >> 4)
+                        umma_f16(tacc, ad + 2 * k, bd + 2 * k, idesc, (kt | k) != 0);
+                    }
+                    umma_commit(empty0 + 8 * s);   // stage reusable once these MMAs have read it
                 }
-                umma_commit(empty0 + 8 * s);   // stage reusable once these MMAs have read it
+                if (ok) umma_commit(tfull0 + 8 * buf);
             }
-            if (ok) umma_commit(tfull);
-            else atomicExch(p.status, 2);
+            if (!ok) atomicExch(p.status, 2);
         }
     } else {
         // ------------------------------------------------------------------------------------ epilogue
         const int q = warp & 3;                 // TMEM lane quarter this warp may read
-        const int row = q * 32 + lane;
-        ok = mbar_wait(tfull, 0);
-        ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-collective: decide as a warp
-        if (!ok && lane == 0) atomicExch(p.status, 3);
-        fence_after_sync();
-        long long m;
-        bool valid;
-        int bidx;
-        if (p.conv) {
-            const int th = row / p.TW, tw = row - th * p.TW;
-            const int h = ch0 + th;
-            valid = h < p.H;
-            m = ((long long)cb * p.H + h) * p.W + cw0 + tw;
-            bidx = cb;
-        } else {
-            m = m0 + row;
-            valid = m < p.M;
-            bidx = p.rowvec ? (int)(m / p.rows_per_batch) : 0;
-        }
-        valid = valid && ok;
+        float* stg = staging + q * NSTG * STG_FLOATS;
+        bool ok = true;
+        uint32_t t = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+            const uint32_t buf = t & 1;
+            const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
+            int m0 = mt * TBM, cb = 0, ch0 = 0, cw0 = 0;
+            if (p.conv) {
+                const int tpi = p.tiles_w * p.tiles_h;
+                cb = mt / tpi;
+                const int r = mt - cb * tpi;
+                const int ty = r / p.tiles_w;
+                ch0 = ty * p.TH;
+                cw0 = (r - ty * p.tiles_w) * p.TW;
+            }
+            const int n0 = nt * BN_OUT;
+            ok = mbar_wait(tfull0 + 8 * buf, (t >> 1) & 1);
+            ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-collective: decide as a warp
+            if (!ok) {
+                if (lane == 0) atomicExch(p.status, 3);
+                break;
+            }
+            fence_after_sync();
+            const uint32_t tacc = tmem_base + buf * 256 + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-        for (int chunk = 0; chunk < BN / 32; ++chunk) {
-            uint32_t r[32];
-            if (ok) {
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + chunk * 32, r);
+            for (int c0 = 0; c0 < BN_OUT; c0 += 32) {
+                const int w = (BN_OUT - c0) < 32 ? (BN_OUT - c0) : 32;   // 32, or a 16-column tail
+                uint32_t r[32], g[GEGLU ? 32 : 1];
+                if (w == 32) {
+                    tmem_ld_32x32(tacc + c0, r);
+                    if (GEGLU) tmem_ld_32x32(tacc + BN / 2 + c0, g);
+                } else {
+                    tmem_ld_32x16(tacc + c0, r);
+                    if (GEGLU) tmem_ld_32x16(tacc + BN / 2 + c0, g);
+                }
                 tmem_ld_wait();
+                // transpose through shared memory: thread = row on the way in, thread = 4-column group on the way out
+                const int nch = w >> 2;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    if (c < nch) {
+                        const int off = lane * 32 + ((c ^ (lane & 7)) << 2);
+                        *reinterpret_cast<float4*>(stg + off) =
+                            make_float4(__uint_as_float(r[4 * c]), __uint_as_float(r[4 * c + 1]), __uint_as_float(r[4 * c + 2]),
+                                        __uint_as_float(r[4 * c + 3]));
+                        if (GEGLU)
+                            *reinterpret_cast<float4*>(stg + STG_FLOATS + off) =
+                                make_float4(__uint_as_float(g[4 * c]), __uint_as_float(g[4 * c + 1]),
+                                            __uint_as_float(g[4 * c + 2]), __uint_as_float(g[4 * c + 3]));
+                    }
+                }
+                __syncwarp();
+                const int lanes_per_row = nch;                  // 8 or 4
+                const int rows_per_it = 32 / lanes_per_row;     // 4 or 8
+                const int cg = lane % lanes_per_row;
+                const int nb = n0 + c0 + cg * 4;
+                float bias4[4] = {0.f, 0.f, 0.f, 0.f}, gbias4[4] = {0.f, 0.f, 0.f, 0.f};
+                const bool col_ok = nb < p.N;
+                if (p.bias && col_ok) {
+                    const uint2 u = *reinterpret_cast<const uint2*>(p.bias + nb);
+                    float2 a = unpack_half2(u.x), b2 = unpack_half2(u.y);
+                    bias4[0] = a.x; bias4[1] = a.y; bias4[2] = b2.x; bias4[3] = b2.y;
+                    if (GEGLU) {
+                        const uint2 v = *reinterpret_cast<const uint2*>(p.bias + p.geglu_F + nb);
+                        float2 c2 = unpack_half2(v.x), d2 = unpack_half2(v.y);
+                        gbias4[0] = c2.x; gbias4[1] = c2.y; gbias4[2] = d2.x; gbias4[3] = d2.y;
+                    }
+                }
+                for (int i = 0; i < 32; i += rows_per_it) {
+                    const int rl = i + lane / lanes_per_row;    // row inside this warp's 32
+                    const int row = q * 32 + rl;                // row inside the 128-row tile
+                    long long m;
+                    bool valid;
+                    int bidx;
+                    if (p.conv) {
+                        const int th = row / p.TW, tw = row - th * p.TW;
+                        const int h = ch0 + th;
+                        valid = h < p.H;
+                        m = ((long long)cb * p.H + h) * p.W + cw0 + tw;
+                        bidx = cb;
+                    } else {
+                        m = m0 + row;
+                        valid = m < p.M;
+                        bidx = p.rowvec ? (int)(m / p.rows_per_batch) : 0;
+                    }
+                    if (!valid || !col_ok) continue;
+                    const int off = rl * 32 + ((cg ^ (rl & 7)) << 2);
+                    const float4 a4 = *reinterpret_cast<const float4*>(stg + off);
+                    float v[4] = {a4.x + bias4[0], a4.y + bias4[1], a4.z + bias4[2], a4.w + bias4[3]};
+                    if (GEGLU) {
+                        const float4 g4 = *reinterpret_cast<const float4*>(stg + STG_FLOATS + off);
+                        const float gg[4] = {g4.x + gbias4[0], g4.y + gbias4[1], g4.z + gbias4[2], g4.w + gbias4[3]};
+                        // activations.py:146-149 on fp16 tensors: proj output, gelu and product each round to half
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) v[e] = rhalf(v[e]) * rhalf(gelu_erf_f(rhalf(gg[e])));
+                    }
+                    if (p.rowvec) {
+                        const uint2 u = *reinterpret_cast<const uint2*>(p.rowvec + (size_t)bidx * p.ld_rowvec + nb);
+                        float2 a = unpack_half2(u.x), b2 = unpack_half2(u.y);
+                        v[0] += a.x; v[1] += a.y; v[2] += b2.x; v[3] += b2.y;
+                    }
+                    if (p.act == 1) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) v[e] = silu_f(v[e]);
+                    }
+                    if (p.residual) {
+                        const uint2 u = *reinterpret_cast<const uint2*>(p.residual + (size_t)m * p.ldr + nb);
+                        float2 a = unpack_half2(u.x), b2 = unpack_half2(u.y);
+                        v[0] += a.x; v[1] += a.y; v[2] += b2.x; v[3] += b2.y;
+                    }
+                    uint2 o;
+                    o.x = pack_half2(v[0] * p.out_scale, v[1] * p.out_scale);
+                    o.y = pack_half2(v[2] * p.out_scale, v[3] * p.out_scale);
+                    *reinterpret_cast<uint2*>(p.C + (size_t)m * p.ldc + nb) = o;
+                }
+                __syncwarp();
             }
-            if (!valid) continue;
-#pragma unroll
-            for (int g8 = 0; g8 < 4; ++g8) {
-                const int nb = n0 + chunk * 32 + g8 * 8;
-                if (nb >= p.N) break;
-                float v[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[g8 * 8 + e]);
-                if (p.bias) {
-                    const uint4 u = *reinterpret_cast<const uint4*>(p.bias + nb);
-                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        float2 f = unpack_half2(w[e]);
-                        v[2 * e] += f.x;
-                        v[2 * e + 1] += f.y;
-                    }
-                }
-                if (p.rowvec) {
-                    const uint4 u = *reinterpret_cast<const uint4*>(p.rowvec + (size_t)bidx * p.ld_rowvec + nb);
-                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        float2 f = unpack_half2(w[e]);
-                        v[2 * e] += f.x;
-                        v[2 * e + 1] += f.y;
-                    }
-                }
-                if (p.act == 1) {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) v[e] = silu_f(v[e]);
-                }
-                if (p.residual) {
-                    const uint4 u = *reinterpret_cast<const uint4*>(p.residual + (size_t)m * p.ldr + nb);
-                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        float2 f = unpack_half2(w[e]);
-                        v[2 * e] += f.x;
-                        v[2 * e + 1] += f.y;
-                    }
-                }
-                uint4 o;
-                o.x = pack_half2(v[0] * p.out_scale, v[1] * p.out_scale);
-                o.y = pack_half2(v[2] * p.out_scale, v[3] * p.out_scale);
-                o.z = pack_half2(v[4] * p.out_scale, v[5] * p.out_scale);
-                o.w = pack_half2(v[6] * p.out_scale, v[7] * p.out_scale);
-                *reinterpret_cast<uint4*>(p.C + (size_t)m * p.ldc + nb) = o;
-            }
+            // this warp is done reading the accumulator buffer
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
         }
     }
     // ---------------------------------------------------------------------------------------- teardown
@@ -225,7 +313,7 @@ __global__ void __launch_bounds__(TC_THREADS) tc05_gemm_kernel(const __grid_cons
     __syncthreads();
     if (warp == 1) {
         fence_after_sync();
-        tmem_dealloc(tmem_base, BN);
+        tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 
@@ -275,21 +363,34 @@ static int encode_nhwc(CUtensorMap* map, const void* base, int B, int H, int W, 
     return r == CUDA_SUCCESS ? 0 : KATZ_EINVAL;
 }
 
-template <int BN, int STAGES>
-static constexpr int tc05_smem() {
-    return STAGES * (TBM * TBK * 2 + BN * TBK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+static int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+    }
+    return n;
 }
 
-template <int BN, int STAGES>
-static int launch_tc05(const CUtensorMap& a, const CUtensorMap& b, const Tc05Params& p, dim3 grid, cudaStream_t st) {
+template <int BN, int STAGES, bool GEGLU>
+static constexpr int tc05_smem() {
+    return STAGES * (TBM * TBK * 2 + BN * TBK * 2) + 4 * (GEGLU ? 2 : 1) * STG_FLOATS * 4 + (2 * STAGES + 4) * 8 + 16 + 1024;
+}
+
+template <int BN, int STAGES, bool GEGLU>
+static int launch_tc05(const CUtensorMap& a, const CUtensorMap& b, const Tc05Params& p, cudaStream_t st) {
     static bool attr = false;
-    constexpr int smem = tc05_smem<BN, STAGES>();
+    constexpr int smem = tc05_smem<BN, STAGES, GEGLU>();
+    static_assert(smem <= 232448, "shared memory budget");
     if (!attr) {
-        cudaError_t e = cudaFuncSetAttribute(tc05_gemm_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(tc05_gemm_kernel<BN, STAGES, GEGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         attr = true;
     }
-    tc05_gemm_kernel<BN, STAGES><<<grid, TC_THREADS, smem, st>>>(a, b, p);
+    const int total = p.m_tiles * p.n_tiles;
+    const int grid = total < sm_count() ? total : sm_count();
+    tc05_gemm_kernel<BN, STAGES, GEGLU><<<grid, TC_THREADS, smem, st>>>(a, b, p);
     KATZ_LAUNCH_RET();
 }
 
@@ -302,16 +403,34 @@ static int* status_ptr() {
     return ptr;
 }
 
-static int dispatch(const CUtensorMap& a, const CUtensorMap& b, Tc05Params& p, int m_tiles, cudaStream_t st) {
+// Tile width by wave efficiency: tiles of width bn cost ~bn per wave; pick the width with the least total cost.
+static int pick_bn(int m_tiles, int n_out, bool geglu) {
+    const int sms = sm_count();
+    const int cand[3] = {256, 160, 128};
+    int best = 128;
+    double best_cost = 1e30;
+    for (int i = 0; i < 3; ++i) {
+        const int bn = cand[i];
+        const int out_w = geglu ? bn / 2 : bn;
+        const long long tiles = (long long)m_tiles * ceil_div(n_out, out_w);
+        const long long waves = (tiles + sms - 1) / sms;
+        // per-tile time ~ MMA time (prop. to bn) + fixed overhead per tile (epilogue drain, barrier round trips)
+        const double cost = (double)waves * (bn + 24.0);
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    return best;
+}
+
+template <bool GEGLU>
+static int dispatch(const CUtensorMap& a, const CUtensorMap& b, Tc05Params& p, int bn, cudaStream_t st) {
     p.status = status_ptr();
     if (!p.status) return KATZ_ENOTREADY;
-    // Tile width: 256 halves the A-operand re-reads per MMA when the grid still fills the machine; 128 otherwise,
-    // with the shallow ring when two CTAs can share an SM.
-    const int t256 = ceil_div(p.N, 256) * m_tiles, t128 = ceil_div(p.N, 128) * m_tiles;
-    if (m_tiles > 65535) return KATZ_ESIZE;
-    if (p.N % 256 == 0 && t256 >= 148) return launch_tc05<256, 4>(a, b, p, dim3(ceil_div(p.N, 256), m_tiles), st);
-    if (t128 > 148) return launch_tc05<128, 3>(a, b, p, dim3(ceil_div(p.N, 128), m_tiles), st);
-    return launch_tc05<128, 6>(a, b, p, dim3(ceil_div(p.N, 128), m_tiles), st);
+    if (bn == 256) return launch_tc05<256, 4, GEGLU>(a, b, p, st);
+    if (bn == 160) return launch_tc05<160, 5, GEGLU>(a, b, p, st);
+    return launch_tc05<128, 6, GEGLU>(a, b, p, st);
 }
 
 }  // namespace katz
@@ -329,30 +448,47 @@ extern "C" int katz_tc05_clear_status(void) {
     return cudaMemcpyToSymbol(g_tc05_status, &v, sizeof(int)) == cudaSuccess ? 0 : KATZ_ENOTREADY;
 }
 
-extern "C" int katz_linear_f16(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, int K,
-                               const void* bias, const void* rowvec, int ld_rowvec, int rows_per_batch,
-                               const void* residual, int ldr, int act, float out_scale, void* stream) {
+static int linear_common(const void* A, int lda, const void* W, void* C, int ldc, int M, int N_out, int K, const void* bias,
+                         const void* rowvec, int ld_rowvec, int rows_per_batch, const void* residual, int ldr, int act,
+                         float out_scale, int geglu_F, void* stream) {
     KATZ_CHECK_ARG(A && W && C, KATZ_EINVAL);
-    KATZ_CHECK_ARG(M > 0 && N > 0 && K > 0, KATZ_ESIZE);
-    KATZ_CHECK_ARG(K % TBK == 0 && N % 8 == 0, KATZ_ESIZE);
-    KATZ_CHECK_ARG(lda % 8 == 0 && ldc % 8 == 0, KATZ_EALIGN);
-    KATZ_CHECK_ARG(aligned16(A) && aligned16(W) && aligned16(C), KATZ_EALIGN);
-    KATZ_CHECK_ARG(!bias || aligned16(bias), KATZ_EALIGN);
-    KATZ_CHECK_ARG(!rowvec || (aligned16(rowvec) && ld_rowvec % 8 == 0 && rows_per_batch > 0), KATZ_EALIGN);
-    KATZ_CHECK_ARG(!residual || (aligned16(residual) && ldr % 8 == 0), KATZ_EALIGN);
+    KATZ_CHECK_ARG(M > 0 && N_out > 0 && K > 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(K % TBK == 0 && N_out % 8 == 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(lda % 8 == 0 && ldc % 4 == 0, KATZ_EALIGN);
+    KATZ_CHECK_ARG(aligned16(A) && aligned16(W) && ((uintptr_t)C & 7) == 0, KATZ_EALIGN);
+    KATZ_CHECK_ARG(!bias || ((uintptr_t)bias & 7) == 0, KATZ_EALIGN);
+    KATZ_CHECK_ARG(!rowvec || (((uintptr_t)rowvec & 7) == 0 && ld_rowvec % 4 == 0 && rows_per_batch > 0), KATZ_EALIGN);
+    KATZ_CHECK_ARG(!residual || (((uintptr_t)residual & 7) == 0 && ldr % 4 == 0), KATZ_EALIGN);
     CUtensorMap ta, tb;
     int rc = encode_2d(&ta, A, K, M, (uint64_t)lda * 2, TBK, TBM);
     if (rc) return rc;
     Tc05Params p{};
     p.C = (__half*)C; p.bias = (const __half*)bias; p.rowvec = (const __half*)rowvec; p.residual = (const __half*)residual;
-    p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = ldr; p.ld_rowvec = ld_rowvec; p.rows_per_batch = rows_per_batch;
-    p.act = act; p.out_scale = out_scale;
-    const int m_tiles = ceil_div(M, TBM);
-    const int t256 = ceil_div(N, 256) * m_tiles;
-    const int bn = (N % 256 == 0 && t256 >= 148) ? 256 : 128;
-    rc = encode_2d(&tb, W, K, N, (uint64_t)K * 2, TBK, bn);
+    p.M = M; p.N = N_out; p.K = K; p.ldc = ldc; p.ldr = ldr; p.ld_rowvec = ld_rowvec; p.rows_per_batch = rows_per_batch;
+    p.act = act; p.out_scale = out_scale; p.geglu_F = geglu_F;
+    p.m_tiles = ceil_div(M, TBM);
+    KATZ_CHECK_ARG((long long)p.m_tiles * ceil_div(N_out, 64) < (1ll << 30), KATZ_ESIZE);
+    const bool geglu = geglu_F > 0;
+    const int bn = pick_bn(p.m_tiles, N_out, geglu);
+    const int out_w = geglu ? bn / 2 : bn;
+    p.n_tiles = ceil_div(N_out, out_w);
+    const uint64_t w_rows = geglu ? 2ull * geglu_F : (uint64_t)N_out;
+    rc = encode_2d(&tb, W, K, w_rows, (uint64_t)K * 2, TBK, geglu ? bn / 2 : bn);
     if (rc) return rc;
-    return dispatch(ta, tb, p, m_tiles, (cudaStream_t)stream);
+    return geglu ? dispatch<true>(ta, tb, p, bn, (cudaStream_t)stream) : dispatch<false>(ta, tb, p, bn, (cudaStream_t)stream);
+}
+
+extern "C" int katz_linear_f16(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, int K,
+                               const void* bias, const void* rowvec, int ld_rowvec, int rows_per_batch,
+                               const void* residual, int ldr, int act, float out_scale, void* stream) {
+    return linear_common(A, lda, W, C, ldc, M, N, K, bias, rowvec, ld_rowvec, rows_per_batch, residual, ldr, act, out_scale, 0,
+                         stream);
+}
+
+extern "C" int katz_linear_geglu_f16(const void* A, int lda, const void* W, void* C, int ldc, int M, int F, int K,
+                                     const void* bias, void* stream) {
+    KATZ_CHECK_ARG(F > 0 && F % 16 == 0, KATZ_ESIZE);
+    return linear_common(A, lda, W, C, ldc, M, F, K, bias, nullptr, 0, 0, nullptr, 0, 0, 1.0f, F, stream);
 }
 
 extern "C" int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int B, int H, int Wd, int Cin, int Cout,
@@ -364,10 +500,10 @@ extern "C" int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int 
     const int TW = Wd < 128 ? Wd : 128;
     KATZ_CHECK_ARG((TW & (TW - 1)) == 0 && TW >= 8 && Wd % TW == 0, KATZ_ESIZE);
     const int TH = 128 / TW;
-    KATZ_CHECK_ARG(aligned16(X) && aligned16(W) && aligned16(Y), KATZ_EALIGN);
-    KATZ_CHECK_ARG(!bias || aligned16(bias), KATZ_EALIGN);
-    KATZ_CHECK_ARG(!rowvec || (aligned16(rowvec) && ld_rowvec % 8 == 0), KATZ_EALIGN);
-    KATZ_CHECK_ARG(!residual || aligned16(residual), KATZ_EALIGN);
+    KATZ_CHECK_ARG(aligned16(X) && aligned16(W) && ((uintptr_t)Y & 7) == 0, KATZ_EALIGN);
+    KATZ_CHECK_ARG(!bias || ((uintptr_t)bias & 7) == 0, KATZ_EALIGN);
+    KATZ_CHECK_ARG(!rowvec || (((uintptr_t)rowvec & 7) == 0 && ld_rowvec % 4 == 0), KATZ_EALIGN);
+    KATZ_CHECK_ARG(!residual || ((uintptr_t)residual & 7) == 0, KATZ_EALIGN);
     CUtensorMap ta, tb;
     int rc = encode_nhwc(&ta, X, B, H, Wd, Cin, TW, TH);
     if (rc) return rc;
@@ -377,10 +513,10 @@ extern "C" int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int 
     p.act = act; p.out_scale = out_scale;
     p.conv = 1; p.H = H; p.W = Wd; p.TW = TW; p.TH = TH; p.tiles_w = Wd / TW; p.tiles_h = ceil_div(H, TH);
     p.cin_chunks = Cin / TBK; p.ksize = 3; p.pad = 1;
-    const int m_tiles = B * p.tiles_w * p.tiles_h;
-    const int t256 = ceil_div(Cout, 256) * m_tiles;
-    const int bn = (Cout % 256 == 0 && t256 >= 148) ? 256 : 128;
+    p.m_tiles = B * p.tiles_w * p.tiles_h;
+    const int bn = pick_bn(p.m_tiles, Cout, false);
+    p.n_tiles = ceil_div(Cout, bn);
     rc = encode_2d(&tb, W, (uint64_t)9 * Cin, Cout, (uint64_t)9 * Cin * 2, TBK, bn);
     if (rc) return rc;
-    return dispatch(ta, tb, p, m_tiles, (cudaStream_t)stream);
+    return dispatch<false>(ta, tb, p, bn, (cudaStream_t)stream);
 }

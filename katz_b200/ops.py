@@ -56,6 +56,22 @@ def tc05_status():
     return _lib.load().katz_tc05_status()
 
 
+def feed_forward_geglu(x, w, bias, out=None):
+    """GEGLU feed-forward projection: x[M,K], w[2F,K] (the unsplit `proj`), bias[2F] -> [M,F] = h * gelu(g).
+    One fused tcgen05 GEMM when the shape allows, else GEMM + gating kernel."""
+    _f16(x, "x"), _f16(w, "w")
+    M, K = x.shape
+    F = w.shape[0] // 2
+    if out is None:
+        out = torch.empty((M, F), dtype=torch.float16, device=x.device)
+    if (_use_tc05() and os.environ.get("KATZ_FUSED_GEGLU", "1") == "1" and K % 64 == 0 and F % 16 == 0
+            and x.stride(1) == 1 and x.stride(0) % 8 == 0 and w.is_contiguous() and _al16(x) and _al16(w) and _al16(out)
+            and _al16(bias) and out.stride(0) % 8 == 0):
+        call("katz_linear_geglu_f16", _p(x), x.stride(0), _p(w), _p(out), out.stride(0), M, F, K, _p(bias), _stream())
+        return out
+    return geglu_erf(linear(x, w, bias), out=out)
+
+
 def upsample_nearest2x(x, out=None):
     _f16(x, "x")
     B, H, W, C = x.shape
@@ -298,20 +314,20 @@ def nhwc_to_nchw(x, c=None, out=None):
     return out
 
 
-def euler_scale_input(x, sigma, copies=1, out=None):
+def euler_scale_input(x, sigma, copies=1, out=None, cpu_torch_rounding=False):
+    """half(x / sqrt(sigma^2 + 1)), written `copies` times. See euler_cfg_step for `cpu_torch_rounding`."""
     _f16(x, "x")
     if out is None:
         out = torch.empty((copies * x.shape[0],) + tuple(x.shape[1:]), dtype=torch.float16, device=x.device)
-    call("katz_euler_scale_input", _p(x), _p(out), x.numel(), float(sigma), copies, _stream())
+    call("katz_euler_scale_input", _p(x), _p(out), x.numel(), float(sigma), copies, 1 if cpu_torch_rounding else 0, _stream())
     return out
 
 
 def euler_cfg_step(x, eps_uncond, eps_cond, guidance, sigma, sigma_next, cpu_torch_rounding=False):
-    """In-place Euler step on the fp16 latent x with classifier-free guidance. `cpu_torch_rounding` reproduces torch's
-    CPU kernels, which round sigma to fp16 before `sigma * eps`; the default is what torch does on CUDA."""
+    """In-place Euler step on the fp16 latent x with classifier-free guidance. The default reproduces torch's CUDA
+    kernels (division by a host scalar = multiplication by its reciprocal; fp32 sigma); `cpu_torch_rounding`
+    reproduces torch's CPU kernels (true division; sigma rounded to fp16 before `sigma * eps`)."""
     _f16(x, "x"), _f16(eps_uncond, "eps_uncond")
-    sigma = float(sigma)
-    smul = float(torch.tensor(sigma, dtype=torch.float32).half()) if cpu_torch_rounding else sigma
-    call("katz_euler_cfg_step", _p(x), _p(eps_uncond), _p(eps_cond), x.numel(), float(guidance), sigma,
-         float(sigma_next), smul, _stream())
+    call("katz_euler_cfg_step", _p(x), _p(eps_uncond), _p(eps_cond), x.numel(), float(guidance), float(sigma),
+         float(sigma_next), 1 if cpu_torch_rounding else 0, _stream())
     return x

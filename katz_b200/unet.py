@@ -266,8 +266,7 @@ class _Net:
             a = ops.attention(q, kv[:, :, off:off + C], kv[:, :, off + C:off + 2 * C], heads)
             h = ops.linear(a.view(M, C), P(b + ".attn2.to_out.0.weight"), P(b + ".attn2.to_out.0.bias"), residual=h)
             n = ops.layer_norm(h, P(b + ".norm3.weight"), P(b + ".norm3.bias"))
-            hg = ops.linear(n, P(b + ".ff.net.0.proj.weight"), P(b + ".ff.net.0.proj.bias"))
-            f = ops.geglu_erf(hg)
+            f = ops.feed_forward_geglu(n, P(b + ".ff.net.0.proj.weight"), P(b + ".ff.net.0.proj.bias"))
             h = ops.linear(f, P(b + ".ff.net.2.weight"), P(b + ".ff.net.2.bias"), residual=h)
         out = ops.linear(h, P(p + ".proj_out.weight"), P(p + ".proj_out.bias"), residual=x.view(M, C))
         return out.view(B, H, W, C)

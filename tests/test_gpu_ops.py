@@ -188,7 +188,7 @@ def test_small_kernels(cuda_device, golden_dir):
     sig = gz["sigmas"]
     lat = torch.from_numpy(gz["latent0"]).cuda()
     for i in range(4):
-        inp = ops.euler_scale_input(lat, sig[i], copies=2)
+        inp = ops.euler_scale_input(lat, sig[i], copies=2, cpu_torch_rounding=True)
         assert torch.equal(inp[0].cpu(), torch.from_numpy(gz["scaled_%d" % i])[0])
         assert torch.equal(inp[1].cpu(), torch.from_numpy(gz["scaled_%d" % i])[0])
         ops.euler_cfg_step(lat, torch.from_numpy(gz["eps_u_%d" % i]).cuda(), torch.from_numpy(gz["eps_c_%d" % i]).cuda(),
@@ -199,6 +199,7 @@ def test_small_kernels(cuda_device, golden_dir):
     ref = lat.clone()
     for i in range(4):
         u, c = torch.from_numpy(gz["eps_u_%d" % i]).cuda(), torch.from_numpy(gz["eps_c_%d" % i]).cuda()
+        assert torch.equal(ops.euler_scale_input(lat, sig[i]), unet_oracle.euler_scale_model_input(ref, float(sig[i])))
         ops.euler_cfg_step(lat, u, c, 5.0, sig[i], sig[i + 1])
         ref = unet_oracle.euler_step(ref, unet_oracle.cfg_combine(u, c, 5.0), float(sig[i]), float(sig[i + 1]))
         assert torch.equal(lat, ref)
@@ -265,3 +266,23 @@ def test_conv3x3_tcgen05(cuda_device, B, H, W, Cin, Cout, up, monkeypatch):
                      rowvec=temb, residual=res.permute(0, 2, 3, 1).contiguous())
     assert ops.tc05_status() == 0
     assert _rel(out.permute(0, 3, 1, 2), ref) < 2e-3
+
+
+@pytest.mark.parametrize("M,F,K", [(2048, 5120, 1280), (8192, 2560, 640), (300, 64, 64), (256, 80, 128)])
+def test_feed_forward_geglu_fused(cuda_device, M, F, K, monkeypatch):
+    monkeypatch.setenv("KATZ_GEMM", "tc05")
+    from katz_b200 import ops
+    from oracle import kernels_oracle
+    g = torch.Generator().manual_seed(13)
+    x = torch.randn(M, K, generator=g).half().cuda()
+    w = (torch.randn(2 * F, K, generator=g) / K ** 0.5).half().cuda()
+    b = torch.randn(2 * F, generator=g).half().cuda()
+    hg = (x.float() @ w.float().t() + b.float()).half()
+    ref = kernels_oracle.geglu_erf(hg.cpu())
+    out = ops.feed_forward_geglu(x, w, b)
+    assert ops.tc05_status() == 0
+    d = (out.cpu().float() - ref.float()).abs()
+    assert float(d.max()) <= 2e-2 and _rel(out, ref) < 4e-3
+    monkeypatch.setenv("KATZ_FUSED_GEGLU", "0")
+    out2 = ops.feed_forward_geglu(x, w, b)
+    assert _rel(out, out2.cpu()) < 4e-3
