@@ -180,6 +180,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-step", action="store_true",
                     help="run ONE eager UNet step between cudaProfilerStart/Stop and exit (for `ncu --profile-from-start off`)")
+    ap.add_argument("--profile-gemm", action="store_true",
+                    help="launch the dominant linear GEMM shapes between cudaProfilerStart/Stop and exit")
     ap.add_argument("--profile-merge", action="store_true",
                     help="run ONE LoRA merge over a reduced layer set between cudaProfilerStart/Stop and exit")
     ap.add_argument("--latent", type=int, default=128, help="latent height = width (128 = 1024^2 images)")
@@ -211,6 +213,25 @@ def main():
     cfg = SDXL_UNET_CONFIG
     B, HW = 2, args.latent
 
+    if args.profile_gemm:
+        # the dominant GEMM shapes of the step, each launched 3 times under the profiler range
+        shapes = [(2048, 10240, 1280), (2048, 1280, 1280), (8192, 640, 2560)]
+        outs = []
+        for (M, N, K) in shapes:
+            xs = torch.randn(M, K, device=dev).half()
+            ws = (torch.randn(N, K, device=dev) * 0.03).half()
+            outs.append((xs, ws, torch.empty(M, N, dtype=torch.float16, device=dev)))
+        for xs, ws, o in outs:
+            ops.linear(xs, ws, out=o)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        for xs, ws, o in outs:
+            for _ in range(3):
+                ops.linear(xs, ws, out=o)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"profiled": "linear GEMMs", "shapes": shapes, "kernel": ops.gemm_kernel_name()}))
+        return
     # ---- model: random-init SDXL UNet (seed 0), weights drawn on the device
     sd = init_state_dict(unet_param_shapes(cfg), seed=0, dtype=torch.float16, device=dev, generator_device=dev)
     unet = KatzUNet(cfg, dev, sd)

@@ -8,9 +8,13 @@
 // With W0 == nullptr the update is in place (sign = -1 gives the subtractive unmerge of
 // diffusers/models/lora.py:427-449, which is not bit-exact in floating point).
 //
-// The work is bound by streaming W through HBM once; the rank-r product runs on tensor cores (mma.sync, fp16 inputs
-// or 3xTF32 for fp32 inputs) from shared-memory tiles while the W tile is in flight. Rounding follows the reference:
-// fp16: delta = half(acc); delta = half(delta * s); W = half(W + delta), per LoRA in order. fp32: W += acc * s.
+// The work is bound by streaming W through HBM once. One persistent CTA per SM walks the global tile list with a ring
+// of shared-memory stages: while tile i is being updated and written back with 16-byte stores, the 16-byte async
+// copies of tiles i+1 (and i+2) — the W tile and the first adapter's B and A tiles — are already in flight. The rank-r
+// product runs on tensor cores (mma.sync; fp16 inputs, or 3xTF32 for fp32 inputs) out of swizzled shared memory.
+// Further adapters / rank chunks beyond 64 are fetched synchronously into a side buffer.
+// Rounding follows the reference: fp16: delta = half(acc); delta = half(delta * s); W = half(W + delta), per adapter
+// in order. fp32: W += acc * s.
 #include "common.cuh"
 #include "katz_b200.h"
 
@@ -25,20 +29,24 @@ struct LmCfg;
 template <>
 struct LmCfg<__half> {
     static constexpr int TM = 128;
+    static constexpr int NST = 3;
     static constexpr int W_BYTES = TM * LM_TN * 2;        // 32 KB, 256 B rows, 16 chunks, swizzled
     static constexpr int B_BYTES = TM * 128;              // [TM][64 halfs], 128 B rows, swizzled
     static constexpr int A_BYTES = LM_MAXR * LM_TN * 2;   // [64][128 halfs], 256 B rows, swizzled
-    static constexpr int SMEM = W_BYTES + B_BYTES + A_BYTES;
+    static constexpr int STAGE = W_BYTES + B_BYTES + A_BYTES;
+    static constexpr int SMEM = NST * STAGE + B_BYTES + A_BYTES;
 };
 template <>
 struct LmCfg<float> {
     static constexpr int TM = 64;
+    static constexpr int NST = 2;
     static constexpr int BP = 68;    // B tile pitch in floats (bank-conflict-free fragment reads)
     static constexpr int AP = 136;   // A tile pitch in floats
     static constexpr int W_BYTES = TM * LM_TN * 4;        // 32 KB, 512 B rows, 32 chunks, swizzled
     static constexpr int B_BYTES = TM * BP * 4;
     static constexpr int A_BYTES = LM_MAXR * AP * 4;
-    static constexpr int SMEM = W_BYTES + B_BYTES + A_BYTES;
+    static constexpr int STAGE = W_BYTES + B_BYTES + A_BYTES;
+    static constexpr int SMEM = NST * STAGE + B_BYTES + A_BYTES;
 };
 
 __device__ __forceinline__ int find_layer(const int* __restrict__ tile_start, int n_layers, int tile) {
@@ -51,203 +59,282 @@ __device__ __forceinline__ int find_layer(const int* __restrict__ tile_start, in
 }
 
 template <typename T>
-__global__ void __launch_bounds__(LM_THREADS, 2) lora_merge_kernel(const katz_lora_layer* __restrict__ layers,
+struct TileRef {
+    const katz_lora_layer* L;
+    int row0, col0, out_f, in_f, n_lora;
+};
+
+template <typename T>
+__device__ __forceinline__ TileRef<T> decode_tile(const katz_lora_layer* __restrict__ layers, const int* __restrict__ tile_start,
+                                                  int n_layers, int tile) {
+    TileRef<T> t;
+    const int li = find_layer(tile_start, n_layers, tile);
+    t.L = layers + li;
+    t.out_f = t.L->out_features;
+    t.in_f = t.L->in_features;
+    t.n_lora = t.L->n_lora;
+    const int rel = tile - tile_start[li];
+    const int tiles_n = (t.in_f + LM_TN - 1) / LM_TN;
+    const int tm = rel / tiles_n;
+    t.row0 = tm * LmCfg<T>::TM;
+    t.col0 = (rel - tm * tiles_n) * LM_TN;
+    return t;
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t w_off(int r, int c) {
+    if constexpr (sizeof(T) == 2) return r * 256 + ((c ^ (r & 7)) << 4);
+    else return r * 512 + ((c ^ ((r & 3) << 1)) << 4);
+}
+template <typename T>
+__device__ __forceinline__ uint32_t b_off(int r, int c) {
+    if constexpr (sizeof(T) == 2) return r * 128 + ((c ^ (r & 7)) << 4);
+    else return (r * LmCfg<float>::BP + c * 4) * 4;
+}
+template <typename T>
+__device__ __forceinline__ uint32_t a_off(int r, int c) {
+    if constexpr (sizeof(T) == 2) return r * 256 + ((c ^ (r & 7)) << 4);
+    else return (r * LmCfg<float>::AP + c * 4) * 4;
+}
+
+// Adapter tiles for rank chunk [k0, k0+kr) of adapter l: B rows row0.., A cols col0..; ASYNC = cp.async into the ring,
+// otherwise plain 16-byte loads and stores into the side buffer.
+template <typename T, bool ASYNC>
+__device__ __forceinline__ void load_adapter_tiles(const TileRef<T>& t, int l, int k0, unsigned char* sB, unsigned char* sA) {
+    constexpr int ES = sizeof(T), EPC = 16 / ES, TM = LmCfg<T>::TM, W_CHUNKS_ROW = LM_TN / EPC;
+    const T* Bm = reinterpret_cast<const T*>(t.L->B[l]);
+    const T* Am = reinterpret_cast<const T*>(t.L->A[l]);
+    const int rank = t.L->rank[l];
+    const int kr = min(LM_MAXR, rank - k0);
+    const int kpad = (kr + 15) & ~15;
+    const int bchunks = kpad / EPC;
+    for (int idx = threadIdx.x; idx < TM * bchunks; idx += LM_THREADS) {
+        const int r = idx / bchunks, c = idx - r * bchunks;
+        const int gr = t.row0 + r;
+        const bool ok = gr < t.out_f && (c * EPC) < kr;
+        const T* src = ok ? Bm + (size_t)gr * rank + k0 + c * EPC : Bm;
+        if (ASYNC) {
+            cp_async16(smem_u32(sB + b_off<T>(r, c)), src, ok ? 16 : 0);
+        } else {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (ok) v = *reinterpret_cast<const uint4*>(src);
+            *reinterpret_cast<uint4*>(sB + b_off<T>(r, c)) = v;
+        }
+    }
+    for (int idx = threadIdx.x; idx < kpad * W_CHUNKS_ROW; idx += LM_THREADS) {
+        const int r = idx / W_CHUNKS_ROW, c = idx - r * W_CHUNKS_ROW;
+        const int gc = t.col0 + c * EPC;
+        const bool ok = r < kr && gc < t.in_f;
+        const T* src = ok ? Am + (size_t)(k0 + r) * t.in_f + gc : Am;
+        if (ASYNC) {
+            cp_async16(smem_u32(sA + a_off<T>(r, c)), src, ok ? 16 : 0);
+        } else {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (ok) v = *reinterpret_cast<const uint4*>(src);
+            *reinterpret_cast<uint4*>(sA + a_off<T>(r, c)) = v;
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(LM_THREADS, 1) lora_merge_kernel(const katz_lora_layer* __restrict__ layers,
                                                                    const int* __restrict__ tile_start, int n_layers,
-                                                                   float sign) {
+                                                                   int total_tiles, float sign) {
     using Cfg = LmCfg<T>;
-    constexpr int TM = Cfg::TM;
+    constexpr int TM = Cfg::TM, NST = Cfg::NST;
     constexpr int ES = sizeof(T);
     constexpr int EPC = 16 / ES;                 // elements per 16-byte chunk
     constexpr int W_CHUNKS_ROW = LM_TN / EPC;    // 16 (fp16) / 32 (fp32)
+    constexpr int NF = ES == 2 ? 8 : 4;          // n-fragments per warp
     extern __shared__ __align__(128) unsigned char smem[];
-    unsigned char* sW = smem;
-    unsigned char* sB = smem + Cfg::W_BYTES;
-    unsigned char* sA = sB + Cfg::B_BYTES;
+    unsigned char* xB = smem + NST * Cfg::STAGE;           // side buffer for further adapters / rank chunks
+    unsigned char* xA = xB + Cfg::B_BYTES;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int li = find_layer(tile_start, n_layers, blockIdx.x);
-    const katz_lora_layer L = layers[li];
-    const int t = blockIdx.x - tile_start[li];
-    const int tiles_n = (L.in_features + LM_TN - 1) / LM_TN;
-    const int tm = t / tiles_n, tn = t - tm * tiles_n;
-    const int row0 = tm * TM, col0 = tn * LM_TN;
-    T* Wdst = reinterpret_cast<T*>(L.W);
-    const T* Wsrc = L.W0 ? reinterpret_cast<const T*>(L.W0) : Wdst;
-    const int out_f = L.out_features, in_f = L.in_features;
 
-    auto w_off = [&](int r, int c) -> uint32_t {
-        if constexpr (ES == 2) return r * 256 + ((c ^ (r & 7)) << 4);
-        else return r * 512 + ((c ^ ((r & 3) << 1)) << 4);
+    auto issue = [&](int j) {
+        const int tile = blockIdx.x + j * gridDim.x;
+        if (tile < total_tiles) {
+            unsigned char* sW = smem + (j % NST) * Cfg::STAGE;
+            const TileRef<T> t = decode_tile<T>(layers, tile_start, n_layers, tile);
+            const T* Wdst = reinterpret_cast<const T*>(t.L->W);
+            const T* Wsrc = t.L->W0 ? reinterpret_cast<const T*>(t.L->W0) : Wdst;
+            for (int idx = tid; idx < TM * W_CHUNKS_ROW; idx += LM_THREADS) {
+                const int r = idx / W_CHUNKS_ROW, c = idx - r * W_CHUNKS_ROW;
+                const int gr = t.row0 + r, gc = t.col0 + c * EPC;
+                const bool ok = gr < t.out_f && gc < t.in_f;
+                const T* src = ok ? Wsrc + (size_t)gr * t.in_f + gc : Wsrc;
+                cp_async16(smem_u32(sW + w_off<T>(r, c)), src, ok ? 16 : 0);
+            }
+            if (t.n_lora > 0) load_adapter_tiles<T, true>(t, 0, 0, sW + Cfg::W_BYTES, sW + Cfg::W_BYTES + Cfg::B_BYTES);
+        }
+        cp_async_commit();
     };
 
-    // ---- W tile in flight
-    for (int idx = tid; idx < TM * W_CHUNKS_ROW; idx += LM_THREADS) {
-        int r = idx / W_CHUNKS_ROW, c = idx - r * W_CHUNKS_ROW;
-        int gr = row0 + r, gc = col0 + c * EPC;
-        bool ok = gr < out_f && gc < in_f;
-        const T* src = ok ? Wsrc + (size_t)gr * in_f + gc : Wsrc;
-        cp_async16(smem_u32(sW + w_off(r, c)), src, ok ? 16 : 0);
-    }
-    cp_async_commit();
+#pragma unroll
+    for (int j = 0; j < NST - 1; ++j) issue(j);
 
-    for (int l = 0; l < L.n_lora; ++l) {
-        const T* Bm = reinterpret_cast<const T*>(L.B[l]);
-        const T* Am = reinterpret_cast<const T*>(L.A[l]);
-        const int rank = L.rank[l];
-        const float s = L.scale[l] * sign;
-        float acc[2][ES == 2 ? 8 : 4][4];
-#pragma unroll
-        for (int i = 0; i < 2; ++i)
-#pragma unroll
-            for (int j = 0; j < (ES == 2 ? 8 : 4); ++j)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+    for (int j = 0;; ++j) {
+        const int tile = blockIdx.x + j * gridDim.x;
+        if (tile >= total_tiles) break;
+        cp_async_wait<NST - 2>();
+        __syncthreads();               // stage j landed for everyone; everyone has finished with stage j-1
+        issue(j + NST - 1);            // refills the stage that tile j-1 used
 
-        for (int k0 = 0; k0 < rank; k0 += LM_MAXR) {
-            const int kr = min(LM_MAXR, rank - k0);   // multiple of 8 (checked on the host)
-            __syncthreads();                          // previous pass / LoRA done with sA, sB
-            // B tile: TM rows x kr ; A tile: kr rows x 128 cols. Unused k columns/rows are zero-filled up to 16.
-            const int kpad = (kr + 15) & ~15;
-            {
-                const int bchunks = kpad / EPC;
-                for (int idx = tid; idx < TM * bchunks; idx += LM_THREADS) {
-                    int r = idx / bchunks, c = idx - r * bchunks;
-                    int gr = row0 + r, gk = k0 + c * EPC;
-                    bool ok = gr < out_f && (c * EPC) < kr;
-                    const T* src = ok ? Bm + (size_t)gr * rank + gk : Bm;
-                    uint32_t off;
-                    if constexpr (ES == 2) off = r * 128 + ((c ^ (r & 7)) << 4);
-                    else off = (r * Cfg::BP + c * 4) * 4;
-                    cp_async16(smem_u32(sB + off), src, ok ? 16 : 0);
+        unsigned char* sW = smem + (j % NST) * Cfg::STAGE;
+        const TileRef<T> t = decode_tile<T>(layers, tile_start, n_layers, tile);
+
+        for (int l = 0; l < t.n_lora; ++l) {
+            const int rank = t.L->rank[l];
+            const float s = t.L->scale[l] * sign;
+            float acc[2][NF][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int jn = 0; jn < NF; ++jn)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[i][jn][e] = 0.f;
+
+            for (int k0 = 0; k0 < rank; k0 += LM_MAXR) {
+                const unsigned char* sB;
+                const unsigned char* sA;
+                if (l == 0 && k0 == 0) {
+                    sB = sW + Cfg::W_BYTES;
+                    sA = sB + Cfg::B_BYTES;
+                } else {
+                    __syncthreads();   // previous users of the side buffer are done
+                    load_adapter_tiles<T, false>(t, l, k0, xB, xA);
+                    __syncthreads();
+                    sB = xB;
+                    sA = xA;
                 }
-                for (int idx = tid; idx < kpad * W_CHUNKS_ROW; idx += LM_THREADS) {
-                    int r = idx / W_CHUNKS_ROW, c = idx - r * W_CHUNKS_ROW;
-                    int gc = col0 + c * EPC;
-                    bool ok = r < kr && gc < in_f;
-                    const T* src = ok ? Am + (size_t)(k0 + r) * in_f + gc : Am;
-                    uint32_t off;
-                    if constexpr (ES == 2) off = r * 256 + ((c ^ (r & 7)) << 4);
-                    else off = (r * Cfg::AP + c * 4) * 4;
-                    cp_async16(smem_u32(sA + off), src, ok ? 16 : 0);
-                }
-            }
-            cp_async_commit();
-            cp_async_wait<0>();
-            __syncthreads();
-
-            if constexpr (ES == 2) {
-                const int warp_m = warp & 3, warp_n = warp >> 2;   // 4 x 2 warps, warp tile 32 x 64
-                for (int ks = 0; ks < kpad / 16; ++ks) {
-                    uint32_t af[2][4];
-#pragma unroll
-                    for (int mf = 0; mf < 2; ++mf) {
-                        int r = warp_m * 32 + mf * 16 + (lane & 15);
-                        int ch = ks * 2 + (lane >> 4);
-                        ldmatrix_x4(af[mf][0], af[mf][1], af[mf][2], af[mf][3], smem_u32(sB + r * 128 + ((ch ^ (r & 7)) << 4)));
-                    }
-#pragma unroll
-                    for (int np = 0; np < 4; ++np) {
-                        uint32_t bf[4];
-                        int r = ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
-                        int ch = warp_n * 8 + np * 2 + (lane >> 4);
-                        ldmatrix_x4_trans(bf[0], bf[1], bf[2], bf[3], smem_u32(sA + r * 256 + ((ch ^ (r & 7)) << 4)));
+                const int kr = min(LM_MAXR, rank - k0);
+                const int kpad = (kr + 15) & ~15;
+                if constexpr (ES == 2) {
+                    const int warp_m = warp & 3, warp_n = warp >> 2;   // 4 x 2 warps, warp tile 32 x 64
+                    for (int ks = 0; ks < kpad / 16; ++ks) {
+                        uint32_t af[2][4];
 #pragma unroll
                         for (int mf = 0; mf < 2; ++mf) {
-                            mma_f16_16816(acc[mf][np * 2], af[mf], bf);
-                            mma_f16_16816(acc[mf][np * 2 + 1], af[mf], bf + 2);
+                            const int r = warp_m * 32 + mf * 16 + (lane & 15);
+                            const int ch = ks * 2 + (lane >> 4);
+                            ldmatrix_x4(af[mf][0], af[mf][1], af[mf][2], af[mf][3], smem_u32(sB + b_off<T>(r, ch)));
+                        }
+#pragma unroll
+                        for (int np = 0; np < 4; ++np) {
+                            uint32_t bf[4];
+                            const int r = ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+                            const int ch = warp_n * 8 + np * 2 + (lane >> 4);
+                            ldmatrix_x4_trans(bf[0], bf[1], bf[2], bf[3], smem_u32(sA + a_off<T>(r, ch)));
+#pragma unroll
+                            for (int mf = 0; mf < 2; ++mf) {
+                                mma_f16_16816(acc[mf][np * 2], af[mf], bf);
+                                mma_f16_16816(acc[mf][np * 2 + 1], af[mf], bf + 2);
+                            }
                         }
                     }
-                }
-            } else {
-                const int warp_m = warp & 1, warp_n = warp >> 1;   // 2 x 4 warps, warp tile 32 x 32
-                const float* fB = reinterpret_cast<const float*>(sB);
-                const float* fA = reinterpret_cast<const float*>(sA);
-                const int g = lane >> 2, q = lane & 3;
-                for (int ks = 0; ks < kpad / 8; ++ks) {
-                    uint32_t ahi[2][4], alo[2][4], bhi[4][2], blo[4][2];
+                } else {
+                    const int warp_m = warp & 1, warp_n = warp >> 1;   // 2 x 4 warps, warp tile 32 x 32
+                    const float* fB = reinterpret_cast<const float*>(sB);
+                    const float* fA = reinterpret_cast<const float*>(sA);
+                    const int g = lane >> 2, q = lane & 3;
+                    for (int ks = 0; ks < kpad / 8; ++ks) {
+                        uint32_t ahi[2][4], alo[2][4], bhi[4][2], blo[4][2];
 #pragma unroll
-                    for (int mf = 0; mf < 2; ++mf) {
-                        int r = warp_m * 32 + mf * 16 + g;
+                        for (int mf = 0; mf < 2; ++mf) {
+                            const int r = warp_m * 32 + mf * 16 + g;
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            float v = fB[(r + (e & 1) * 8) * Cfg::BP + ks * 8 + q + (e >> 1) * 4];
-                            ahi[mf][e] = f32_to_tf32(v);
-                            alo[mf][e] = f32_to_tf32(v - __uint_as_float(ahi[mf][e]));
+                            for (int e = 0; e < 4; ++e) {
+                                const float v = fB[(r + (e & 1) * 8) * Cfg::BP + ks * 8 + q + (e >> 1) * 4];
+                                ahi[mf][e] = f32_to_tf32(v);
+                                alo[mf][e] = f32_to_tf32(v - __uint_as_float(ahi[mf][e]));
+                            }
                         }
-                    }
-#pragma unroll
-                    for (int nf = 0; nf < 4; ++nf) {
-                        int n = warp_n * 32 + nf * 8 + g;
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            float v = fA[(ks * 8 + q + e * 4) * Cfg::AP + n];
-                            bhi[nf][e] = f32_to_tf32(v);
-                            blo[nf][e] = f32_to_tf32(v - __uint_as_float(bhi[nf][e]));
-                        }
-                    }
-#pragma unroll
-                    for (int mf = 0; mf < 2; ++mf)
 #pragma unroll
                         for (int nf = 0; nf < 4; ++nf) {
-                            mma_tf32_1688(acc[mf][nf], alo[mf], bhi[nf]);
-                            mma_tf32_1688(acc[mf][nf], ahi[mf], blo[nf]);
-                            mma_tf32_1688(acc[mf][nf], ahi[mf], bhi[nf]);
+                            const int n = warp_n * 32 + nf * 8 + g;
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const float v = fA[(ks * 8 + q + e * 4) * Cfg::AP + n];
+                                bhi[nf][e] = f32_to_tf32(v);
+                                blo[nf][e] = f32_to_tf32(v - __uint_as_float(bhi[nf][e]));
+                            }
                         }
+#pragma unroll
+                        for (int mf = 0; mf < 2; ++mf)
+#pragma unroll
+                            for (int nf = 0; nf < 4; ++nf) {
+                                mma_tf32_1688(acc[mf][nf], alo[mf], bhi[nf]);
+                                mma_tf32_1688(acc[mf][nf], ahi[mf], blo[nf]);
+                                mma_tf32_1688(acc[mf][nf], ahi[mf], bhi[nf]);
+                            }
+                    }
                 }
             }
-        }
 
-        // ---- fold this LoRA's delta into the W tile held in shared memory (each element has one owner thread)
-        if constexpr (ES == 2) {
-            const int warp_m = warp & 3, warp_n = warp >> 2;
+            // ---- fold this adapter's delta into the W tile held in shared memory (each element has one owner thread)
+            if constexpr (ES == 2) {
+                const int warp_m = warp & 3, warp_n = warp >> 2;
 #pragma unroll
-            for (int mf = 0; mf < 2; ++mf)
+                for (int mf = 0; mf < 2; ++mf)
 #pragma unroll
-                for (int hr = 0; hr < 2; ++hr) {
-                    int r = warp_m * 32 + mf * 16 + (lane >> 2) + hr * 8;
+                    for (int hr = 0; hr < 2; ++hr) {
+                        const int r = warp_m * 32 + mf * 16 + (lane >> 2) + hr * 8;
 #pragma unroll
-                    for (int nf = 0; nf < 8; ++nf) {
-                        int c = warp_n * 64 + nf * 8 + (lane & 3) * 2;
-                        __half2* wp = reinterpret_cast<__half2*>(sW + r * 256 + (((c >> 3) ^ (r & 7)) << 4) + (c & 7) * 2);
-                        float2 w = __half22float2(*wp);
-                        float d0 = __half2float(__float2half_rn(acc[mf][nf][hr * 2]));
-                        float d1 = __half2float(__float2half_rn(acc[mf][nf][hr * 2 + 1]));
-                        d0 = __half2float(__float2half_rn(d0 * s));
-                        d1 = __half2float(__float2half_rn(d1 * s));
-                        *wp = __floats2half2_rn(w.x + d0, w.y + d1);
+                        for (int nf = 0; nf < 8; ++nf) {
+                            const int c = warp_n * 64 + nf * 8 + (lane & 3) * 2;
+                            __half2* wp = reinterpret_cast<__half2*>(sW + w_off<T>(r, c >> 3) + (c & 7) * 2);
+                            const float2 w = __half22float2(*wp);
+                            float d0 = __half2float(__float2half_rn(acc[mf][nf][hr * 2]));
+                            float d1 = __half2float(__float2half_rn(acc[mf][nf][hr * 2 + 1]));
+                            d0 = __half2float(__float2half_rn(d0 * s));
+                            d1 = __half2float(__float2half_rn(d1 * s));
+                            *wp = __floats2half2_rn(w.x + d0, w.y + d1);
+                        }
                     }
-                }
-        } else {
-            const int warp_m = warp & 1, warp_n = warp >> 1;
+            } else {
+                const int warp_m = warp & 1, warp_n = warp >> 1;
 #pragma unroll
-            for (int mf = 0; mf < 2; ++mf)
+                for (int mf = 0; mf < 2; ++mf)
 #pragma unroll
-                for (int hr = 0; hr < 2; ++hr) {
-                    int r = warp_m * 32 + mf * 16 + (lane >> 2) + hr * 8;
+                    for (int hr = 0; hr < 2; ++hr) {
+                        const int r = warp_m * 32 + mf * 16 + (lane >> 2) + hr * 8;
 #pragma unroll
-                    for (int nf = 0; nf < 4; ++nf) {
-                        int c = warp_n * 32 + nf * 8 + (lane & 3) * 2;
-                        float2* wp = reinterpret_cast<float2*>(sW + r * 512 + (((c >> 2) ^ ((r & 3) << 1)) << 4) + (c & 3) * 4);
-                        float2 w = *wp;
-                        w.x = w.x + acc[mf][nf][hr * 2] * s;
-                        w.y = w.y + acc[mf][nf][hr * 2 + 1] * s;
-                        *wp = w;
+                        for (int nf = 0; nf < 4; ++nf) {
+                            const int c = warp_n * 32 + nf * 8 + (lane & 3) * 2;
+                            float2* wp = reinterpret_cast<float2*>(sW + w_off<T>(r, c >> 2) + (c & 3) * 4);
+                            float2 w = *wp;
+                            w.x = __fadd_rn(w.x, __fmul_rn(acc[mf][nf][hr * 2], s));
+                            w.y = __fadd_rn(w.y, __fmul_rn(acc[mf][nf][hr * 2 + 1], s));
+                            *wp = w;
+                        }
                     }
-                }
+            }
+        }
+        __syncthreads();
+
+        // ---- write-back, 16 bytes per thread, whole rows of the tile contiguous
+        T* Wdst = reinterpret_cast<T*>(t.L->W);
+        for (int idx = tid; idx < TM * W_CHUNKS_ROW; idx += LM_THREADS) {
+            const int r = idx / W_CHUNKS_ROW, c = idx - r * W_CHUNKS_ROW;
+            const int gr = t.row0 + r, gc = t.col0 + c * EPC;
+            if (gr < t.out_f && gc < t.in_f) {
+                const uint4 v = *reinterpret_cast<const uint4*>(sW + w_off<T>(r, c));
+                *reinterpret_cast<uint4*>(Wdst + (size_t)gr * t.in_f + gc) = v;
+            }
         }
     }
-    cp_async_wait<0>();   // covers n_lora == 0 (plain restore copy)
-    __syncthreads();
+    cp_async_wait<0>();
+}
 
-    // ---- coalesced write-back
-    for (int idx = tid; idx < TM * W_CHUNKS_ROW; idx += LM_THREADS) {
-        int r = idx / W_CHUNKS_ROW, c = idx - r * W_CHUNKS_ROW;
-        int gr = row0 + r, gc = col0 + c * EPC;
-        if (gr < out_f && gc < in_f) {
-            uint4 v = *reinterpret_cast<const uint4*>(sW + w_off(r, c));
-            *reinterpret_cast<uint4*>(Wdst + (size_t)gr * in_f + gc) = v;
-        }
+static int lm_sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
     }
+    return n;
 }
 
 }  // namespace katz
@@ -272,10 +359,11 @@ extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_til
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
+    const int grid = total_tiles < lm_sm_count() ? total_tiles : lm_sm_count();
     if (w_dtype == KATZ_DTYPE_F16)
-        lora_merge_kernel<__half><<<total_tiles, LM_THREADS, LmCfg<__half>::SMEM, st>>>(d_layers, d_tile_start, n_layers, sign);
+        lora_merge_kernel<__half><<<grid, LM_THREADS, LmCfg<__half>::SMEM, st>>>(d_layers, d_tile_start, n_layers, total_tiles, sign);
     else
-        lora_merge_kernel<float><<<total_tiles, LM_THREADS, LmCfg<float>::SMEM, st>>>(d_layers, d_tile_start, n_layers, sign);
+        lora_merge_kernel<float><<<grid, LM_THREADS, LmCfg<float>::SMEM, st>>>(d_layers, d_tile_start, n_layers, total_tiles, sign);
     KATZ_LAUNCH_RET();
 }
 
