@@ -18,14 +18,11 @@ constexpr int GN_MAXG = 64;
 
 __global__ void __launch_bounds__(GN_THREADS) gn_stats_nhwc_kernel(const __half* __restrict__ x, float* __restrict__ partial,
                                                                    int HW, int C, int G, int rows_per_slab) {
-    __shared__ float s_sum[GN_MAXG], s_sq[GN_MAXG];
+    // per-thread partials parked in shared memory and summed per group in a FIXED order: the statistics, and with them
+    // every GroupNorm output, are bit-reproducible from run to run (no floating-point atomics)
+    __shared__ float2 s_part[GN_MAXP][GN_THREADS];
     const int slab = blockIdx.x, b = blockIdx.y, nslab = gridDim.x;
     const int tid = threadIdx.x;
-    if (tid < G) {
-        s_sum[tid] = 0.f;
-        s_sq[tid] = 0.f;
-    }
-    __syncthreads();
     const int CP = C >> 1, cpg = C / G;
     const int r0 = slab * rows_per_slab;
     const int r1 = min(HW, r0 + rows_per_slab);
@@ -46,19 +43,19 @@ __global__ void __launch_bounds__(GN_THREADS) gn_stats_nhwc_kernel(const __half*
         }
     }
 #pragma unroll
-    for (int i = 0; i < GN_MAXP; ++i) {
-        int cp = tid + i * GN_THREADS;
-        if (cp < CP) {
-            int g = (cp * 2) / cpg;
-            atomicAdd(&s_sum[g], sum[i]);
-            atomicAdd(&s_sq[g], sq[i]);
-        }
-    }
+    for (int i = 0; i < GN_MAXP; ++i) s_part[i][tid] = make_float2(sum[i], sq[i]);
     __syncthreads();
     if (tid < G) {
+        const int cp0 = tid * (cpg >> 1), cp1 = cp0 + (cpg >> 1);
+        float s = 0.f, q = 0.f;
+        for (int cp = cp0; cp < cp1; ++cp) {
+            const float2 v = s_part[cp / GN_THREADS][cp % GN_THREADS];
+            s += v.x;
+            q += v.y;
+        }
         float* o = partial + (((size_t)b * nslab + slab) * G + tid) * 2;
-        o[0] = s_sum[tid];
-        o[1] = s_sq[tid];
+        o[0] = s;
+        o[1] = q;
     }
 }
 
@@ -120,6 +117,135 @@ __global__ void __launch_bounds__(GN_THREADS) gn_apply_nhwc_kernel(const __half*
             }
         }
     }
+}
+
+// ---- 16-byte vectorised NHWC kernels (C % 8 == 0). Thread = (row lane, 8-channel chunk): the chunk stays fixed while
+// the thread walks rows, so per-channel accumulators (stats) or per-channel scale/shift (apply) live in registers and
+// every global access is a full 16-byte load or store with several rows in flight per thread.
+__global__ void gn_stats_v8_kernel(const __half* __restrict__ x, float* __restrict__ partial, int HW, int C, int G,
+                                   int rows_per_slab, int R) {
+    extern __shared__ float s_dyn[];    // [blockDim][16]: 8 channel sums then 8 channel sums of squares
+    const int slab = blockIdx.x, b = blockIdx.y, nslab = gridDim.x;
+    const int NC = C >> 3, cpg = C / G;
+    const int tid = threadIdx.x;
+    const int cc = tid % NC, rl = tid / NC;
+    const int r0 = slab * rows_per_slab, r1 = min(HW, r0 + rows_per_slab);
+    float sm[8], sq[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sm[e] = sq[e] = 0.f;
+    const uint4* xb = reinterpret_cast<const uint4*>(x) + (size_t)b * HW * NC + cc;
+    int r = r0 + rl;
+    for (; r + 3 * R < r1; r += 4 * R) {
+        uint4 u[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) u[k] = xb[(size_t)(r + k * R) * NC];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t w[4] = {u[k].x, u[k].y, u[k].z, u[k].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = unpack_half2(w[e]);
+                sm[2 * e] += f.x; sq[2 * e] += f.x * f.x;
+                sm[2 * e + 1] += f.y; sq[2 * e + 1] += f.y * f.y;
+            }
+        }
+    }
+    for (; r < r1; r += R) {
+        const uint4 u = xb[(size_t)r * NC];
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack_half2(w[e]);
+            sm[2 * e] += f.x; sq[2 * e] += f.x * f.x;
+            sm[2 * e + 1] += f.y; sq[2 * e + 1] += f.y * f.y;
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        s_dyn[tid * 16 + e] = sm[e];
+        s_dyn[tid * 16 + 8 + e] = sq[e];
+    }
+    __syncthreads();
+    if (tid < G) {
+        // fixed summation order: channels of the group, then row lanes -> bit-reproducible statistics
+        float s = 0.f, q = 0.f;
+        for (int c = tid * cpg; c < (tid + 1) * cpg; ++c) {
+            const int ch = c >> 3, e = c & 7;
+            for (int l = 0; l < R; ++l) {
+                s += s_dyn[(l * NC + ch) * 16 + e];
+                q += s_dyn[(l * NC + ch) * 16 + 8 + e];
+            }
+        }
+        float* o = partial + (((size_t)b * nslab + slab) * G + tid) * 2;
+        o[0] = s;
+        o[1] = q;
+    }
+}
+
+__global__ void gn_apply_v8_kernel(const __half* __restrict__ x, __half* __restrict__ y, const float* __restrict__ partial,
+                                   int nslab_stats, const __half* __restrict__ gamma, const __half* __restrict__ beta, int HW,
+                                   int C, int G, int rows_per_slab, int R, double n_total, float eps, int act) {
+    extern __shared__ float s_dyn[];    // [C] scale, [C] shift
+    __shared__ float s_mean[GN_MAXG], s_rstd[GN_MAXG];
+    const int slab = blockIdx.x, b = blockIdx.y;
+    const int NC = C >> 3, cpg = C / G;
+    const int tid = threadIdx.x;
+    if (tid < G) {
+        double s = 0.0, q = 0.0;
+        const float* pp = partial + ((size_t)b * nslab_stats * G + tid) * 2;
+        for (int i = 0; i < nslab_stats; ++i) {
+            s += (double)pp[(size_t)i * G * 2];
+            q += (double)pp[(size_t)i * G * 2 + 1];
+        }
+        const double mean = s / n_total;
+        double var = q / n_total - mean * mean;
+        if (var < 0.0) var = 0.0;
+        s_mean[tid] = (float)mean;
+        s_rstd[tid] = (float)(1.0 / sqrt(var + (double)eps));
+    }
+    __syncthreads();
+    for (int c = tid; c < C; c += blockDim.x) {
+        const int g = c / cpg;
+        const float ga = gamma ? __half2float(gamma[c]) : 1.f, be = beta ? __half2float(beta[c]) : 0.f;
+        const float sc = s_rstd[g] * ga;
+        s_dyn[c] = sc;
+        s_dyn[C + c] = be - s_mean[g] * sc;
+    }
+    __syncthreads();
+    const int cc = tid % NC, rl = tid / NC;
+    float sc[8], sh[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        sc[e] = s_dyn[cc * 8 + e];
+        sh[e] = s_dyn[C + cc * 8 + e];
+    }
+    const int r0 = slab * rows_per_slab, r1 = min(HW, r0 + rows_per_slab);
+    const uint4* xb = reinterpret_cast<const uint4*>(x) + (size_t)b * HW * NC + cc;
+    uint4* yb = reinterpret_cast<uint4*>(y) + (size_t)b * HW * NC + cc;
+    auto norm8 = [&](const uint4& u) -> uint4 {
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack_half2(w[e]);
+            float a0 = f.x * sc[2 * e] + sh[2 * e], a1 = f.y * sc[2 * e + 1] + sh[2 * e + 1];
+            if (act == 1) {
+                a0 = silu_f(a0);
+                a1 = silu_f(a1);
+            }
+            o[e] = pack_half2(a0, a1);
+        }
+        return make_uint4(o[0], o[1], o[2], o[3]);
+    };
+    int r = r0 + rl;
+    for (; r + 3 * R < r1; r += 4 * R) {
+        uint4 u[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) u[k] = xb[(size_t)(r + k * R) * NC];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) yb[(size_t)(r + k * R) * NC] = norm8(u[k]);
+    }
+    for (; r < r1; r += R) yb[(size_t)r * NC] = norm8(xb[(size_t)r * NC]);
 }
 
 // Channels-first variant: each (batch, group) is one contiguous run of (C/G)*HW values.
@@ -264,6 +390,22 @@ extern "C" int katz_group_norm_nhwc_f16(const void* x, void* y, const void* gamm
     const int nslab = ceil_div(HW, rows);
     dim3 grid(nslab, B);
     cudaStream_t st = (cudaStream_t)stream;
+    const int NC = C / 8;
+    if (C % 8 == 0 && NC <= 1024 && aligned16(x) && aligned16(y)) {
+        const int R = NC >= 256 ? 1 : 256 / NC;
+        const int threads = NC * R;
+        static bool attr = false;
+        if (!attr) {
+            cudaFuncSetAttribute(gn_stats_v8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 * 64);
+            cudaFuncSetAttribute(gn_apply_v8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 8192 * 4);
+            attr = true;
+        }
+        gn_stats_v8_kernel<<<grid, threads, threads * 64, st>>>((const __half*)x, (float*)scratch, HW, C, G, rows, R);
+        gn_apply_v8_kernel<<<grid, threads, 2 * C * 4, st>>>((const __half*)x, (__half*)y, (const float*)scratch, nslab,
+                                                             (const __half*)gamma, (const __half*)beta, HW, C, G, rows, R,
+                                                             (double)HW * (C / G), eps, act);
+        KATZ_LAUNCH_RET();
+    }
     gn_stats_nhwc_kernel<<<grid, GN_THREADS, 0, st>>>((const __half*)x, (float*)scratch, HW, C, G, rows);
     gn_apply_nhwc_kernel<<<grid, GN_THREADS, 0, st>>>((const __half*)x, (__half*)y, (const float*)scratch, nslab,
                                                       (const __half*)gamma, (const __half*)beta, HW, C, G, rows, eps, act);
