@@ -65,9 +65,11 @@ int katz_lora_layer_check(const katz_lora_layer* h_layer, int w_dtype);
  * Replaces lora_utils.patch_on_lora's loop (lora_utils.py:28-33), StableDiffusionXLControlNetPipelineKatz.patch_on_lora
  * (pipelines/controlnet/pipeline_controlnet_sd_xl_katz.py:1741-1747) and, with n_lora = 0 and W0 set, the restore
  * `unet.load_state_dict(deepcopy(default_unet_state_dict))` (sdxl_unet_server.py:217). sign = -1 with W0 = NULL is the
- * subtractive unmerge of LoRACompatibleLinear._unfuse_lora (diffusers/models/lora.py:427-449). */
+ * subtractive unmerge of LoRACompatibleLinear._unfuse_lora (diffusers/models/lora.py:427-449).
+ * `max_tiles_per_layer` (the largest per-layer tile count, or 0 if unknown) lets the kernel keep the tile -> layer table
+ * in shared memory. */
 int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_tile_start, int n_layers, int total_tiles, int w_dtype,
-                    float sign, void* stream);
+                    float sign, int max_tiles_per_layer, void* stream);
 
 /* -------------------------------------------------------------------------------------- fast_kernel drop-ins ---- */
 /* fast_kernel::group_norm_fp16 (fast_kernel/csrc/group_norm.cuh:7-15, group_norm.cu:224-274), channels-last input.
@@ -75,6 +77,13 @@ int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_tile_start, in
 long long katz_group_norm_scratch_bytes(int B, int HW, int C, int G);
 int katz_group_norm_nhwc_f16(const void* x, void* y, const void* gamma, const void* beta, int B, int HW, int C, int G,
                              float eps, int act, void* scratch, long long scratch_bytes, void* stream);
+/* The same GroupNorm in two halves, for a tensor that is row-split across GPUs: `stats` leaves the shard's
+ * (sum, sum of squares) per (batch, group) as fp64 in sums[B, G, 2]; the caller sums those across ranks; `apply`
+ * normalises the shard with the global sums and n_total = (total rows) * (C / G). Needs C % 8 == 0. */
+int katz_group_norm_stats_nhwc_f16(const void* x, double* sums, int B, int HW, int C, int G, void* scratch,
+                                   long long scratch_bytes, void* stream);
+int katz_group_norm_apply_nhwc_f16(const void* x, void* y, const double* sums, const void* gamma, const void* beta, int B,
+                                   int HW, int C, int G, double n_total, float eps, int act, void* stream);
 /* Same op for a channels-first tensor (the `channels_first` branch of group_norm.cu:162-206). */
 int katz_group_norm_nchw_f16(const void* x, void* y, const void* gamma, const void* beta, int B, int HW, int C, int G,
                              float eps, int act, void* stream);
@@ -110,9 +119,10 @@ int katz_linear_f16(const void* A, int lda, const void* W, void* C, int ldc, int
 int katz_linear_geglu_f16(const void* A, int lda, const void* W, void* C, int ldc, int M, int F, int K, const void* bias,
                           void* stream);
 /* 3x3, stride 1, padding 1 NHWC convolution on the tcgen05 path (nn.Conv2d of ResnetBlock2D, resnet.py:378,408).
- * X[B,H,W,Cin], W[Cout,3,3,Cin], Y[B,H,W,Cout]; needs Cin % 64 == 0, Cout % 8 == 0 and W a power of two >= 8 or a
+ * X[B,Hin,W,Cin], W[Cout,3,3,Cin], Y[B,Hout,W,Cout] with Hout = Hin + 2*pad_h - 2: pad_h = 1 is the usual padding,
+ * pad_h = 0 is for a row shard whose input already carries its halo rows (latent-row parallelism). Needs Cin % 64 == 0, Cout % 8 == 0 and W a power of two >= 8 or a
  * multiple of 128. Epilogue as katz_conv2d_nhwc_f16_mma. */
-int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int B, int H, int Wd, int Cin, int Cout,
+int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int B, int Hin, int Wd, int Cin, int Cout, int pad_h,
                           const void* bias, const void* rowvec, int ld_rowvec, const void* residual, int act,
                           float out_scale, void* stream);
 /* Status word of the tcgen05 kernels: 0, or which bounded device-side wait gave up (1 producer, 2 MMA issuer,
@@ -128,16 +138,19 @@ int katz_upsample_nearest2x_nhwc_f16(const void* x, void* y, int B, int H, int W
  * Hin, Win are the upsampled sizes. Epilogue as katz_linear_f16 with rows_per_batch = Hout*Wout (the time-embedding
  * add of ResnetBlock2D, resnet.py:381-390, and its shortcut add, resnet.py:410-413). */
 int katz_conv2d_nhwc_f16_mma(const void* X, const void* X2, const void* W, void* Y, int B, int Hin, int Win, int C1,
-                             int C2, int Cout, int ksize, int stride, int pad, int upsample, const void* bias,
+                             int C2, int Cout, int ksize, int stride, int pad_h, int pad_w, int upsample, const void* bias,
                              const void* rowvec, int ld_rowvec, const void* residual, int act, float out_scale,
                              void* stream);
 
 /* softmax(Q K^T * scale) V per (batch, head), head_dim 64, no mask (F.scaled_dot_product_attention as called at
  * attention_processor.py:1276). Q/K/V/O are [B, S, ld*] token-major with head h at columns [64h, 64h+64);
- * bs* are batch strides in elements. */
+ * bs* are batch strides in elements. With 0 < kv_chunk_rows < Sk (a multiple of 64) key/value row j is read from
+ * chunk j / kv_chunk_rows at element offset chunk * kv_chunk_stride: the layout an all-gather of per-rank K/V shards
+ * leaves when the latent is row-split; 0 means one contiguous run. */
 int katz_attention_f16_mma(const void* Q, const void* K, const void* V, void* O, int B, int H, int Sq, int Sk,
                            int head_dim, int ldq, int ldk, int ldv, int ldo, long long bsq, long long bsk,
-                           long long bsv, long long bso, float scale, void* stream);
+                           long long bsv, long long bso, float scale, int kv_chunk_rows, long long kv_chunk_stride,
+                           void* stream);
 
 /* dst = src + half(sum_i scales[i] * residuals[i]) — ControlNet residual intake (unet_2d_condition.py:1281-1292; the
  * sum / mean over nets of :1418-1439). `h_residuals` and `h_scales` are HOST arrays of n_res entries (device pointers

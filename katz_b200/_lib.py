@@ -53,9 +53,11 @@ SIGNATURES = {
     "katz_lora_tile_rows": (_I, [_I]),
     "katz_lora_tile_cols": (_I, []),
     "katz_lora_layer_check": (_I, [POINTER(LoraLayer), _I]),
-    "katz_lora_merge": (_I, [_V, _V, _I, _I, _I, _F, _V]),
+    "katz_lora_merge": (_I, [_V, _V, _I, _I, _I, _F, _I, _V]),
     "katz_group_norm_scratch_bytes": (_L, [_I, _I, _I, _I]),
     "katz_group_norm_nhwc_f16": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _F, _I, _V, _L, _V]),
+    "katz_group_norm_stats_nhwc_f16": (_I, [_V, _V, _I, _I, _I, _I, _V, _L, _V]),
+    "katz_group_norm_apply_nhwc_f16": (_I, [_V, _V, _V, _V, _V, _I, _I, _I, _I, ctypes.c_double, _F, _I, _V]),
     "katz_group_norm_nchw_f16": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _F, _I, _V]),
     "katz_fast_gelu_mul_f16": (_I, [_V, _V, _V, _L, _V]),
     "katz_layer_norm_f16": (_I, [_V, _V, _V, _V, _I, _I, _F, _V]),
@@ -63,12 +65,12 @@ SIGNATURES = {
     "katz_linear_f16_mma": (_I, [_V, _I, _V, _V, _I, _I, _I, _I, _V, _V, _I, _I, _V, _I, _I, _F, _V]),
     "katz_linear_f16": (_I, [_V, _I, _V, _V, _I, _I, _I, _I, _V, _V, _I, _I, _V, _I, _I, _F, _V]),
     "katz_linear_geglu_f16": (_I, [_V, _I, _V, _V, _I, _I, _I, _I, _V, _V]),
-    "katz_conv3x3_nhwc_f16": (_I, [_V, _V, _V, _I, _I, _I, _I, _I, _V, _V, _I, _V, _I, _F, _V]),
+    "katz_conv3x3_nhwc_f16": (_I, [_V, _V, _V, _I, _I, _I, _I, _I, _I, _V, _V, _I, _V, _I, _F, _V]),
     "katz_tc05_status": (_I, []),
     "katz_tc05_clear_status": (_I, []),
     "katz_upsample_nearest2x_nhwc_f16": (_I, [_V, _V, _I, _I, _I, _I, _V]),
-    "katz_conv2d_nhwc_f16_mma": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _V, _V, _I, _V, _I, _F, _V]),
-    "katz_attention_f16_mma": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _V]),
+    "katz_conv2d_nhwc_f16_mma": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _V, _V, _I, _V, _I, _F, _V]),
+    "katz_attention_f16_mma": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _L, _V]),
     "katz_residual_intake_f16": (_I, [_V, _V, POINTER(c_void_p), POINTER(c_float), _I, _L, _V]),
     "katz_timestep_embedding_f16": (_I, [_V, _V, _I, _I, _I, _V]),
     "katz_silu_f16": (_I, [_V, _V, _L, _V]),
@@ -114,7 +116,7 @@ def check(code, what):
 
 
 # kernels launched per successful entry-point call (everything else launches one)
-_KERNELS_PER_CALL = {"katz_group_norm_nhwc_f16": 2}
+_KERNELS_PER_CALL = {"katz_group_norm_nhwc_f16": 2, "katz_group_norm_stats_nhwc_f16": 2}
 _launches = 0
 
 

@@ -18,7 +18,8 @@ __global__ void __launch_bounds__(ATHREADS) attention_d64_kernel(const __half* _
                                                                  const __half* __restrict__ V, __half* __restrict__ O,
                                                                  int Sq, int Sk, int ldq, int ldk, int ldv, int ldo,
                                                                  long long bsq, long long bsk, long long bsv,
-                                                                 long long bso, float scale_log2e) {
+                                                                 long long bso, float scale_log2e, int kv_chunk_rows,
+                                                                 long long kv_chunk_stride) {
     __shared__ __align__(128) unsigned char sQ[ABM * 128];
     __shared__ __align__(128) unsigned char sK[2][ABN * 128];
     __shared__ __align__(128) unsigned char sV[2][ABN * 128];
@@ -45,8 +46,16 @@ __global__ void __launch_bounds__(ATHREADS) attention_d64_kernel(const __half* _
     load_tile(sQ, Qb, q0, Sq, ldq);
     cp_async_commit();
     const int NT = ceil_div(Sk, ABN);
-    load_tile(sK[0], Kb, 0, Sk, ldk);
-    load_tile(sV[0], Vb, 0, Sk, ldv);
+    // K/V may arrive as equal chunks of rows that are not adjacent in memory (one chunk per rank after an all-gather):
+    // key row j lives at chunk (j / kv_chunk_rows), row (j % kv_chunk_rows); chunks are multiples of the 64-row tile.
+    auto load_kv = [&](int buf, int row0) {
+        const int chunk = row0 / kv_chunk_rows;
+        const long long shift = (long long)chunk * kv_chunk_stride - (long long)chunk * kv_chunk_rows * ldk;
+        const long long shiftv = (long long)chunk * kv_chunk_stride - (long long)chunk * kv_chunk_rows * ldv;
+        load_tile(sK[buf], Kb + shift, row0, Sk, ldk);
+        load_tile(sV[buf], Vb + shiftv, row0, Sk, ldv);
+    };
+    load_kv(0, 0);
     cp_async_commit();
 
     float o[8][4];
@@ -59,8 +68,7 @@ __global__ void __launch_bounds__(ATHREADS) attention_d64_kernel(const __half* _
 
     for (int t = 0; t < NT; ++t) {
         if (t + 1 < NT) {
-            load_tile(sK[(t + 1) & 1], Kb, (t + 1) * ABN, Sk, ldk);
-            load_tile(sV[(t + 1) & 1], Vb, (t + 1) * ABN, Sk, ldv);
+            load_kv((t + 1) & 1, (t + 1) * ABN);
         }
         cp_async_commit();
         cp_async_wait<1>();
@@ -178,7 +186,8 @@ using namespace katz;
 
 extern "C" int katz_attention_f16_mma(const void* Q, const void* K, const void* V, void* O, int B, int H, int Sq, int Sk,
                                       int head_dim, int ldq, int ldk, int ldv, int ldo, long long bsq, long long bsk,
-                                      long long bsv, long long bso, float scale, void* stream) {
+                                      long long bsv, long long bso, float scale, int kv_chunk_rows,
+                                      long long kv_chunk_stride, void* stream) {
     KATZ_CHECK_ARG(Q && K && V && O, KATZ_EINVAL);
     KATZ_CHECK_ARG(head_dim == 64, KATZ_ESIZE);
     KATZ_CHECK_ARG(B > 0 && H > 0 && Sq > 0 && Sk > 0, KATZ_ESIZE);
@@ -186,9 +195,15 @@ extern "C" int katz_attention_f16_mma(const void* Q, const void* K, const void* 
     KATZ_CHECK_ARG(ldq % 8 == 0 && ldk % 8 == 0 && ldv % 8 == 0 && ldo % 2 == 0, KATZ_EALIGN);
     KATZ_CHECK_ARG(bsq % 8 == 0 && bsk % 8 == 0 && bsv % 8 == 0 && bso % 2 == 0, KATZ_EALIGN);
     KATZ_CHECK_ARG(aligned16(Q) && aligned16(K) && aligned16(V) && ((uintptr_t)O & 3) == 0, KATZ_EALIGN);
+    if (kv_chunk_rows <= 0 || kv_chunk_rows >= Sk) {
+        kv_chunk_rows = Sk > 0 ? ((Sk + ABN - 1) / ABN) * ABN : ABN;   // one chunk
+        kv_chunk_stride = 0;
+    } else {
+        KATZ_CHECK_ARG(kv_chunk_rows % ABN == 0 && kv_chunk_stride % 8 == 0, KATZ_ESIZE);
+    }
     dim3 grid(ceil_div(Sq, ABM), H, B);
     attention_d64_kernel<<<grid, ATHREADS, 0, (cudaStream_t)stream>>>(
         (const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, Sq, Sk, ldq, ldk, ldv, ldo, bsq, bsk, bsv, bso,
-        scale * 1.44269504088896340736f);
+        scale * 1.44269504088896340736f, kv_chunk_rows, kv_chunk_stride);
     KATZ_LAUNCH_RET();
 }

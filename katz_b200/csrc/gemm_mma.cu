@@ -27,7 +27,7 @@ struct IgemmParams {
     int M, N, K;
     int lda, ldc, ldr, ld_rowvec, rows_per_batch;
     // conv geometry (logical input Hin x Win is the post-upsample size)
-    int Hin, Win, C1, C2, Hout, Wout, ksize, stride, pad, upsample;
+    int Hin, Win, C1, C2, Hout, Wout, ksize, stride, pad_h, pad_w, upsample;
     int act;
     float out_scale;
 };
@@ -92,8 +92,8 @@ __global__ void __launch_bounds__(NTHREADS) igemm_kernel(const IgemmParams p) {
                 int bytes = 0;
                 if (k_ok && a_ok[i]) {
                     if (CONV) {
-                        int iy = a_oy[i] * p.stride - p.pad + ky;
-                        int ix = a_ox[i] * p.stride - p.pad + kx;
+                        int iy = a_oy[i] * p.stride - p.pad_h + ky;
+                        int ix = a_ox[i] * p.stride - p.pad_w + kx;
                         if (iy >= 0 && iy < p.Hin && ix >= 0 && ix < p.Win) {
                             if (p.upsample) {
                                 iy >>= 1;
@@ -263,7 +263,7 @@ extern "C" int katz_linear_f16_mma(const void* A, int lda, const void* W, void* 
 }
 
 extern "C" int katz_conv2d_nhwc_f16_mma(const void* X, const void* X2, const void* W, void* Y, int B, int Hin, int Win,
-                                        int C1, int C2, int Cout, int ksize, int stride, int pad, int upsample,
+                                        int C1, int C2, int Cout, int ksize, int stride, int pad_h, int pad_w, int upsample,
                                         const void* bias, const void* rowvec, int ld_rowvec, const void* residual,
                                         int act, float out_scale, void* stream) {
     KATZ_CHECK_ARG(X && W && Y, KATZ_EINVAL);
@@ -271,7 +271,7 @@ extern "C" int katz_conv2d_nhwc_f16_mma(const void* X, const void* X2, const voi
     KATZ_CHECK_ARG(C2 == 0 || X2, KATZ_EINVAL);
     KATZ_CHECK_ARG(C1 % 8 == 0 && C2 % 8 == 0, KATZ_EALIGN);
     KATZ_CHECK_ARG(aligned16(X) && aligned16(W) && (!X2 || aligned16(X2)), KATZ_EALIGN);
-    KATZ_CHECK_ARG(ksize >= 1 && stride >= 1 && pad >= 0, KATZ_EINVAL);
+    KATZ_CHECK_ARG(ksize >= 1 && stride >= 1 && pad_h >= 0 && pad_w >= 0, KATZ_EINVAL);
     KATZ_CHECK_ARG(!upsample || (Hin % 2 == 0 && Win % 2 == 0), KATZ_EINVAL);
     IgemmParams p{};
     p.A = (const __half*)X;
@@ -282,9 +282,9 @@ extern "C" int katz_conv2d_nhwc_f16_mma(const void* X, const void* X2, const voi
     p.rowvec = (const __half*)rowvec;
     p.residual = (const __half*)residual;
     p.Hin = Hin; p.Win = Win; p.C1 = C1; p.C2 = C2;
-    p.ksize = ksize; p.stride = stride; p.pad = pad; p.upsample = upsample;
-    p.Hout = (Hin + 2 * pad - ksize) / stride + 1;
-    p.Wout = (Win + 2 * pad - ksize) / stride + 1;
+    p.ksize = ksize; p.stride = stride; p.pad_h = pad_h; p.pad_w = pad_w; p.upsample = upsample;
+    p.Hout = (Hin + 2 * pad_h - ksize) / stride + 1;
+    p.Wout = (Win + 2 * pad_w - ksize) / stride + 1;
     KATZ_CHECK_ARG(p.Hout > 0 && p.Wout > 0, KATZ_ESIZE);
     long long M = (long long)B * p.Hout * p.Wout;
     KATZ_CHECK_ARG(M < (1ll << 31), KATZ_ESIZE);

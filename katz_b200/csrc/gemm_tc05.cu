@@ -43,7 +43,7 @@ struct Tc05Params {
     int m_tiles, n_tiles;
     int geglu_F;            // > 0: GEGLU mode, weight has 2F rows
     // convolution geometry (stride 1, output size = input size)
-    int conv, H, W, TW, TH, tiles_w, tiles_h, cin_chunks, ksize, pad;
+    int conv, H, W, TW, TH, tiles_w, tiles_h, cin_chunks, ksize, pad_h, pad_w;   // H, W: OUTPUT size
     int* status;
 };
 
@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                         const int tap = kt / p.cin_chunks;
                         const int cc = kt - tap * p.cin_chunks;
                         const int ky = tap / p.ksize, kx = tap - ky * p.ksize;
-                        tma_load_4d(sa, &tmA, cc * TBK, cw0 + kx - p.pad, ch0 + ky - p.pad, cb, fb);
+                        tma_load_4d(sa, &tmA, cc * TBK, cw0 + kx - p.pad_w, ch0 + ky - p.pad_h, cb, fb);
                     } else {
                         tma_load_2d(sa, &tmA, kt * TBK, m0, fb);
                     }
@@ -491,11 +491,14 @@ extern "C" int katz_linear_geglu_f16(const void* A, int lda, const void* W, void
     return linear_common(A, lda, W, C, ldc, M, F, K, bias, nullptr, 0, 0, nullptr, 0, 0, 1.0f, F, stream);
 }
 
-extern "C" int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int B, int H, int Wd, int Cin, int Cout,
-                                     const void* bias, const void* rowvec, int ld_rowvec, const void* residual, int act,
+extern "C" int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int B, int Hin, int Wd, int Cin, int Cout,
+                                     int pad_h, const void* bias, const void* rowvec, int ld_rowvec, const void* residual, int act,
                                      float out_scale, void* stream) {
     KATZ_CHECK_ARG(X && W && Y, KATZ_EINVAL);
-    KATZ_CHECK_ARG(B > 0 && H > 0 && Wd > 0 && Cin > 0 && Cout > 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(B > 0 && Hin > 0 && Wd > 0 && Cin > 0 && Cout > 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(pad_h == 0 || pad_h == 1, KATZ_EINVAL);
+    const int H = Hin + 2 * pad_h - 2;   // output rows
+    KATZ_CHECK_ARG(H > 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(Cin % TBK == 0 && Cout % 8 == 0, KATZ_ESIZE);
     const int TW = Wd < 128 ? Wd : 128;
     KATZ_CHECK_ARG((TW & (TW - 1)) == 0 && TW >= 8 && Wd % TW == 0, KATZ_ESIZE);
@@ -505,14 +508,14 @@ extern "C" int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int 
     KATZ_CHECK_ARG(!rowvec || (((uintptr_t)rowvec & 7) == 0 && ld_rowvec % 4 == 0), KATZ_EALIGN);
     KATZ_CHECK_ARG(!residual || ((uintptr_t)residual & 7) == 0, KATZ_EALIGN);
     CUtensorMap ta, tb;
-    int rc = encode_nhwc(&ta, X, B, H, Wd, Cin, TW, TH);
+    int rc = encode_nhwc(&ta, X, B, Hin, Wd, Cin, TW, TH);
     if (rc) return rc;
     Tc05Params p{};
     p.C = (__half*)Y; p.bias = (const __half*)bias; p.rowvec = (const __half*)rowvec; p.residual = (const __half*)residual;
     p.M = B * H * Wd; p.N = Cout; p.K = 9 * Cin; p.ldc = Cout; p.ldr = Cout; p.ld_rowvec = ld_rowvec; p.rows_per_batch = H * Wd;
     p.act = act; p.out_scale = out_scale;
     p.conv = 1; p.H = H; p.W = Wd; p.TW = TW; p.TH = TH; p.tiles_w = Wd / TW; p.tiles_h = ceil_div(H, TH);
-    p.cin_chunks = Cin / TBK; p.ksize = 3; p.pad = 1;
+    p.cin_chunks = Cin / TBK; p.ksize = 3; p.pad_h = pad_h; p.pad_w = 1;
     p.m_tiles = B * p.tiles_w * p.tiles_h;
     const int bn = pick_bn(p.m_tiles, Cout, false);
     p.n_tiles = ceil_div(Cout, bn);

@@ -23,6 +23,7 @@ namespace katz {
 constexpr int LM_THREADS = 256;
 constexpr int LM_TN = 128;        // tile columns
 constexpr int LM_MAXR = 64;       // rank processed per pass; larger ranks loop
+constexpr int LM_MAX_LAYERS_SMEM = 1024;   // per-layer tile counts cached in shared memory up to this many layers
 
 template <typename T>
 struct LmCfg;
@@ -61,19 +62,23 @@ __device__ __forceinline__ int find_layer(const int* __restrict__ tile_start, in
 template <typename T>
 struct TileRef {
     const katz_lora_layer* L;
-    int row0, col0, out_f, in_f, n_lora;
+    T* W;
+    int row0, col0, out_f, in_f, n_lora, rank0;
+    float scale0;
 };
 
 template <typename T>
-__device__ __forceinline__ TileRef<T> decode_tile(const katz_lora_layer* __restrict__ layers, const int* __restrict__ tile_start,
-                                                  int n_layers, int tile) {
+__device__ __forceinline__ TileRef<T> decode_tile(const katz_lora_layer* __restrict__ layers, int li, int layer_start,
+                                                  int tile) {
     TileRef<T> t;
-    const int li = find_layer(tile_start, n_layers, tile);
     t.L = layers + li;
+    t.W = reinterpret_cast<T*>(t.L->W);
     t.out_f = t.L->out_features;
     t.in_f = t.L->in_features;
     t.n_lora = t.L->n_lora;
-    const int rel = tile - tile_start[li];
+    t.rank0 = t.L->rank[0];
+    t.scale0 = t.L->scale[0];
+    const int rel = tile - layer_start;
     const int tiles_n = (t.in_f + LM_TN - 1) / LM_TN;
     const int tm = rel / tiles_n;
     t.row0 = tm * LmCfg<T>::TM;
@@ -104,12 +109,14 @@ __device__ __forceinline__ void load_adapter_tiles(const TileRef<T>& t, int l, i
     constexpr int ES = sizeof(T), EPC = 16 / ES, TM = LmCfg<T>::TM, W_CHUNKS_ROW = LM_TN / EPC;
     const T* Bm = reinterpret_cast<const T*>(t.L->B[l]);
     const T* Am = reinterpret_cast<const T*>(t.L->A[l]);
-    const int rank = t.L->rank[l];
+    const int rank = l == 0 ? t.rank0 : t.L->rank[l];
     const int kr = min(LM_MAXR, rank - k0);
     const int kpad = (kr + 15) & ~15;
+    constexpr int BSLOTS = LM_MAXR / EPC;        // 16-byte chunk slots per B row (8 for fp16, 16 for fp32)
     const int bchunks = kpad / EPC;
-    for (int idx = threadIdx.x; idx < TM * bchunks; idx += LM_THREADS) {
-        const int r = idx / bchunks, c = idx - r * bchunks;
+    for (int idx = threadIdx.x; idx < TM * BSLOTS; idx += LM_THREADS) {
+        const int r = idx / BSLOTS, c = idx % BSLOTS;
+        if (c >= bchunks) continue;
         const int gr = t.row0 + r;
         const bool ok = gr < t.out_f && (c * EPC) < kr;
         const T* src = ok ? Bm + (size_t)gr * rank + k0 + c * EPC : Bm;
@@ -139,7 +146,7 @@ __device__ __forceinline__ void load_adapter_tiles(const TileRef<T>& t, int l, i
 template <typename T>
 __global__ void __launch_bounds__(LM_THREADS, 1) lora_merge_kernel(const katz_lora_layer* __restrict__ layers,
                                                                    const int* __restrict__ tile_start, int n_layers,
-                                                                   int total_tiles, float sign) {
+                                                                   int total_tiles, float sign, int counts_in_smem) {
     using Cfg = LmCfg<T>;
     constexpr int TM = Cfg::TM, NST = Cfg::NST;
     constexpr int ES = sizeof(T);
@@ -149,15 +156,36 @@ __global__ void __launch_bounds__(LM_THREADS, 1) lora_merge_kernel(const katz_lo
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* xB = smem + NST * Cfg::STAGE;           // side buffer for further adapters / rank chunks
     unsigned char* xA = xB + Cfg::B_BYTES;
+    // The tile -> layer search runs once per tile on the issue side, over a shared-memory copy of the prefix table; the
+    // decoded tile travels to the compute side through a small ring, so the update loop makes no dependent global loads.
+    __shared__ unsigned short s_count[LM_MAX_LAYERS_SMEM];
+    __shared__ TileRef<T> s_ref[NST];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // counts_in_smem is decided on the host (every layer has < 65536 tiles and the table fits)
+    if (counts_in_smem) {
+        for (int i = tid; i < n_layers; i += LM_THREADS)
+            s_count[i] = (unsigned short)((i + 1 < n_layers ? tile_start[i + 1] : total_tiles) - tile_start[i]);
+        __syncthreads();
+    }
+    int cur_li = 0, cur_start = 0;     // issue-side cursor: tiles are visited in increasing order
 
     auto issue = [&](int j) {
         const int tile = blockIdx.x + j * gridDim.x;
         if (tile < total_tiles) {
             unsigned char* sW = smem + (j % NST) * Cfg::STAGE;
-            const TileRef<T> t = decode_tile<T>(layers, tile_start, n_layers, tile);
-            const T* Wdst = reinterpret_cast<const T*>(t.L->W);
+            if (counts_in_smem) {
+                while (tile >= cur_start + (int)s_count[cur_li]) {
+                    cur_start += s_count[cur_li];
+                    ++cur_li;
+                }
+            } else {
+                cur_li = find_layer(tile_start, n_layers, tile);
+                cur_start = tile_start[cur_li];
+            }
+            const TileRef<T> t = decode_tile<T>(layers, cur_li, cur_start, tile);
+            if (tid == 0) s_ref[j % NST] = t;
+            const T* Wdst = t.W;
             const T* Wsrc = t.L->W0 ? reinterpret_cast<const T*>(t.L->W0) : Wdst;
             for (int idx = tid; idx < TM * W_CHUNKS_ROW; idx += LM_THREADS) {
                 const int r = idx / W_CHUNKS_ROW, c = idx - r * W_CHUNKS_ROW;
@@ -182,11 +210,11 @@ __global__ void __launch_bounds__(LM_THREADS, 1) lora_merge_kernel(const katz_lo
         issue(j + NST - 1);            // refills the stage that tile j-1 used
 
         unsigned char* sW = smem + (j % NST) * Cfg::STAGE;
-        const TileRef<T> t = decode_tile<T>(layers, tile_start, n_layers, tile);
+        const TileRef<T> t = s_ref[j % NST];
 
         for (int l = 0; l < t.n_lora; ++l) {
-            const int rank = t.L->rank[l];
-            const float s = t.L->scale[l] * sign;
+            const int rank = l == 0 ? t.rank0 : t.L->rank[l];
+            const float s = (l == 0 ? t.scale0 : t.L->scale[l]) * sign;
             float acc[2][NF][4];
 #pragma unroll
             for (int i = 0; i < 2; ++i)
@@ -314,7 +342,7 @@ __global__ void __launch_bounds__(LM_THREADS, 1) lora_merge_kernel(const katz_lo
         __syncthreads();
 
         // ---- write-back, 16 bytes per thread, whole rows of the tile contiguous
-        T* Wdst = reinterpret_cast<T*>(t.L->W);
+        T* Wdst = t.W;
         for (int idx = tid; idx < TM * W_CHUNKS_ROW; idx += LM_THREADS) {
             const int r = idx / W_CHUNKS_ROW, c = idx - r * W_CHUNKS_ROW;
             const int gr = t.row0 + r, gc = t.col0 + c * EPC;
@@ -345,7 +373,7 @@ extern "C" int katz_lora_tile_rows(int w_dtype) { return w_dtype == KATZ_DTYPE_F
 extern "C" int katz_lora_tile_cols(void) { return LM_TN; }
 
 extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_tile_start, int n_layers, int total_tiles,
-                               int w_dtype, float sign, void* stream) {
+                               int w_dtype, float sign, int max_tiles_per_layer, void* stream) {
     KATZ_CHECK_ARG(d_layers && d_tile_start, KATZ_EINVAL);
     KATZ_CHECK_ARG(n_layers > 0 && total_tiles > 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(w_dtype == KATZ_DTYPE_F16 || w_dtype == KATZ_DTYPE_F32, KATZ_EINVAL);
@@ -360,10 +388,11 @@ extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_til
         attr_set = true;
     }
     const int grid = total_tiles < lm_sm_count() ? total_tiles : lm_sm_count();
+    const int in_smem = (n_layers <= LM_MAX_LAYERS_SMEM && max_tiles_per_layer > 0 && max_tiles_per_layer < 65536) ? 1 : 0;
     if (w_dtype == KATZ_DTYPE_F16)
-        lora_merge_kernel<__half><<<grid, LM_THREADS, LmCfg<__half>::SMEM, st>>>(d_layers, d_tile_start, n_layers, total_tiles, sign);
+        lora_merge_kernel<__half><<<grid, LM_THREADS, LmCfg<__half>::SMEM, st>>>(d_layers, d_tile_start, n_layers, total_tiles, sign, in_smem);
     else
-        lora_merge_kernel<float><<<grid, LM_THREADS, LmCfg<float>::SMEM, st>>>(d_layers, d_tile_start, n_layers, total_tiles, sign);
+        lora_merge_kernel<float><<<grid, LM_THREADS, LmCfg<float>::SMEM, st>>>(d_layers, d_tile_start, n_layers, total_tiles, sign, in_smem);
     KATZ_LAUNCH_RET();
 }
 

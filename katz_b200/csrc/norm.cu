@@ -184,7 +184,8 @@ __global__ void gn_stats_v8_kernel(const __half* __restrict__ x, float* __restri
 
 __global__ void gn_apply_v8_kernel(const __half* __restrict__ x, __half* __restrict__ y, const float* __restrict__ partial,
                                    int nslab_stats, const __half* __restrict__ gamma, const __half* __restrict__ beta, int HW,
-                                   int C, int G, int rows_per_slab, int R, double n_total, float eps, int act) {
+                                   int C, int G, int rows_per_slab, int R, double n_total, float eps, int act,
+                                   const double* __restrict__ dsums) {
     extern __shared__ float s_dyn[];    // [C] scale, [C] shift
     __shared__ float s_mean[GN_MAXG], s_rstd[GN_MAXG];
     const int slab = blockIdx.x, b = blockIdx.y;
@@ -192,10 +193,15 @@ __global__ void gn_apply_v8_kernel(const __half* __restrict__ x, __half* __restr
     const int tid = threadIdx.x;
     if (tid < G) {
         double s = 0.0, q = 0.0;
-        const float* pp = partial + ((size_t)b * nslab_stats * G + tid) * 2;
-        for (int i = 0; i < nslab_stats; ++i) {
-            s += (double)pp[(size_t)i * G * 2];
-            q += (double)pp[(size_t)i * G * 2 + 1];
+        if (dsums) {
+            s = dsums[((size_t)b * G + tid) * 2];
+            q = dsums[((size_t)b * G + tid) * 2 + 1];
+        } else {
+            const float* pp = partial + ((size_t)b * nslab_stats * G + tid) * 2;
+            for (int i = 0; i < nslab_stats; ++i) {
+                s += (double)pp[(size_t)i * G * 2];
+                q += (double)pp[(size_t)i * G * 2 + 1];
+            }
         }
         const double mean = s / n_total;
         double var = q / n_total - mean * mean;
@@ -246,6 +252,21 @@ __global__ void gn_apply_v8_kernel(const __half* __restrict__ x, __half* __restr
         for (int k = 0; k < 4; ++k) yb[(size_t)(r + k * R) * NC] = norm8(u[k]);
     }
     for (; r < r1; r += R) yb[(size_t)r * NC] = norm8(xb[(size_t)r * NC]);
+}
+
+// Folds the per-slab partials of one shard into [B, G, 2] fp64 sums (fixed order): the quantity that is summed across
+// ranks when the latent is row-split.
+__global__ void gn_fold_kernel(const float* __restrict__ partial, int nslab, int G, double* __restrict__ sums) {
+    const int b = blockIdx.x, g = threadIdx.x;
+    if (g >= G) return;
+    double s = 0.0, q = 0.0;
+    const float* pp = partial + ((size_t)b * nslab * G + g) * 2;
+    for (int i = 0; i < nslab; ++i) {
+        s += (double)pp[(size_t)i * G * 2];
+        q += (double)pp[(size_t)i * G * 2 + 1];
+    }
+    sums[((size_t)b * G + g) * 2] = s;
+    sums[((size_t)b * G + g) * 2 + 1] = q;
 }
 
 // Channels-first variant: each (batch, group) is one contiguous run of (C/G)*HW values.
@@ -403,12 +424,60 @@ extern "C" int katz_group_norm_nhwc_f16(const void* x, void* y, const void* gamm
         gn_stats_v8_kernel<<<grid, threads, threads * 64, st>>>((const __half*)x, (float*)scratch, HW, C, G, rows, R);
         gn_apply_v8_kernel<<<grid, threads, 2 * C * 4, st>>>((const __half*)x, (__half*)y, (const float*)scratch, nslab,
                                                              (const __half*)gamma, (const __half*)beta, HW, C, G, rows, R,
-                                                             (double)HW * (C / G), eps, act);
+                                                             (double)HW * (C / G), eps, act, nullptr);
         KATZ_LAUNCH_RET();
     }
     gn_stats_nhwc_kernel<<<grid, GN_THREADS, 0, st>>>((const __half*)x, (float*)scratch, HW, C, G, rows);
     gn_apply_nhwc_kernel<<<grid, GN_THREADS, 0, st>>>((const __half*)x, (__half*)y, (const float*)scratch, nslab,
                                                       (const __half*)gamma, (const __half*)beta, HW, C, G, rows, eps, act);
+    KATZ_LAUNCH_RET();
+}
+
+static int gn_v8_setup(int C, int* R, int* threads) {
+    const int NC = C / 8;
+    if (C % 8 != 0 || NC > 1024) return KATZ_ESIZE;
+    *R = NC >= 256 ? 1 : 256 / NC;
+    *threads = NC * (*R);
+    static bool attr = false;
+    if (!attr) {
+        cudaFuncSetAttribute(gn_stats_v8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 * 64);
+        cudaFuncSetAttribute(gn_apply_v8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 8192 * 4);
+        attr = true;
+    }
+    return 0;
+}
+
+extern "C" int katz_group_norm_stats_nhwc_f16(const void* x, double* sums, int B, int HW, int C, int G, void* scratch,
+                                              long long scratch_bytes, void* stream) {
+    KATZ_CHECK_ARG(x && sums && scratch, KATZ_EINVAL);
+    KATZ_CHECK_ARG(B > 0 && B <= 65535 && HW > 0 && C > 0 && G > 0 && G <= GN_MAXG && C % G == 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(aligned16(x) && ((uintptr_t)sums & 7) == 0 && ((uintptr_t)scratch & 3) == 0, KATZ_EALIGN);
+    KATZ_CHECK_ARG(scratch_bytes >= katz_group_norm_scratch_bytes(B, HW, C, G), KATZ_ESIZE);
+    int R, threads;
+    int rc = gn_v8_setup(C, &R, &threads);
+    if (rc) return rc;
+    const int rows = gn_rows_per_slab(HW, B);
+    const int nslab = ceil_div(HW, rows);
+    cudaStream_t st = (cudaStream_t)stream;
+    gn_stats_v8_kernel<<<dim3(nslab, B), threads, threads * 64, st>>>((const __half*)x, (float*)scratch, HW, C, G, rows, R);
+    gn_fold_kernel<<<B, GN_MAXG, 0, st>>>((const float*)scratch, nslab, G, sums);
+    KATZ_LAUNCH_RET();
+}
+
+extern "C" int katz_group_norm_apply_nhwc_f16(const void* x, void* y, const double* sums, const void* gamma, const void* beta,
+                                              int B, int HW, int C, int G, double n_total, float eps, int act, void* stream) {
+    KATZ_CHECK_ARG(x && y && sums, KATZ_EINVAL);
+    KATZ_CHECK_ARG(B > 0 && B <= 65535 && HW > 0 && C > 0 && G > 0 && G <= GN_MAXG && C % G == 0 && n_total > 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(act == 0 || act == 1, KATZ_EINVAL);
+    KATZ_CHECK_ARG(aligned16(x) && aligned16(y) && ((uintptr_t)sums & 7) == 0, KATZ_EALIGN);
+    int R, threads;
+    int rc = gn_v8_setup(C, &R, &threads);
+    if (rc) return rc;
+    const int rows = gn_rows_per_slab(HW, B);
+    const int nslab = ceil_div(HW, rows);
+    gn_apply_v8_kernel<<<dim3(nslab, B), threads, 2 * C * 4, (cudaStream_t)stream>>>(
+        (const __half*)x, (__half*)y, nullptr, 0, (const __half*)gamma, (const __half*)beta, HW, C, G, rows, R, n_total, eps, act,
+        sums);
     KATZ_LAUNCH_RET();
 }
 

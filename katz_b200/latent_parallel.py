@@ -1,0 +1,148 @@
+"""Latent-row parallelism: the latent (and every activation derived from it) is split by rows across the GPUs of one
+node, one process per GPU, and only three operator classes exchange data:
+
+  * 3x3 convolutions need one halo row from each neighbour (stride 2: the upper neighbour only; the upsampling
+    convolution exchanges the rows BEFORE the 2x upsample);
+  * GroupNorm statistics are summed over all shards (fp64 (sum, sum of squares) per (batch, group));
+  * self-attention keeps its query rows local and all-gathers the K/V shards.
+
+Everything else (linears, LayerNorm, GEGLU, cross-attention, residual and ControlNet adds, 1x1 convolutions) is local.
+The reference has no such split (its "latent_parallel" flag is a 2-GPU classifier-free-guidance split,
+sdxl_unet_server.py:41,199-215); parity is therefore against the single-GPU result, to which a synchronous row split
+is equal up to the order of the GroupNorm reduction.
+
+Collectives go through torch.distributed (NCCL on GPUs). The communication primitives at the top of `RowParallel`
+are backend-agnostic and are exercised with gloo on CPU tensors in the tests.
+"""
+import torch
+import torch.distributed as dist
+
+from .ops import KatzError
+
+
+class RowParallel:
+    def __init__(self, rank=None, world=None, group=None):
+        self.group = group
+        self.rank = dist.get_rank(group) if rank is None else rank
+        self.world = dist.get_world_size(group) if world is None else world
+        if self.world < 1 or not (0 <= self.rank < self.world):
+            raise KatzError("bad rank/world for RowParallel: %s/%s" % (self.rank, self.world))
+
+    # ---- sharding -------------------------------------------------------------------------------------------------
+    def rows_of(self, H):
+        """(first row, row count) this rank owns of an H-row tensor. H must split evenly into an even row count
+        (the stride-2 convolutions halve it)."""
+        if H % self.world:
+            raise KatzError("%d rows do not split over %d ranks" % (H, self.world))
+        h = H // self.world
+        return self.rank * h, h
+
+    def shard_rows(self, x_full):
+        """[B, H, W, C] -> this rank's [B, H/P, W, C] (contiguous copy)."""
+        r0, h = self.rows_of(x_full.shape[1])
+        return x_full[:, r0:r0 + h].contiguous()
+
+    # ---- communication primitives (any backend, any device) --------------------------------------------------------
+    def exchange_halo(self, x):
+        """x: [B, h, W, C] local rows. Returns (top, bottom): the neighbouring ranks' adjacent rows as [B, W, C]
+        tensors, zeros at the image edge. One all-gather of every rank's first and last row."""
+        if self.world == 1:
+            z = torch.zeros_like(x[:, 0])
+            return z, z.clone()
+        edges = torch.stack([x[:, 0], x[:, -1]]).contiguous()              # [2, B, W, C]
+        allg = self.gather_shards(edges)                                    # [P, 2, B, W, C]
+        top = allg[self.rank - 1, 1] if self.rank > 0 else torch.zeros_like(edges[0])
+        bottom = allg[self.rank + 1, 0] if self.rank < self.world - 1 else torch.zeros_like(edges[0])
+        return top, bottom
+
+    def gather_shards(self, t):
+        """t: contiguous local shard -> [P, *t.shape], rank-major (the K/V all-gather and the final row gather)."""
+        if self.world == 1:
+            return t.unsqueeze(0)
+        t = t.contiguous()
+        # the concatenated form (dim 0 = P * t.shape[0]) is the one every backend accepts
+        out = torch.empty((self.world * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t, group=self.group)
+        return out.view((self.world,) + tuple(t.shape))
+
+    def reduce_stats(self, sums):
+        """In-place sum over ranks of the fp64 GroupNorm sums [B, G, 2]."""
+        if self.world > 1:
+            dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=self.group)
+        return sums
+
+    def gather_rows(self, x_local):
+        """[B, h, W, C] shards -> the whole [B, H, W, C] on every rank."""
+        g = self.gather_shards(x_local)                                     # [P, B, h, W, C]
+        P, B, h, W, C = g.shape
+        return g.permute(1, 0, 2, 3, 4).reshape(B, P * h, W, C).contiguous()
+
+    def pad_rows(self, x, top=True, bottom=True):
+        """x [B, h, W, C] -> [B, h + top + bottom, W, C] with the neighbours' rows (zeros at image edges) attached."""
+        B, h, W, C = x.shape
+        t, b = self.exchange_halo(x)
+        out = torch.empty((B, h + int(top) + int(bottom), W, C), dtype=x.dtype, device=x.device)
+        o = 0
+        if top:
+            out[:, 0].copy_(t)
+            o = 1
+        out[:, o:o + h].copy_(x)
+        if bottom:
+            out[:, o + h].copy_(b)
+        return out
+
+    # ---- operators on the CUDA kernels ----------------------------------------------------------------------------
+    def conv3x3(self, x, w, bias, stride=1, upsample=False, **epi):
+        from . import ops
+        B, h, W, C = x.shape
+        if upsample:
+            # exchange the rows before the upsample, upsample the padded shard, drop the outermost upsampled rows:
+            # rows [1, 2h+3) of the upsampled padded shard are exactly the 2h+2 input rows the 2h output rows read
+            up = ops.upsample_nearest2x(self.pad_rows(x))
+            return ops.conv2d(up[:, 1:2 * h + 3].contiguous(), w, bias, stride=1, pad=1, pad_h=0, **epi)
+        if stride == 2:
+            if h % 2:
+                raise KatzError("a stride-2 convolution needs an even number of rows per rank (got %d)" % h)
+            return ops.conv2d(self.pad_rows(x, bottom=False), w, bias, stride=2, pad=1, pad_h=0, **epi)
+        return ops.conv2d(self.pad_rows(x), w, bias, stride=1, pad=1, pad_h=0, **epi)
+
+    def group_norm(self, x, gamma, beta, groups, eps, act):
+        from . import ops
+        B, C = x.shape[0], x.shape[-1]
+        rows_local = x.numel() // (B * C)
+        sums = ops.group_norm_stats(x, groups)
+        self.reduce_stats(sums)
+        return ops.group_norm_apply(x, sums, gamma, beta, groups, float(rows_local) * self.world * (C // groups), eps, act)
+
+    def self_attention(self, qkv, C, heads):
+        """qkv: [B, s, 3C] local tokens. Queries stay local; K/V shards are all-gathered ([P, B, s, 2C]) and read in
+        place by the attention kernel as P chunks."""
+        from . import ops
+        B, s, _ = qkv.shape
+        g = self.gather_shards(qkv[:, :, C:].contiguous())                  # [P, B, s, 2C]
+        if s % 64 == 0:
+            return ops.attention(qkv[:, :, :C], g[0][:, :, :C], g[0][:, :, C:], heads,
+                                 kv_chunks=(self.world, s, B * s * 2 * C))
+        kv = g.permute(1, 0, 2, 3).reshape(B, self.world * s, 2 * C)        # small shards: make the keys contiguous
+        return ops.attention(qkv[:, :, :C], kv[:, :, :C], kv[:, :, C:], heads)
+
+
+class RowParallelStep:
+    """CUDA-graph step of a row-split UNet: same interface as engine.GraphedStep. Every rank passes the same inputs
+    and receives the whole prediction."""
+
+    def __init__(self, unet, batch, height, width, rank, world, text_len=77, group=None, warmup=2):
+        from .engine import GraphedStep
+        rp = RowParallel(rank, world, group)
+        rp.rows_of(height)
+        for lvl in range(len(unet.cfg["block_out_channels"])):
+            if (height >> lvl) % world or ((height >> lvl) // world) % (2 if lvl < len(unet.cfg["block_out_channels"]) - 1 else 1):
+                raise KatzError("latent height %d cannot be row-split over %d ranks at every UNet level" % (height, world))
+        unet.rp = rp
+        self._inner = GraphedStep(unet, batch, height, width, text_len=text_len, warmup=warmup)
+        self.graph = self._inner.graph
+        self.launches_per_step = self._inner.launches_per_step
+        self.static = self._inner.static
+
+    def run(self, **tensors):
+        return self._inner.run(**tensors)

@@ -56,10 +56,12 @@ class LoraMerger:
         lib = _lib.load()
         self.tile_rows = lib.katz_lora_tile_rows(self.code)
         self.tile_cols = lib.katz_lora_tile_cols()
-        starts, total = [], 0
+        starts, total, self.max_tiles_per_layer = [], 0, 0
         for w in self.weights.values():
             starts.append(total)
-            total += -(-w.shape[0] // self.tile_rows) * -(-w.shape[1] // self.tile_cols)
+            n = -(-w.shape[0] // self.tile_rows) * -(-w.shape[1] // self.tile_cols)
+            self.max_tiles_per_layer = max(self.max_tiles_per_layer, n)
+            total += n
         self.total_tiles = total
         self.d_tile_start = torch.tensor(starts, dtype=torch.int32, device=self.device)
         self.pristine = None
@@ -132,7 +134,8 @@ class LoraMerger:
         lib = _lib.load()
         st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
         _lib.check(lib.katz_lora_merge(ctypes.c_void_p(self._d_table.data_ptr()), ctypes.c_void_p(self.d_tile_start.data_ptr()),
-                                       len(self.keys), self.total_tiles, self.code, float(sign), st), "katz_lora_merge")
+                                       len(self.keys), self.total_tiles, self.code, float(sign), self.max_tiles_per_layer, st),
+                   "katz_lora_merge")
         _lib.note_launches(1)
 
     # -- operations ---------------------------------------------------------------------------------------------

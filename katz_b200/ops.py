@@ -105,10 +105,11 @@ def linear(x, w, bias=None, residual=None, act=ACT_NONE, rowvec=None, rows_per_b
 
 
 def conv2d(x, w, bias=None, ksize=3, stride=1, pad=1, upsample=False, x2=None, rowvec=None, residual=None,
-           act=ACT_NONE, out=None, out_scale=1.0):
+           act=ACT_NONE, out=None, out_scale=1.0, pad_h=None):
     """NHWC convolution. x: [B,Hs,Ws,C1] (+ optional x2 [B,Hs,Ws,C2] concatenated along channels); w: [Cout,k,k,C1+C2].
     With upsample=True the input is read through a nearest 2x upsample. rowvec: [B, >=Cout] row-strided view added per
-    batch element; residual: [B,Hout,Wout,Cout]."""
+    batch element; residual: [B,Hout,Wout,Cout]. `pad_h` overrides the vertical padding (0 for a row shard whose input
+    already carries its halo rows)."""
     _f16(x, "x"), _f16(w, "w")
     if not x.is_contiguous() or not w.is_contiguous():
         raise KatzError("conv2d: x and w must be contiguous")
@@ -121,22 +122,23 @@ def conv2d(x, w, bias=None, ksize=3, stride=1, pad=1, upsample=False, x2=None, r
     Cout = w.shape[0]
     if w.numel() != Cout * ksize * ksize * (C1 + C2):
         raise KatzError("conv2d: weight does not match [Cout,k,k,Cin]")
+    ph = pad if pad_h is None else pad_h
     Hin, Win = (Hs * 2, Ws * 2) if upsample else (Hs, Ws)
-    Hout = (Hin + 2 * pad - ksize) // stride + 1
+    Hout = (Hin + 2 * ph - ksize) // stride + 1
     Wout = (Win + 2 * pad - ksize) // stride + 1
     if out is None:
         out = torch.empty((B, Hout, Wout, Cout), dtype=torch.float16, device=x.device)
     if residual is not None and (tuple(residual.shape) != (B, Hout, Wout, Cout) or not residual.is_contiguous()):
         raise KatzError("conv2d: bad residual")
-    tw = min(Ws * (2 if upsample else 1), 128)
-    if (_use_tc05() and ksize == 3 and stride == 1 and pad == 1 and x2 is None and C1 % 64 == 0 and Cout % 8 == 0
-            and tw >= 8 and (tw & (tw - 1)) == 0 and Win % tw == 0 and _al16(x) and _al16(w) and _al16(out) and _al16(bias)
-            and _al16(residual) and (rowvec is None or (_al16(rowvec) and rowvec.stride(0) % 8 == 0))):
+    tw = min(Win, 128)
+    if (_use_tc05() and ksize == 3 and stride == 1 and pad == 1 and ph in (0, 1) and x2 is None and C1 % 64 == 0
+            and Cout % 8 == 0 and tw >= 8 and (tw & (tw - 1)) == 0 and Win % tw == 0 and _al16(x) and _al16(w) and _al16(out)
+            and _al16(bias) and _al16(residual) and (rowvec is None or (_al16(rowvec) and rowvec.stride(0) % 8 == 0))):
         src = upsample_nearest2x(x) if upsample else x
-        call("katz_conv3x3_nhwc_f16", _p(src), _p(w), _p(out), B, Hin, Win, C1, Cout, _p(bias), _p(rowvec),
+        call("katz_conv3x3_nhwc_f16", _p(src), _p(w), _p(out), B, Hin, Win, C1, Cout, ph, _p(bias), _p(rowvec),
              rowvec.stride(0) if rowvec is not None else 0, _p(residual), act, float(out_scale), _stream())
         return out
-    call("katz_conv2d_nhwc_f16_mma", _p(x), _p(x2), _p(w), _p(out), B, Hin, Win, C1, C2, Cout, ksize, stride, pad,
+    call("katz_conv2d_nhwc_f16_mma", _p(x), _p(x2), _p(w), _p(out), B, Hin, Win, C1, C2, Cout, ksize, stride, ph, pad,
          1 if upsample else 0, _p(bias), _p(rowvec), rowvec.stride(0) if rowvec is not None else 0, _p(residual), act,
          float(out_scale), _stream())
     return out
@@ -170,6 +172,39 @@ def group_norm_nhwc(x, gamma, beta, groups, eps, act=ACT_NONE, out=None):
     scratch = _scratch(x.device, need)
     call("katz_group_norm_nhwc_f16", _p(x), _p(out), _p(gamma), _p(beta), B, HW, C, groups, float(eps), act,
          _p(scratch), scratch.numel(), _stream())
+    return out
+
+
+def group_norm_stats(x, groups):
+    """fp64 (sum, sum of squares) per (batch, group) of an NHWC shard: [B, G, 2]. First half of a GroupNorm whose
+    statistics span several GPUs."""
+    _f16(x, "x")
+    if not x.is_contiguous():
+        raise KatzError("group_norm: x must be contiguous")
+    B, C = x.shape[0], x.shape[-1]
+    HW = x.numel() // (B * C)
+    lib = _lib.load()
+    need = lib.katz_group_norm_scratch_bytes(B, HW, C, groups)
+    if need < 0:
+        raise KatzError("group_norm: bad shape")
+    scratch = _scratch(x.device, need)
+    sums = torch.empty((B, groups, 2), dtype=torch.float64, device=x.device)
+    call("katz_group_norm_stats_nhwc_f16", _p(x), _p(sums), B, HW, C, groups, _p(scratch), scratch.numel(), _stream())
+    return sums
+
+
+def group_norm_apply(x, sums, gamma, beta, groups, n_total, eps, act=ACT_NONE, out=None):
+    """Second half: normalise the shard with the (globally summed) statistics; n_total = elements per (batch, group)
+    over the WHOLE tensor."""
+    _f16(x, "x")
+    B, C = x.shape[0], x.shape[-1]
+    HW = x.numel() // (B * C)
+    if sums.dtype != torch.float64 or tuple(sums.shape) != (B, groups, 2) or not sums.is_contiguous():
+        raise KatzError("group_norm_apply: sums must be a contiguous fp64 [B, G, 2] tensor")
+    if out is None:
+        out = torch.empty_like(x)
+    call("katz_group_norm_apply_nhwc_f16", _p(x), _p(out), _p(sums), _p(gamma), _p(beta), B, HW, C, groups, float(n_total),
+         float(eps), act, _stream())
     return out
 
 
@@ -222,21 +257,28 @@ def fast_gelu_mul(x, m, out=None):
     return out
 
 
-def attention(q, k, v, heads, out=None, scale=None):
-    """q: [B,Sq,>=H*64] view, k/v: [B,Sk,...] views (unit last stride, any row/batch stride); returns [B,Sq,H*64]."""
+def attention(q, k, v, heads, out=None, scale=None, kv_chunks=None):
+    """q: [B,Sq,>=H*64] view, k/v: [B,Sk,...] views (unit last stride, any row/batch stride); returns [B,Sq,H*64].
+    kv_chunks=(n_chunks, chunk_rows, chunk_stride): k/v describe the FIRST chunk ([B, chunk_rows, ...]); chunk c of the
+    keys/values starts `c * chunk_stride` elements later (the [P, B, s, C] result of an all-gather of row shards)."""
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _f16(t, n)
         if t.dim() != 3 or t.stride(2) != 1:
             raise KatzError("attention: %s must be [B,S,C] with unit last stride" % n)
     B, Sq, _ = q.shape
     Sk = k.shape[1]
+    chunk_rows, chunk_stride = 0, 0
+    if kv_chunks is not None:
+        n_chunks, chunk_rows, chunk_stride = kv_chunks
+        Sk = n_chunks * chunk_rows
     D = 64
     if out is None:
         out = torch.empty((B, Sq, heads * D), dtype=torch.float16, device=q.device)
     if scale is None:
         scale = D ** -0.5
     call("katz_attention_f16_mma", _p(q), _p(k), _p(v), _p(out), B, heads, Sq, Sk, D, q.stride(1), k.stride(1),
-         v.stride(1), out.stride(1), q.stride(0), k.stride(0), v.stride(0), out.stride(0), float(scale), _stream())
+         v.stride(1), out.stride(1), q.stride(0), k.stride(0), v.stride(0), out.stride(0), float(scale), chunk_rows,
+         chunk_stride, _stream())
     return out
 
 

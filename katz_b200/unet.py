@@ -164,6 +164,7 @@ class _Net:
         self.w = _Weights(shapes, self.device)
         self.w.alloc()
         self.dtype = torch.float16
+        self.rp = None                 # latent_parallel.RowParallel when the latent is row-split across GPUs
         self.cache_text_kv = False     # optional hoist of the step-invariant cross-attention K/V (off: reference semantics)
         self._kv_cache_key = None
         self._kv_cache = None
@@ -233,32 +234,48 @@ class _Net:
             self._kv_cache_key, self._kv_cache = key, kv
         return kv
 
+    # ---- the three operator classes that need an exchange when the latent is row-split (self.rp set)
+    def _conv3x3(self, x, w, bias, stride=1, upsample=False, **epi):
+        if self.rp is None:
+            return ops.conv2d(x, w, bias, stride=stride, pad=1, upsample=upsample, **epi)
+        return self.rp.conv3x3(x, w, bias, stride=stride, upsample=upsample, **epi)
+
+    def _gn(self, x, gamma, beta, eps, act):
+        if self.rp is None:
+            return ops.group_norm_nhwc(x, gamma, beta, self.cfg["norm_num_groups"], eps, act)
+        return self.rp.group_norm(x, gamma, beta, self.cfg["norm_num_groups"], eps, act)
+
+    def _self_attention(self, qkv, C, heads):
+        if self.rp is None:
+            return ops.attention(qkv[:, :, :C], qkv[:, :, C:2 * C], qkv[:, :, 2 * C:], heads)
+        return self.rp.self_attention(qkv, C, heads)
+
     def _resnet(self, p, x, temb_all):
         cfg, P = self.cfg, self._P
-        g, eps = cfg["norm_num_groups"], cfg["norm_eps"]
+        eps = cfg["norm_eps"]
         B, H, W, Cin = x.shape
         off, cout = self.w.temb_offset[p]
-        h = ops.group_norm_nhwc(x, P(p + ".norm_silu1.0.weight"), P(p + ".norm_silu1.0.bias"), g, eps, ACT_SILU)
-        h = ops.conv2d(h, P(p + ".conv1.weight"), P(p + ".conv1.bias"), rowvec=temb_all[:, off:off + cout])
-        h = ops.group_norm_nhwc(h, P(p + ".norm_silu2.0.weight"), P(p + ".norm_silu2.0.bias"), g, eps, ACT_SILU)
+        h = self._gn(x, P(p + ".norm_silu1.0.weight"), P(p + ".norm_silu1.0.bias"), eps, ACT_SILU)
+        h = self._conv3x3(h, P(p + ".conv1.weight"), P(p + ".conv1.bias"), rowvec=temb_all[:, off:off + cout])
+        h = self._gn(h, P(p + ".norm_silu2.0.weight"), P(p + ".norm_silu2.0.bias"), eps, ACT_SILU)
         if (p + ".conv_shortcut.weight") in self.w.t:
             sc = ops.linear(x.view(B * H * W, Cin), P(p + ".conv_shortcut.weight").view(cout, Cin),
                             P(p + ".conv_shortcut.bias")).view(B, H, W, cout)
         else:
             sc = x
-        return ops.conv2d(h, P(p + ".conv2.weight"), P(p + ".conv2.bias"), residual=sc)
+        return self._conv3x3(h, P(p + ".conv2.weight"), P(p + ".conv2.bias"), residual=sc)
 
     def _transformer(self, p, x, kv, heads, n_layers):
         cfg, P = self.cfg, self._P
         B, H, W, C = x.shape
         M = B * H * W
-        h = ops.group_norm_nhwc(x, P(p + ".norm.weight"), P(p + ".norm.bias"), cfg["norm_num_groups"], 1e-6, ACT_NONE)
+        h = self._gn(x, P(p + ".norm.weight"), P(p + ".norm.bias"), 1e-6, ACT_NONE)
         h = ops.linear(h.view(M, C), P(p + ".proj_in.weight"), P(p + ".proj_in.bias"))
         for i in range(n_layers):
             b = "%s.transformer_blocks.%d" % (p, i)
             n = ops.layer_norm(h, P(b + ".norm1.weight"), P(b + ".norm1.bias"))
             qkv = ops.linear(n, self.w.fused[b + ".attn1.qkv"]).view(B, H * W, 3 * C)
-            a = ops.attention(qkv[:, :, :C], qkv[:, :, C:2 * C], qkv[:, :, 2 * C:], heads)
+            a = self._self_attention(qkv, C, heads)
             h = ops.linear(a.view(M, C), P(b + ".attn1.to_out.0.weight"), P(b + ".attn1.to_out.0.bias"), residual=h)
             n = ops.layer_norm(h, P(b + ".norm2.weight"), P(b + ".norm2.bias"))
             q = ops.linear(n, P(b + ".attn2.to_q.weight")).view(B, H * W, C)
@@ -285,7 +302,7 @@ class _Net:
                 res.append(sample)
             if bi != nb - 1:
                 p = "down_blocks.%d.downsamplers.0.conv" % bi
-                sample = ops.conv2d(sample, P(p + ".weight"), P(p + ".bias"), stride=2, pad=1)
+                sample = self._conv3x3(sample, P(p + ".weight"), P(p + ".bias"), stride=2)
                 res.append(sample)
         heads = cfg["attention_head_dim"][-1]
         sample = self._resnet("mid_block.resnets.0", sample, temb_all)
@@ -335,7 +352,9 @@ class KatzUNet(_Net):
         emb, temb_all = self._embeddings(timestep, te, ti, B)
         kv = self._cross_kv(ctx)
         h = ops.nchw_to_nhwc(x, cpad=self.w.conv_cin_pad["conv_in.weight"])
-        h = ops.conv2d(h, self._P("conv_in.weight"), self._P("conv_in.bias"))
+        if self.rp is not None:
+            h = self.rp.shard_rows(h)          # every rank holds the whole latent; keep this rank's rows
+        h = self._conv3x3(h, self._P("conv_in.weight"), self._P("conv_in.bias"))
         mid, res = self._down_and_mid(h, temb_all, kv)
         return mid, temb_all, res, kv
 
@@ -350,9 +369,13 @@ class KatzUNet(_Net):
             scales = combine_scales or [1.0] * len(nets)
             if any(len(n) != len(res) for n in nets):
                 raise KatzError("expected %d down residuals per ControlNet" % len(res))
-            res = [ops.residual_intake(r, [_to_nhwc_residual(n[j], self.device) for n in nets], scales)
-                   for j, r in enumerate(res)]
-            sample = ops.residual_intake(sample, [_to_nhwc_residual(m, self.device) for m in mids], scales)
+            def fit(t, like):
+                t = _to_nhwc_residual(t, self.device)
+                if self.rp is not None and t.shape[1] != like.shape[1]:
+                    t = self.rp.shard_rows(t)     # a full-height residual from a ControlNet that is not row-split
+                return t
+            res = [ops.residual_intake(r, [fit(n[j], r) for n in nets], scales) for j, r in enumerate(res)]
+            sample = ops.residual_intake(sample, [fit(m, sample) for m in mids], scales)
         nb = len(cfg["block_out_channels"])
         rev_heads = tuple(reversed(cfg["attention_head_dim"]))
         rev_layers = tuple(reversed(cfg["transformer_layers_per_block"]))
@@ -368,10 +391,11 @@ class KatzUNet(_Net):
                                                rev_layers[bi])
             if bi != nb - 1:
                 p = "up_blocks.%d.upsamplers.0.conv" % bi
-                sample = ops.conv2d(sample, P(p + ".weight"), P(p + ".bias"), upsample=True)
-        h = ops.group_norm_nhwc(sample, P("conv_norm_silu.0.weight"), P("conv_norm_silu.0.bias"), cfg["norm_num_groups"],
-                                cfg["norm_eps"], ACT_SILU)
-        out = ops.conv2d(h, P("conv_out.weight"), P("conv_out.bias"))
+                sample = self._conv3x3(sample, P(p + ".weight"), P(p + ".bias"), upsample=True)
+        h = self._gn(sample, P("conv_norm_silu.0.weight"), P("conv_norm_silu.0.bias"), cfg["norm_eps"], ACT_SILU)
+        out = self._conv3x3(h, P("conv_out.weight"), P("conv_out.bias"))
+        if self.rp is not None:
+            out = self.rp.gather_rows(out)     # [B, H, W, c]: every rank returns the whole prediction
         return ops.nhwc_to_nchw(out, c=cfg["out_channels"])
 
     def __call__(self, sample, timestep, encoder_hidden_states, timestep_cond=None, cross_attention_kwargs=None,
