@@ -1,0 +1,50 @@
+"""Run under torchrun on N GPUs (one process per GPU): the row-split UNet step must equal the single-GPU step.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 tests/row_parallel_check.py
+
+Prints one line per rank and exits non-zero on a mismatch. tests/test_gpu_latent_parallel.py launches it when the box
+has at least two GPUs."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    from katz_b200.latent_parallel import RowParallel
+    from katz_b200.params import TINY_UNET_CONFIG, controlnet_param_shapes, init_state_dict, unet_param_shapes
+    from katz_b200.unet import KatzControlNet, KatzUNet
+    from tests.golden.make_golden import tiny_inputs
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dist.init_process_group("nccl", device_id=dev)
+    cfg = dict(TINY_UNET_CONFIG)
+    cfg["sample_size"] = 32          # 32 rows: 8 per rank at world 4 on the finest level, 2 on the coarsest
+    unet = KatzUNet(cfg, dev, init_state_dict(unet_param_shapes(cfg), seed=0, dtype=torch.float16))
+    cn = KatzControlNet(cfg, dev, init_state_dict(controlnet_param_shapes(cfg), seed=2, dtype=torch.float16))
+    sample, ctx, te, ti, cond = (t.half().to(dev) for t in tiny_inputs(cfg))
+    kw = dict(encoder_hidden_states=ctx, added_cond_kwargs={"text_embeds": te, "time_ids": ti})
+    t = torch.tensor([500.0], device=dev)
+    down, mid = cn(sample, t, controlnet_cond=cond, **kw)
+    ref = unet(sample, t, down_block_additional_residuals=down, mid_block_additional_residual=mid, **kw)[0]
+    unet.rp = RowParallel(rank, world)
+    out = unet(sample, t, down_block_additional_residuals=down, mid_block_additional_residual=mid, **kw)[0]
+    torch.cuda.synchronize()
+    err = float((out.float() - ref.float()).abs().max())
+    rel = float((out.float() - ref.float()).norm() / ref.float().norm())
+    ok = err <= 1e-2 and rel <= 2e-3
+    print("rank %d/%d row-split vs single-GPU: max-abs %.3e rel-l2 %.3e %s" % (rank, world, err, rel, "OK" if ok else "MISMATCH"),
+          flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if ok else 1)
+
+
+if __name__ == "__main__":
+    main()

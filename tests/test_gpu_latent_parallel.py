@@ -81,3 +81,20 @@ def test_row_parallel_unet_world1_matches_plain(cuda_device):
     split = unet(sample, t, **kw)[0]
     unet.rp = None
     assert _rel(split, plain) < 2e-3
+
+
+def test_row_split_equals_single_gpu_on_all_gpus(cuda_device):
+    """One process per GPU under torchrun (NCCL): needs at least two GPUs on the box."""
+    import os
+    import subprocess
+    import sys
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs >= 2 GPUs")
+    n = 4 if n >= 4 else 2
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(n), "--master-addr", "127.0.0.1",
+           "--master-port", "29533", os.path.join(root, "tests", "row_parallel_check.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("OK") == n
