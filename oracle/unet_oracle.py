@@ -289,3 +289,31 @@ def euler_step(x, eps, sigma, sigma_next):
     derivative = (sample - pred) / sigma
     prev = sample + derivative * (sigma_next - sigma)
     return prev.to(eps.dtype)
+
+
+def denoise_loop(sd, cfg, latents, prompt_embeds, text_embeds, time_ids, num_inference_steps, guidance_scale=5.0,
+                 controlnets=(), controlnet_cond=None, conditioning_scales=None, combine="sum", half_latents=True):
+    """The denoise loop of pipeline_controlnet_sd_xl_katz.py:1508-1675 for this path: per step scale_model_input on the
+    CFG batch, ControlNets (residuals summed as multicontrolnet.py:47-73 does, or averaged as
+    unet_2d_condition.py:1418-1439 does), UNet, guidance combine, Euler step. The model runs in the dtype of `sd`
+    (fp32 in the tests); the latent is kept in fp16 between steps as the reference does when `half_latents`."""
+    ts, sig, _ = euler_sigmas(num_inference_steps)
+    scales = list(conditioning_scales) if conditioning_scales else [0.5] * len(controlnets)
+    wdt = next(iter(sd.values())).dtype
+    for i in range(num_inference_steps):
+        x = euler_scale_model_input(latents, sig[i])
+        x2 = torch.cat([x, x]).to(wdt)
+        down = mid = None
+        for cn_sd, s in zip(controlnets, scales):
+            d, m = controlnet_step(cn_sd, cfg, x2, float(ts[i]), prompt_embeds.to(wdt), controlnet_cond.to(wdt),
+                                   text_embeds.to(wdt), time_ids.to(wdt), s)
+            down = d if down is None else [a + b for a, b in zip(down, d)]
+            mid = m if mid is None else mid + m
+        if down is not None and combine == "mean":
+            down = [a / len(controlnets) for a in down]
+            mid = mid / len(controlnets)
+        eps = unet_step(sd, cfg, x2, float(ts[i]), prompt_embeds.to(wdt), text_embeds.to(wdt), time_ids.to(wdt), down, mid)
+        eps = eps.to(latents.dtype) if half_latents else eps
+        e = cfg_combine(eps[0:1], eps[1:2], guidance_scale)
+        latents = euler_step(latents, e, sig[i], sig[i + 1])
+    return latents
