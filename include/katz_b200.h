@@ -84,6 +84,20 @@ int katz_group_norm_stats_nhwc_f16(const void* x, double* sums, int B, int HW, i
                                    long long scratch_bytes, void* stream);
 int katz_group_norm_apply_nhwc_f16(const void* x, void* y, const double* sums, const void* gamma, const void* beta, int B,
                                    int HW, int C, int G, double n_total, float eps, int act, void* stream);
+/* katz_group_norm_nhwc_f16 for callers that cannot allocate device memory (no counterpart in the reference: its op
+ * takes scratch from torch's allocator). A serving process that gave all device memory to another allocator at
+ * start-up, or a plugin inside a runtime that forbids allocations after initialisation, has no buffer to pass as
+ * `scratch`; here the partial sums live in a fixed 512 KiB array inside the library's device image, held by every GPU
+ * that loads the library until the process exits. The call itself allocates nothing.
+ *   - Limit: shapes with katz_group_norm_scratch_bytes(B, HW, C, G) > katz_group_norm_static_scratch_bytes() return
+ *     KATZ_E_SIZE; C must be a multiple of 8.
+ *   - The first call on each device looks up the array's device address (that device must be current); make that
+ *     first call outside any stream capture.
+ *   - All calls on a device share the one array: calls that may overlap on the GPU (different streams without an
+ *     ordering between them) race. Nothing has to be cleared between calls — each call overwrites what it reads. */
+long long katz_group_norm_static_scratch_bytes(void);
+int katz_group_norm_nhwc_f16_noalloc(const void* x, void* y, const void* gamma, const void* beta, int B, int HW, int C,
+                                     int G, float eps, int act, void* stream);
 /* Same op for a channels-first tensor (the `channels_first` branch of group_norm.cu:162-206). */
 int katz_group_norm_nchw_f16(const void* x, void* y, const void* gamma, const void* beta, int B, int HW, int C, int G,
                              float eps, int act, void* stream);

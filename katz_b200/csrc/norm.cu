@@ -503,3 +503,69 @@ extern "C" int katz_layer_norm_f16(const void* x, void* y, const void* gamma, co
         (const __half*)x, (__half*)y, (const __half*)gamma, (const __half*)beta, rows, C, eps);
     KATZ_LAUNCH_RET();
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// GroupNorm for callers that cannot allocate device memory.
+//
+// Some hosts of this library may not call cudaMalloc on the path that runs the step: a serving process whose memory
+// is fully handed to another allocator at start-up, a plugin loaded into a runtime that forbids driver allocations
+// after initialisation, or code running inside a region where an allocation would synchronise the device. For them
+// the per-slab partial sums live in a fixed array in the library's own device image instead of caller-provided
+// scratch. Every GPU that loads the library holds these 512 KiB until the process exits.
+constexpr long long GN_STATIC_SCRATCH_BYTES = 512 * 1024;
+static __device__ __align__(256) float g_gn_static_scratch[GN_STATIC_SCRATCH_BYTES / sizeof(float)];
+
+// In host code the array's name is only a handle; the device address is looked up once per device, with that device
+// current, and cached. Returns nullptr and sets *err on failure.
+static float* gn_static_scratch_ptr(int* err) {
+    constexpr int MAX_DEV = 64;
+    static float* ptrs[MAX_DEV] = {nullptr};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        *err = (int)e;
+        return nullptr;
+    }
+    if (dev < 0 || dev >= MAX_DEV) {
+        *err = KATZ_ENOTREADY;
+        return nullptr;
+    }
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_gn_static_scratch);
+        if (e != cudaSuccess || !p) {
+            *err = e != cudaSuccess ? (int)e : KATZ_ENOTREADY;
+            return nullptr;
+        }
+        ptrs[dev] = static_cast<float*>(p);
+    }
+    *err = 0;
+    return ptrs[dev];
+}
+
+extern "C" long long katz_group_norm_static_scratch_bytes(void) { return GN_STATIC_SCRATCH_BYTES; }
+
+extern "C" int katz_group_norm_nhwc_f16_noalloc(const void* x, void* y, const void* gamma, const void* beta, int B, int HW,
+                                                int C, int G, float eps, int act, void* stream) {
+    KATZ_CHECK_ARG(x && y, KATZ_EINVAL);
+    KATZ_CHECK_ARG(B > 0 && B <= 65535 && HW > 0 && C > 0 && G > 0 && G <= GN_MAXG && C % G == 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(act == 0 || act == 1, KATZ_EINVAL);
+    KATZ_CHECK_ARG(aligned16(x) && aligned16(y), KATZ_EALIGN);
+    // sizes whose partial sums do not fit the fixed array are refused, never truncated
+    KATZ_CHECK_ARG(katz_group_norm_scratch_bytes(B, HW, C, G) <= GN_STATIC_SCRATCH_BYTES, KATZ_ESIZE);
+    int R, threads;
+    int rc = gn_v8_setup(C, &R, &threads);
+    if (rc) return rc;
+    int err = 0;
+    float* scratch = gn_static_scratch_ptr(&err);
+    if (!scratch) return err;
+    const int rows = gn_rows_per_slab(HW, B);
+    const int nslab = ceil_div(HW, rows);
+    cudaStream_t st = (cudaStream_t)stream;
+    // the statistics pass overwrites every partial the apply pass reads, so nothing left by an earlier call is used
+    gn_stats_v8_kernel<<<dim3(nslab, B), threads, threads * 64, st>>>((const __half*)x, scratch, HW, C, G, rows, R);
+    gn_apply_v8_kernel<<<dim3(nslab, B), threads, 2 * C * 4, st>>>((const __half*)x, (__half*)y, scratch, nslab,
+                                                                   (const __half*)gamma, (const __half*)beta, HW, C, G, rows, R,
+                                                                   (double)HW * (C / G), eps, act, nullptr);
+    KATZ_LAUNCH_RET();
+}
