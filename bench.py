@@ -409,7 +409,13 @@ def main():
                                               "scaled by FLOPs to the benchmark step (%.3f TFLOP)" % (fl / 1e12, dt, flops["total"] / 1e12)}
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Tearing the NCCL communicator down while CUDA graphs that captured its collectives are still alive blocks in
+        # the process-group watchdog. The measurement is printed; leave without running destructors.
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -166,6 +166,13 @@ int katz_attention_f16_mma(const void* Q, const void* K, const void* V, void* O,
                            long long bsv, long long bso, float scale, int kv_chunk_rows, long long kv_chunk_stride,
                            void* stream);
 
+/* Same contract on the tcgen05 path (TMA-fed, S and O accumulators in TMEM, one query row per softmax thread). Needs
+ * ld* and bs* multiples of 8, 16-byte aligned pointers, and kv_chunk_rows a multiple of 128 when chunked; other
+ * layouts belong to the _mma entry point. */
+int katz_attention_f16(const void* Q, const void* K, const void* V, void* O, int B, int H, int Sq, int Sk, int head_dim,
+                       int ldq, int ldk, int ldv, int ldo, long long bsq, long long bsk, long long bsv, long long bso,
+                       float scale, int kv_chunk_rows, long long kv_chunk_stride, void* stream);
+
 /* dst = src + half(sum_i scales[i] * residuals[i]) — ControlNet residual intake (unet_2d_condition.py:1281-1292; the
  * sum / mean over nets of :1418-1439). `h_residuals` and `h_scales` are HOST arrays of n_res entries (device pointers
  * inside). */

@@ -1,0 +1,390 @@
+// Flash-style attention on the tcgen05 tensor path: head_dim 64, fp16 in/out, fp32 softmax, no mask, non-causal.
+// Replaces F.scaled_dot_product_attention as called by AttnProcessor2_0
+// (diffusers/models/attention_processor.py:1276): softmax(Q K^T / sqrt(64)) V per (batch, head).
+//
+// One CTA owns 128 query rows of one (batch, head) and walks the keys in tiles of 128:
+//   * warp 0, one elected thread: TMA loads of Q (once) and of the K and V tiles into 3-stage rings (128-byte swizzle;
+//     Q/K/V are read in place from the [B, S, ld] projection outputs, head h = columns [64h, 64h+64));
+//   * warp 1, one elected thread: S = Q K^T (tcgen05.mma, 128x128x64, K-major operands) into one of two TMEM
+//     accumulators, then O += P V (128x64x128; V is the MN-major operand, P comes from shared memory) into a third;
+//   * warps 2-5: softmax. A thread owns one query row (= one TMEM lane), so row maxima and sums need no shuffles. It
+//     reads S with tcgen05.ld, keeps a running reference maximum that is only raised when the tile maximum exceeds it
+//     by more than 2^8 (so the O accumulator is rescaled rarely: tcgen05.ld / scale / tcgen05.st), writes
+//     P = exp2(S*scale - m) as fp16 into swizzled shared memory for the second MMA, and at the end normalises O.
+// S[j+1] = Q K[j+1]^T is issued before the softmax of tile j has finished, so the two MMAs and the softmax overlap.
+// Every mbarrier wait is bounded; a time-out records a status word (shared with the GEMM kernels) and the CTA unwinds.
+#include "tc05.cuh"
+#include "katz_b200.h"
+
+namespace katz {
+
+using namespace tc05;
+
+constexpr int FA_BM = 128, FA_BN = 128, FA_D = 64, FA_ST = 3;
+constexpr int FA_THREADS = 192;
+constexpr int FA_TILE = 128 * 128;                     // bytes of a 128-row x 64-half tile
+constexpr int FA_SMEM = FA_TILE * (1 + 2 * FA_ST + 4) + 1024 + 256;
+constexpr float FA_RESCALE_THRESHOLD = 8.0f;           // log2 units
+
+int* tc05_status_device_ptr();   // defined next to the status word (gemm_tc05.cu)
+
+struct FaParams {
+    __half* O;
+    int Sq, Sk, ldo;
+    long long bso;
+    float scale_log2e;
+    int kv_chunk_rows;
+    int* status;
+};
+
+__device__ __forceinline__ void tma_load_4d_fa(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+    tma_load_4d(dst, map, c0, c1, c2, c3, bar);
+}
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+        "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// kind::f16 instruction descriptor with an MN-major B operand (bit 16)
+__host__ __device__ constexpr uint32_t idesc_f16_bmn(int M, int N) { return idesc_f16(M, N) | (1u << 16); }
+
+__global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
+                                                                       const __grid_constant__ CUtensorMap tmK,
+                                                                       const __grid_constant__ CUtensorMap tmV, const FaParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t sQ = smem_u32(smem);
+    const uint32_t sK0 = sQ + FA_TILE, sV0 = sK0 + FA_ST * FA_TILE, sP0 = sV0 + FA_ST * FA_TILE;   // sP: 2 buffers x 2 tiles
+    unsigned char* sP_gen = smem + FA_TILE * (1 + 2 * FA_ST);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FA_TILE * (1 + 2 * FA_ST + 4));
+    // barrier map
+    const uint32_t b0 = smem_u32(bars);
+    const uint32_t q_full = b0, k_full = b0 + 8, k_empty = k_full + 8 * FA_ST, v_full = k_empty + 8 * FA_ST,
+                   v_empty = v_full + 8 * FA_ST, s_full = v_empty + 8 * FA_ST, s_free = s_full + 16, p_full = s_free + 16,
+                   p_free = p_full + 16, o_done = p_free + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1 + 4 * FA_ST + 9);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q0 = blockIdx.x * FA_BM, h = blockIdx.y, b = blockIdx.z;
+    const int NT = (p.Sk + FA_BN - 1) / FA_BN;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        mbar_init(q_full, 1);
+        for (int s = 0; s < FA_ST; ++s) {
+            mbar_init(k_full + 8 * s, 1);
+            mbar_init(k_empty + 8 * s, 1);
+            mbar_init(v_full + 8 * s, 1);
+            mbar_init(v_empty + 8 * s, 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(s_full + 8 * i, 1);
+            mbar_init(s_free + 8 * i, 4);
+            mbar_init(p_full + 8 * i, 4);
+            mbar_init(p_free + 8 * i, 1);
+        }
+        mbar_init(o_done, 1);
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tS0 = tmem_base, tO = tmem_base + 256;      // S buffers at columns 0 and 128, O at 256..319
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            bool ok = true;
+            mbar_expect_tx(q_full, FA_TILE);
+            tma_load_4d_fa(sQ, &tmQ, h * FA_D, q0, b, 0, q_full);
+            for (int j = 0; j < NT && ok; ++j) {
+                const int s = j % FA_ST;
+                const uint32_t ph = (j / FA_ST) & 1;
+                const int key0 = j * FA_BN;
+                const int chunk = key0 / p.kv_chunk_rows, row = key0 - chunk * p.kv_chunk_rows;
+                if (!mbar_wait(k_empty + 8 * s, ph ^ 1)) { ok = false; break; }
+                mbar_expect_tx(k_full + 8 * s, FA_TILE);
+                tma_load_4d_fa(sK0 + s * FA_TILE, &tmK, h * FA_D, row, b, chunk, k_full + 8 * s);
+                if (!mbar_wait(v_empty + 8 * s, ph ^ 1)) { ok = false; break; }
+                mbar_expect_tx(v_full + 8 * s, FA_TILE);
+                tma_load_4d_fa(sV0 + s * FA_TILE, &tmV, h * FA_D, row, b, chunk, v_full + 8 * s);
+            }
+            if (!ok) atomicExch(p.status, 11);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            constexpr uint32_t idesc_qk = idesc_f16(FA_BM, FA_BN);
+            constexpr uint32_t idesc_pv = idesc_f16_bmn(FA_BM, FA_D);
+            bool ok = mbar_wait(q_full, 0);
+            auto issue_qk = [&](int j) -> bool {
+                const int s = j % FA_ST, buf = j & 1;
+                if (!mbar_wait(k_full + 8 * s, (j / FA_ST) & 1)) return false;
+                if (!mbar_wait(s_free + 8 * buf, ((j >> 1) & 1) ^ 1)) return false;
+                fence_after_sync();
+                const uint64_t ad = smem_desc_sw128(sQ), bd = smem_desc_sw128(sK0 + s * FA_TILE);
+#pragma unroll
+                for (int k = 0; k < FA_D / 16; ++k) umma_f16(tS0 + buf * FA_BN, ad + 2 * k, bd + 2 * k, idesc_qk, k != 0);
+                umma_commit(s_full + 8 * buf);
+                umma_commit(k_empty + 8 * s);
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; j < NT && ok; ++j) {
+                if (j + 1 < NT) {
+                    ok = issue_qk(j + 1);
+                    if (!ok) break;
+                }
+                const int s = j % FA_ST, buf = j & 1;
+                if (!mbar_wait(p_full + 8 * buf, (j >> 1) & 1)) { ok = false; break; }
+                if (!mbar_wait(v_full + 8 * s, (j / FA_ST) & 1)) { ok = false; break; }
+                fence_after_sync();
+                const uint32_t pa = sP0 + buf * 2 * FA_TILE, va = sV0 + s * FA_TILE;
+#pragma unroll
+                for (int k = 0; k < FA_BN / 16; ++k) {
+                    // A = P: two 64-key sub-tiles, +32 B per 16-key step inside a sub-tile.
+                    // B = V (MN-major): 16 key rows per step = two 8-row swizzle groups = 2048 B.
+                    const uint64_t ad = smem_desc_sw128(pa + (k >> 2) * FA_TILE) + 2 * (k & 3);
+                    const uint64_t bd = smem_desc_sw128(va + k * 2048);
+                    umma_f16(tO, ad, bd, idesc_pv, (j | k) != 0);
+                }
+                umma_commit(v_empty + 8 * s);
+                umma_commit(p_free + 8 * buf);
+                umma_commit(o_done);
+            }
+            if (!ok) atomicExch(p.status, 12);
+        }
+    } else {
+        // ------------------------------------------------------------------------------------ softmax, one row per thread
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+        float m_used = -INFINITY, l_sum = 0.f;
+        bool ok = true;
+        for (int j = 0; j < NT; ++j) {
+            const int buf = j & 1;
+            ok = mbar_wait(s_full + 8 * buf, (j >> 1) & 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            fence_after_sync();
+            const uint32_t tS = tS0 + buf * FA_BN + lane_base;
+            const int kbase = j * FA_BN;
+            const bool tail = kbase + FA_BN > p.Sk;
+            // pass 1: row maximum of this tile (log2 domain)
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < FA_BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tS + c, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    float v = __uint_as_float(r[e]) * p.scale_log2e;
+                    if (tail && kbase + c + e >= p.Sk) v = -INFINITY;
+                    mx = fmaxf(mx, v);
+                }
+            }
+            // raise the reference maximum only when it is far too low; O and l are rescaled then
+            const bool raise = mx > m_used + FA_RESCALE_THRESHOLD;
+            const float m_new = raise ? mx : m_used;
+            const float corr = (raise && j > 0) ? exp2f(m_used - m_new) : 1.0f;
+            if (j > 0) {
+                // O += P V of the previous tile has landed. Waited for on EVERY tile: a parity wait is only meaningful
+                // when the waiter is at most one phase behind the barrier.
+                ok = mbar_wait(o_done, (j - 1) & 1);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                fence_after_sync();
+            }
+            if (j > 0 && __any_sync(0xffffffffu, raise)) {
+#pragma unroll 1
+                for (int c = 0; c < FA_D; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tO + lane_base + c, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * corr);
+                    tmem_st_32x32(tO + lane_base + c, r);
+                }
+                tmem_st_wait();
+                fence_before_sync();
+            }
+            l_sum *= corr;
+            m_used = m_new;
+            // P buffer free? (the P V MMA of tile j-2 has finished reading it)
+            ok = mbar_wait(p_free + 8 * buf, ((j >> 1) & 1) ^ 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            // pass 2: P = exp2(S*scale - m), row sum, fp16 into swizzled shared memory
+            unsigned char* prow = sP_gen + buf * 2 * FA_TILE + row * 128;
+#pragma unroll 1
+            for (int c = 0; c < FA_BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tS + c, r);
+                tmem_ld_wait();
+                uint32_t pk[16];
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    float v0 = __uint_as_float(r[e]) * p.scale_log2e, v1 = __uint_as_float(r[e + 1]) * p.scale_log2e;
+                    float p0 = exp2f(v0 - m_used), p1 = exp2f(v1 - m_used);
+                    if (tail) {
+                        if (kbase + c + e >= p.Sk) p0 = 0.f;
+                        if (kbase + c + e + 1 >= p.Sk) p1 = 0.f;
+                    }
+                    l_sum += p0 + p1;
+                    pk[e >> 1] = pack_half2(p0, p1);
+                }
+                unsigned char* dst = prow + (c >> 6) * FA_TILE;
+                const int ch0 = (c & 63) >> 3;                 // first 16-byte chunk of these 32 keys inside the sub-tile row
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4)
+                    *reinterpret_cast<uint4*>(dst + (((ch0 + k4) ^ (row & 7)) << 4)) =
+                        make_uint4(pk[4 * k4], pk[4 * k4 + 1], pk[4 * k4 + 2], pk[4 * k4 + 3]);
+            }
+            // S consumed; P visible to the tensor core (generic -> async proxy), then signal
+            fence_before_sync();
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(s_free + 8 * buf);
+                mbar_arrive(p_full + 8 * buf);
+            }
+        }
+        if (ok) {
+            ok = mbar_wait(o_done, (NT - 1) & 1);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (!ok) {
+            if (lane == 0) atomicExch(p.status, 13);
+        } else {
+            fence_after_sync();
+            const float inv = 1.0f / l_sum;
+            const int qrow = q0 + row;
+            __half* op = p.O + (size_t)b * p.bso + (size_t)qrow * p.ldo + h * FA_D;
+#pragma unroll 1
+            for (int c = 0; c < FA_D; c += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tO + lane_base + c, r);
+                tmem_ld_wait();
+                if (qrow < p.Sq) {
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; ++k4) {
+                        uint4 o;
+                        o.x = pack_half2(__uint_as_float(r[8 * k4]) * inv, __uint_as_float(r[8 * k4 + 1]) * inv);
+                        o.y = pack_half2(__uint_as_float(r[8 * k4 + 2]) * inv, __uint_as_float(r[8 * k4 + 3]) * inv);
+                        o.z = pack_half2(__uint_as_float(r[8 * k4 + 4]) * inv, __uint_as_float(r[8 * k4 + 5]) * inv);
+                        o.w = pack_half2(__uint_as_float(r[8 * k4 + 6]) * inv, __uint_as_float(r[8 * k4 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(op + c + 8 * k4) = o;
+                    }
+                }
+            }
+        }
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        fence_after_sync();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------------
+typedef CUresult (*FaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static FaEncodeFn fa_encode_fn() {
+    static FaEncodeFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<FaEncodeFn>(f);
+    }
+    return fn;
+}
+
+// [chunks][B][rows][cols] view of a token-major buffer: box = 64 columns x 128 rows
+static int fa_encode(CUtensorMap* map, const void* base, int cols, long long rows, int B, int chunks, long long ld,
+                     long long bs, long long chunk_stride) {
+    FaEncodeFn enc = fa_encode_fn();
+    if (!enc) return KATZ_ENOTREADY;
+    cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)B, (cuuint64_t)chunks};
+    cuuint64_t strides[3] = {(cuuint64_t)ld * 2, (cuuint64_t)bs * 2, (cuuint64_t)chunk_stride * 2};
+    cuuint32_t box[4] = {(cuuint32_t)FA_D, (cuuint32_t)FA_BN, 1, 1};
+    cuuint32_t es[4] = {1, 1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, es,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : KATZ_EINVAL;
+}
+
+}  // namespace katz
+
+using namespace katz;
+
+extern "C" int katz_attention_f16(const void* Q, const void* K, const void* V, void* O, int B, int H, int Sq, int Sk,
+                                  int head_dim, int ldq, int ldk, int ldv, int ldo, long long bsq, long long bsk,
+                                  long long bsv, long long bso, float scale, int kv_chunk_rows, long long kv_chunk_stride,
+                                  void* stream) {
+    KATZ_CHECK_ARG(Q && K && V && O, KATZ_EINVAL);
+    KATZ_CHECK_ARG(head_dim == 64, KATZ_ESIZE);
+    KATZ_CHECK_ARG(B > 0 && H > 0 && Sq > 0 && Sk > 0 && B <= 65535 && H <= 65535, KATZ_ESIZE);
+    KATZ_CHECK_ARG(ldq % 8 == 0 && ldk % 8 == 0 && ldv % 8 == 0 && ldo % 8 == 0, KATZ_EALIGN);
+    KATZ_CHECK_ARG(bsq % 8 == 0 && bsk % 8 == 0 && bsv % 8 == 0 && bso % 8 == 0, KATZ_EALIGN);
+    KATZ_CHECK_ARG(aligned16(Q) && aligned16(K) && aligned16(V) && aligned16(O), KATZ_EALIGN);
+    KATZ_CHECK_ARG(ldq >= H * 64 && ldk >= H * 64 && ldv >= H * 64, KATZ_ESIZE);
+    int chunks = 1;
+    long long rows = Sk, cstride = 0;
+    if (kv_chunk_rows > 0 && kv_chunk_rows < Sk) {
+        KATZ_CHECK_ARG(kv_chunk_rows % FA_BN == 0 && Sk % kv_chunk_rows == 0 && kv_chunk_stride % 8 == 0 && kv_chunk_stride > 0,
+                       KATZ_ESIZE);
+        chunks = Sk / kv_chunk_rows;
+        rows = kv_chunk_rows;
+        cstride = kv_chunk_stride;
+    } else {
+        kv_chunk_rows = ((Sk + FA_BN - 1) / FA_BN) * FA_BN;
+    }
+    // strides of size-1 dimensions still have to be valid (non-zero multiples of 16 bytes)
+    const long long bsq_e = B > 1 ? bsq : (long long)Sq * ldq, bsk_e = B > 1 ? bsk : rows * ldk, bsv_e = B > 1 ? bsv : rows * ldv;
+    KATZ_CHECK_ARG(bsq_e > 0 && bsk_e > 0 && bsv_e > 0, KATZ_ESIZE);
+    CUtensorMap tq, tk, tv;
+    int rc = fa_encode(&tq, Q, H * 64, Sq, B, 1, ldq, bsq_e, bsq_e * B);
+    if (rc) return rc;
+    rc = fa_encode(&tk, K, H * 64, rows, B, chunks, ldk, bsk_e, chunks > 1 ? cstride : bsk_e * B);
+    if (rc) return rc;
+    rc = fa_encode(&tv, V, H * 64, rows, B, chunks, ldv, bsv_e, chunks > 1 ? cstride : bsv_e * B);
+    if (rc) return rc;
+    FaParams p{};
+    p.O = (__half*)O; p.Sq = Sq; p.Sk = Sk; p.ldo = ldo; p.bso = bso;
+    p.scale_log2e = scale * 1.44269504088896340736f;
+    p.kv_chunk_rows = kv_chunk_rows;
+    p.status = tc05_status_device_ptr();
+    if (!p.status) return KATZ_ENOTREADY;
+    static bool attr = false;
+    if (!attr) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tc05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attr = true;
+    }
+    dim3 grid((Sq + FA_BM - 1) / FA_BM, H, B);
+    attention_tc05_kernel<<<grid, FA_THREADS, FA_SMEM, (cudaStream_t)stream>>>(tq, tk, tv, p);
+    KATZ_LAUNCH_RET();
+}

@@ -403,6 +403,8 @@ static int* status_ptr() {
     return ptr;
 }
 
+int* tc05_status_device_ptr() { return status_ptr(); }
+
 // Tile width by wave efficiency: tiles of width bn cost ~bn per wave; pick the width with the least total cost.
 static int pick_bn(int m_tiles, int n_out, bool geglu) {
     const int sms = sm_count();

@@ -276,9 +276,14 @@ def attention(q, k, v, heads, out=None, scale=None, kv_chunks=None):
         out = torch.empty((B, Sq, heads * D), dtype=torch.float16, device=q.device)
     if scale is None:
         scale = D ** -0.5
-    call("katz_attention_f16_mma", _p(q), _p(k), _p(v), _p(out), B, heads, Sq, Sk, D, q.stride(1), k.stride(1),
-         v.stride(1), out.stride(1), q.stride(0), k.stride(0), v.stride(0), out.stride(0), float(scale), chunk_rows,
-         chunk_stride, _stream())
+    args = (_p(q), _p(k), _p(v), _p(out), B, heads, Sq, Sk, D, q.stride(1), k.stride(1), v.stride(1), out.stride(1),
+            q.stride(0), k.stride(0), v.stride(0), out.stride(0), float(scale), chunk_rows, chunk_stride, _stream())
+    strides_ok = all(t.stride(1) % 8 == 0 and t.stride(0) % 8 == 0 and _al16(t) for t in (q, k, v, out))
+    if (_use_tc05() and os.environ.get("KATZ_ATTN", "tc05") != "mma" and strides_ok
+            and (chunk_rows == 0 or (chunk_rows % 128 == 0 and chunk_stride % 8 == 0))):
+        call("katz_attention_f16", *args)
+    else:
+        call("katz_attention_f16_mma", *args)
     return out
 
 

@@ -36,7 +36,12 @@ def test_attention_reads_gathered_kv_chunks(cuda_device, B, H, s, P):
     ref = ops.attention(q, kv[:, :, :C], kv[:, :, C:], H)
     gathered = kv.view(B, P, s, 2 * C).permute(1, 0, 2, 3).contiguous()      # [P, B, s, 2C]: what the all-gather leaves
     out = ops.attention(q, gathered[0][:, :, :C], gathered[0][:, :, C:], H, kv_chunks=(P, s, B * s * 2 * C))
-    assert torch.equal(out, ref)
+    # same kernel on both sides when the chunks are multiples of its 128-key tile (bit-equal); 64-row chunks go to the
+    # mma.sync kernel, which differs from the tcgen05 one by accumulation order only
+    if s % 128 == 0:
+        assert torch.equal(out, ref)
+    else:
+        assert float((out.float() - ref.float()).abs().max()) < 4e-3
 
 
 @pytest.mark.parametrize("gemm", ["tc05", "mma"])

@@ -286,3 +286,45 @@ def test_feed_forward_geglu_fused(cuda_device, M, F, K, monkeypatch):
     monkeypatch.setenv("KATZ_FUSED_GEGLU", "0")
     out2 = ops.feed_forward_geglu(x, w, b)
     assert _rel(out, out2.cpu()) < 4e-3
+
+
+@pytest.mark.parametrize("B,H,Sq,Sk", [(2, 2, 256, 256), (2, 5, 1024, 77), (1, 3, 200, 130), (2, 10, 4096, 4096),
+                                       (2, 20, 1024, 1024), (1, 1, 128, 128)])
+def test_attention_tcgen05(cuda_device, B, H, Sq, Sk, monkeypatch):
+    from katz_b200 import ops
+    g = torch.Generator().manual_seed(14)
+    C = H * 64
+    qkv = (torch.randn(B, Sq, 3 * C, generator=g) * 1.5).half().cuda()
+    kv = torch.randn(B, Sk, 2 * C, generator=g).half().cuda()
+    q = qkv[:, :, :C]
+    k, v = (kv[:, :, :C], kv[:, :, C:]) if Sk != Sq else (qkv[:, :, C:2 * C], qkv[:, :, 2 * C:])
+
+    def heads(t):
+        return t.float().reshape(B, -1, H, 64).transpose(1, 2)
+    ref = F.scaled_dot_product_attention(heads(q), heads(k), heads(v)).transpose(1, 2).reshape(B, Sq, C)
+    monkeypatch.setenv("KATZ_ATTN", "tc05")
+    out = ops.attention(q, k, v, H)
+    assert ops.tc05_status() == 0
+    assert float((out.float() - ref).abs().max()) < 4e-3
+    monkeypatch.setenv("KATZ_ATTN", "mma")
+    out2 = ops.attention(q, k, v, H)
+    assert float((out.float() - out2.float()).abs().max()) < 4e-3
+
+
+def test_attention_tcgen05_large_logits_rescale(cuda_device, monkeypatch):
+    """Logits that grow along the key axis force the reference maximum (and the O accumulator) to be raised often."""
+    from katz_b200 import ops
+    monkeypatch.setenv("KATZ_ATTN", "tc05")
+    g = torch.Generator().manual_seed(15)
+    B, H, S = 1, 2, 1024
+    q = (torch.randn(B, S, H * 64, generator=g) * 3).half().cuda()
+    ramp = torch.linspace(0.2, 4.0, S)[None, :, None]
+    k = (torch.randn(B, S, H * 64, generator=g) * ramp).half().cuda()
+    v = torch.randn(B, S, H * 64, generator=g).half().cuda()
+
+    def heads(t):
+        return t.float().reshape(B, -1, H, 64).transpose(1, 2)
+    ref = F.scaled_dot_product_attention(heads(q), heads(k), heads(v)).transpose(1, 2).reshape(B, S, H * 64)
+    out = ops.attention(q, k, v, H)
+    assert ops.tc05_status() == 0
+    assert float((out.float() - ref).abs().max()) < 8e-3
