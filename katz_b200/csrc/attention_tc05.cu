@@ -50,6 +50,11 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t* r)
         "r"(r[30]), "r"(r[31])
         : "memory");
 }
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // kind::f16 instruction descriptor with an MN-major B operand (bit 16)
@@ -193,24 +198,24 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __g
                 tmem_ld_wait();
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
-                    float v = __uint_as_float(r[e]) * p.scale_log2e;
+                    float v = __uint_as_float(r[e]);
                     if (tail && kbase + c + e >= p.Sk) v = -INFINITY;
                     mx = fmaxf(mx, v);
                 }
             }
+            mx *= p.scale_log2e;                             // the scale is positive: max commutes with it
             // raise the reference maximum only when it is far too low; O and l are rescaled then
             const bool raise = mx > m_used + FA_RESCALE_THRESHOLD;
             const float m_new = raise ? mx : m_used;
             const float corr = (raise && j > 0) ? exp2f(m_used - m_new) : 1.0f;
-            if (j > 0) {
-                // O += P V of the previous tile has landed. Waited for on EVERY tile: a parity wait is only meaningful
-                // when the waiter is at most one phase behind the barrier.
-                ok = mbar_wait(o_done, (j - 1) & 1);
+            if (j > 0 && __any_sync(0xffffffffu, raise)) {
+                // O is about to be rescaled: O += P V of tile j-1 must have landed. That MMA signals p_free of the other
+                // P buffer; this thread last observed that barrier one phase back (at tile j-1, for tile j-3), so the
+                // parity wait is unambiguous.
+                ok = mbar_wait(p_free + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 fence_after_sync();
-            }
-            if (j > 0 && __any_sync(0xffffffffu, raise)) {
 #pragma unroll 1
                 for (int c = 0; c < FA_D; c += 32) {
                     uint32_t r[32];
@@ -239,8 +244,8 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __g
                 uint32_t pk[16];
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
-                    float v0 = __uint_as_float(r[e]) * p.scale_log2e, v1 = __uint_as_float(r[e + 1]) * p.scale_log2e;
-                    float p0 = exp2f(v0 - m_used), p1 = exp2f(v1 - m_used);
+                    float p0 = ex2_approx(fmaf(__uint_as_float(r[e]), p.scale_log2e, -m_used));
+                    float p1 = ex2_approx(fmaf(__uint_as_float(r[e + 1]), p.scale_log2e, -m_used));
                     if (tail) {
                         if (kbase + c + e >= p.Sk) p0 = 0.f;
                         if (kbase + c + e + 1 >= p.Sk) p1 = 0.f;
@@ -265,7 +270,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __g
             }
         }
         if (ok) {
-            ok = mbar_wait(o_done, (NT - 1) & 1);
+            ok = mbar_wait(p_free + 8 * ((NT - 1) & 1), ((NT - 1) >> 1) & 1);     // the last O += P V has landed
             ok = __all_sync(0xffffffffu, ok);
         }
         if (!ok) {

@@ -15,7 +15,9 @@
 // Further adapters / rank chunks beyond 64 are fetched synchronously into a side buffer.
 // Rounding follows the reference: fp16: delta = half(acc); delta = half(delta * s); W = half(W + delta), per adapter
 // in order. fp32: W += acc * s.
-#include "common.cuh"
+#include <cstdlib>
+
+#include "tc05.cuh"
 #include "katz_b200.h"
 
 namespace katz {
@@ -23,7 +25,7 @@ namespace katz {
 constexpr int LM_THREADS = 256;
 constexpr int LM_TN = 128;        // tile columns
 constexpr int LM_MAXR = 64;       // rank processed per pass; larger ranks loop
-constexpr int LM_MAX_LAYERS_SMEM = 1024;   // per-layer tile counts cached in shared memory up to this many layers
+constexpr int LM_MAX_LAYERS_SMEM = 896;    // per-layer tile counts cached in shared memory up to this many layers
 
 template <typename T>
 struct LmCfg;
@@ -96,15 +98,18 @@ __device__ __forceinline__ uint32_t b_off(int r, int c) {
     if constexpr (sizeof(T) == 2) return r * 128 + ((c ^ (r & 7)) << 4);
     else return (r * LmCfg<float>::BP + c * 4) * 4;
 }
-template <typename T>
+// TC05: the A tile is the MN-major operand of tcgen05.mma: two blocks of [64 k-rows][64 columns], each row 128 bytes
+// with the 128-byte swizzle, 8 KB per block (the layout a TMA SWIZZLE_128B load of the block would produce).
+template <typename T, bool TC05 = false>
 __device__ __forceinline__ uint32_t a_off(int r, int c) {
-    if constexpr (sizeof(T) == 2) return r * 256 + ((c ^ (r & 7)) << 4);
+    if constexpr (TC05) return (c >> 3) * 8192 + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+    else if constexpr (sizeof(T) == 2) return r * 256 + ((c ^ (r & 7)) << 4);
     else return (r * LmCfg<float>::AP + c * 4) * 4;
 }
 
 // Adapter tiles for rank chunk [k0, k0+kr) of adapter l: B rows row0.., A cols col0..; ASYNC = cp.async into the ring,
 // otherwise plain 16-byte loads and stores into the side buffer.
-template <typename T, bool ASYNC>
+template <typename T, bool ASYNC, bool TC05 = false>
 __device__ __forceinline__ void load_adapter_tiles(const TileRef<T>& t, int l, int k0, unsigned char* sB, unsigned char* sA) {
     constexpr int ES = sizeof(T), EPC = 16 / ES, TM = LmCfg<T>::TM, W_CHUNKS_ROW = LM_TN / EPC;
     const T* Bm = reinterpret_cast<const T*>(t.L->B[l]);
@@ -134,11 +139,11 @@ __device__ __forceinline__ void load_adapter_tiles(const TileRef<T>& t, int l, i
         const bool ok = r < kr && gc < t.in_f;
         const T* src = ok ? Am + (size_t)(k0 + r) * t.in_f + gc : Am;
         if (ASYNC) {
-            cp_async16(smem_u32(sA + a_off<T>(r, c)), src, ok ? 16 : 0);
+            cp_async16(smem_u32(sA + a_off<T, TC05>(r, c)), src, ok ? 16 : 0);
         } else {
             uint4 v = make_uint4(0, 0, 0, 0);
             if (ok) v = *reinterpret_cast<const uint4*>(src);
-            *reinterpret_cast<uint4*>(sA + a_off<T>(r, c)) = v;
+            *reinterpret_cast<uint4*>(sA + a_off<T, TC05>(r, c)) = v;
         }
     }
 }
@@ -355,6 +360,179 @@ __global__ void __launch_bounds__(LM_THREADS, 1) lora_merge_kernel(const katz_lo
     cp_async_wait<0>();
 }
 
+// ---- fp16 weights, rank-r product on the tcgen05 tensor path -------------------------------------------------------
+// Same ring, same tile walk and the same rounding as lora_merge_kernel<__half>; the difference is where the product
+// is computed. The B tile ([128 rows][64 k], K-major) and the A tile (two [64 k][64 n] MN-major blocks) sit in shared
+// memory in the 128-byte-swizzled layouts tcgen05.mma reads, one elected thread issues 128x64x16 MMAs into a 128-column
+// TMEM accumulator, and all eight warps read the accumulator back (a thread owns one tile row: tcgen05.ld 32x32b) and
+// fold it into the W tile in shared memory with 16-byte accesses. The CUDA cores no longer run ldmatrix/mma.sync.
+__global__ void __launch_bounds__(LM_THREADS, 1) lora_merge_f16_tc05_kernel(const katz_lora_layer* __restrict__ layers,
+                                                                           const int* __restrict__ tile_start, int n_layers,
+                                                                           int total_tiles, float sign, int counts_in_smem,
+                                                                           int* __restrict__ status) {
+    using namespace tc05;
+    using T = __half;
+    using Cfg = LmCfg<__half>;
+    constexpr int TM = Cfg::TM, NST = Cfg::NST, EPC = 8, W_CHUNKS_ROW = LM_TN / EPC;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* xB = smem + NST * Cfg::STAGE;
+    unsigned char* xA = xB + Cfg::B_BYTES;
+    __shared__ unsigned short s_count[LM_MAX_LAYERS_SMEM];
+    __shared__ TileRef<T> s_ref[NST];
+    __shared__ __align__(8) uint64_t s_bar;
+    __shared__ uint32_t s_tmem;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        mbar_init(smem_u32(&s_bar), 1);
+        fence_barrier_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&s_tmem), 128);
+        tmem_relinquish();
+    }
+    if (counts_in_smem)
+        for (int i = tid; i < n_layers; i += LM_THREADS)
+            s_count[i] = (unsigned short)((i + 1 < n_layers ? tile_start[i + 1] : total_tiles) - tile_start[i]);
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = s_tmem;
+    const uint32_t bar = smem_u32(&s_bar);
+    uint32_t bar_phase = 0;
+    bool ok = true;
+    int cur_li = 0, cur_start = 0;
+
+    auto issue = [&](int j) {
+        const int tile = blockIdx.x + j * gridDim.x;
+        if (tile < total_tiles) {
+            unsigned char* sW = smem + (j % NST) * Cfg::STAGE;
+            if (counts_in_smem) {
+                while (tile >= cur_start + (int)s_count[cur_li]) {
+                    cur_start += s_count[cur_li];
+                    ++cur_li;
+                }
+            } else {
+                cur_li = find_layer(tile_start, n_layers, tile);
+                cur_start = tile_start[cur_li];
+            }
+            const TileRef<T> t = decode_tile<T>(layers, cur_li, cur_start, tile);
+            if (tid == 0) s_ref[j % NST] = t;
+            const T* Wsrc = t.L->W0 ? reinterpret_cast<const T*>(t.L->W0) : t.W;
+            for (int idx = tid; idx < TM * W_CHUNKS_ROW; idx += LM_THREADS) {
+                const int r = idx / W_CHUNKS_ROW, c = idx - r * W_CHUNKS_ROW;
+                const int gr = t.row0 + r, gc = t.col0 + c * EPC;
+                const bool in = gr < t.out_f && gc < t.in_f;
+                const T* src = in ? Wsrc + (size_t)gr * t.in_f + gc : Wsrc;
+                cp_async16(smem_u32(sW + w_off<T>(r, c)), src, in ? 16 : 0);
+            }
+            if (t.n_lora > 0)
+                load_adapter_tiles<T, true, true>(t, 0, 0, sW + Cfg::W_BYTES, sW + Cfg::W_BYTES + Cfg::B_BYTES);
+        }
+        cp_async_commit();
+    };
+
+#pragma unroll
+    for (int j = 0; j < NST - 1; ++j) issue(j);
+
+    const int q = warp & 3, half = warp >> 2;          // TMEM lane quarter, 64-column half of the tile
+    const int row = q * 32 + lane;
+    for (int j = 0;; ++j) {
+        const int tile = blockIdx.x + j * gridDim.x;
+        if (tile >= total_tiles) break;
+        cp_async_wait<NST - 2>();
+        fence_proxy_async();           // the copied tiles are about to be read by the tensor core (async proxy)
+        __syncthreads();
+        issue(j + NST - 1);
+
+        unsigned char* sW = smem + (j % NST) * Cfg::STAGE;
+        const TileRef<T> t = s_ref[j % NST];
+
+        for (int l = 0; l < t.n_lora; ++l) {
+            const int rank = l == 0 ? t.rank0 : t.L->rank[l];
+            const float s = (l == 0 ? t.scale0 : t.L->scale[l]) * sign;
+            for (int k0 = 0; k0 < rank; k0 += LM_MAXR) {
+                uint32_t sBa, sAa;
+                if (l == 0 && k0 == 0) {
+                    sBa = smem_u32(sW + Cfg::W_BYTES);
+                    sAa = sBa + Cfg::B_BYTES;
+                } else {
+                    __syncthreads();
+                    load_adapter_tiles<T, false, true>(t, l, k0, xB, xA);
+                    fence_proxy_async();
+                    __syncthreads();
+                    sBa = smem_u32(xB);
+                    sAa = smem_u32(xA);
+                }
+                const int kpad = (min(LM_MAXR, rank - k0) + 15) & ~15;
+                if (tid == 0) {
+                    fence_after_sync();
+                    constexpr uint32_t idesc = idesc_f16(128, 64) | (1u << 16);     // B operand MN-major
+#pragma unroll
+                    for (int nb = 0; nb < 2; ++nb)
+                        for (int ks = 0; ks < kpad / 16; ++ks)
+                            umma_f16(tmem_base + nb * 64, smem_desc_sw128(sBa) + 2 * ks,
+                                     smem_desc_sw128(sAa + nb * 8192 + ks * 2048), idesc, (k0 | ks) != 0);
+                    umma_commit(bar);
+                }
+                ok = ok && mbar_wait(bar, bar_phase);
+                bar_phase ^= 1;
+                fence_after_sync();
+            }
+            ok = __syncthreads_and(ok);        // block-uniform: either every warp goes on or every warp unwinds
+            if (!ok) break;
+            // fold: thread = tile row, 64 columns of this warp's half, 8 columns (16 bytes of W) at a time
+#pragma unroll
+            for (int c = 0; c < 64; c += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + half * 64 + c, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int g8 = 0; g8 < 4; ++g8) {
+                    const int chunk = (half * 64 + c + g8 * 8) >> 3;
+                    uint4* wp = reinterpret_cast<uint4*>(sW + w_off<T>(row, chunk));
+                    uint4 w = *wp;
+                    uint32_t wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 wf = unpack_half2(wv[e]);
+                        float d0 = __half2float(__float2half_rn(__uint_as_float(r[g8 * 8 + 2 * e])));
+                        float d1 = __half2float(__float2half_rn(__uint_as_float(r[g8 * 8 + 2 * e + 1])));
+                        d0 = __half2float(__float2half_rn(d0 * s));
+                        d1 = __half2float(__float2half_rn(d1 * s));
+                        wv[e] = pack_half2(wf.x + d0, wf.y + d1);
+                    }
+                    *wp = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                }
+            }
+            fence_before_sync();       // accumulator reads done before the next MMA may overwrite it (after a barrier)
+        }
+        if (!ok) break;
+        __syncthreads();
+
+        T* Wdst = t.W;
+        for (int idx = tid; idx < TM * W_CHUNKS_ROW; idx += LM_THREADS) {
+            const int r = idx / W_CHUNKS_ROW, c = idx - r * W_CHUNKS_ROW;
+            const int gr = t.row0 + r, gc = t.col0 + c * EPC;
+            if (gr < t.out_f && gc < t.in_f) {
+                const uint4 v = *reinterpret_cast<const uint4*>(sW + w_off<T>(r, c));
+                *reinterpret_cast<uint4*>(Wdst + (size_t)gr * t.in_f + gc) = v;
+            }
+        }
+    }
+    cp_async_wait<0>();
+    if (!ok && tid == 0) atomicExch(status, 21);
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 0) {
+        fence_after_sync();
+        tmem_dealloc(tmem_base, 128);
+    }
+}
+
+int* tc05_status_device_ptr();   // gemm_tc05.cu
+
 static int lm_sm_count() {
     static int n = 0;
     if (!n) {
@@ -389,7 +567,24 @@ extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_til
     }
     const int grid = total_tiles < lm_sm_count() ? total_tiles : lm_sm_count();
     const int in_smem = (n_layers <= LM_MAX_LAYERS_SMEM && max_tiles_per_layer > 0 && max_tiles_per_layer < 65536) ? 1 : 0;
-    if (w_dtype == KATZ_DTYPE_F16)
+    static int use_tc05 = -1;
+    if (use_tc05 < 0) {
+        const char* e = getenv("KATZ_LORA_MMA");
+        use_tc05 = (e && e[0] == '1') ? 0 : 1;
+    }
+    if (w_dtype == KATZ_DTYPE_F16 && use_tc05) {
+        static bool attr2 = false;
+        if (!attr2) {
+            cudaError_t e = cudaFuncSetAttribute(lora_merge_f16_tc05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 LmCfg<__half>::SMEM + 1024);
+            if (e != cudaSuccess) return (int)e;
+            attr2 = true;
+        }
+        int* status = tc05_status_device_ptr();
+        if (!status) return KATZ_ENOTREADY;
+        lora_merge_f16_tc05_kernel<<<grid, LM_THREADS, LmCfg<__half>::SMEM + 1024, st>>>(d_layers, d_tile_start, n_layers,
+                                                                                          total_tiles, sign, in_smem, status);
+    } else if (w_dtype == KATZ_DTYPE_F16)
         lora_merge_kernel<__half><<<grid, LM_THREADS, LmCfg<__half>::SMEM, st>>>(d_layers, d_tile_start, n_layers, total_tiles, sign, in_smem);
     else
         lora_merge_kernel<float><<<grid, LM_THREADS, LmCfg<float>::SMEM, st>>>(d_layers, d_tile_start, n_layers, total_tiles, sign, in_smem);
