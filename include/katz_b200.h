@@ -67,9 +67,12 @@ int katz_lora_layer_check(const katz_lora_layer* h_layer, int w_dtype);
  * `unet.load_state_dict(deepcopy(default_unet_state_dict))` (sdxl_unet_server.py:217). sign = -1 with W0 = NULL is the
  * subtractive unmerge of LoRACompatibleLinear._unfuse_lora (diffusers/models/lora.py:427-449).
  * `max_tiles_per_layer` (the largest per-layer tile count, or 0 if unknown) lets the kernel keep the tile -> layer table
- * in shared memory. */
+ * in shared memory. `flags`: KATZ_LORA_UNIFORM_TILES promises that every layer has out and in multiples of 128, at
+ * most one adapter, and that adapter's rank is a multiple of 16 not above 64 — the fp16 fast path (bulk-copy staged,
+ * warp-specialised) needs it; without the flag the general kernel runs. */
+#define KATZ_LORA_UNIFORM_TILES 1
 int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_tile_start, int n_layers, int total_tiles, int w_dtype,
-                    float sign, int max_tiles_per_layer, void* stream);
+                    float sign, int max_tiles_per_layer, int flags, void* stream);
 
 /* -------------------------------------------------------------------------------------- fast_kernel drop-ins ---- */
 /* fast_kernel::group_norm_fp16 (fast_kernel/csrc/group_norm.cuh:7-15, group_norm.cu:224-274), channels-last input.

@@ -189,20 +189,28 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __g
             const uint32_t tS = tS0 + buf * FA_BN + lane_base;
             const int kbase = j * FA_BN;
             const bool tail = kbase + FA_BN > p.Sk;
-            // pass 1: row maximum of this tile (log2 domain)
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < FA_BN; c += 32) {
-                uint32_t r[32];
-                tmem_ld_32x32(tS + c, r);
-                tmem_ld_wait();
+            // the whole S row (128 fp32) comes into registers with ONE wait: four TMEM loads in flight together
+            uint32_t r[FA_BN];
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    float v = __uint_as_float(r[e]);
-                    if (tail && kbase + c + e >= p.Sk) v = -INFINITY;
-                    mx = fmaxf(mx, v);
-                }
+            for (int c = 0; c < FA_BN; c += 32) tmem_ld_32x32(tS + c, r + c);
+            tmem_ld_wait();
+            // S is in registers: the accumulator buffer can take the next Q K^T already
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free + 8 * buf);
+            if (tail) {
+#pragma unroll
+                for (int e = 0; e < FA_BN; ++e)
+                    if (kbase + e >= p.Sk) r[e] = __float_as_uint(-INFINITY);
             }
+            // row maximum with four independent chains
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int e = 0; e < FA_BN; e += 4) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], __uint_as_float(r[e + u]));
+            }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             mx *= p.scale_log2e;                             // the scale is positive: max commutes with it
             // raise the reference maximum only when it is far too low; O and l are rescaled then
             const bool raise = mx > m_used + FA_RESCALE_THRESHOLD;
@@ -234,23 +242,17 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __g
             ok = mbar_wait(p_free + 8 * buf, ((j >> 1) & 1) ^ 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            // pass 2: P = exp2(S*scale - m), row sum, fp16 into swizzled shared memory
+            // P = exp2(S*scale - m) (masked keys hold -inf -> 0), row sum on four chains, fp16 into swizzled shared memory
             unsigned char* prow = sP_gen + buf * 2 * FA_TILE + row * 128;
-#pragma unroll 1
+            float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
             for (int c = 0; c < FA_BN; c += 32) {
-                uint32_t r[32];
-                tmem_ld_32x32(tS + c, r);
-                tmem_ld_wait();
                 uint32_t pk[16];
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
-                    float p0 = ex2_approx(fmaf(__uint_as_float(r[e]), p.scale_log2e, -m_used));
-                    float p1 = ex2_approx(fmaf(__uint_as_float(r[e + 1]), p.scale_log2e, -m_used));
-                    if (tail) {
-                        if (kbase + c + e >= p.Sk) p0 = 0.f;
-                        if (kbase + c + e + 1 >= p.Sk) p1 = 0.f;
-                    }
-                    l_sum += p0 + p1;
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(r[c + e]), p.scale_log2e, -m_used));
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(r[c + e + 1]), p.scale_log2e, -m_used));
+                    ls4[(e >> 1) & 3] += p0 + p1;
                     pk[e >> 1] = pack_half2(p0, p1);
                 }
                 unsigned char* dst = prow + (c >> 6) * FA_TILE;
@@ -260,14 +262,11 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __g
                     *reinterpret_cast<uint4*>(dst + (((ch0 + k4) ^ (row & 7)) << 4)) =
                         make_uint4(pk[4 * k4], pk[4 * k4 + 1], pk[4 * k4 + 2], pk[4 * k4 + 3]);
             }
-            // S consumed; P visible to the tensor core (generic -> async proxy), then signal
-            fence_before_sync();
+            l_sum += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+            // P visible to the tensor core (generic -> async proxy), then signal
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(s_free + 8 * buf);
-                mbar_arrive(p_full + 8 * buf);
-            }
+            if (lane == 0) mbar_arrive(p_full + 8 * buf);
         }
         if (ok) {
             ok = mbar_wait(p_free + 8 * ((NT - 1) & 1), ((NT - 1) >> 1) & 1);     // the last O += P V has landed

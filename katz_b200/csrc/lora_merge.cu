@@ -531,6 +531,208 @@ __global__ void __launch_bounds__(LM_THREADS, 1) lora_merge_f16_tc05_kernel(cons
     }
 }
 
+// ---- fp16, warp-specialised, bulk-copy staged ------------------------------------------------------------------------
+// The fast path for the common request: every layer has at most one adapter of rank <= 64 and dimensions that are
+// multiples of the 128x128 tile. Three roles per persistent CTA, so no role ever waits for another's latency:
+//   * warps 0-1 (producers): find the tile's layer, start 128 bulk copies (one 256-byte W row each, completion counted
+//     on an mbarrier) into a padded row-major tile, and copy the adapter's B and A tiles with 16-byte async copies
+//     into the swizzled layouts tcgen05.mma reads;
+//   * warp 2, one thread: delta = B A as 128x64x16 tcgen05.mma instructions into one of two TMEM accumulators;
+//   * warps 4-7 (128 threads, one per tile row): read the row's delta from TMEM, fold it into the row of W in shared
+//     memory with the reference's rounding, and send the finished row back to HBM with one 256-byte bulk store.
+// Stage reuse is gated on the bulk stores having read the stage (cp.async.bulk.wait_group.read), so loads of tile
+// j+2, the product of tile j+1 and the write-back of tile j are all in flight together.
+constexpr int WS_NST = 3;
+constexpr int WS_WPITCH = 272;                                   // 256-byte rows + 16: conflict-free 16-byte row accesses
+constexpr int WS_W_BYTES = 128 * WS_WPITCH;                       // 34816
+constexpr int WS_W_PAD = 36 * 1024;                               // B tile must start on a 1024-byte boundary
+constexpr int WS_STAGE = WS_W_PAD + 16384 + 16384;                // 69632
+constexpr int WS_SMEM = WS_NST * WS_STAGE + 1024;
+constexpr int WS_THREADS = 256;
+
+__global__ void __launch_bounds__(WS_THREADS, 1) lora_merge_f16_ws_kernel(const katz_lora_layer* __restrict__ layers,
+                                                                         const int* __restrict__ tile_start, int n_layers,
+                                                                         int total_tiles, float sign, int counts_in_smem,
+                                                                         int* __restrict__ status) {
+    using namespace tc05;
+    using T = __half;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ unsigned short s_count[LM_MAX_LAYERS_SMEM];
+    __shared__ TileRef<T> s_ref[WS_NST];
+    __shared__ __align__(8) uint64_t s_bars[2 * WS_NST + 4];
+    __shared__ uint32_t s_tmem;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t full0 = smem_u32(s_bars), empty0 = full0 + 8 * WS_NST, afull0 = empty0 + 8 * WS_NST, aempty0 = afull0 + 16;
+    if (tid == 0) {
+        for (int s = 0; s < WS_NST; ++s) {
+            mbar_init(full0 + 8 * s, 1 + 64);      // one expect_tx arrival + one async-copy arrival per producer thread
+            mbar_init(empty0 + 8 * s, 128);        // one arrival per fold thread (its row's store has read the stage)
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(afull0 + 8 * b, 1);
+            mbar_init(aempty0 + 8 * b, 4);
+        }
+        fence_barrier_init();
+    }
+    if (warp == 2) {
+        tmem_alloc(smem_u32(&s_tmem), 256);
+        tmem_relinquish();
+    }
+    if (counts_in_smem)
+        for (int i = tid; i < n_layers; i += WS_THREADS)
+            s_count[i] = (unsigned short)((i + 1 < n_layers ? tile_start[i + 1] : total_tiles) - tile_start[i]);
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = s_tmem;
+    bool ok = true;
+
+    if (warp < 2) {
+        // ------------------------------------------------------------------------------------ producers (64 threads)
+        int cur_li = 0, cur_start = 0;
+        int j = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++j) {
+            const int s = j % WS_NST;
+            if (!mbar_wait(empty0 + 8 * s, ((j / WS_NST) & 1) ^ 1)) { ok = false; break; }
+            if (counts_in_smem) {
+                while (tile >= cur_start + (int)s_count[cur_li]) {
+                    cur_start += s_count[cur_li];
+                    ++cur_li;
+                }
+            } else {
+                cur_li = find_layer(tile_start, n_layers, tile);
+                cur_start = tile_start[cur_li];
+            }
+            const TileRef<T> t = decode_tile<T>(layers, cur_li, cur_start, tile);
+            unsigned char* sW = smem + s * WS_STAGE;
+            const uint32_t fb = full0 + 8 * s;
+            if (tid == 0) {
+                s_ref[s] = t;
+                mbar_expect_tx(fb, 128 * 256);
+            }
+            __syncwarp();
+            const T* Wsrc = t.L->W0 ? reinterpret_cast<const T*>(t.L->W0) : t.W;
+            // thread 0 arms the barrier and publishes the tile, then both producer warps copy
+            asm volatile("bar.sync 1, 64;" ::: "memory");     // named barrier: the two producer warps only
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int r = tid + i * 64;
+                bulk_load(smem_u32(sW + r * WS_WPITCH), Wsrc + (size_t)(t.row0 + r) * t.in_f + t.col0, 256, fb);
+            }
+            if (t.n_lora > 0) {
+                unsigned char* sB = sW + WS_W_PAD;
+                unsigned char* sA = sB + 16384;
+                const T* Bm = reinterpret_cast<const T*>(t.L->B[0]);
+                const T* Am = reinterpret_cast<const T*>(t.L->A[0]);
+                const int rank = t.rank0;
+                const int kpad = (rank + 15) & ~15;
+                const int bchunks = kpad >> 3;
+                for (int idx = tid; idx < 128 * 8; idx += 64) {
+                    const int r = idx >> 3, c = idx & 7;
+                    if (c >= bchunks) continue;
+                    const bool in = (c * 8) < rank;
+                    const T* src = in ? Bm + (size_t)(t.row0 + r) * rank + c * 8 : Bm;
+                    cp_async16(smem_u32(sB + b_off<T>(r, c)), src, in ? 16 : 0);
+                }
+                for (int idx = tid; idx < kpad * 16; idx += 64) {
+                    const int r = idx >> 4, c = idx & 15;
+                    const bool in = r < rank;
+                    const T* src = in ? Am + (size_t)r * t.in_f + t.col0 + c * 8 : Am;
+                    cp_async16(smem_u32(sA + a_off<T, true>(r, c)), src, in ? 16 : 0);
+                }
+            }
+            cp_async_mbar_arrive_noinc(fb);
+        }
+        if (!ok && lane == 0) atomicExch(status, 31);
+        cp_async_wait<0>();
+    } else if (warp == 2) {
+        // ------------------------------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            int j = 0;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++j) {
+                const int s = j % WS_NST, b = j & 1;
+                if (!mbar_wait(full0 + 8 * s, (j / WS_NST) & 1)) { ok = false; break; }
+                if (!mbar_wait(aempty0 + 8 * b, ((j >> 1) & 1) ^ 1)) { ok = false; break; }
+                const TileRef<T> t = s_ref[s];
+                if (t.n_lora > 0) {
+                    fence_proxy_async();          // async-copy writes of B/A -> tensor-core reads
+                    fence_after_sync();
+                    const uint32_t sBa = smem_u32(smem + s * WS_STAGE + WS_W_PAD), sAa = sBa + 16384;
+                    const int kpad = (t.rank0 + 15) & ~15;
+                    constexpr uint32_t idesc = idesc_f16(128, 64) | (1u << 16);     // B operand MN-major
+#pragma unroll
+                    for (int nb = 0; nb < 2; ++nb)
+                        for (int ks = 0; ks < kpad / 16; ++ks)
+                            umma_f16(tmem_base + b * 128 + nb * 64, smem_desc_sw128(sBa) + 2 * ks,
+                                     smem_desc_sw128(sAa + nb * 8192 + ks * 2048), idesc, ks != 0);
+                }
+                umma_commit(afull0 + 8 * b);      // with no MMA outstanding this arrives at once (plain restore tiles)
+            }
+            if (!ok) atomicExch(status, 32);
+        }
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------------------------------ fold + write-back (128 threads)
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        int j = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++j) {
+            const int s = j % WS_NST, b = j & 1;
+            ok = mbar_wait(full0 + 8 * s, (j / WS_NST) & 1) && mbar_wait(afull0 + 8 * b, (j >> 1) & 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            fence_after_sync();
+            const TileRef<T> t = s_ref[s];
+            unsigned char* wrow = smem + s * WS_STAGE + row * WS_WPITCH;
+            if (t.n_lora > 0) {
+                const float sc = t.scale0 * sign;
+                uint32_t r[128];
+#pragma unroll
+                for (int c = 0; c < 128; c += 32) tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + b * 128 + c, r + c);
+                tmem_ld_wait();
+                fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(aempty0 + 8 * b);
+#pragma unroll
+                for (int ch = 0; ch < 16; ++ch) {
+                    uint4* wp = reinterpret_cast<uint4*>(wrow + ch * 16);
+                    const uint4 w = *wp;
+                    uint32_t wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 wf = unpack_half2(wv[e]);
+                        float d0 = __half2float(__float2half_rn(__uint_as_float(r[ch * 8 + 2 * e])));
+                        float d1 = __half2float(__float2half_rn(__uint_as_float(r[ch * 8 + 2 * e + 1])));
+                        d0 = __half2float(__float2half_rn(d0 * sc));
+                        d1 = __half2float(__float2half_rn(d1 * sc));
+                        wv[e] = pack_half2(wf.x + d0, wf.y + d1);
+                    }
+                    *wp = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                }
+                fence_proxy_async();              // this thread's row update -> visible to its bulk store
+            } else {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(aempty0 + 8 * b);
+            }
+            bulk_store(t.W + (size_t)(t.row0 + row) * t.in_f + t.col0, smem_u32(wrow), 256);
+            bulk_commit();
+            if (j > 0) {
+                bulk_wait_read<1>();              // the previous tile's store has read its stage
+                mbar_arrive(empty0 + 8 * ((j - 1) % WS_NST));
+            }
+        }
+        bulk_wait<0>();
+        if (!ok && lane == 0) atomicExch(status, 33);
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 2) {
+        fence_after_sync();
+        tmem_dealloc(tmem_base, 256);
+    }
+}
+
 int* tc05_status_device_ptr();   // gemm_tc05.cu
 
 static int lm_sm_count() {
@@ -551,7 +753,7 @@ extern "C" int katz_lora_tile_rows(int w_dtype) { return w_dtype == KATZ_DTYPE_F
 extern "C" int katz_lora_tile_cols(void) { return LM_TN; }
 
 extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_tile_start, int n_layers, int total_tiles,
-                               int w_dtype, float sign, int max_tiles_per_layer, void* stream) {
+                               int w_dtype, float sign, int max_tiles_per_layer, int flags, void* stream) {
     KATZ_CHECK_ARG(d_layers && d_tile_start, KATZ_EINVAL);
     KATZ_CHECK_ARG(n_layers > 0 && total_tiles > 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(w_dtype == KATZ_DTYPE_F16 || w_dtype == KATZ_DTYPE_F32, KATZ_EINVAL);
@@ -572,7 +774,18 @@ extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_til
         const char* e = getenv("KATZ_LORA_MMA");
         use_tc05 = (e && e[0] == '1') ? 0 : 1;
     }
-    if (w_dtype == KATZ_DTYPE_F16 && use_tc05) {
+    if (w_dtype == KATZ_DTYPE_F16 && use_tc05 && (flags & KATZ_LORA_UNIFORM_TILES)) {
+        static bool attr3 = false;
+        if (!attr3) {
+            cudaError_t e = cudaFuncSetAttribute(lora_merge_f16_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WS_SMEM);
+            if (e != cudaSuccess) return (int)e;
+            attr3 = true;
+        }
+        int* status = tc05_status_device_ptr();
+        if (!status) return KATZ_ENOTREADY;
+        lora_merge_f16_ws_kernel<<<grid, WS_THREADS, WS_SMEM, st>>>(d_layers, d_tile_start, n_layers, total_tiles, sign, in_smem,
+                                                                    status);
+    } else if (w_dtype == KATZ_DTYPE_F16 && use_tc05) {
         static bool attr2 = false;
         if (!attr2) {
             cudaError_t e = cudaFuncSetAttribute(lora_merge_f16_tc05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -125,6 +125,14 @@ class LoraMerger:
             e.n_lora = n
             _lib.check(lib.katz_lora_layer_check(ctypes.byref(e), self.code), "katz_lora_layer_check(%s)" % k)
         self._keepalive = keep
+        # the fast path's promise: 128-aligned dimensions, at most one adapter per layer, rank a multiple of 16 up to 64
+        uniform = all(w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0 for w in self.weights.values())
+        for i in range(len(self.keys)):
+            e = self._h_table[i]
+            if e.n_lora > 1 or (e.n_lora == 1 and (e.rank[0] % 16 or e.rank[0] > 64)):
+                uniform = False
+                break
+        self._flags = 1 if uniform else 0
         ctypes.memmove(self._h_pinned.data_ptr(), ctypes.addressof(self._h_table), ctypes.sizeof(self._h_table))
         self._d_table.copy_(self._h_pinned, non_blocking=True)
         self._upload_done = torch.cuda.Event()
@@ -134,7 +142,8 @@ class LoraMerger:
         lib = _lib.load()
         st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
         _lib.check(lib.katz_lora_merge(ctypes.c_void_p(self._d_table.data_ptr()), ctypes.c_void_p(self.d_tile_start.data_ptr()),
-                                       len(self.keys), self.total_tiles, self.code, float(sign), self.max_tiles_per_layer, st),
+                                       len(self.keys), self.total_tiles, self.code, float(sign), self.max_tiles_per_layer,
+                                       self._flags, st),
                    "katz_lora_merge")
         _lib.note_launches(1)
 
