@@ -272,8 +272,10 @@ def main():
     # ---- LoRA merge: HBM-bound pass, timed alone (weights 4.4 GB >> L2)
     for _ in range(3):
         merger.merge(lora, 1.0)
-    merge_ms = time_events(lambda: merger.merge(lora, 1.0), 10)
-    restore_ms = time_events(lambda: merger.restore(), 5)
+    merge_request_ms = time_events(lambda: merger.merge(lora, 1.0), 10)     # host table build + upload + kernel
+    merge_ms = time_events(lambda: merger.replay(), 10)                     # the kernel alone, table resident
+    merger.restore()
+    restore_ms = time_events(lambda: merger.replay(), 5)
     merger.merge(lora, 1.0)
     merge_bytes = merger.algorithmic_bytes([64])
     merge_gbs = merge_bytes / (merge_ms * 1e-3) / 1e9
@@ -396,7 +398,7 @@ def main():
                               "unit": "TFLOP/s", "frac": step_tflops / peaks["bf16_tflops_sustained"],
                               "peak_source": peaks["_source"] + " sustained", "flop_per_step": flops["total"],
                               "note": "per-GPU algorithmic FLOPs of the whole step / step time"},
-            "lora_merge": {"bound": "hbm", "ms": merge_ms, "restore_ms": restore_ms, "bytes": merge_bytes, "achieved": merge_gbs,
+            "lora_merge": {"bound": "hbm", "ms": merge_ms, "restore_ms": restore_ms, "request_ms": merge_request_ms, "bytes": merge_bytes, "achieved": merge_gbs,
                            "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": merge_gbs / peaks["hbm_gbs"],
                            "layers": len(keys), "rank": 64, "peak_source": peaks["_source"]},
         }

@@ -61,18 +61,28 @@ int katz_lora_tile_rows(int w_dtype);
 int katz_lora_tile_cols(void);
 /* Host-side validation of one table entry before it is uploaded. */
 int katz_lora_layer_check(const katz_lora_layer* h_layer, int w_dtype);
+/* The same over a whole host table; *bad_index (optional) receives the index of the first bad entry. */
+int katz_lora_table_check(const katz_lora_layer* h_layers, int n_layers, int w_dtype, int* bad_index);
 /* W = (W0 ? W0 : W) + sign * sum_i scale_i * B_i @ A_i over every layer of the table, one launch.
  * Replaces lora_utils.patch_on_lora's loop (lora_utils.py:28-33), StableDiffusionXLControlNetPipelineKatz.patch_on_lora
  * (pipelines/controlnet/pipeline_controlnet_sd_xl_katz.py:1741-1747) and, with n_lora = 0 and W0 set, the restore
  * `unet.load_state_dict(deepcopy(default_unet_state_dict))` (sdxl_unet_server.py:217). sign = -1 with W0 = NULL is the
  * subtractive unmerge of LoRACompatibleLinear._unfuse_lora (diffusers/models/lora.py:427-449).
  * `max_tiles_per_layer` (the largest per-layer tile count, or 0 if unknown) lets the kernel keep the tile -> layer table
- * in shared memory. `flags`: KATZ_LORA_UNIFORM_TILES promises that every layer has out and in multiples of 128, at
- * most one adapter, and that adapter's rank is a multiple of 16 not above 64 — the fp16 fast path (bulk-copy staged,
- * warp-specialised) needs it; without the flag the general kernel runs. */
+ * in shared memory. `flags`: KATZ_LORA_UNIFORM_TILES promises that every layer has at most one adapter and that its rank
+ * is at most 64. With the flag, fp16 weights and `d_tile_maps` (device copy of what katz_lora_encode_tile_maps wrote, 64-byte
+ * aligned) the TMA-tiled warp-specialised kernel runs; otherwise, or with d_tile_maps NULL, the general kernel. */
 #define KATZ_LORA_UNIFORM_TILES 1
+/* KATZ_LORA_NO_ADAPTERS additionally promises n_lora == 0 in every layer (a pure restore): a scheduling hint only. */
+#define KATZ_LORA_NO_ADAPTERS 2
 int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_tile_start, int n_layers, int total_tiles, int w_dtype,
-                    float sign, int max_tiles_per_layer, int flags, void* stream);
+                    float sign, int max_tiles_per_layer, int flags, const void* d_tile_maps, void* stream);
+
+/* Encodes, on the host, the TMA tensor maps of the fp16 fast path: 2 x 128 bytes per layer into h_maps ([2i] = W0, or W
+ * when W0 is NULL; [2i+1] = W). They depend only on the weight pointers and shapes: encode once per weight set, upload,
+ * and pass the device copy to katz_lora_merge. No reference counterpart (the reference merges layer by layer in
+ * PyTorch, lora_utils.py:29-33). */
+int katz_lora_encode_tile_maps(const katz_lora_layer* h_layers, int n_layers, void* h_maps);
 
 /* -------------------------------------------------------------------------------------- fast_kernel drop-ins ---- */
 /* fast_kernel::group_norm_fp16 (fast_kernel/csrc/group_norm.cuh:7-15, group_norm.cu:224-274), channels-last input.

@@ -17,6 +17,8 @@
 // in order. fp32: W += acc * s.
 #include <cstdlib>
 
+#include <cstring>
+
 #include "tc05.cuh"
 #include "katz_b200.h"
 
@@ -531,136 +533,223 @@ __global__ void __launch_bounds__(LM_THREADS, 1) lora_merge_f16_tc05_kernel(cons
     }
 }
 
-// ---- fp16, warp-specialised, bulk-copy staged ------------------------------------------------------------------------
-// The fast path for the common request: every layer has at most one adapter of rank <= 64 and dimensions that are
-// multiples of the 128x128 tile. Three roles per persistent CTA, so no role ever waits for another's latency:
-//   * warps 0-1 (producers): find the tile's layer, start 128 bulk copies (one 256-byte W row each, completion counted
-//     on an mbarrier) into a padded row-major tile, and copy the adapter's B and A tiles with 16-byte async copies
-//     into the swizzled layouts tcgen05.mma reads;
-//   * warp 2, one thread: delta = B A as 128x64x16 tcgen05.mma instructions into one of two TMEM accumulators;
-//   * warps 4-7 (128 threads, one per tile row): read the row's delta from TMEM, fold it into the row of W in shared
-//     memory with the reference's rounding, and send the finished row back to HBM with one 256-byte bulk store.
-// Stage reuse is gated on the bulk stores having read the stage (cp.async.bulk.wait_group.read), so loads of tile
-// j+2, the product of tile j+1 and the write-back of tile j are all in flight together.
-constexpr int WS_NST = 3;
-constexpr int WS_WPITCH = 272;                                   // 256-byte rows + 16: conflict-free 16-byte row accesses
-constexpr int WS_W_BYTES = 128 * WS_WPITCH;                       // 34816
-constexpr int WS_W_PAD = 36 * 1024;                               // B tile must start on a 1024-byte boundary
-constexpr int WS_STAGE = WS_W_PAD + 16384 + 16384;                // 69632
-constexpr int WS_SMEM = WS_NST * WS_STAGE + 1024;
-constexpr int WS_THREADS = 256;
+// ---- fp16, warp-specialised, TMA-tiled ---------------------------------------------------------------------------------
+// The fast path for the common request: every layer has at most one adapter of rank <= 64. W moves by tiled TMA, one
+// request per 128x64 box, through per-layer tensor maps that the host encodes once (the weights do not move between
+// requests); 256-byte bulk copies per row were request-rate bound in the TMA unit and slower than plain 16-byte loads.
+// Tiles are dealt to the persistent CTAs round-robin in chunks of 4 consecutive tiles, which walk along one 128-row band
+// of one layer: the layer's table entry and the adapter's B tile are read once per chunk, while neighbouring CTAs
+// still stream neighbouring addresses (whole contiguous ranges per CTA measured 35% slower, single tiles 30%: the
+// first loses DRAM locality, the second re-reads B and the table entry for every tile). A pure restore (no adapters)
+// has nothing to reuse and runs with chunks of 1.
+// Four roles, each with its own ring so that no role waits for another's latency:
+//   * warps 0-3 (one thread per tile row): read the row's delta from TMEM, fold it into the row of W in shared memory
+//     with the reference's rounding, then thread 0 sends the tile back with TMA stores (clipped at the matrix edge);
+//   * warp 4, one thread: starts the TMA loads of the pristine W tile (ring of 4 x 32 KB, two swizzled 128x64 boxes per
+//     tile; boxes past the matrix edge are zero-filled by the TMA unit);
+//   * warp 5, one thread: delta = B A as 128x64x16 tcgen05.mma instructions into one of two TMEM accumulators; the
+//     instructions' completion frees the adapter stages;
+//   * warps 6-9: copy the adapter's A tile (ring of 3) and, at the start of a band, its B tile (2 buffers) with 16-byte
+//     async copies into the layouts tcgen05.mma reads.
+// A W stage is reused once the TMA store has read it (cp.async.bulk.wait_group.read), so loads of tiles j+1..j+3, the
+// product of tile j+1 and the write-back of tile j are in flight together.
+constexpr int WS_NW = 4;                        // W ring
+constexpr int WS_NA = 3;                        // A ring
+constexpr int WS_W_BYTES = 32768;
+constexpr int WS_A_BYTES = 16384;
+constexpr int WS_B_BYTES = 16384;
+constexpr int WS_SMEM = WS_NW * WS_W_BYTES + WS_NA * WS_A_BYTES + 2 * WS_B_BYTES + 1024;
+constexpr int WS_THREADS = 320;
+constexpr int WS_PRODUCERS = 128;
+constexpr int WS_CHUNK = 4;                     // consecutive tiles per CTA turn
+constexpr int WS_MAX_LAYERS_SMEM = 2048;       // tile_start cached in shared memory up to this many layers
+
+struct WsTile {
+    int li, row0, col0, in_f, n_lora;
+    float scale;
+};
+
+// One role's view of the layer that owns the current tile; the table entry is re-read only when the layer changes.
+struct WsLayer {
+    int li = -1, start = 0, end = 0;
+    int in_f = 0, out_f = 0, n_lora = 0, rank = 0, tiles_n = 1;
+    float scale = 0.f;
+    const __half* B = nullptr;
+    const __half* A = nullptr;
+    bool has_w0 = false;
+    __device__ __forceinline__ void seek(const katz_lora_layer* __restrict__ layers, const int* tile_start, int n_layers,
+                                         int total_tiles, int tile) {
+        if (li >= 0 && tile >= start && tile < end) return;
+        li = find_layer(tile_start, n_layers, tile);
+        start = tile_start[li];
+        end = li + 1 < n_layers ? tile_start[li + 1] : total_tiles;
+        const katz_lora_layer* L = layers + li;
+        in_f = L->in_features;
+        out_f = L->out_features;
+        n_lora = L->n_lora;
+        rank = L->rank[0];
+        scale = L->scale[0];
+        B = reinterpret_cast<const __half*>(L->B[0]);
+        A = reinterpret_cast<const __half*>(L->A[0]);
+        has_w0 = L->W0 != nullptr;
+        tiles_n = (in_f + 127) >> 7;
+    }
+};
 
 __global__ void __launch_bounds__(WS_THREADS, 1) lora_merge_f16_ws_kernel(const katz_lora_layer* __restrict__ layers,
+                                                                         const CUtensorMap* __restrict__ maps,
                                                                          const int* __restrict__ tile_start, int n_layers,
-                                                                         int total_tiles, float sign, int counts_in_smem,
-                                                                         int* __restrict__ status) {
+                                                                         int total_tiles, float sign,
+                                                                         int* __restrict__ status, int CH) {
     using namespace tc05;
     using T = __half;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ unsigned short s_count[LM_MAX_LAYERS_SMEM];
-    __shared__ TileRef<T> s_ref[WS_NST];
-    __shared__ __align__(8) uint64_t s_bars[2 * WS_NST + 4];
+    unsigned char* smem_a = smem + WS_NW * WS_W_BYTES;
+    unsigned char* smem_b = smem_a + WS_NA * WS_A_BYTES;
+    __shared__ WsTile s_tile[WS_NW];
+    __shared__ int4 s_ab[WS_NA];                 // {n_lora, rank, B buffer, first tile of a band} for the A stage's tile
+    __shared__ __align__(8) uint64_t s_bars[2 * WS_NW + 2 * WS_NA + 2 + 4];
     __shared__ uint32_t s_tmem;
+    __shared__ int s_start[WS_MAX_LAYERS_SMEM];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t full0 = smem_u32(s_bars), empty0 = full0 + 8 * WS_NST, afull0 = empty0 + 8 * WS_NST, aempty0 = afull0 + 16;
+    if (n_layers <= WS_MAX_LAYERS_SMEM) {
+        for (int i = tid; i < n_layers; i += WS_THREADS) s_start[i] = tile_start[i];
+        tile_start = s_start;
+    }
+    const uint32_t wfull0 = smem_u32(s_bars), wempty0 = wfull0 + 8 * WS_NW, afull0 = wempty0 + 8 * WS_NW,
+                   aempty0 = afull0 + 8 * WS_NA, bempty0 = aempty0 + 8 * WS_NA, dfull0 = bempty0 + 16, dempty0 = dfull0 + 16;
     if (tid == 0) {
-        for (int s = 0; s < WS_NST; ++s) {
-            mbar_init(full0 + 8 * s, 1 + 64);      // one expect_tx arrival + one async-copy arrival per producer thread
-            mbar_init(empty0 + 8 * s, 128);        // one arrival per fold thread (its row's store has read the stage)
+        for (int s = 0; s < WS_NW; ++s) {
+            mbar_init(wfull0 + 8 * s, 1);          // the loader's expect_tx arrival; the TMA bytes complete it
+            mbar_init(wempty0 + 8 * s, 1);         // the storing thread, once the TMA store has read the stage
+        }
+        for (int s = 0; s < WS_NA; ++s) {
+            mbar_init(afull0 + 8 * s, 1 + WS_PRODUCERS);   // one plain arrival (publishes s_ab) + one async-copy arrival each
+            mbar_init(aempty0 + 8 * s, 1);                 // tcgen05.commit
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(afull0 + 8 * b, 1);
-            mbar_init(aempty0 + 8 * b, 4);
+            mbar_init(bempty0 + 8 * b, 1);         // tcgen05.commit at the end of the band that used the buffer
+            mbar_init(dfull0 + 8 * b, 1);          // delta accumulator ready (tcgen05.commit)
+            mbar_init(dempty0 + 8 * b, 4);         // delta accumulator read (one arrival per fold warp)
         }
         fence_barrier_init();
     }
-    if (warp == 2) {
+    if (warp == 5) {
         tmem_alloc(smem_u32(&s_tmem), 256);
         tmem_relinquish();
     }
-    if (counts_in_smem)
-        for (int i = tid; i < n_layers; i += WS_THREADS)
-            s_count[i] = (unsigned short)((i + 1 < n_layers ? tile_start[i + 1] : total_tiles) - tile_start[i]);
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem_base = s_tmem;
+    // chunks of CH consecutive tiles are dealt round-robin: tile of this CTA's j-th step, or -1 past the end
+    auto tile_of = [&](int j) {
+        const int t = (blockIdx.x + (j / CH) * gridDim.x) * CH + j % CH;
+        return t < total_tiles ? t : -1;
+    };
     bool ok = true;
 
-    if (warp < 2) {
-        // ------------------------------------------------------------------------------------ producers (64 threads)
-        int cur_li = 0, cur_start = 0;
-        int j = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++j) {
-            const int s = j % WS_NST;
-            if (!mbar_wait(empty0 + 8 * s, ((j / WS_NST) & 1) ^ 1)) { ok = false; break; }
-            if (counts_in_smem) {
-                while (tile >= cur_start + (int)s_count[cur_li]) {
-                    cur_start += s_count[cur_li];
-                    ++cur_li;
-                }
-            } else {
-                cur_li = find_layer(tile_start, n_layers, tile);
-                cur_start = tile_start[cur_li];
-            }
-            const TileRef<T> t = decode_tile<T>(layers, cur_li, cur_start, tile);
-            unsigned char* sW = smem + s * WS_STAGE;
-            const uint32_t fb = full0 + 8 * s;
-            if (tid == 0) {
-                s_ref[s] = t;
-                mbar_expect_tx(fb, 128 * 256);
-            }
-            __syncwarp();
-            const T* Wsrc = t.L->W0 ? reinterpret_cast<const T*>(t.L->W0) : t.W;
-            // thread 0 arms the barrier and publishes the tile, then both producer warps copy
-            asm volatile("bar.sync 1, 64;" ::: "memory");     // named barrier: the two producer warps only
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int r = tid + i * 64;
-                bulk_load(smem_u32(sW + r * WS_WPITCH), Wsrc + (size_t)(t.row0 + r) * t.in_f + t.col0, 256, fb);
-            }
+    if (warp < 4) {
+        // ------------------------------------------------------------------------------------ fold + write-back (128 threads)
+        const int row = tid;                      // TMEM lane = tile row; warp w reads lane quarter w
+        for (int j = 0, tile; (tile = tile_of(j)) >= 0; ++j) {
+            const int s = j % WS_NW, b = j & 1;
+            ok = mbar_wait(wfull0 + 8 * s, (j / WS_NW) & 1) && mbar_wait(dfull0 + 8 * b, (j >> 1) & 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            fence_after_sync();
+            const WsTile t = s_tile[s];
+            unsigned char* wtile = smem + s * WS_W_BYTES;
             if (t.n_lora > 0) {
-                unsigned char* sB = sW + WS_W_PAD;
-                unsigned char* sA = sB + 16384;
-                const T* Bm = reinterpret_cast<const T*>(t.L->B[0]);
-                const T* Am = reinterpret_cast<const T*>(t.L->A[0]);
-                const int rank = t.rank0;
-                const int kpad = (rank + 15) & ~15;
-                const int bchunks = kpad >> 3;
-                for (int idx = tid; idx < 128 * 8; idx += 64) {
-                    const int r = idx >> 3, c = idx & 7;
-                    if (c >= bchunks) continue;
-                    const bool in = (c * 8) < rank;
-                    const T* src = in ? Bm + (size_t)(t.row0 + r) * rank + c * 8 : Bm;
-                    cp_async16(smem_u32(sB + b_off<T>(r, c)), src, in ? 16 : 0);
+                const float sc = t.scale * sign;
+                uint32_t r[128];
+#pragma unroll
+                for (int c = 0; c < 128; c += 32) tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + b * 128 + c, r + c);
+                tmem_ld_wait();
+                fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(dempty0 + 8 * b);
+#pragma unroll
+                for (int ch = 0; ch < 16; ++ch) {
+                    // column chunk ch of this row: box ch/8, 128-byte row, 16-byte chunks XOR-swizzled by the row
+                    uint4* wp = reinterpret_cast<uint4*>(wtile + (ch >> 3) * 16384 + row * 128 + (((ch & 7) ^ (row & 7)) << 4));
+                    uint4 w = *wp;
+                    __half2* wv = reinterpret_cast<__half2*>(&w);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        // half(acc) -> half(. * scale) -> half(W + .): the fp32 sum of two halfs rounds to the same half as
+                        // the half-precision add (24 >= 2*11+2 significand bits), so the last step is one hadd2
+                        const float2 d = __half22float2(__floats2half2_rn(__uint_as_float(r[ch * 8 + 2 * e]),
+                                                                          __uint_as_float(r[ch * 8 + 2 * e + 1])));
+                        wv[e] = __hadd2(wv[e], __floats2half2_rn(__fmul_rn(d.x, sc), __fmul_rn(d.y, sc)));
+                    }
+                    *wp = w;
                 }
-                for (int idx = tid; idx < kpad * 16; idx += 64) {
-                    const int r = idx >> 4, c = idx & 15;
-                    const bool in = r < rank;
-                    const T* src = in ? Am + (size_t)r * t.in_f + t.col0 + c * 8 : Am;
-                    cp_async16(smem_u32(sA + a_off<T, true>(r, c)), src, in ? 16 : 0);
+                fence_proxy_async();              // this thread's row update -> visible to the TMA store
+            } else {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(dempty0 + 8 * b);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");     // named barrier: the four fold warps only
+            if (tid == 0) {
+                const CUtensorMap* m = maps + 2 * t.li + 1;
+                tma_store_2d(m, t.col0, t.row0, smem_u32(wtile));
+                if (t.col0 + 64 < t.in_f) tma_store_2d(m, t.col0 + 64, t.row0, smem_u32(wtile) + 16384);
+                bulk_commit();
+                if (j > 0) {
+                    bulk_wait_read<1>();          // the previous tile's store has read its stage
+                    mbar_arrive(wempty0 + 8 * ((j - 1) % WS_NW));
                 }
             }
-            cp_async_mbar_arrive_noinc(fb);
         }
-        if (!ok && lane == 0) atomicExch(status, 31);
-        cp_async_wait<0>();
-    } else if (warp == 2) {
-        // ------------------------------------------------------------------------------------ MMA issuer
+        if (tid == 0) bulk_wait<0>();
+        if (!ok && lane == 0) atomicExch(status, 33);
+    } else if (warp == 4) {
+        // ------------------------------------------------------------------------------------ W loader (one thread)
         if (elect_one()) {
-            int j = 0;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++j) {
-                const int s = j % WS_NST, b = j & 1;
-                if (!mbar_wait(full0 + 8 * s, (j / WS_NST) & 1)) { ok = false; break; }
-                if (!mbar_wait(aempty0 + 8 * b, ((j >> 1) & 1) ^ 1)) { ok = false; break; }
-                const TileRef<T> t = s_ref[s];
-                if (t.n_lora > 0) {
+            WsLayer lay;
+            for (int j = 0, tile; (tile = tile_of(j)) >= 0; ++j) {
+                const int s = j % WS_NW;
+                if (!mbar_wait(wempty0 + 8 * s, ((j / WS_NW) & 1) ^ 1)) { ok = false; break; }
+                lay.seek(layers, tile_start, n_layers, total_tiles, tile);
+                const int rel = tile - lay.start, tm = rel / lay.tiles_n;
+                WsTile t;
+                t.li = lay.li;
+                t.in_f = lay.in_f;
+                t.n_lora = lay.n_lora;
+                t.scale = lay.scale;
+                t.row0 = tm * 128;
+                t.col0 = (rel - tm * lay.tiles_n) * 128;
+                s_tile[s] = t;
+                const CUtensorMap* m = maps + 2 * lay.li + (lay.has_w0 ? 0 : 1);
+                const bool two = t.col0 + 64 < t.in_f;
+                const uint32_t fb = wfull0 + 8 * s, dst = smem_u32(smem + s * WS_W_BYTES);
+                mbar_expect_tx(fb, two ? 32768u : 16384u);
+                tma_load_2d(dst, m, t.col0, t.row0, fb);
+                if (two) tma_load_2d(dst + 16384, m, t.col0 + 64, t.row0, fb);
+            }
+            if (!ok) atomicExch(status, 31);
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------------------------------ MMA issuer (one thread)
+        if (elect_one()) {
+            int prev_bs = -1;
+            for (int j = 0, tile; (tile = tile_of(j)) >= 0; ++j) {
+                const int s = j % WS_NA, b = j & 1;
+                if (!mbar_wait(afull0 + 8 * s, (j / WS_NA) & 1)) { ok = false; break; }
+                if (!mbar_wait(dempty0 + 8 * b, ((j >> 1) & 1) ^ 1)) { ok = false; break; }
+                const int4 info = s_ab[s];
+                if (info.x > 0) {
+                    if (info.w) {
+                        if (prev_bs >= 0) umma_commit(bempty0 + 8 * prev_bs);     // the previous band's products are done
+                        prev_bs = info.z;
+                    }
                     fence_proxy_async();          // async-copy writes of B/A -> tensor-core reads
                     fence_after_sync();
-                    const uint32_t sBa = smem_u32(smem + s * WS_STAGE + WS_W_PAD), sAa = sBa + 16384;
-                    const int kpad = (t.rank0 + 15) & ~15;
+                    const uint32_t sBa = smem_u32(smem_b + info.z * WS_B_BYTES), sAa = smem_u32(smem_a + s * WS_A_BYTES);
+                    const int kpad = (info.y + 15) & ~15;
                     constexpr uint32_t idesc = idesc_f16(128, 64) | (1u << 16);     // B operand MN-major
 #pragma unroll
                     for (int nb = 0; nb < 2; ++nb)
@@ -668,66 +757,74 @@ __global__ void __launch_bounds__(WS_THREADS, 1) lora_merge_f16_ws_kernel(const 
                             umma_f16(tmem_base + b * 128 + nb * 64, smem_desc_sw128(sBa) + 2 * ks,
                                      smem_desc_sw128(sAa + nb * 8192 + ks * 2048), idesc, ks != 0);
                 }
-                umma_commit(afull0 + 8 * b);      // with no MMA outstanding this arrives at once (plain restore tiles)
+                umma_commit(dfull0 + 8 * b);      // with no MMA outstanding these arrive at once (plain restore tiles)
+                umma_commit(aempty0 + 8 * s);
             }
             if (!ok) atomicExch(status, 32);
         }
-    } else if (warp >= 4) {
-        // ------------------------------------------------------------------------------------ fold + write-back (128 threads)
-        const int q = warp & 3;
-        const int row = q * 32 + lane;
-        int j = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++j) {
-            const int s = j % WS_NST, b = j & 1;
-            ok = mbar_wait(full0 + 8 * s, (j / WS_NST) & 1) && mbar_wait(afull0 + 8 * b, (j >> 1) & 1);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            fence_after_sync();
-            const TileRef<T> t = s_ref[s];
-            unsigned char* wrow = smem + s * WS_STAGE + row * WS_WPITCH;
-            if (t.n_lora > 0) {
-                const float sc = t.scale0 * sign;
-                uint32_t r[128];
+    } else {
+        // ------------------------------------------------------------------------------------ adapter tiles (128 threads)
+        const int pt = tid - 192;
+        WsLayer lay;
+        int band = -1, prev_li = -1, prev_row0 = -1;      // bands with an adapter so far; B buffer = band & 1
+        for (int j = 0, tile; (tile = tile_of(j)) >= 0; ++j) {
+            const int s = j % WS_NA;
+            if (!mbar_wait(aempty0 + 8 * s, ((j / WS_NA) & 1) ^ 1)) { ok = false; break; }
+            lay.seek(layers, tile_start, n_layers, total_tiles, tile);
+            const int rel = tile - lay.start, tm = rel / lay.tiles_n;
+            const int row0 = tm * 128, col0 = (rel - tm * lay.tiles_n) * 128;
+            const int rank = lay.rank, kpad = (rank + 15) & ~15;
+            const uint32_t fb = afull0 + 8 * s;
+            bool new_band = false;
+            if (lay.n_lora > 0) {
+                new_band = lay.li != prev_li || row0 != prev_row0;
+                prev_li = lay.li;
+                prev_row0 = row0;
+                if (new_band) {
+                    ++band;
+                    // the buffer is free once the products of the band before last are complete
+                    if (!mbar_wait(bempty0 + 8 * (band & 1), ((band >> 1) & 1) ^ 1)) { ok = false; break; }
+                    const int rows = min(128, lay.out_f - row0);
+                    const int c = pt & 7;
+                    if (c < (kpad >> 3)) {
+                        const uint32_t sB = smem_u32(smem_b + (band & 1) * WS_B_BYTES);
 #pragma unroll
-                for (int c = 0; c < 128; c += 32) tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + b * 128 + c, r + c);
-                tmem_ld_wait();
-                fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(aempty0 + 8 * b);
-#pragma unroll
-                for (int ch = 0; ch < 16; ++ch) {
-                    uint4* wp = reinterpret_cast<uint4*>(wrow + ch * 16);
-                    const uint4 w = *wp;
-                    uint32_t wv[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 wf = unpack_half2(wv[e]);
-                        float d0 = __half2float(__float2half_rn(__uint_as_float(r[ch * 8 + 2 * e])));
-                        float d1 = __half2float(__float2half_rn(__uint_as_float(r[ch * 8 + 2 * e + 1])));
-                        d0 = __half2float(__float2half_rn(d0 * sc));
-                        d1 = __half2float(__float2half_rn(d1 * sc));
-                        wv[e] = pack_half2(wf.x + d0, wf.y + d1);
+                        for (int i = 0; i < 8; ++i) {
+                            const int r = (pt >> 3) + 16 * i;
+                            const bool in = (c * 8) < rank && r < rows;
+                            const T* src = in ? lay.B + (size_t)(row0 + r) * rank + c * 8 : lay.B;
+                            cp_async16(sB + b_off<T>(r, c), src, in ? 16 : 0);
+                        }
                     }
-                    *wp = make_uint4(wv[0], wv[1], wv[2], wv[3]);
                 }
-                fence_proxy_async();              // this thread's row update -> visible to its bulk store
-            } else {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(aempty0 + 8 * b);
             }
-            bulk_store(t.W + (size_t)(t.row0 + row) * t.in_f + t.col0, smem_u32(wrow), 256);
-            bulk_commit();
-            if (j > 0) {
-                bulk_wait_read<1>();              // the previous tile's store has read its stage
-                mbar_arrive(empty0 + 8 * ((j - 1) % WS_NST));
+            if (pt == 0) {
+                s_ab[s] = make_int4(lay.n_lora, rank, band & 1, new_band ? 1 : 0);
+                mbar_arrive(fb);
             }
+            if (lay.n_lora > 0) {
+                const int cols = min(128, lay.in_f - col0);
+                const int c = pt & 15;
+                const bool col_in = (c * 8) < cols;
+                const uint32_t sA = smem_u32(smem_a + s * WS_A_BYTES);
+                const T* src0 = lay.A + col0 + c * 8;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int r = (pt >> 4) + 8 * i;
+                    if (r < kpad) {
+                        const bool in = r < rank && col_in;
+                        cp_async16(sA + a_off<T, true>(r, c), in ? src0 + (size_t)r * lay.in_f : lay.A, in ? 16 : 0);
+                    }
+                }
+            }
+            cp_async_mbar_arrive_noinc(fb);
         }
-        bulk_wait<0>();
-        if (!ok && lane == 0) atomicExch(status, 33);
+        if (!ok && lane == 0) atomicExch(status, 34);
+        cp_async_wait<0>();
     }
     fence_before_sync();
     __syncthreads();
-    if (warp == 2) {
+    if (warp == 5) {
         fence_after_sync();
         tmem_dealloc(tmem_base, 256);
     }
@@ -753,7 +850,8 @@ extern "C" int katz_lora_tile_rows(int w_dtype) { return w_dtype == KATZ_DTYPE_F
 extern "C" int katz_lora_tile_cols(void) { return LM_TN; }
 
 extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_tile_start, int n_layers, int total_tiles,
-                               int w_dtype, float sign, int max_tiles_per_layer, int flags, void* stream) {
+                               int w_dtype, float sign, int max_tiles_per_layer, int flags, const void* d_tile_maps,
+                               void* stream) {
     KATZ_CHECK_ARG(d_layers && d_tile_start, KATZ_EINVAL);
     KATZ_CHECK_ARG(n_layers > 0 && total_tiles > 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(w_dtype == KATZ_DTYPE_F16 || w_dtype == KATZ_DTYPE_F32, KATZ_EINVAL);
@@ -774,7 +872,8 @@ extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_til
         const char* e = getenv("KATZ_LORA_MMA");
         use_tc05 = (e && e[0] == '1') ? 0 : 1;
     }
-    if (w_dtype == KATZ_DTYPE_F16 && use_tc05 && (flags & KATZ_LORA_UNIFORM_TILES)) {
+    if (w_dtype == KATZ_DTYPE_F16 && use_tc05 && (flags & KATZ_LORA_UNIFORM_TILES) && d_tile_maps) {
+        KATZ_CHECK_ARG((reinterpret_cast<uintptr_t>(d_tile_maps) & 63) == 0, KATZ_EALIGN);
         static bool attr3 = false;
         if (!attr3) {
             cudaError_t e = cudaFuncSetAttribute(lora_merge_f16_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WS_SMEM);
@@ -783,8 +882,9 @@ extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_til
         }
         int* status = tc05_status_device_ptr();
         if (!status) return KATZ_ENOTREADY;
-        lora_merge_f16_ws_kernel<<<grid, WS_THREADS, WS_SMEM, st>>>(d_layers, d_tile_start, n_layers, total_tiles, sign, in_smem,
-                                                                    status);
+        lora_merge_f16_ws_kernel<<<grid, WS_THREADS, WS_SMEM, st>>>(d_layers, reinterpret_cast<const CUtensorMap*>(d_tile_maps),
+                                                                    d_tile_start, n_layers, total_tiles, sign, status,
+                                                                    (flags & KATZ_LORA_NO_ADAPTERS) ? 1 : WS_CHUNK);
     } else if (w_dtype == KATZ_DTYPE_F16 && use_tc05) {
         static bool attr2 = false;
         if (!attr2) {
@@ -802,6 +902,59 @@ extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_til
     else
         lora_merge_kernel<float><<<grid, LM_THREADS, LmCfg<float>::SMEM, st>>>(d_layers, d_tile_start, n_layers, total_tiles, sign, in_smem);
     KATZ_LAUNCH_RET();
+}
+
+// Tensor maps of the fast path, two per layer (128 bytes each): [2i] the pristine copy W0 (W when there is none), [2i+1]
+// the live W; 128-row x 64-column boxes with the 128-byte swizzle. They depend only on the weight pointers and shapes,
+// so a caller encodes them once and keeps them in device memory.
+extern "C" int katz_lora_encode_tile_maps(const katz_lora_layer* h_layers, int n_layers, void* h_maps) {
+    KATZ_CHECK_ARG(h_layers && h_maps, KATZ_EINVAL);
+    KATZ_CHECK_ARG(n_layers > 0, KATZ_ESIZE);
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn enc = nullptr;
+    if (!enc) {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            return KATZ_ENOTREADY;
+        enc = reinterpret_cast<EncodeFn>(f);
+    }
+    CUtensorMap* out = reinterpret_cast<CUtensorMap*>(h_maps);
+    for (int i = 0; i < n_layers; ++i) {
+        const katz_lora_layer& L = h_layers[i];
+        KATZ_CHECK_ARG(L.W && aligned16(L.W) && (!L.W0 || aligned16(L.W0)), KATZ_EALIGN);
+        KATZ_CHECK_ARG(L.out_features > 0 && L.in_features > 0 && L.in_features % 8 == 0, KATZ_ESIZE);
+        cuuint64_t dims[2] = {(cuuint64_t)L.in_features, (cuuint64_t)L.out_features};
+        cuuint64_t strides[1] = {(cuuint64_t)L.in_features * 2};
+        cuuint32_t box[2] = {64, 128};
+        cuuint32_t es[2] = {1, 1};
+        for (int k = 0; k < 2; ++k) {
+            void* base = (k == 0 && L.W0) ? const_cast<void*>(L.W0) : L.W;
+            CUtensorMap tmp;
+            CUresult r = enc(&tmp, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return KATZ_EINVAL;
+            memcpy(out + 2 * i + k, &tmp, sizeof(CUtensorMap));      // the caller's buffer need not be 64-byte aligned
+        }
+    }
+    return KATZ_OK;
+}
+
+// Host-side validation of a whole table in one call. Returns 0, or the negative argument error of the first bad entry
+// with its index in *bad_index (when given).
+extern "C" int katz_lora_table_check(const katz_lora_layer* h_layers, int n_layers, int w_dtype, int* bad_index) {
+    KATZ_CHECK_ARG(h_layers, KATZ_EINVAL);
+    for (int i = 0; i < n_layers; ++i) {
+        const int rc = katz_lora_layer_check(h_layers + i, w_dtype);
+        if (rc != KATZ_OK) {
+            if (bad_index) *bad_index = i;
+            return rc;
+        }
+    }
+    return KATZ_OK;
 }
 
 // Host-side validation of one table entry (the table itself lives in device memory, so the caller validates before

@@ -112,3 +112,34 @@ def test_merge_rejects_bad_adapters(cuda_device):
         m.merge(bad, 1.0)       # rank 7 is not a multiple of 8
     with pytest.raises(KatzError):
         m.merge(OrderedDict((k, (u.cuda().float(), d.cuda().float())) for k, (u, d) in ad.items()), 1.0)
+
+
+@pytest.mark.parametrize("rank", [8, 24, 48])
+def test_merge_fast_path_odd_ranks_and_layers_without_adapter(cuda_device, rank):
+    """One adapter of rank <= 64 per layer takes the bulk-copy staged kernel: ranks that are not multiples of 16, ragged
+    edge tiles, and layers the adapter does not touch (restored from the pristine copy)."""
+    from katz_b200 import ops
+    from katz_b200.lora import LoraMerger
+    from oracle import lora_oracle
+    shapes = [(320, 320), (640, 320), (200, 136), (1280, 2048), (384, 1280)]
+    W, ad = _make(shapes, rank, torch.float16, 5 + rank)
+    skipped = "layer3.weight"
+    del ad[skipped]
+    Wg = _cuda(W)
+    m = LoraMerger(Wg, keep_pristine=True)
+    m.merge(_cuda(ad), 2.0)
+    ref = lora_oracle.merge_set(W, [ad], [2.0])
+    for k in W:
+        if k == skipped:
+            assert torch.equal(Wg[k].cpu(), W[k])
+            continue
+        d = (Wg[k].cpu().float() - ref[k].float()).abs()
+        assert float(d.max()) <= 2 ** -9 * float(ref[k].float().abs().max()) and float((d > 0).float().mean()) < 0.02, k
+    m.merge(_cuda(ad), 2.0)                      # a second merge starts from the pristine weights again
+    for k in ad:
+        d = (Wg[k].cpu().float() - ref[k].float()).abs()
+        assert float(d.max()) <= 2 ** -9 * float(ref[k].float().abs().max()), k
+    m.restore()
+    for k in W:
+        assert torch.equal(Wg[k].cpu(), W[k]), k
+    assert ops.tc05_status() == 0
