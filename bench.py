@@ -378,7 +378,11 @@ def main():
         ach = 2.0 * M * N * K / (gemm_ms * 1e-3) / 1e12
         roof = {"bound": "tensor", "kernel": ops.gemm_kernel_name(), "shape": [M, N, K], "achieved": ach,
                 "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"],
-                "peak_source": peaks["_source"] + " burst", "launch_ms": gemm_ms, "traffic": None}
+                "peak_source": peaks["_source"] + " burst", "launch_ms": gemm_ms,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape, from the ncu capture summarised
+                # in profiles/tc05_gemm_linear_2048x10240x1280.md (31.55 MB + 8.04 MB; algorithmic bytes 73.4 MB, the
+                # output is still in L2 when the launch ends)
+                "traffic": 39593216 if (M, N, K) == (2048, 10240, 1280) else None, "traffic_unit": "bytes"}
 
     if rank == 0:
         step_tflops = flops["total"] / world / (ms * 1e-3) / 1e12
@@ -400,7 +404,9 @@ def main():
                               "note": "per-GPU algorithmic FLOPs of the whole step / step time"},
             "lora_merge": {"bound": "hbm", "ms": merge_ms, "restore_ms": restore_ms, "request_ms": merge_request_ms, "bytes": merge_bytes, "achieved": merge_gbs,
                            "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": merge_gbs / peaks["hbm_gbs"],
-                           "layers": len(keys), "rank": 64, "peak_source": peaks["_source"]},
+                           "layers": len(keys), "rank": 64, "peak_source": peaks["_source"],
+                           # ncu capture of a 102-layer subset scaled by weight bytes (profiles/lora_merge_ws_*.md)
+                           "traffic": int(0.965 * merge_bytes)},
         }
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1

@@ -6,9 +6,10 @@
 //     ahead across tile boundaries;
 //   * warp 1, one elected thread: tcgen05.mma kind::f16 (128 x BN x 16 per instruction), fp32 accumulators in TMEM,
 //     two accumulator buffers so tile i+1's main loop overlaps tile i's epilogue;
-//   * warps 2-5: epilogue. tcgen05.ld brings a 32-row x 32-column block per warp into registers, the block is
-//     transposed through swizzled shared memory, and bias / per-batch row vector / SiLU / residual / scale are applied
-//     on the way out with every global access covering whole 32-byte sectors of a row.
+//   * warps 2-5: epilogue. tcgen05.ld brings a 32-row x 32-column block per warp into registers with one row per
+//     thread, so a thread owns 64 contiguous bytes of an output row: bias / per-batch row vector / SiLU / residual /
+//     scale are applied in registers and the row segment leaves as 16-byte stores; residual and row-vector values
+//     are requested two chunks ahead, the first two while the tile's main loop is still running.
 // Linear layers read A through a 2-D tensor map. The 3x3 stride-1 convolution reads the NHWC activation through a 4-D
 // tensor map as nine shifted tile loads per channel chunk (out-of-image pixels arrive as zeros): no im2col buffer.
 // GEGLU mode loads the two halves of the projection weight into one B tile (rows n..n+BN/2 and F+n..F+n+BN/2), so
@@ -29,7 +30,7 @@ using namespace tc05;
 constexpr int TBM = 128, TBK = 64;
 constexpr int TC_THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
 constexpr int TMEM_COLS = 512;    // two accumulator buffers at columns 0 and 256
-constexpr int STG_FLOATS = 32 * 32;
+constexpr int STG_BYTES = 4 * 1024;   // bias slices of the four epilogue warps (bias + gate bias, 256 halfs each)
 
 struct Tc05Params {
     __half* C;
@@ -58,6 +59,13 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t* r) {
         : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+
 __device__ __forceinline__ float rhalf(float v) { return __half2float(__float2half_rn(v)); }
 
 template <int BN, int STAGES, bool GEGLU>
@@ -68,12 +76,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
     constexpr int B_BYTES = BN * TBK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr int BN_OUT = GEGLU ? BN / 2 : BN;      // output columns per tile
-    constexpr int NSTG = GEGLU ? 2 : 1;              // staging blocks per epilogue warp
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte alignment: the swizzle pattern and the UMMA descriptors assume it
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    float* staging = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + 4 * NSTG * STG_FLOATS * 4);
+    unsigned char* staging = smem + STAGES * STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + STG_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
@@ -184,23 +191,68 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
         }
     } else {
         // ------------------------------------------------------------------------------------ epilogue
+        // Thread = tile row (the TMEM lane it may read); its 32 accumulator columns of a chunk are 64 contiguous bytes
+        // of the output row, so residual, row vector and output move as 16-byte vectors straight from and to global
+        // memory. Everything the epilogue reads from global memory is requested before it is needed: the tile's bias
+        // goes to shared memory and the first two chunks' residual / row-vector values to registers while the main
+        // loop of the tile is still running; later chunks are requested two chunks ahead.
         const int q = warp & 3;                 // TMEM lane quarter this warp may read
-        float* stg = staging + q * NSTG * STG_FLOATS;
+        __half* sbias = reinterpret_cast<__half*>(staging) + q * 512;      // [0,256): bias, [256,512): gate bias
+        constexpr int NCH = (BN_OUT + 31) / 32;
         bool ok = true;
         uint32_t t = 0;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
             const uint32_t buf = t & 1;
             const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
-            int m0 = mt * TBM, cb = 0, ch0 = 0, cw0 = 0;
+            const int n0 = nt * BN_OUT;
+            const int row = q * 32 + lane;
+            long long m;
+            bool valid;
+            int bidx;
             if (p.conv) {
                 const int tpi = p.tiles_w * p.tiles_h;
-                cb = mt / tpi;
+                const int cb = mt / tpi;
                 const int r = mt - cb * tpi;
                 const int ty = r / p.tiles_w;
-                ch0 = ty * p.TH;
-                cw0 = (r - ty * p.tiles_w) * p.TW;
+                const int th = row / p.TW, tw = row - th * p.TW;
+                const int h = ty * p.TH + th;
+                valid = h < p.H;
+                m = ((long long)cb * p.H + h) * p.W + (r - ty * p.tiles_w) * p.TW + tw;
+                bidx = cb;
+            } else {
+                m = (long long)mt * TBM + row;
+                valid = m < p.M;
+                bidx = p.rowvec ? (int)(m / p.rows_per_batch) : 0;
             }
-            const int n0 = nt * BN_OUT;
+            __half* crow = p.C + (size_t)m * p.ldc + n0;
+            const __half* rrow = p.residual ? p.residual + (size_t)m * p.ldr + n0 : nullptr;
+            const __half* vrow = p.rowvec ? p.rowvec + (size_t)bidx * p.ld_rowvec + n0 : nullptr;
+            // bias slice of the tile -> shared memory (zeros past N or without a bias)
+            {
+                uint4 bv = make_uint4(0, 0, 0, 0), gv = make_uint4(0, 0, 0, 0);
+                const int col = n0 + lane * 8;
+                if (p.bias && lane * 8 < BN_OUT && col < p.N) {
+                    bv = *reinterpret_cast<const uint4*>(p.bias + col);
+                    if (GEGLU) gv = *reinterpret_cast<const uint4*>(p.bias + p.geglu_F + col);
+                }
+                *reinterpret_cast<uint4*>(sbias + lane * 8) = bv;
+                if (GEGLU) *reinterpret_cast<uint4*>(sbias + 256 + lane * 8) = gv;
+            }
+            uint4 pre_res[2][4], pre_rv[2][4];
+            auto prefetch = [&](int c, uint4* res, uint4* rv) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int col = c * 32 + k * 8;
+                    const bool in = valid && col < BN_OUT && n0 + col < p.N;
+                    res[k] = (in && rrow) ? *reinterpret_cast<const uint4*>(rrow + col) : make_uint4(0, 0, 0, 0);
+                    rv[k] = (in && vrow) ? *reinterpret_cast<const uint4*>(vrow + col) : make_uint4(0, 0, 0, 0);
+                }
+            };
+            if (!GEGLU) {
+                prefetch(0, pre_res[0], pre_rv[0]);
+                if (NCH > 1) prefetch(1, pre_res[1], pre_rv[1]);
+            }
+            __syncwarp();
             ok = mbar_wait(tfull0 + 8 * buf, (t >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-collective: decide as a warp
             if (!ok) {
@@ -209,100 +261,88 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
             }
             fence_after_sync();
             const uint32_t tacc = tmem_base + buf * 256 + ((uint32_t)(q * 32) << 16);
+            if constexpr (GEGLU) {
+                // the gate's erf makes this epilogue instruction-bound: a rolled loop over 8-column groups keeps the code
+                // small enough for the instruction cache (fully unrolled it ran 2.5x slower)
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN_OUT; c0 += 32) {
-                const int w = (BN_OUT - c0) < 32 ? (BN_OUT - c0) : 32;   // 32, or a 16-column tail
+                for (int col = 0; col < BN_OUT; col += 8) {
+                    uint32_t r[8], g[8];
+                    tmem_ld_32x8(tacc + col, r);
+                    tmem_ld_32x8(tacc + BN / 2 + col, g);
+                    tmem_ld_wait();
+                    const uint4 b4 = *reinterpret_cast<const uint4*>(sbias + col);
+                    const uint4 g4 = *reinterpret_cast<const uint4*>(sbias + 256 + col);
+                    const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w}, gw[4] = {g4.x, g4.y, g4.z, g4.w};
+                    uint32_t ow[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        // activations.py:146-149 on fp16 tensors: proj output, gelu and product each round to half
+                        const float2 bf = unpack_half2(bw[e]), gb = unpack_half2(gw[e]);
+                        const float v0 = __uint_as_float(r[2 * e]) + bf.x, v1 = __uint_as_float(r[2 * e + 1]) + bf.y;
+                        const float g0 = __uint_as_float(g[2 * e]) + gb.x, g1 = __uint_as_float(g[2 * e + 1]) + gb.y;
+                        ow[e] = pack_half2(rhalf(v0) * rhalf(gelu_erf_f(rhalf(g0))) * p.out_scale,
+                                           rhalf(v1) * rhalf(gelu_erf_f(rhalf(g1))) * p.out_scale);
+                    }
+                    if (valid && n0 + col < p.N) *reinterpret_cast<uint4*>(crow + col) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                }
+            } else {
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+                const bool tail16 = (BN_OUT % 32 != 0) && c == NCH - 1;       // a 16-column last chunk
                 uint32_t r[32], g[GEGLU ? 32 : 1];
-                if (w == 32) {
-                    tmem_ld_32x32(tacc + c0, r);
-                    if (GEGLU) tmem_ld_32x32(tacc + BN / 2 + c0, g);
+                if (!tail16) {
+                    tmem_ld_32x32(tacc + c * 32, r);
+                    if (GEGLU) tmem_ld_32x32(tacc + BN / 2 + c * 32, g);
                 } else {
-                    tmem_ld_32x16(tacc + c0, r);
-                    if (GEGLU) tmem_ld_32x16(tacc + BN / 2 + c0, g);
+                    tmem_ld_32x16(tacc + c * 32, r);
+                    if (GEGLU) tmem_ld_32x16(tacc + BN / 2 + c * 32, g);
                 }
                 tmem_ld_wait();
-                // transpose through shared memory: thread = row on the way in, thread = 4-column group on the way out
-                const int nch = w >> 2;
+                uint4* res = pre_res[c & 1];
+                uint4* rv = pre_rv[c & 1];
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    if (c < nch) {
-                        const int off = lane * 32 + ((c ^ (lane & 7)) << 2);
-                        *reinterpret_cast<float4*>(stg + off) =
-                            make_float4(__uint_as_float(r[4 * c]), __uint_as_float(r[4 * c + 1]), __uint_as_float(r[4 * c + 2]),
-                                        __uint_as_float(r[4 * c + 3]));
-                        if (GEGLU)
-                            *reinterpret_cast<float4*>(stg + STG_FLOATS + off) =
-                                make_float4(__uint_as_float(g[4 * c]), __uint_as_float(g[4 * c + 1]),
-                                            __uint_as_float(g[4 * c + 2]), __uint_as_float(g[4 * c + 3]));
-                    }
-                }
-                __syncwarp();
-                const int lanes_per_row = nch;                  // 8 or 4
-                const int rows_per_it = 32 / lanes_per_row;     // 4 or 8
-                const int cg = lane % lanes_per_row;
-                const int nb = n0 + c0 + cg * 4;
-                float bias4[4] = {0.f, 0.f, 0.f, 0.f}, gbias4[4] = {0.f, 0.f, 0.f, 0.f};
-                const bool col_ok = nb < p.N;
-                if (p.bias && col_ok) {
-                    const uint2 u = *reinterpret_cast<const uint2*>(p.bias + nb);
-                    float2 a = unpack_half2(u.x), b2 = unpack_half2(u.y);
-                    bias4[0] = a.x; bias4[1] = a.y; bias4[2] = b2.x; bias4[3] = b2.y;
+                for (int k = 0; k < (tail16 ? 2 : 4); ++k) {
+                    const int col = c * 32 + k * 8;
+                    const uint4 b4 = *reinterpret_cast<const uint4*>(sbias + col);
+                    const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w};
+                    const uint32_t rw[4] = {res[k].x, res[k].y, res[k].z, res[k].w};
+                    const uint32_t vw[4] = {rv[k].x, rv[k].y, rv[k].z, rv[k].w};
+                    uint32_t gw[4] = {0, 0, 0, 0};
                     if (GEGLU) {
-                        const uint2 v = *reinterpret_cast<const uint2*>(p.bias + p.geglu_F + nb);
-                        float2 c2 = unpack_half2(v.x), d2 = unpack_half2(v.y);
-                        gbias4[0] = c2.x; gbias4[1] = c2.y; gbias4[2] = d2.x; gbias4[3] = d2.y;
+                        const uint4 g4 = *reinterpret_cast<const uint4*>(sbias + 256 + col);
+                        gw[0] = g4.x; gw[1] = g4.y; gw[2] = g4.z; gw[3] = g4.w;
                     }
-                }
-                for (int i = 0; i < 32; i += rows_per_it) {
-                    const int rl = i + lane / lanes_per_row;    // row inside this warp's 32
-                    const int row = q * 32 + rl;                // row inside the 128-row tile
-                    long long m;
-                    bool valid;
-                    int bidx;
-                    if (p.conv) {
-                        const int th = row / p.TW, tw = row - th * p.TW;
-                        const int h = ch0 + th;
-                        valid = h < p.H;
-                        m = ((long long)cb * p.H + h) * p.W + cw0 + tw;
-                        bidx = cb;
-                    } else {
-                        m = m0 + row;
-                        valid = m < p.M;
-                        bidx = p.rowvec ? (int)(m / p.rows_per_batch) : 0;
-                    }
-                    if (!valid || !col_ok) continue;
-                    const int off = rl * 32 + ((cg ^ (rl & 7)) << 2);
-                    const float4 a4 = *reinterpret_cast<const float4*>(stg + off);
-                    float v[4] = {a4.x + bias4[0], a4.y + bias4[1], a4.z + bias4[2], a4.w + bias4[3]};
-                    if (GEGLU) {
-                        const float4 g4 = *reinterpret_cast<const float4*>(stg + STG_FLOATS + off);
-                        const float gg[4] = {g4.x + gbias4[0], g4.y + gbias4[1], g4.z + gbias4[2], g4.w + gbias4[3]};
-                        // activations.py:146-149 on fp16 tensors: proj output, gelu and product each round to half
+                    uint32_t ow[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) v[e] = rhalf(v[e]) * rhalf(gelu_erf_f(rhalf(gg[e])));
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 bf = unpack_half2(bw[e]);
+                        float v0 = __uint_as_float(r[k * 8 + 2 * e]) + bf.x, v1 = __uint_as_float(r[k * 8 + 2 * e + 1]) + bf.y;
+                        if (GEGLU) {
+                            // activations.py:146-149 on fp16 tensors: proj output, gelu and product each round to half
+                            const float2 gb = unpack_half2(gw[e]);
+                            const float g0 = __uint_as_float(g[k * 8 + 2 * e]) + gb.x, g1 = __uint_as_float(g[k * 8 + 2 * e + 1]) + gb.y;
+                            v0 = rhalf(v0) * rhalf(gelu_erf_f(rhalf(g0)));
+                            v1 = rhalf(v1) * rhalf(gelu_erf_f(rhalf(g1)));
+                        }
+                        if (p.rowvec) {
+                            const float2 a = unpack_half2(vw[e]);
+                            v0 += a.x; v1 += a.y;
+                        }
+                        if (p.act == 1) {
+                            v0 = silu_f(v0); v1 = silu_f(v1);
+                        }
+                        if (p.residual) {
+                            const float2 a = unpack_half2(rw[e]);
+                            v0 += a.x; v1 += a.y;
+                        }
+                        ow[e] = pack_half2(v0 * p.out_scale, v1 * p.out_scale);
                     }
-                    if (p.rowvec) {
-                        const uint2 u = *reinterpret_cast<const uint2*>(p.rowvec + (size_t)bidx * p.ld_rowvec + nb);
-                        float2 a = unpack_half2(u.x), b2 = unpack_half2(u.y);
-                        v[0] += a.x; v[1] += a.y; v[2] += b2.x; v[3] += b2.y;
-                    }
-                    if (p.act == 1) {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) v[e] = silu_f(v[e]);
-                    }
-                    if (p.residual) {
-                        const uint2 u = *reinterpret_cast<const uint2*>(p.residual + (size_t)m * p.ldr + nb);
-                        float2 a = unpack_half2(u.x), b2 = unpack_half2(u.y);
-                        v[0] += a.x; v[1] += a.y; v[2] += b2.x; v[3] += b2.y;
-                    }
-                    uint2 o;
-                    o.x = pack_half2(v[0] * p.out_scale, v[1] * p.out_scale);
-                    o.y = pack_half2(v[2] * p.out_scale, v[3] * p.out_scale);
-                    *reinterpret_cast<uint2*>(p.C + (size_t)m * p.ldc + nb) = o;
+                    if (valid && n0 + col < p.N) *reinterpret_cast<uint4*>(crow + col) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                 }
-                __syncwarp();
+                if (c + 2 < NCH) prefetch(c + 2, pre_res[c & 1], pre_rv[c & 1]);
             }
-            // this warp is done reading the accumulator buffer
+            }
+            // this warp is done reading the accumulator buffer (and the bias slice)
             fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
@@ -375,7 +415,7 @@ static int sm_count() {
 
 template <int BN, int STAGES, bool GEGLU>
 static constexpr int tc05_smem() {
-    return STAGES * (TBM * TBK * 2 + BN * TBK * 2) + 4 * (GEGLU ? 2 : 1) * STG_FLOATS * 4 + (2 * STAGES + 4) * 8 + 16 + 1024;
+    return STAGES * (TBM * TBK * 2 + BN * TBK * 2) + STG_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
 }
 
 template <int BN, int STAGES, bool GEGLU>
@@ -431,7 +471,7 @@ static int dispatch(const CUtensorMap& a, const CUtensorMap& b, Tc05Params& p, i
     p.status = status_ptr();
     if (!p.status) return KATZ_ENOTREADY;
     if (bn == 256) return launch_tc05<256, 4, GEGLU>(a, b, p, st);
-    if (bn == 160) return launch_tc05<160, 5, GEGLU>(a, b, p, st);
+    if (bn == 160) return launch_tc05<160, 6, GEGLU>(a, b, p, st);
     return launch_tc05<128, 6, GEGLU>(a, b, p, st);
 }
 
@@ -456,11 +496,11 @@ static int linear_common(const void* A, int lda, const void* W, void* C, int ldc
     KATZ_CHECK_ARG(A && W && C, KATZ_EINVAL);
     KATZ_CHECK_ARG(M > 0 && N_out > 0 && K > 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(K % TBK == 0 && N_out % 8 == 0, KATZ_ESIZE);
-    KATZ_CHECK_ARG(lda % 8 == 0 && ldc % 4 == 0, KATZ_EALIGN);
-    KATZ_CHECK_ARG(aligned16(A) && aligned16(W) && ((uintptr_t)C & 7) == 0, KATZ_EALIGN);
-    KATZ_CHECK_ARG(!bias || ((uintptr_t)bias & 7) == 0, KATZ_EALIGN);
-    KATZ_CHECK_ARG(!rowvec || (((uintptr_t)rowvec & 7) == 0 && ld_rowvec % 4 == 0 && rows_per_batch > 0), KATZ_EALIGN);
-    KATZ_CHECK_ARG(!residual || (((uintptr_t)residual & 7) == 0 && ldr % 4 == 0), KATZ_EALIGN);
+    KATZ_CHECK_ARG(lda % 8 == 0 && ldc % 8 == 0, KATZ_EALIGN);
+    KATZ_CHECK_ARG(aligned16(A) && aligned16(W) && aligned16(C), KATZ_EALIGN);
+    KATZ_CHECK_ARG(!bias || aligned16(bias), KATZ_EALIGN);
+    KATZ_CHECK_ARG(!rowvec || (aligned16(rowvec) && ld_rowvec % 8 == 0 && rows_per_batch > 0), KATZ_EALIGN);
+    KATZ_CHECK_ARG(!residual || (aligned16(residual) && ldr % 8 == 0), KATZ_EALIGN);
     CUtensorMap ta, tb;
     int rc = encode_2d(&ta, A, K, M, (uint64_t)lda * 2, TBK, TBM);
     if (rc) return rc;
@@ -505,10 +545,10 @@ extern "C" int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int 
     const int TW = Wd < 128 ? Wd : 128;
     KATZ_CHECK_ARG((TW & (TW - 1)) == 0 && TW >= 8 && Wd % TW == 0, KATZ_ESIZE);
     const int TH = 128 / TW;
-    KATZ_CHECK_ARG(aligned16(X) && aligned16(W) && ((uintptr_t)Y & 7) == 0, KATZ_EALIGN);
-    KATZ_CHECK_ARG(!bias || ((uintptr_t)bias & 7) == 0, KATZ_EALIGN);
-    KATZ_CHECK_ARG(!rowvec || (((uintptr_t)rowvec & 7) == 0 && ld_rowvec % 4 == 0), KATZ_EALIGN);
-    KATZ_CHECK_ARG(!residual || ((uintptr_t)residual & 7) == 0, KATZ_EALIGN);
+    KATZ_CHECK_ARG(aligned16(X) && aligned16(W) && aligned16(Y), KATZ_EALIGN);
+    KATZ_CHECK_ARG(!bias || aligned16(bias), KATZ_EALIGN);
+    KATZ_CHECK_ARG(!rowvec || (aligned16(rowvec) && ld_rowvec % 8 == 0), KATZ_EALIGN);
+    KATZ_CHECK_ARG(!residual || aligned16(residual), KATZ_EALIGN);
     CUtensorMap ta, tb;
     int rc = encode_nhwc(&ta, X, B, Hin, Wd, Cin, TW, TH);
     if (rc) return rc;
