@@ -30,6 +30,9 @@ using namespace tc05;
 constexpr int TBM = 128, TBK = 64;
 constexpr int TC_THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
 constexpr int TMEM_COLS = 512;    // two accumulator buffers at columns 0 and 256
+constexpr int BOX_BYTES = 32 * 64;    // epilogue box: 32 rows x 32 fp16 columns, 64-byte swizzle
+// boxes per epilogue warp: residual loads run NBOX - 2 chunks ahead of the stores (the 256-wide tile has no room for 4)
+__host__ __device__ constexpr int tc05_nbox(int bn) { return bn == 256 ? 3 : 4; }
 constexpr int STG_BYTES = 4 * 1024;   // bias slices of the four epilogue warps (bias + gate bias, 256 halfs each)
 
 struct Tc05Params {
@@ -43,6 +46,7 @@ struct Tc05Params {
     float out_scale;
     int m_tiles, n_tiles;
     int geglu_F;            // > 0: GEGLU mode, weight has 2F rows
+    int rows_img;           // rows of one image of the output tensor map (M for a linear layer, H*W for a convolution)
     // convolution geometry (stride 1, output size = input size)
     int conv, H, W, TW, TH, tiles_w, tiles_h, cin_chunks, ksize, pad_h, pad_w;   // H, W: OUTPUT size
     int* status;
@@ -68,10 +72,46 @@ __device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t* r) {
 
 __device__ __forceinline__ float rhalf(float v) { return __half2float(__float2half_rn(v)); }
 
+// One thread's 32 accumulator columns of a chunk -> its 64-byte row of the box: + bias + row vector (zeros when the
+// layer has none), SiLU, + residual (already in the box), * scale, rounded to fp16.
+template <bool ACT, bool RES>
+__device__ __forceinline__ void epilogue_chunk(const uint32_t* r, unsigned char* rowp, uint32_t swz, const __half* sb,
+                                               float out_scale) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        uint4* cell = reinterpret_cast<uint4*>(rowp + (((uint32_t)k ^ swz) << 4));
+        const uint4 b4 = *reinterpret_cast<const uint4*>(sb + k * 8);
+        const uint4 v4 = *reinterpret_cast<const uint4*>(sb + 256 + k * 8);
+        uint4 r4 = make_uint4(0, 0, 0, 0);
+        if (RES) r4 = *cell;
+        const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w}, vw[4] = {v4.x, v4.y, v4.z, v4.w}, rw[4] = {r4.x, r4.y, r4.z, r4.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 bf = unpack_half2(bw[e]), vf = unpack_half2(vw[e]);
+            float v0 = (__uint_as_float(r[k * 8 + 2 * e]) + bf.x) + vf.x, v1 = (__uint_as_float(r[k * 8 + 2 * e + 1]) + bf.y) + vf.y;
+            if (ACT) {
+                v0 = silu_f(v0);
+                v1 = silu_f(v1);
+            }
+            if (RES) {
+                const float2 a = unpack_half2(rw[e]);
+                v0 += a.x;
+                v1 += a.y;
+            }
+            ow[e] = pack_half2(v0 * out_scale, v1 * out_scale);
+        }
+        *cell = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
 template <int BN, int STAGES, bool GEGLU>
 __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                   const __grid_constant__ CUtensorMap tmB,
+                                                                  const __grid_constant__ CUtensorMap tmC,
+                                                                  const __grid_constant__ CUtensorMap tmR,
                                                                   const Tc05Params p) {
+    constexpr int NBOX = tc05_nbox(BN);
     constexpr int A_BYTES = TBM * TBK * 2;
     constexpr int B_BYTES = BN * TBK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -79,9 +119,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte alignment: the swizzle pattern and the UMMA descriptors assume it
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* staging = smem + STAGES * STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + STG_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    unsigned char* box_base = smem + STAGES * STAGE_BYTES;                 // 1024-byte aligned (stages are multiples of 1 KB)
+    unsigned char* staging = box_base + 4 * NBOX * BOX_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + STG_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + 4 * NBOX);
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
     const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
@@ -101,6 +142,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
             mbar_init(tfull0 + 8 * b, 1);
             mbar_init(tempty0 + 8 * b, 4);    // one arrival per epilogue warp
         }
+        for (int b = 0; b < 4 * NBOX; ++b) mbar_init(smem_u32(bars + 2 * STAGES + 4 + b), 1);   // residual boxes
+        tma_prefetch_desc(&tmC);
+        if (p.residual) tma_prefetch_desc(&tmR);
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -191,66 +235,67 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
         }
     } else {
         // ------------------------------------------------------------------------------------ epilogue
-        // Thread = tile row (the TMEM lane it may read); its 32 accumulator columns of a chunk are 64 contiguous bytes
-        // of the output row, so residual, row vector and output move as 16-byte vectors straight from and to global
-        // memory. Everything the epilogue reads from global memory is requested before it is needed: the tile's bias
-        // goes to shared memory and the first two chunks' residual / row-vector values to registers while the main
-        // loop of the tile is still running; later chunks are requested two chunks ahead.
+        // Thread = tile row (the TMEM lane it may read). A chunk of 32 output columns of the warp's 32 rows is one
+        // 32 x 64-byte box: the residual box arrives by TMA (requested ahead: the first ones while the tile's main loop
+        // is still running), each thread updates its own row of the box in shared memory, and the box leaves by TMA
+        // store, which clips rows past M (or past the image) and columns past N. Per-row global accesses from the
+        // threads themselves cost 32 cache lines per instruction and made the epilogue slower than the main loop.
         const int q = warp & 3;                 // TMEM lane quarter this warp may read
-        __half* sbias = reinterpret_cast<__half*>(staging) + q * 512;      // [0,256): bias, [256,512): gate bias
-        constexpr int NCH = (BN_OUT + 31) / 32;
+        __half* sbias = reinterpret_cast<__half*>(staging) + q * 512;      // [0,256): bias, [256,512): gate bias / row vector
+        unsigned char* boxes = box_base + q * NBOX * BOX_BYTES;
+        const uint32_t rfull0 = smem_u32(bars + 2 * STAGES + 4 + q * NBOX);
+        constexpr int NCH = BN_OUT / 32;
+        static_assert(BN_OUT % 32 == 0, "output tile width must be a multiple of the 32-column box");
+        constexpr int AHEAD = NBOX - 2;         // residual boxes requested this many chunks ahead
+        const bool has_res = p.residual != nullptr;
+        const uint32_t swz = (uint32_t)((lane >> 1) & 3);      // 64-byte swizzle: 16-byte chunk index ^ ((row >> 1) & 3)
         bool ok = true;
-        uint32_t t = 0;
+        uint32_t t = 0, g = 0;                  // tiles and chunks (boxes) done by this warp
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
             const uint32_t buf = t & 1;
             const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
             const int n0 = nt * BN_OUT;
-            const int row = q * 32 + lane;
-            long long m;
-            bool valid;
-            int bidx;
+            // coordinates of this warp's 32 rows in the output tensor map {N, rows per image, images}
+            int y0, z0;
             if (p.conv) {
                 const int tpi = p.tiles_w * p.tiles_h;
-                const int cb = mt / tpi;
-                const int r = mt - cb * tpi;
+                z0 = mt / tpi;
+                const int r = mt - z0 * tpi;
                 const int ty = r / p.tiles_w;
-                const int th = row / p.TW, tw = row - th * p.TW;
-                const int h = ty * p.TH + th;
-                valid = h < p.H;
-                m = ((long long)cb * p.H + h) * p.W + (r - ty * p.tiles_w) * p.TW + tw;
-                bidx = cb;
+                y0 = ty * p.TH * p.W + (r - ty * p.tiles_w) * p.TW + q * 32;
             } else {
-                m = (long long)mt * TBM + row;
-                valid = m < p.M;
-                bidx = p.rowvec ? (int)(m / p.rows_per_batch) : 0;
+                y0 = mt * TBM + q * 32;
+                z0 = 0;
             }
-            __half* crow = p.C + (size_t)m * p.ldc + n0;
-            const __half* rrow = p.residual ? p.residual + (size_t)m * p.ldr + n0 : nullptr;
-            const __half* vrow = p.rowvec ? p.rowvec + (size_t)bidx * p.ld_rowvec + n0 : nullptr;
-            // bias slice of the tile -> shared memory (zeros past N or without a bias)
+            auto request_residual = [&](int c, uint32_t b) {     // lane 0 only: chunk c of this tile into box b
+                const uint32_t bar = rfull0 + 8 * b;
+                mbar_expect_tx(bar, BOX_BYTES);
+                tma_load_3d(smem_u32(boxes + b * BOX_BYTES), &tmR, n0 + c * 32, y0, z0, bar);
+            };
+            const bool rows_in = y0 < p.rows_img;      // warp-uniform: do any of this warp's 32 rows exist?
+            if (lane == 0 && has_res && rows_in) {
+                // the boxes these loads land in were last stored at least three chunks ago: all but the newest two
+                // stores must have been read out of shared memory
+                bulk_wait_read<2>();
+#pragma unroll
+                for (int c = 0; c < AHEAD && c < NCH; ++c)
+                    if (n0 + c * 32 < p.N) request_residual(c, (g + c) % NBOX);
+            }
+            // bias slice (and the image's row vector) of the tile -> shared memory; zeros past N or when absent
             {
                 uint4 bv = make_uint4(0, 0, 0, 0), gv = make_uint4(0, 0, 0, 0);
                 const int col = n0 + lane * 8;
-                if (p.bias && lane * 8 < BN_OUT && col < p.N) {
-                    bv = *reinterpret_cast<const uint4*>(p.bias + col);
-                    if (GEGLU) gv = *reinterpret_cast<const uint4*>(p.bias + p.geglu_F + col);
+                if (lane * 8 < BN_OUT && col < p.N) {
+                    if (p.bias) bv = *reinterpret_cast<const uint4*>(p.bias + col);
+                    if (GEGLU) {
+                        if (p.bias) gv = *reinterpret_cast<const uint4*>(p.bias + p.geglu_F + col);
+                    } else if (p.rowvec) {
+                        const int bidx = p.conv ? z0 : (mt * TBM) / p.rows_per_batch;
+                        gv = *reinterpret_cast<const uint4*>(p.rowvec + (size_t)bidx * p.ld_rowvec + col);
+                    }
                 }
                 *reinterpret_cast<uint4*>(sbias + lane * 8) = bv;
-                if (GEGLU) *reinterpret_cast<uint4*>(sbias + 256 + lane * 8) = gv;
-            }
-            uint4 pre_res[2][4], pre_rv[2][4];
-            auto prefetch = [&](int c, uint4* res, uint4* rv) {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int col = c * 32 + k * 8;
-                    const bool in = valid && col < BN_OUT && n0 + col < p.N;
-                    res[k] = (in && rrow) ? *reinterpret_cast<const uint4*>(rrow + col) : make_uint4(0, 0, 0, 0);
-                    rv[k] = (in && vrow) ? *reinterpret_cast<const uint4*>(vrow + col) : make_uint4(0, 0, 0, 0);
-                }
-            };
-            if (!GEGLU) {
-                prefetch(0, pre_res[0], pre_rv[0]);
-                if (NCH > 1) prefetch(1, pre_res[1], pre_rv[1]);
+                *reinterpret_cast<uint4*>(sbias + 256 + lane * 8) = gv;
             }
             __syncwarp();
             ok = mbar_wait(tfull0 + 8 * buf, (t >> 1) & 1);
@@ -261,92 +306,80 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
             }
             fence_after_sync();
             const uint32_t tacc = tmem_base + buf * 256 + ((uint32_t)(q * 32) << 16);
-            if constexpr (GEGLU) {
-                // the gate's erf makes this epilogue instruction-bound: a rolled loop over 8-column groups keeps the code
-                // small enough for the instruction cache (fully unrolled it ran 2.5x slower)
-#pragma unroll 1
-                for (int col = 0; col < BN_OUT; col += 8) {
-                    uint32_t r[8], g[8];
-                    tmem_ld_32x8(tacc + col, r);
-                    tmem_ld_32x8(tacc + BN / 2 + col, g);
-                    tmem_ld_wait();
-                    const uint4 b4 = *reinterpret_cast<const uint4*>(sbias + col);
-                    const uint4 g4 = *reinterpret_cast<const uint4*>(sbias + 256 + col);
-                    const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w}, gw[4] = {g4.x, g4.y, g4.z, g4.w};
-                    uint32_t ow[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        // activations.py:146-149 on fp16 tensors: proj output, gelu and product each round to half
-                        const float2 bf = unpack_half2(bw[e]), gb = unpack_half2(gw[e]);
-                        const float v0 = __uint_as_float(r[2 * e]) + bf.x, v1 = __uint_as_float(r[2 * e + 1]) + bf.y;
-                        const float g0 = __uint_as_float(g[2 * e]) + gb.x, g1 = __uint_as_float(g[2 * e + 1]) + gb.y;
-                        ow[e] = pack_half2(rhalf(v0) * rhalf(gelu_erf_f(rhalf(g0))) * p.out_scale,
-                                           rhalf(v1) * rhalf(gelu_erf_f(rhalf(g1))) * p.out_scale);
-                    }
-                    if (valid && n0 + col < p.N) *reinterpret_cast<uint4*>(crow + col) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-                }
-            } else {
 #pragma unroll
             for (int c = 0; c < NCH; ++c) {
-                const bool tail16 = (BN_OUT % 32 != 0) && c == NCH - 1;       // a 16-column last chunk
-                uint32_t r[32], g[GEGLU ? 32 : 1];
-                if (!tail16) {
-                    tmem_ld_32x32(tacc + c * 32, r);
-                    if (GEGLU) tmem_ld_32x32(tacc + BN / 2 + c * 32, g);
+                if (!rows_in || n0 + c * 32 >= p.N) break;      // nothing of this box (or of the rest) exists
+                const uint32_t b = g % NBOX;
+                unsigned char* rowp = boxes + b * BOX_BYTES + lane * 64;
+                uint32_t r[GEGLU ? 1 : 32];
+                if (!GEGLU) tmem_ld_32x32(tacc + c * 32, r);
+                if (has_res) {
+                    ok = mbar_wait(rfull0 + 8 * b, (g / NBOX) & 1);
                 } else {
-                    tmem_ld_32x16(tacc + c * 32, r);
-                    if (GEGLU) tmem_ld_32x16(tacc + BN / 2 + c * 32, g);
+                    if (lane == 0) bulk_wait_read<NBOX - 1>();   // the store that last used this box has read it
                 }
-                tmem_ld_wait();
-                uint4* res = pre_res[c & 1];
-                uint4* rv = pre_rv[c & 1];
-#pragma unroll
-                for (int k = 0; k < (tail16 ? 2 : 4); ++k) {
-                    const int col = c * 32 + k * 8;
-                    const uint4 b4 = *reinterpret_cast<const uint4*>(sbias + col);
-                    const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w};
-                    const uint32_t rw[4] = {res[k].x, res[k].y, res[k].z, res[k].w};
-                    const uint32_t vw[4] = {rv[k].x, rv[k].y, rv[k].z, rv[k].w};
-                    uint32_t gw[4] = {0, 0, 0, 0};
-                    if (GEGLU) {
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    if (!GEGLU) tmem_ld_wait();
+                    if (lane == 0) atomicExch(p.status, 4);
+                    break;
+                }
+                if constexpr (GEGLU) {
+                    // the gate's erf makes this epilogue instruction-bound: a rolled loop over 8-column groups keeps the
+                    // code small enough for the instruction cache (fully unrolled it ran 2.5x slower)
+#pragma unroll 1
+                    for (int k = 0; k < 4; ++k) {
+                        const int col = c * 32 + k * 8;
+                        uint32_t v8[8], g8[8];
+                        tmem_ld_32x8(tacc + col, v8);
+                        tmem_ld_32x8(tacc + BN / 2 + col, g8);
+                        tmem_ld_wait();
+                        const uint4 b4 = *reinterpret_cast<const uint4*>(sbias + col);
                         const uint4 g4 = *reinterpret_cast<const uint4*>(sbias + 256 + col);
-                        gw[0] = g4.x; gw[1] = g4.y; gw[2] = g4.z; gw[3] = g4.w;
-                    }
-                    uint32_t ow[4];
+                        const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w}, gw[4] = {g4.x, g4.y, g4.z, g4.w};
+                        uint32_t ow[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 bf = unpack_half2(bw[e]);
-                        float v0 = __uint_as_float(r[k * 8 + 2 * e]) + bf.x, v1 = __uint_as_float(r[k * 8 + 2 * e + 1]) + bf.y;
-                        if (GEGLU) {
+                        for (int e = 0; e < 4; ++e) {
                             // activations.py:146-149 on fp16 tensors: proj output, gelu and product each round to half
-                            const float2 gb = unpack_half2(gw[e]);
-                            const float g0 = __uint_as_float(g[k * 8 + 2 * e]) + gb.x, g1 = __uint_as_float(g[k * 8 + 2 * e + 1]) + gb.y;
-                            v0 = rhalf(v0) * rhalf(gelu_erf_f(rhalf(g0)));
-                            v1 = rhalf(v1) * rhalf(gelu_erf_f(rhalf(g1)));
+                            const float2 bf = unpack_half2(bw[e]), gb = unpack_half2(gw[e]);
+                            const float v0 = __uint_as_float(v8[2 * e]) + bf.x, v1 = __uint_as_float(v8[2 * e + 1]) + bf.y;
+                            const float g0 = __uint_as_float(g8[2 * e]) + gb.x, g1 = __uint_as_float(g8[2 * e + 1]) + gb.y;
+                            ow[e] = pack_half2(rhalf(v0) * rhalf(gelu_erf_f(rhalf(g0))) * p.out_scale,
+                                               rhalf(v1) * rhalf(gelu_erf_f(rhalf(g1))) * p.out_scale);
                         }
-                        if (p.rowvec) {
-                            const float2 a = unpack_half2(vw[e]);
-                            v0 += a.x; v1 += a.y;
-                        }
-                        if (p.act == 1) {
-                            v0 = silu_f(v0); v1 = silu_f(v1);
-                        }
-                        if (p.residual) {
-                            const float2 a = unpack_half2(rw[e]);
-                            v0 += a.x; v1 += a.y;
-                        }
-                        ow[e] = pack_half2(v0 * p.out_scale, v1 * p.out_scale);
+                        *reinterpret_cast<uint4*>(rowp + (((uint32_t)k ^ swz) << 4)) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                     }
-                    if (valid && n0 + col < p.N) *reinterpret_cast<uint4*>(crow + col) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                } else {
+                    tmem_ld_wait();
+                    // act and residual are uniform over the launch: one branch per chunk picks a straight-line body
+                    // (per-element branches left the single warp of this scheduler nothing to overlap)
+                    if (p.act == 1) {
+                        if (has_res) epilogue_chunk<true, true>(r, rowp, swz, sbias + c * 32, p.out_scale);
+                        else epilogue_chunk<true, false>(r, rowp, swz, sbias + c * 32, p.out_scale);
+                    } else {
+                        if (has_res) epilogue_chunk<false, true>(r, rowp, swz, sbias + c * 32, p.out_scale);
+                        else epilogue_chunk<false, false>(r, rowp, swz, sbias + c * 32, p.out_scale);
+                    }
                 }
-                if (c + 2 < NCH) prefetch(c + 2, pre_res[c & 1], pre_rv[c & 1]);
+                fence_proxy_async();            // this thread's row of the box -> visible to the TMA store
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_3d(&tmC, n0 + c * 32, y0, z0, smem_u32(boxes + b * BOX_BYTES));
+                    bulk_commit();
+                    if (has_res && c + AHEAD < NCH && n0 + (c + AHEAD) * 32 < p.N) {
+                        bulk_wait_read<2>();    // the box of chunk g + AHEAD was last stored two chunks ago
+                        request_residual(c + AHEAD, (g + AHEAD) % NBOX);
+                    }
+                }
+                ++g;
             }
-            }
+            if (!ok) break;
             // this warp is done reading the accumulator buffer (and the bias slice)
             fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
         }
+        if (lane == 0) bulk_wait<0>();          // every store has left shared memory and reached global memory
     }
     // ---------------------------------------------------------------------------------------- teardown
     fence_before_sync();
@@ -390,6 +423,21 @@ static int encode_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_
     return r == CUDA_SUCCESS ? 0 : KATZ_EINVAL;
 }
 
+// Output / residual tensor as {N columns, rows per image, images} with 32 x 32 boxes (64-byte rows, 64-byte swizzle):
+// what an epilogue warp stores per chunk. A linear layer is one image of M rows.
+static int encode_out(CUtensorMap* map, const void* base, int N, long long rows_per_image, int images, int ld) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return KATZ_ENOTREADY;
+    cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)rows_per_image, (cuuint64_t)images};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)rows_per_image * ld * 2};
+    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t es[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, es,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : KATZ_EINVAL;
+}
+
 static int encode_nhwc(CUtensorMap* map, const void* base, int B, int H, int W, int C, int TW, int TH) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return KATZ_ENOTREADY;
@@ -415,11 +463,13 @@ static int sm_count() {
 
 template <int BN, int STAGES, bool GEGLU>
 static constexpr int tc05_smem() {
-    return STAGES * (TBM * TBK * 2 + BN * TBK * 2) + STG_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
+    return STAGES * (TBM * TBK * 2 + BN * TBK * 2) + 4 * tc05_nbox(BN) * BOX_BYTES + STG_BYTES +
+           (2 * STAGES + 4 + 4 * tc05_nbox(BN)) * 8 + 16 + 1024;
 }
 
 template <int BN, int STAGES, bool GEGLU>
-static int launch_tc05(const CUtensorMap& a, const CUtensorMap& b, const Tc05Params& p, cudaStream_t st) {
+static int launch_tc05(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const CUtensorMap& r,
+                       const Tc05Params& p, cudaStream_t st) {
     static bool attr = false;
     constexpr int smem = tc05_smem<BN, STAGES, GEGLU>();
     static_assert(smem <= 232448, "shared memory budget");
@@ -430,7 +480,7 @@ static int launch_tc05(const CUtensorMap& a, const CUtensorMap& b, const Tc05Par
     }
     const int total = p.m_tiles * p.n_tiles;
     const int grid = total < sm_count() ? total : sm_count();
-    tc05_gemm_kernel<BN, STAGES, GEGLU><<<grid, TC_THREADS, smem, st>>>(a, b, p);
+    tc05_gemm_kernel<BN, STAGES, GEGLU><<<grid, TC_THREADS, smem, st>>>(a, b, c, r, p);
     KATZ_LAUNCH_RET();
 }
 
@@ -453,6 +503,7 @@ static int pick_bn(int m_tiles, int n_out, bool geglu) {
     double best_cost = 1e30;
     for (int i = 0; i < 3; ++i) {
         const int bn = cand[i];
+        if (geglu && bn == 160) continue;        // its 80 output columns are not a whole number of 32-column boxes
         const int out_w = geglu ? bn / 2 : bn;
         const long long tiles = (long long)m_tiles * ceil_div(n_out, out_w);
         const long long waves = (tiles + sms - 1) / sms;
@@ -467,12 +518,20 @@ static int pick_bn(int m_tiles, int n_out, bool geglu) {
 }
 
 template <bool GEGLU>
-static int dispatch(const CUtensorMap& a, const CUtensorMap& b, Tc05Params& p, int bn, cudaStream_t st) {
+static int dispatch(const CUtensorMap& a, const CUtensorMap& b, Tc05Params& p, int bn, int rows_per_image, int images,
+                    cudaStream_t st) {
     p.status = status_ptr();
     if (!p.status) return KATZ_ENOTREADY;
-    if (bn == 256) return launch_tc05<256, 4, GEGLU>(a, b, p, st);
-    if (bn == 160) return launch_tc05<160, 6, GEGLU>(a, b, p, st);
-    return launch_tc05<128, 6, GEGLU>(a, b, p, st);
+    CUtensorMap c, r;
+    int rc = encode_out(&c, p.C, p.N, rows_per_image, images, p.ldc);
+    if (rc) return rc;
+    rc = encode_out(&r, p.residual ? p.residual : p.C, p.N, rows_per_image, images, p.residual ? p.ldr : p.ldc);
+    if (rc) return rc;
+    if (bn == 256) return launch_tc05<256, 4, GEGLU>(a, b, c, r, p, st);
+    if constexpr (!GEGLU) {
+        if (bn == 160) return launch_tc05<160, 5, GEGLU>(a, b, c, r, p, st);
+    }
+    return launch_tc05<128, 5, GEGLU>(a, b, c, r, p, st);
 }
 
 }  // namespace katz
@@ -499,7 +558,9 @@ static int linear_common(const void* A, int lda, const void* W, void* C, int ldc
     KATZ_CHECK_ARG(lda % 8 == 0 && ldc % 8 == 0, KATZ_EALIGN);
     KATZ_CHECK_ARG(aligned16(A) && aligned16(W) && aligned16(C), KATZ_EALIGN);
     KATZ_CHECK_ARG(!bias || aligned16(bias), KATZ_EALIGN);
-    KATZ_CHECK_ARG(!rowvec || (aligned16(rowvec) && ld_rowvec % 8 == 0 && rows_per_batch > 0), KATZ_EALIGN);
+    KATZ_CHECK_ARG(!rowvec || (aligned16(rowvec) && ld_rowvec % 8 == 0), KATZ_EALIGN);
+    // a tile's 128 rows must share one row vector
+    KATZ_CHECK_ARG(!rowvec || (rows_per_batch > 0 && rows_per_batch % TBM == 0), KATZ_ESIZE);
     KATZ_CHECK_ARG(!residual || (aligned16(residual) && ldr % 8 == 0), KATZ_EALIGN);
     CUtensorMap ta, tb;
     int rc = encode_2d(&ta, A, K, M, (uint64_t)lda * 2, TBK, TBM);
@@ -509,6 +570,7 @@ static int linear_common(const void* A, int lda, const void* W, void* C, int ldc
     p.M = M; p.N = N_out; p.K = K; p.ldc = ldc; p.ldr = ldr; p.ld_rowvec = ld_rowvec; p.rows_per_batch = rows_per_batch;
     p.act = act; p.out_scale = out_scale; p.geglu_F = geglu_F;
     p.m_tiles = ceil_div(M, TBM);
+    p.rows_img = M;
     KATZ_CHECK_ARG((long long)p.m_tiles * ceil_div(N_out, 64) < (1ll << 30), KATZ_ESIZE);
     const bool geglu = geglu_F > 0;
     const int bn = pick_bn(p.m_tiles, N_out, geglu);
@@ -517,7 +579,7 @@ static int linear_common(const void* A, int lda, const void* W, void* C, int ldc
     const uint64_t w_rows = geglu ? 2ull * geglu_F : (uint64_t)N_out;
     rc = encode_2d(&tb, W, K, w_rows, (uint64_t)K * 2, TBK, geglu ? bn / 2 : bn);
     if (rc) return rc;
-    return geglu ? dispatch<true>(ta, tb, p, bn, (cudaStream_t)stream) : dispatch<false>(ta, tb, p, bn, (cudaStream_t)stream);
+    return geglu ? dispatch<true>(ta, tb, p, bn, M, 1, (cudaStream_t)stream) : dispatch<false>(ta, tb, p, bn, M, 1, (cudaStream_t)stream);
 }
 
 extern "C" int katz_linear_f16(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, int K,
@@ -559,9 +621,10 @@ extern "C" int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int 
     p.conv = 1; p.H = H; p.W = Wd; p.TW = TW; p.TH = TH; p.tiles_w = Wd / TW; p.tiles_h = ceil_div(H, TH);
     p.cin_chunks = Cin / TBK; p.ksize = 3; p.pad_h = pad_h; p.pad_w = 1;
     p.m_tiles = B * p.tiles_w * p.tiles_h;
+    p.rows_img = H * Wd;
     const int bn = pick_bn(p.m_tiles, Cout, false);
     p.n_tiles = ceil_div(Cout, bn);
     rc = encode_2d(&tb, W, (uint64_t)9 * Cin, Cout, (uint64_t)9 * Cin * 2, TBK, bn);
     if (rc) return rc;
-    return dispatch<false>(ta, tb, p, bn, (cudaStream_t)stream);
+    return dispatch<false>(ta, tb, p, bn, H * Wd, B, (cudaStream_t)stream);
 }

@@ -46,6 +46,11 @@ def _tc05_linear_ok(x, w, bias, residual, rowvec, out):
     return True
 
 
+def _tc05_rowvec_ok(rowvec, rows_per_batch):
+    """The tcgen05 epilogue adds one row vector per 128-row tile."""
+    return rowvec is None or (rows_per_batch > 0 and rows_per_batch % 128 == 0)
+
+
 def gemm_kernel_name():
     """Which GEMM family `linear` dispatches large aligned shapes to."""
     return "tcgen05" if _use_tc05() else "mma.sync"
@@ -97,7 +102,8 @@ def linear(x, w, bias=None, residual=None, act=ACT_NONE, rowvec=None, rows_per_b
         raise KatzError("linear: bad out")
     if residual is not None and (residual.shape != (M, N) or residual.stride(1) != 1):
         raise KatzError("linear: bad residual")
-    name = "katz_linear_f16" if (_use_tc05() and _tc05_linear_ok(x, w, bias, residual, rowvec, out)) else "katz_linear_f16_mma"
+    name = ("katz_linear_f16" if (_use_tc05() and _tc05_linear_ok(x, w, bias, residual, rowvec, out)
+                                  and _tc05_rowvec_ok(rowvec, rows_per_batch)) else "katz_linear_f16_mma")
     call(name, _p(x), x.stride(0), _p(w), _p(out), out.stride(0), M, N, K, _p(bias), _p(rowvec),
          rowvec.stride(0) if rowvec is not None else 0, rows_per_batch, _p(residual),
          residual.stride(0) if residual is not None else 0, act, float(out_scale), _stream())
