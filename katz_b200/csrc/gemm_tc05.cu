@@ -6,10 +6,10 @@
 //     ahead across tile boundaries;
 //   * warp 1, one elected thread: tcgen05.mma kind::f16 (128 x BN x 16 per instruction), fp32 accumulators in TMEM,
 //     two accumulator buffers so tile i+1's main loop overlaps tile i's epilogue;
-//   * warps 2-5: epilogue. tcgen05.ld brings a 32-row x 32-column block per warp into registers with one row per
-//     thread, so a thread owns 64 contiguous bytes of an output row: bias / per-batch row vector / SiLU / residual /
-//     scale are applied in registers and the row segment leaves as 16-byte stores; residual and row-vector values
-//     are requested two chunks ahead, the first two while the tile's main loop is still running.
+//   * warps 2-9: epilogue, two warps per TMEM lane quarter taking alternate 32-column chunks. tcgen05.ld brings a
+//     32-row x 32-column block into registers with one row per thread; bias / per-batch row vector / SiLU / residual /
+//     scale are applied there, and the block moves to and from global memory as a 32 x 64-byte TMA box (residual in,
+//     result out) staged in swizzled shared memory.
 // Linear layers read A through a 2-D tensor map. The 3x3 stride-1 convolution reads the NHWC activation through a 4-D
 // tensor map as nine shifted tile loads per channel chunk (out-of-image pixels arrive as zeros): no im2col buffer.
 // GEGLU mode loads the two halves of the projection weight into one B tile (rows n..n+BN/2 and F+n..F+n+BN/2), so
@@ -28,12 +28,10 @@ namespace katz {
 using namespace tc05;
 
 constexpr int TBM = 128, TBK = 64;
-constexpr int TC_THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int TC_THREADS = 320;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: epilogue
 constexpr int TMEM_COLS = 512;    // two accumulator buffers at columns 0 and 256
 constexpr int BOX_BYTES = 32 * 64;    // epilogue box: 32 rows x 32 fp16 columns, 64-byte swizzle
-// boxes per epilogue warp: residual loads run NBOX - 2 chunks ahead of the stores (the 256-wide tile has no room for 4)
-__host__ __device__ constexpr int tc05_nbox(int bn) { return bn == 256 ? 3 : 4; }
-constexpr int STG_BYTES = 4 * 1024;   // bias slices of the four epilogue warps (bias + gate bias, 256 halfs each)
+constexpr int EPI_WARPS = 8, EPI_BOXES = 2 * EPI_WARPS;      // two boxes per epilogue warp
 
 struct Tc05Params {
     __half* C;
@@ -70,21 +68,35 @@ __device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t* r) {
                  : "memory");
 }
 
+// Exact-form GELU x * Phi(x) with erf from Abramowitz & Stegun 7.1.26 (|error| <= 1.5e-7 on erf, far below the fp16
+// rounding that follows): 1 - erf(z) = (a1 t + ... + a5 t^5) exp(-z^2), t = 1 / (1 + p z), z = |x| / sqrt(2).
+// About 15 instructions against erff's 30; the GEGLU epilogue is instruction-issue bound.
+__device__ __forceinline__ float gelu_erf_fast(float x) {
+    const float ax = fabsf(x);
+    const float t = __frcp_rn(fmaf(ax, 0.3275911f * 0.70710678f, 1.0f));
+    float h = fmaf(t, 0.5f * 1.061405429f, 0.5f * -1.453152027f);
+    h = fmaf(t, h, 0.5f * 1.421413741f);
+    h = fmaf(t, h, 0.5f * -0.284496736f);
+    h = fmaf(t, h, 0.5f * 0.254829592f);
+    h = h * t * exp2f(x * x * (-0.5f * 1.4426950408889634f));      // 0.5 * (1 - erf(z))
+    const float r = x * h;                                          // x * Phi(-|x|)
+    return x >= 0.f ? x - r : r;
+}
+
 __device__ __forceinline__ float rhalf(float v) { return __half2float(__float2half_rn(v)); }
 
 // One thread's 32 accumulator columns of a chunk -> its 64-byte row of the box: + bias + row vector (zeros when the
 // layer has none), SiLU, + residual (already in the box), * scale, rounded to fp16.
 template <bool ACT, bool RES>
-__device__ __forceinline__ void epilogue_chunk(const uint32_t* r, unsigned char* rowp, uint32_t swz, const __half* sb,
-                                               float out_scale) {
+__device__ __forceinline__ void epilogue_chunk(const uint32_t* r, unsigned char* rowp, uint32_t swz, const uint4* b4,
+                                               const uint4* v4, float out_scale) {
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         uint4* cell = reinterpret_cast<uint4*>(rowp + (((uint32_t)k ^ swz) << 4));
-        const uint4 b4 = *reinterpret_cast<const uint4*>(sb + k * 8);
-        const uint4 v4 = *reinterpret_cast<const uint4*>(sb + 256 + k * 8);
         uint4 r4 = make_uint4(0, 0, 0, 0);
         if (RES) r4 = *cell;
-        const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w}, vw[4] = {v4.x, v4.y, v4.z, v4.w}, rw[4] = {r4.x, r4.y, r4.z, r4.w};
+        const uint32_t bw[4] = {b4[k].x, b4[k].y, b4[k].z, b4[k].w}, vw[4] = {v4[k].x, v4[k].y, v4[k].z, v4[k].w},
+                       rw[4] = {r4.x, r4.y, r4.z, r4.w};
         uint32_t ow[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -111,7 +123,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                                                                   const __grid_constant__ CUtensorMap tmC,
                                                                   const __grid_constant__ CUtensorMap tmR,
                                                                   const Tc05Params p) {
-    constexpr int NBOX = tc05_nbox(BN);
     constexpr int A_BYTES = TBM * TBK * 2;
     constexpr int B_BYTES = BN * TBK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -120,9 +131,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
     // 1024-byte alignment: the swizzle pattern and the UMMA descriptors assume it
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* box_base = smem + STAGES * STAGE_BYTES;                 // 1024-byte aligned (stages are multiples of 1 KB)
-    unsigned char* staging = box_base + 4 * NBOX * BOX_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + STG_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + 4 * NBOX);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(box_base + EPI_BOXES * BOX_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + EPI_BOXES);
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
     const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
@@ -140,9 +150,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tfull0 + 8 * b, 1);
-            mbar_init(tempty0 + 8 * b, 4);    // one arrival per epilogue warp
+            mbar_init(tempty0 + 8 * b, EPI_WARPS);    // one arrival per epilogue warp
         }
-        for (int b = 0; b < 4 * NBOX; ++b) mbar_init(smem_u32(bars + 2 * STAGES + 4 + b), 1);   // residual boxes
+        for (int b = 0; b < EPI_BOXES; ++b) mbar_init(smem_u32(bars + 2 * STAGES + 4 + b), 1);   // residual boxes
         tma_prefetch_desc(&tmC);
         if (p.residual) tma_prefetch_desc(&tmR);
         fence_barrier_init();
@@ -235,22 +245,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
         }
     } else {
         // ------------------------------------------------------------------------------------ epilogue
-        // Thread = tile row (the TMEM lane it may read). A chunk of 32 output columns of the warp's 32 rows is one
-        // 32 x 64-byte box: the residual box arrives by TMA (requested ahead: the first ones while the tile's main loop
-        // is still running), each thread updates its own row of the box in shared memory, and the box leaves by TMA
-        // store, which clips rows past M (or past the image) and columns past N. Per-row global accesses from the
-        // threads themselves cost 32 cache lines per instruction and made the epilogue slower than the main loop.
+        // Eight warps: two per TMEM lane quarter, taking alternate 32-column chunks of the tile. Thread = tile row. A
+        // chunk of the warp's 32 rows is one 32 x 64-byte box: the residual box arrives by TMA (requested one of the
+        // warp's chunks ahead: the first while the tile's main loop is still running), each thread updates its own
+        // row of the box in shared memory, and the box leaves by TMA store, which clips rows past M (or past the
+        // image) and columns past N. Bias and row-vector values are the same for every row: broadcast loads, requested
+        // one chunk ahead. (Per-row global accesses from the threads cost 32 cache lines per instruction and made the
+        // epilogue slower than the main loop; so did per-element branches on the launch-uniform options.)
+        const int ew = warp - 2;                // epilogue warp 0..7
         const int q = warp & 3;                 // TMEM lane quarter this warp may read
-        __half* sbias = reinterpret_cast<__half*>(staging) + q * 512;      // [0,256): bias, [256,512): gate bias / row vector
-        unsigned char* boxes = box_base + q * NBOX * BOX_BYTES;
-        const uint32_t rfull0 = smem_u32(bars + 2 * STAGES + 4 + q * NBOX);
+        const int half = ew >> 2;               // which of the quarter's two warps: chunks half, half + 2, ...
+        unsigned char* boxes = box_base + ew * 2 * BOX_BYTES;
+        const uint32_t rfull0 = smem_u32(bars + 2 * STAGES + 4 + ew * 2);
         constexpr int NCH = BN_OUT / 32;
         static_assert(BN_OUT % 32 == 0, "output tile width must be a multiple of the 32-column box");
-        constexpr int AHEAD = NBOX - 2;         // residual boxes requested this many chunks ahead
         const bool has_res = p.residual != nullptr;
         const uint32_t swz = (uint32_t)((lane >> 1) & 3);      // 64-byte swizzle: 16-byte chunk index ^ ((row >> 1) & 3)
         bool ok = true;
-        uint32_t t = 0, g = 0;                  // tiles and chunks (boxes) done by this warp
+        uint32_t t = 0, g = 0;                  // tiles done by the CTA, chunks (boxes) done by this warp
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
             const uint32_t buf = t & 1;
             const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
@@ -267,37 +279,35 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                 y0 = mt * TBM + q * 32;
                 z0 = 0;
             }
+            const bool rows_in = y0 < p.rows_img;      // warp-uniform: do any of this warp's 32 rows exist?
+            const __half* bias_p = p.bias ? p.bias + n0 : nullptr;
+            const __half* aux_p = nullptr;             // gate bias (GEGLU) or the image's row vector
+            if (GEGLU) {
+                if (p.bias) aux_p = p.bias + p.geglu_F + n0;
+            } else if (p.rowvec) {
+                aux_p = p.rowvec + (size_t)(p.conv ? z0 : (mt * TBM) / p.rows_per_batch) * p.ld_rowvec + n0;
+            }
+            auto load_vec = [&](const __half* base, int col) {     // 8 columns of a per-column vector, zeros past N
+                return (base && n0 + col < p.N) ? __ldg(reinterpret_cast<const uint4*>(base + col)) : make_uint4(0, 0, 0, 0);
+            };
             auto request_residual = [&](int c, uint32_t b) {     // lane 0 only: chunk c of this tile into box b
                 const uint32_t bar = rfull0 + 8 * b;
                 mbar_expect_tx(bar, BOX_BYTES);
                 tma_load_3d(smem_u32(boxes + b * BOX_BYTES), &tmR, n0 + c * 32, y0, z0, bar);
             };
-            const bool rows_in = y0 < p.rows_img;      // warp-uniform: do any of this warp's 32 rows exist?
-            if (lane == 0 && has_res && rows_in) {
-                // the boxes these loads land in were last stored at least three chunks ago: all but the newest two
-                // stores must have been read out of shared memory
-                bulk_wait_read<2>();
+            const bool first_in = rows_in && half < NCH && n0 + half * 32 < p.N;
+            if (lane == 0 && has_res && first_in) {
+                bulk_wait_read<1>();            // the box was last stored two of this warp's chunks ago
+                request_residual(half, g & 1);
+            }
+            uint4 nb4[4], nv4[4];               // bias / aux values of the warp's next chunk
+            if (!GEGLU) {
 #pragma unroll
-                for (int c = 0; c < AHEAD && c < NCH; ++c)
-                    if (n0 + c * 32 < p.N) request_residual(c, (g + c) % NBOX);
-            }
-            // bias slice (and the image's row vector) of the tile -> shared memory; zeros past N or when absent
-            {
-                uint4 bv = make_uint4(0, 0, 0, 0), gv = make_uint4(0, 0, 0, 0);
-                const int col = n0 + lane * 8;
-                if (lane * 8 < BN_OUT && col < p.N) {
-                    if (p.bias) bv = *reinterpret_cast<const uint4*>(p.bias + col);
-                    if (GEGLU) {
-                        if (p.bias) gv = *reinterpret_cast<const uint4*>(p.bias + p.geglu_F + col);
-                    } else if (p.rowvec) {
-                        const int bidx = p.conv ? z0 : (mt * TBM) / p.rows_per_batch;
-                        gv = *reinterpret_cast<const uint4*>(p.rowvec + (size_t)bidx * p.ld_rowvec + col);
-                    }
+                for (int k = 0; k < 4; ++k) {
+                    nb4[k] = load_vec(bias_p, half * 32 + k * 8);
+                    nv4[k] = load_vec(aux_p, half * 32 + k * 8);
                 }
-                *reinterpret_cast<uint4*>(sbias + lane * 8) = bv;
-                *reinterpret_cast<uint4*>(sbias + 256 + lane * 8) = gv;
             }
-            __syncwarp();
             ok = mbar_wait(tfull0 + 8 * buf, (t >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-collective: decide as a warp
             if (!ok) {
@@ -307,16 +317,32 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
             fence_after_sync();
             const uint32_t tacc = tmem_base + buf * 256 + ((uint32_t)(q * 32) << 16);
 #pragma unroll
-            for (int c = 0; c < NCH; ++c) {
-                if (!rows_in || n0 + c * 32 >= p.N) break;      // nothing of this box (or of the rest) exists
-                const uint32_t b = g % NBOX;
+            for (int cc = 0; cc < (NCH + 1) / 2; ++cc) {
+                const int c = 2 * cc + half;
+                if (!rows_in || c >= NCH || n0 + c * 32 >= p.N) break;      // nothing of this box (or of the rest) exists
+                const uint32_t b = g & 1;
                 unsigned char* rowp = boxes + b * BOX_BYTES + lane * 64;
                 uint32_t r[GEGLU ? 1 : 32];
-                if (!GEGLU) tmem_ld_32x32(tacc + c * 32, r);
+                uint4 cb4[4], cv4[4];
+                if (!GEGLU) {
+                    tmem_ld_32x32(tacc + c * 32, r);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        cb4[k] = nb4[k];
+                        cv4[k] = nv4[k];
+                    }
+                    if (c + 2 < NCH) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            nb4[k] = load_vec(bias_p, (c + 2) * 32 + k * 8);
+                            nv4[k] = load_vec(aux_p, (c + 2) * 32 + k * 8);
+                        }
+                    }
+                }
                 if (has_res) {
-                    ok = mbar_wait(rfull0 + 8 * b, (g / NBOX) & 1);
+                    ok = mbar_wait(rfull0 + 8 * b, (g >> 1) & 1);
                 } else {
-                    if (lane == 0) bulk_wait_read<NBOX - 1>();   // the store that last used this box has read it
+                    if (lane == 0) bulk_wait_read<1>();          // the store that last used this box has read it
                 }
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) {
@@ -327,38 +353,42 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                 if constexpr (GEGLU) {
                     // the gate's erf makes this epilogue instruction-bound: a rolled loop over 8-column groups keeps the
                     // code small enough for the instruction cache (fully unrolled it ran 2.5x slower)
+                    uint4 b4 = load_vec(bias_p, c * 32), g4 = load_vec(aux_p, c * 32);
 #pragma unroll 1
                     for (int k = 0; k < 4; ++k) {
                         const int col = c * 32 + k * 8;
                         uint32_t v8[8], g8[8];
                         tmem_ld_32x8(tacc + col, v8);
                         tmem_ld_32x8(tacc + BN / 2 + col, g8);
-                        tmem_ld_wait();
-                        const uint4 b4 = *reinterpret_cast<const uint4*>(sbias + col);
-                        const uint4 g4 = *reinterpret_cast<const uint4*>(sbias + 256 + col);
                         const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w}, gw[4] = {g4.x, g4.y, g4.z, g4.w};
+                        if (k < 3) {
+                            b4 = load_vec(bias_p, col + 8);
+                            g4 = load_vec(aux_p, col + 8);
+                        }
+                        tmem_ld_wait();
                         uint32_t ow[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            // activations.py:146-149 on fp16 tensors: proj output, gelu and product each round to half
+                            // activations.py:146-149 on fp16 tensors: proj output, gelu and product each round to half.
+                            // The product of two halfs is exact in fp32, so its rounding is the half2 multiply.
                             const float2 bf = unpack_half2(bw[e]), gb = unpack_half2(gw[e]);
-                            const float v0 = __uint_as_float(v8[2 * e]) + bf.x, v1 = __uint_as_float(v8[2 * e + 1]) + bf.y;
-                            const float g0 = __uint_as_float(g8[2 * e]) + gb.x, g1 = __uint_as_float(g8[2 * e + 1]) + gb.y;
-                            ow[e] = pack_half2(rhalf(v0) * rhalf(gelu_erf_f(rhalf(g0))) * p.out_scale,
-                                               rhalf(v1) * rhalf(gelu_erf_f(rhalf(g1))) * p.out_scale);
+                            const __half2 vh = __floats2half2_rn(__uint_as_float(v8[2 * e]) + bf.x, __uint_as_float(v8[2 * e + 1]) + bf.y);
+                            const float2 gr = __half22float2(
+                                __floats2half2_rn(__uint_as_float(g8[2 * e]) + gb.x, __uint_as_float(g8[2 * e + 1]) + gb.y));
+                            const __half2 oh = __hmul2(vh, __floats2half2_rn(gelu_erf_fast(gr.x), gelu_erf_fast(gr.y)));
+                            ow[e] = *reinterpret_cast<const uint32_t*>(&oh);
                         }
                         *reinterpret_cast<uint4*>(rowp + (((uint32_t)k ^ swz) << 4)) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                     }
                 } else {
                     tmem_ld_wait();
                     // act and residual are uniform over the launch: one branch per chunk picks a straight-line body
-                    // (per-element branches left the single warp of this scheduler nothing to overlap)
                     if (p.act == 1) {
-                        if (has_res) epilogue_chunk<true, true>(r, rowp, swz, sbias + c * 32, p.out_scale);
-                        else epilogue_chunk<true, false>(r, rowp, swz, sbias + c * 32, p.out_scale);
+                        if (has_res) epilogue_chunk<true, true>(r, rowp, swz, cb4, cv4, p.out_scale);
+                        else epilogue_chunk<true, false>(r, rowp, swz, cb4, cv4, p.out_scale);
                     } else {
-                        if (has_res) epilogue_chunk<false, true>(r, rowp, swz, sbias + c * 32, p.out_scale);
-                        else epilogue_chunk<false, false>(r, rowp, swz, sbias + c * 32, p.out_scale);
+                        if (has_res) epilogue_chunk<false, true>(r, rowp, swz, cb4, cv4, p.out_scale);
+                        else epilogue_chunk<false, false>(r, rowp, swz, cb4, cv4, p.out_scale);
                     }
                 }
                 fence_proxy_async();            // this thread's row of the box -> visible to the TMA store
@@ -366,15 +396,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                 if (lane == 0) {
                     tma_store_3d(&tmC, n0 + c * 32, y0, z0, smem_u32(boxes + b * BOX_BYTES));
                     bulk_commit();
-                    if (has_res && c + AHEAD < NCH && n0 + (c + AHEAD) * 32 < p.N) {
-                        bulk_wait_read<2>();    // the box of chunk g + AHEAD was last stored two chunks ago
-                        request_residual(c + AHEAD, (g + AHEAD) % NBOX);
+                    if (has_res && c + 2 < NCH && n0 + (c + 2) * 32 < p.N) {
+                        bulk_wait_read<1>();    // the other box's store (the warp's previous chunk) has read it
+                        request_residual(c + 2, (g + 1) & 1);
                     }
                 }
                 ++g;
             }
             if (!ok) break;
-            // this warp is done reading the accumulator buffer (and the bias slice)
+            // this warp is done reading the accumulator buffer
             fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
@@ -463,8 +493,7 @@ static int sm_count() {
 
 template <int BN, int STAGES, bool GEGLU>
 static constexpr int tc05_smem() {
-    return STAGES * (TBM * TBK * 2 + BN * TBK * 2) + 4 * tc05_nbox(BN) * BOX_BYTES + STG_BYTES +
-           (2 * STAGES + 4 + 4 * tc05_nbox(BN)) * 8 + 16 + 1024;
+    return STAGES * (TBM * TBK * 2 + BN * TBK * 2) + EPI_BOXES * BOX_BYTES + (2 * STAGES + 4 + EPI_BOXES) * 8 + 16 + 1024;
 }
 
 template <int BN, int STAGES, bool GEGLU>
@@ -531,7 +560,7 @@ static int dispatch(const CUtensorMap& a, const CUtensorMap& b, Tc05Params& p, i
     if constexpr (!GEGLU) {
         if (bn == 160) return launch_tc05<160, 5, GEGLU>(a, b, c, r, p, st);
     }
-    return launch_tc05<128, 5, GEGLU>(a, b, c, r, p, st);
+    return launch_tc05<128, 6, GEGLU>(a, b, c, r, p, st);
 }
 
 }  // namespace katz
