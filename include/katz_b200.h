@@ -86,7 +86,9 @@ int katz_lora_encode_tile_maps(const katz_lora_layer* h_layers, int n_layers, vo
 
 /* -------------------------------------------------------------------------------------- fast_kernel drop-ins ---- */
 /* fast_kernel::group_norm_fp16 (fast_kernel/csrc/group_norm.cuh:7-15, group_norm.cu:224-274), channels-last input.
- * `scratch` holds per-slab partial sums: katz_group_norm_scratch_bytes() bytes, contents undefined on return. */
+ * `scratch` (256-byte aligned, katz_group_norm_scratch_bytes() bytes) holds per-image ticket counters in its first 1024
+ * bytes, then the statistics and per-slab partial sums. The caller zero-fills it ONCE before its first use; every call
+ * leaves the counters at zero again, the rest undefined. One scratch buffer serves one stream at a time. */
 long long katz_group_norm_scratch_bytes(int B, int HW, int C, int G);
 int katz_group_norm_nhwc_f16(const void* x, void* y, const void* gamma, const void* beta, int B, int HW, int C, int G,
                              float eps, int act, void* scratch, long long scratch_bytes, void* stream);

@@ -122,8 +122,12 @@ __global__ void __launch_bounds__(GN_THREADS) gn_apply_nhwc_kernel(const __half*
 // ---- 16-byte vectorised NHWC kernels (C % 8 == 0). Thread = (row lane, 8-channel chunk): the chunk stays fixed while
 // the thread walks rows, so per-channel accumulators (stats) or per-channel scale/shift (apply) live in registers and
 // every global access is a full 16-byte load or store with several rows in flight per thread.
+// With `mr_out` set the CTA that finishes last for its image (a ticket counter that wraps back to zero, so it needs no
+// reset) folds all partials of the image, in a fixed order, into mean and 1/std per group: one fold per image instead of
+// one per CTA of the normalising pass.
 __global__ void gn_stats_v8_kernel(const __half* __restrict__ x, float* __restrict__ partial, int HW, int C, int G,
-                                   int rows_per_slab, int R) {
+                                   int rows_per_slab, int R, float* __restrict__ mr_out, unsigned int* __restrict__ tickets,
+                                   double n_total, float eps) {
     extern __shared__ float s_dyn[];    // [blockDim][16]: 8 channel sums then 8 channel sums of squares
     const int slab = blockIdx.x, b = blockIdx.y, nslab = gridDim.x;
     const int NC = C >> 3, cpg = C / G;
@@ -166,24 +170,73 @@ __global__ void gn_stats_v8_kernel(const __half* __restrict__ x, float* __restri
         s_dyn[tid * 16 + 8 + e] = sq[e];
     }
     __syncthreads();
-    if (tid < G) {
-        // fixed summation order: channels of the group, then row lanes -> bit-reproducible statistics
+    // Up to eight threads per group, each summing a strided subset of the group's (channel, row lane) entries, then a
+    // shuffle tree: a fixed summation order, so the statistics are bit-reproducible.
+    int lpg = 8;
+    while (G * lpg > (int)blockDim.x) lpg >>= 1;
+    if ((tid & ~31) < G * lpg) {                  // whole warps take part in the shuffles
+        const int g = tid / lpg, sub = tid % lpg;
         float s = 0.f, q = 0.f;
-        for (int c = tid * cpg; c < (tid + 1) * cpg; ++c) {
-            const int ch = c >> 3, e = c & 7;
-            for (int l = 0; l < R; ++l) {
-                s += s_dyn[(l * NC + ch) * 16 + e];
-                q += s_dyn[(l * NC + ch) * 16 + 8 + e];
+        if (g < G) {
+            const int n = cpg * R;
+            for (int idx = sub; idx < n; idx += lpg) {
+                const int l = idx / cpg, c = g * cpg + (idx - l * cpg);
+                const float* e = s_dyn + (l * NC + (c >> 3)) * 16 + (c & 7);
+                s += e[0];
+                q += e[8];
             }
         }
-        float* o = partial + (((size_t)b * nslab + slab) * G + tid) * 2;
-        o[0] = s;
-        o[1] = q;
+        for (int o = lpg >> 1; o > 0; o >>= 1) {
+            s += __shfl_xor_sync(0xffffffffu, s, o);
+            q += __shfl_xor_sync(0xffffffffu, q, o);
+        }
+        if (g < G && sub == 0) {
+            float* o = partial + (((size_t)b * nslab + slab) * G + g) * 2;
+            o[0] = s;
+            o[1] = q;
+            __threadfence();
+        }
+    }
+    if (!mr_out) return;
+    __shared__ int s_last;
+    __syncthreads();
+    if (tid == 0) s_last = atomicInc(tickets + b, (unsigned int)(nslab - 1)) == (unsigned int)(nslab - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    double* s_part = reinterpret_cast<double*>(s_dyn);      // [parts][G][2]; the per-thread sums above are no longer needed
+    int parts = (int)blockDim.x / G;
+    if (parts > 16) parts = 16;
+    while (parts > 1 && parts * G * 16 > (int)blockDim.x * 64) --parts;
+    if (tid < parts * G) {
+        const int g = tid % G, part = tid / G;
+        double s = 0.0, q = 0.0;
+        const float2* pp = reinterpret_cast<const float2*>(partial) + (size_t)b * nslab * G + g;
+        for (int i = part; i < nslab; i += parts) {
+            const float2 v = __ldcg(pp + (size_t)i * G);
+            s += (double)v.x;
+            q += (double)v.y;
+        }
+        s_part[(part * G + g) * 2] = s;
+        s_part[(part * G + g) * 2 + 1] = q;
+    }
+    __syncthreads();
+    if (tid < G) {
+        double s = 0.0, q = 0.0;
+        for (int i = 0; i < parts; ++i) {
+            s += s_part[(i * G + tid) * 2];
+            q += s_part[(i * G + tid) * 2 + 1];
+        }
+        const double mean = s / n_total;
+        double var = q / n_total - mean * mean;
+        if (var < 0.0) var = 0.0;
+        mr_out[((size_t)b * G + tid) * 2] = (float)mean;
+        mr_out[((size_t)b * G + tid) * 2 + 1] = (float)(1.0 / sqrt(var + (double)eps));
     }
 }
 
-__global__ void gn_apply_v8_kernel(const __half* __restrict__ x, __half* __restrict__ y, const float* __restrict__ partial,
-                                   int nslab_stats, const __half* __restrict__ gamma, const __half* __restrict__ beta, int HW,
+__global__ void gn_apply_v8_kernel(const __half* __restrict__ x, __half* __restrict__ y, const float* __restrict__ mr,
+                                   int unused_, const __half* __restrict__ gamma, const __half* __restrict__ beta, int HW,
                                    int C, int G, int rows_per_slab, int R, double n_total, float eps, int act,
                                    const double* __restrict__ dsums) {
     extern __shared__ float s_dyn[];    // [C] scale, [C] shift
@@ -191,18 +244,11 @@ __global__ void gn_apply_v8_kernel(const __half* __restrict__ x, __half* __restr
     const int slab = blockIdx.x, b = blockIdx.y;
     const int NC = C >> 3, cpg = C / G;
     const int tid = threadIdx.x;
-    if (tid < G) {
-        double s = 0.0, q = 0.0;
-        if (dsums) {
-            s = dsums[((size_t)b * G + tid) * 2];
-            q = dsums[((size_t)b * G + tid) * 2 + 1];
-        } else {
-            const float* pp = partial + ((size_t)b * nslab_stats * G + tid) * 2;
-            for (int i = 0; i < nslab_stats; ++i) {
-                s += (double)pp[(size_t)i * G * 2];
-                q += (double)pp[(size_t)i * G * 2 + 1];
-            }
-        }
+    if (tid < G && mr) {
+        s_mean[tid] = mr[((size_t)b * G + tid) * 2];
+        s_rstd[tid] = mr[((size_t)b * G + tid) * 2 + 1];
+    } else if (tid < G) {
+        const double s = dsums[((size_t)b * G + tid) * 2], q = dsums[((size_t)b * G + tid) * 2 + 1];
         const double mean = s / n_total;
         double var = q / n_total - mean * mean;
         if (var < 0.0) var = 0.0;
@@ -377,9 +423,24 @@ __global__ void __launch_bounds__(256) layer_norm_kernel(const __half* __restric
     }
 }
 
+// Scratch layout of the NHWC kernels: [0, 1024) one ticket counter per image (zero whenever no call is in flight: the
+// counters wrap back by themselves), then mean and 1/std per (image, group), then the per-slab partial sums.
+constexpr int GN_MAX_TICKETS = 256;
+struct GnScratch {
+    unsigned int* tickets;
+    float* mr;
+    float* partial;
+};
+static long long gn_partial_offset(int B, int G) { return (1024 + (long long)B * G * 8 + 255) / 256 * 256; }
+static GnScratch gn_carve(void* scratch, int B, int G) {
+    unsigned char* p = reinterpret_cast<unsigned char*>(scratch);
+    return GnScratch{reinterpret_cast<unsigned int*>(p), reinterpret_cast<float*>(p + 1024),
+                     reinterpret_cast<float*>(p + gn_partial_offset(B, G))};
+}
+
 static int gn_rows_per_slab(int HW, int B) {
-    // aim at >= 4 CTAs per SM over the whole grid, slabs of at least 8 rows
-    int target = (148 * 4 + B - 1) / B;
+    // aim at about 2 CTAs per SM over the whole grid, slabs of at least 8 rows
+    int target = (148 * 2 + B - 1) / B;
     int rows = (HW + target - 1) / target;
     if (rows < 8) rows = 8;
     return rows;
@@ -393,7 +454,7 @@ extern "C" long long katz_group_norm_scratch_bytes(int B, int HW, int C, int G) 
     if (B <= 0 || HW <= 0 || G <= 0) return -1;
     int rows = gn_rows_per_slab(HW, B);
     long long nslab = ceil_div(HW, rows);
-    return (long long)B * nslab * G * 2 * (long long)sizeof(float);
+    return gn_partial_offset(B, G) + (long long)B * nslab * G * 2 * (long long)sizeof(float);
 }
 
 extern "C" int katz_group_norm_nhwc_f16(const void* x, void* y, const void* gamma, const void* beta, int B, int HW, int C,
@@ -412,8 +473,8 @@ extern "C" int katz_group_norm_nhwc_f16(const void* x, void* y, const void* gamm
     dim3 grid(nslab, B);
     cudaStream_t st = (cudaStream_t)stream;
     const int NC = C / 8;
-    if (C % 8 == 0 && NC <= 1024 && aligned16(x) && aligned16(y)) {
-        const int R = NC >= 256 ? 1 : 256 / NC;
+    if (C % 8 == 0 && NC <= 1024 && B <= GN_MAX_TICKETS && aligned16(x) && aligned16(y) && ((uintptr_t)scratch & 255) == 0) {
+        const int R = NC >= 512 ? 1 : 512 / NC;
         const int threads = NC * R;
         static bool attr = false;
         if (!attr) {
@@ -421,14 +482,17 @@ extern "C" int katz_group_norm_nhwc_f16(const void* x, void* y, const void* gamm
             cudaFuncSetAttribute(gn_apply_v8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 8192 * 4);
             attr = true;
         }
-        gn_stats_v8_kernel<<<grid, threads, threads * 64, st>>>((const __half*)x, (float*)scratch, HW, C, G, rows, R);
-        gn_apply_v8_kernel<<<grid, threads, 2 * C * 4, st>>>((const __half*)x, (__half*)y, (const float*)scratch, nslab,
-                                                             (const __half*)gamma, (const __half*)beta, HW, C, G, rows, R,
-                                                             (double)HW * (C / G), eps, act, nullptr);
+        const GnScratch sc = gn_carve(scratch, B, G);
+        const double n_total = (double)HW * (C / G);
+        gn_stats_v8_kernel<<<grid, threads, threads * 64, st>>>((const __half*)x, sc.partial, HW, C, G, rows, R, sc.mr, sc.tickets,
+                                                                n_total, eps);
+        gn_apply_v8_kernel<<<grid, threads, 2 * C * 4, st>>>((const __half*)x, (__half*)y, sc.mr, 0, (const __half*)gamma,
+                                                             (const __half*)beta, HW, C, G, rows, R, n_total, eps, act, nullptr);
         KATZ_LAUNCH_RET();
     }
-    gn_stats_nhwc_kernel<<<grid, GN_THREADS, 0, st>>>((const __half*)x, (float*)scratch, HW, C, G, rows);
-    gn_apply_nhwc_kernel<<<grid, GN_THREADS, 0, st>>>((const __half*)x, (__half*)y, (const float*)scratch, nslab,
+    float* partial = gn_carve(scratch, B, G).partial;      // the ticket counters at the head of the scratch stay untouched
+    gn_stats_nhwc_kernel<<<grid, GN_THREADS, 0, st>>>((const __half*)x, partial, HW, C, G, rows);
+    gn_apply_nhwc_kernel<<<grid, GN_THREADS, 0, st>>>((const __half*)x, (__half*)y, partial, nslab,
                                                       (const __half*)gamma, (const __half*)beta, HW, C, G, rows, eps, act);
     KATZ_LAUNCH_RET();
 }
@@ -436,7 +500,7 @@ extern "C" int katz_group_norm_nhwc_f16(const void* x, void* y, const void* gamm
 static int gn_v8_setup(int C, int* R, int* threads) {
     const int NC = C / 8;
     if (C % 8 != 0 || NC > 1024) return KATZ_ESIZE;
-    *R = NC >= 256 ? 1 : 256 / NC;
+    *R = NC >= 512 ? 1 : 512 / NC;
     *threads = NC * (*R);
     static bool attr = false;
     if (!attr) {
@@ -451,7 +515,7 @@ extern "C" int katz_group_norm_stats_nhwc_f16(const void* x, double* sums, int B
                                               long long scratch_bytes, void* stream) {
     KATZ_CHECK_ARG(x && sums && scratch, KATZ_EINVAL);
     KATZ_CHECK_ARG(B > 0 && B <= 65535 && HW > 0 && C > 0 && G > 0 && G <= GN_MAXG && C % G == 0, KATZ_ESIZE);
-    KATZ_CHECK_ARG(aligned16(x) && ((uintptr_t)sums & 7) == 0 && ((uintptr_t)scratch & 3) == 0, KATZ_EALIGN);
+    KATZ_CHECK_ARG(aligned16(x) && ((uintptr_t)sums & 7) == 0 && ((uintptr_t)scratch & 7) == 0, KATZ_EALIGN);
     KATZ_CHECK_ARG(scratch_bytes >= katz_group_norm_scratch_bytes(B, HW, C, G), KATZ_ESIZE);
     int R, threads;
     int rc = gn_v8_setup(C, &R, &threads);
@@ -459,8 +523,10 @@ extern "C" int katz_group_norm_stats_nhwc_f16(const void* x, double* sums, int B
     const int rows = gn_rows_per_slab(HW, B);
     const int nslab = ceil_div(HW, rows);
     cudaStream_t st = (cudaStream_t)stream;
-    gn_stats_v8_kernel<<<dim3(nslab, B), threads, threads * 64, st>>>((const __half*)x, (float*)scratch, HW, C, G, rows, R);
-    gn_fold_kernel<<<B, GN_MAXG, 0, st>>>((const float*)scratch, nslab, G, sums);
+    const GnScratch sc = gn_carve(scratch, B, G);
+    gn_stats_v8_kernel<<<dim3(nslab, B), threads, threads * 64, st>>>((const __half*)x, sc.partial, HW, C, G, rows, R, nullptr,
+                                                                      nullptr, 0.0, 0.f);
+    gn_fold_kernel<<<B, GN_MAXG, 0, st>>>(sc.partial, nslab, G, sums);
     KATZ_LAUNCH_RET();
 }
 
@@ -548,7 +614,7 @@ extern "C" long long katz_group_norm_static_scratch_bytes(void) { return GN_STAT
 extern "C" int katz_group_norm_nhwc_f16_noalloc(const void* x, void* y, const void* gamma, const void* beta, int B, int HW,
                                                 int C, int G, float eps, int act, void* stream) {
     KATZ_CHECK_ARG(x && y, KATZ_EINVAL);
-    KATZ_CHECK_ARG(B > 0 && B <= 65535 && HW > 0 && C > 0 && G > 0 && G <= GN_MAXG && C % G == 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(B > 0 && B <= GN_MAX_TICKETS && HW > 0 && C > 0 && G > 0 && G <= GN_MAXG && C % G == 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(act == 0 || act == 1, KATZ_EINVAL);
     KATZ_CHECK_ARG(aligned16(x) && aligned16(y), KATZ_EALIGN);
     // sizes whose partial sums do not fit the fixed array are refused, never truncated
@@ -562,10 +628,14 @@ extern "C" int katz_group_norm_nhwc_f16_noalloc(const void* x, void* y, const vo
     const int rows = gn_rows_per_slab(HW, B);
     const int nslab = ceil_div(HW, rows);
     cudaStream_t st = (cudaStream_t)stream;
-    // the statistics pass overwrites every partial the apply pass reads, so nothing left by an earlier call is used
-    gn_stats_v8_kernel<<<dim3(nslab, B), threads, threads * 64, st>>>((const __half*)x, scratch, HW, C, G, rows, R);
-    gn_apply_v8_kernel<<<dim3(nslab, B), threads, 2 * C * 4, st>>>((const __half*)x, (__half*)y, scratch, nslab,
-                                                                   (const __half*)gamma, (const __half*)beta, HW, C, G, rows, R,
-                                                                   (double)HW * (C / G), eps, act, nullptr);
+    // the statistics pass overwrites every partial and statistic the apply pass reads, and the ticket counters return to
+    // zero by themselves, so nothing left by an earlier call is used
+    const GnScratch sc = gn_carve(scratch, B, G);
+    const double n_total = (double)HW * (C / G);
+    gn_stats_v8_kernel<<<dim3(nslab, B), threads, threads * 64, st>>>((const __half*)x, sc.partial, HW, C, G, rows, R, sc.mr,
+                                                                      sc.tickets, n_total, eps);
+    gn_apply_v8_kernel<<<dim3(nslab, B), threads, 2 * C * 4, st>>>((const __half*)x, (__half*)y, sc.mr, 0, (const __half*)gamma,
+                                                                   (const __half*)beta, HW, C, G, rows, R, n_total, eps, act,
+                                                                   nullptr);
     KATZ_LAUNCH_RET();
 }

@@ -156,7 +156,8 @@ _gn_scratch = {}
 def _scratch(device, nbytes):
     buf = _gn_scratch.get(device)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        # zero-filled: the head of the scratch holds the GroupNorm ticket counters, which the kernels return to zero
+        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _gn_scratch[device] = buf
     return buf
 

@@ -31,7 +31,7 @@ def test_no_alloc_group_norm_matches_scratch_entry_point(cuda_device):
         beta = (0.1 * torch.randn(C, generator=g)).half().cuda()
         need = lib.katz_group_norm_scratch_bytes(B, HW, C, 32)
         assert 0 < need <= limit
-        scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
+        scratch = torch.zeros(need, dtype=torch.uint8, device="cuda")      # zero-filled once, as the header asks
         y_ref = torch.empty_like(x)
         rc = lib.katz_group_norm_nhwc_f16(_ptr(x), _ptr(y_ref), _ptr(gamma), _ptr(beta), B, HW, C, 32, 1e-5, act, _ptr(scratch),
                                           need, stream)
