@@ -2,11 +2,15 @@
 // Replaces F.scaled_dot_product_attention as called by AttnProcessor2_0
 // (diffusers/models/attention_processor.py:1276): softmax(Q K^T / sqrt(64)) V per (batch, head).
 //
-// One CTA owns 128 query rows of one (batch, head) and walks the keys in tiles of 128:
-//   * warp 0, one elected thread: TMA loads of Q (once) and of the K and V tiles into 3-stage rings (128-byte swizzle;
+// One CTA owns 128 query rows of one (batch, head) and walks the keys in tiles of 128. The softmax is bound by the
+// special-function unit (one exp2 per score), and a single CTA leaves that unit idle while its four softmax warps wait
+// for TMEM loads, barriers and the row maximum; so the CTA is sized for TWO per SM (113 KB of shared memory, 256 TMEM
+// columns, 168 registers) and the hardware interleaves the two:
+//   * warp 0, one elected thread: TMA loads of Q (once) and of the K and V tiles into 2-stage rings (128-byte swizzle;
 //     Q/K/V are read in place from the [B, S, ld] projection outputs, head h = columns [64h, 64h+64));
-//   * warp 1, one elected thread: S = Q K^T (tcgen05.mma, 128x128x64, K-major operands) into one of two TMEM
-//     accumulators, then O += P V (128x64x128; V is the MN-major operand, P comes from shared memory) into a third;
+//   * warp 1, one elected thread: S = Q K^T (tcgen05.mma, 128x128x64, K-major operands) into a TMEM accumulator that
+//     the softmax frees as soon as the scores sit in registers, then O += P V (128x64x128; V is the MN-major operand,
+//     P comes from shared memory) into a second accumulator;
 //   * warps 2-5: softmax. A thread owns one query row (= one TMEM lane), so row maxima and sums need no shuffles. It
 //     reads S with tcgen05.ld, keeps a running reference maximum that is only raised when the tile maximum exceeds it
 //     by more than 2^8 (so the O accumulator is rescaled rarely: tcgen05.ld / scale / tcgen05.st), writes
@@ -20,10 +24,12 @@ namespace katz {
 
 using namespace tc05;
 
-constexpr int FA_BM = 128, FA_BN = 128, FA_D = 64, FA_ST = 3;
+constexpr int FA_BM = 128, FA_BN = 128, FA_D = 64, FA_ST = 2;
 constexpr int FA_THREADS = 192;
 constexpr int FA_TILE = 128 * 128;                     // bytes of a 128-row x 64-half tile
-constexpr int FA_SMEM = FA_TILE * (1 + 2 * FA_ST + 4) + 1024 + 256;
+constexpr int FA_TMEM_COLS = 256;                      // S at columns 0..127, O at 128..191
+constexpr int FA_SMEM = FA_TILE * (1 + 2 * FA_ST + 2) + 256;     // Q, K ring, V ring, P (two 64-key sub-tiles), barriers
+static_assert(2 * (FA_SMEM + 1024) <= 228 * 1024, "two CTAs must fit one SM");
 constexpr float FA_RESCALE_THRESHOLD = 8.0f;           // log2 units
 
 int* tc05_status_device_ptr();   // defined next to the status word (gemm_tc05.cu)
@@ -60,21 +66,26 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 // kind::f16 instruction descriptor with an MN-major B operand (bit 16)
 __host__ __device__ constexpr uint32_t idesc_f16_bmn(int M, int N) { return idesc_f16(M, N) | (1u << 16); }
 
-__global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
+__global__ void __launch_bounds__(FA_THREADS, 2) attention_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
                                                                        const __grid_constant__ CUtensorMap tmK,
                                                                        const __grid_constant__ CUtensorMap tmV, const FaParams p) {
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // the 128-byte swizzle wants 1024-byte aligned tiles; there is no room for alignment slack when two CTAs share an
+    // SM, so the alignment is requested from the compiler and checked
+    extern __shared__ __align__(1024) unsigned char smem[];
+    if ((smem_u32(smem) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicExch(p.status, 10);
+        return;
+    }
     const uint32_t sQ = smem_u32(smem);
-    const uint32_t sK0 = sQ + FA_TILE, sV0 = sK0 + FA_ST * FA_TILE, sP0 = sV0 + FA_ST * FA_TILE;   // sP: 2 buffers x 2 tiles
+    const uint32_t sK0 = sQ + FA_TILE, sV0 = sK0 + FA_ST * FA_TILE, sP0 = sV0 + FA_ST * FA_TILE;   // sP: two 64-key sub-tiles
     unsigned char* sP_gen = smem + FA_TILE * (1 + 2 * FA_ST);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FA_TILE * (1 + 2 * FA_ST + 4));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FA_TILE * (1 + 2 * FA_ST + 2));
     // barrier map
     const uint32_t b0 = smem_u32(bars);
     const uint32_t q_full = b0, k_full = b0 + 8, k_empty = k_full + 8 * FA_ST, v_full = k_empty + 8 * FA_ST,
-                   v_empty = v_full + 8 * FA_ST, s_full = v_empty + 8 * FA_ST, s_free = s_full + 16, p_full = s_free + 16,
-                   p_free = p_full + 16, o_done = p_free + 16;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1 + 4 * FA_ST + 9);
+                   v_empty = v_full + 8 * FA_ST, s_full = v_empty + 8 * FA_ST, s_free = s_full + 8, p_full = s_free + 8,
+                   p_free = p_full + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1 + 4 * FA_ST + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q0 = blockIdx.x * FA_BM, h = blockIdx.y, b = blockIdx.z;
@@ -91,24 +102,21 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __g
             mbar_init(v_full + 8 * s, 1);
             mbar_init(v_empty + 8 * s, 1);
         }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(s_full + 8 * i, 1);
-            mbar_init(s_free + 8 * i, 4);
-            mbar_init(p_full + 8 * i, 4);
-            mbar_init(p_free + 8 * i, 1);
-        }
-        mbar_init(o_done, 1);
+        mbar_init(s_full, 1);
+        mbar_init(s_free, 4);
+        mbar_init(p_full, 4);
+        mbar_init(p_free, 1);
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_alloc(smem_u32(tmem_slot), FA_TMEM_COLS);
         tmem_relinquish();
     }
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tS0 = tmem_base, tO = tmem_base + 256;      // S buffers at columns 0 and 128, O at 256..319
+    const uint32_t tS0 = tmem_base, tO = tmem_base + 128;      // S at columns 0..127, O at 128..191
 
     if (warp == 0) {
         // ------------------------------------------------------------------------------------ TMA producer
@@ -137,14 +145,14 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __g
             constexpr uint32_t idesc_pv = idesc_f16_bmn(FA_BM, FA_D);
             bool ok = mbar_wait(q_full, 0);
             auto issue_qk = [&](int j) -> bool {
-                const int s = j % FA_ST, buf = j & 1;
+                const int s = j % FA_ST;
                 if (!mbar_wait(k_full + 8 * s, (j / FA_ST) & 1)) return false;
-                if (!mbar_wait(s_free + 8 * buf, ((j >> 1) & 1) ^ 1)) return false;
+                if (!mbar_wait(s_free, (j & 1) ^ 1)) return false;       // the softmax holds tile j-1's scores in registers
                 fence_after_sync();
                 const uint64_t ad = smem_desc_sw128(sQ), bd = smem_desc_sw128(sK0 + s * FA_TILE);
 #pragma unroll
-                for (int k = 0; k < FA_D / 16; ++k) umma_f16(tS0 + buf * FA_BN, ad + 2 * k, bd + 2 * k, idesc_qk, k != 0);
-                umma_commit(s_full + 8 * buf);
+                for (int k = 0; k < FA_D / 16; ++k) umma_f16(tS0, ad + 2 * k, bd + 2 * k, idesc_qk, k != 0);
+                umma_commit(s_full);
                 umma_commit(k_empty + 8 * s);
                 return true;
             };
@@ -154,11 +162,11 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __g
                     ok = issue_qk(j + 1);
                     if (!ok) break;
                 }
-                const int s = j % FA_ST, buf = j & 1;
-                if (!mbar_wait(p_full + 8 * buf, (j >> 1) & 1)) { ok = false; break; }
+                const int s = j % FA_ST;
+                if (!mbar_wait(p_full, j & 1)) { ok = false; break; }
                 if (!mbar_wait(v_full + 8 * s, (j / FA_ST) & 1)) { ok = false; break; }
                 fence_after_sync();
-                const uint32_t pa = sP0 + buf * 2 * FA_TILE, va = sV0 + s * FA_TILE;
+                const uint32_t pa = sP0, va = sV0 + s * FA_TILE;
 #pragma unroll
                 for (int k = 0; k < FA_BN / 16; ++k) {
                     // A = P: two 64-key sub-tiles, +32 B per 16-key step inside a sub-tile.
@@ -168,8 +176,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __g
                     umma_f16(tO, ad, bd, idesc_pv, (j | k) != 0);
                 }
                 umma_commit(v_empty + 8 * s);
-                umma_commit(p_free + 8 * buf);
-                umma_commit(o_done);
+                umma_commit(p_free);
             }
             if (!ok) atomicExch(p.status, 12);
         }
@@ -181,12 +188,11 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __g
         float m_used = -INFINITY, l_sum = 0.f;
         bool ok = true;
         for (int j = 0; j < NT; ++j) {
-            const int buf = j & 1;
-            ok = mbar_wait(s_full + 8 * buf, (j >> 1) & 1);
+            ok = mbar_wait(s_full, j & 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             fence_after_sync();
-            const uint32_t tS = tS0 + buf * FA_BN + lane_base;
+            const uint32_t tS = tS0 + lane_base;
             const int kbase = j * FA_BN;
             const bool tail = kbase + FA_BN > p.Sk;
             // the whole S row (128 fp32) comes into registers with ONE wait: four TMEM loads in flight together
@@ -197,7 +203,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __g
             // S is in registers: the accumulator buffer can take the next Q K^T already
             fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(s_free + 8 * buf);
+            if (lane == 0) mbar_arrive(s_free);
             if (tail) {
 #pragma unroll
                 for (int e = 0; e < FA_BN; ++e)
@@ -217,10 +223,10 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __g
             const float m_new = raise ? mx : m_used;
             const float corr = (raise && j > 0) ? exp2f(m_used - m_new) : 1.0f;
             if (j > 0 && __any_sync(0xffffffffu, raise)) {
-                // O is about to be rescaled: O += P V of tile j-1 must have landed. That MMA signals p_free of the other
-                // P buffer; this thread last observed that barrier one phase back (at tile j-1, for tile j-3), so the
-                // parity wait is unambiguous.
-                ok = mbar_wait(p_free + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1);
+                // O is about to be rescaled: O += P V of tile j-1 must have landed. That MMA signals p_free; this thread
+                // last observed that barrier one phase back (at tile j-1, for tile j-2), so the parity wait is
+                // unambiguous. The same wait below (P free for writing) then passes at once.
+                ok = mbar_wait(p_free, (j - 1) & 1);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 fence_after_sync();
@@ -238,12 +244,12 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __g
             }
             l_sum *= corr;
             m_used = m_new;
-            // P buffer free? (the P V MMA of tile j-2 has finished reading it)
-            ok = mbar_wait(p_free + 8 * buf, ((j >> 1) & 1) ^ 1);
+            // P free? (the P V MMA of tile j-1 has finished reading it; it was issued while this tile's scores were loaded)
+            ok = mbar_wait(p_free, (j & 1) ^ 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             // P = exp2(S*scale - m) (masked keys hold -inf -> 0), row sum on four chains, fp16 into swizzled shared memory
-            unsigned char* prow = sP_gen + buf * 2 * FA_TILE + row * 128;
+            unsigned char* prow = sP_gen + row * 128;
             float ls4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < FA_BN; c += 32) {
@@ -266,10 +272,10 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __g
             // P visible to the tensor core (generic -> async proxy), then signal
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full + 8 * buf);
+            if (lane == 0) mbar_arrive(p_full);
         }
         if (ok) {
-            ok = mbar_wait(p_free + 8 * ((NT - 1) & 1), ((NT - 1) >> 1) & 1);     // the last O += P V has landed
+            ok = mbar_wait(p_free, (NT - 1) & 1);     // the last O += P V has landed
             ok = __all_sync(0xffffffffu, ok);
         }
         if (!ok) {
@@ -302,7 +308,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attention_tc05_kernel(const __g
     __syncthreads();
     if (warp == 1) {
         fence_after_sync();
-        tmem_dealloc(tmem_base, 512);
+        tmem_dealloc(tmem_base, FA_TMEM_COLS);
     }
 }
 
@@ -385,6 +391,9 @@ extern "C" int katz_attention_f16(const void* Q, const void* K, const void* V, v
     static bool attr = false;
     if (!attr) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        // all of the SM's L1/shared storage as shared memory: two CTAs of this kernel per SM
+        e = cudaFuncSetAttribute(attention_tc05_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return (int)e;
         attr = true;
     }
