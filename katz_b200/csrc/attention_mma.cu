@@ -20,6 +20,8 @@ __global__ void __launch_bounds__(ATHREADS) attention_d64_kernel(const __half* _
                                                                  long long bsq, long long bsk, long long bsv,
                                                                  long long bso, float scale_log2e, int kv_chunk_rows,
                                                                  long long kv_chunk_stride) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     __shared__ __align__(128) unsigned char sQ[ABM * 128];
     __shared__ __align__(128) unsigned char sK[2][ABN * 128];
     __shared__ __align__(128) unsigned char sV[2][ABN * 128];
@@ -202,8 +204,7 @@ extern "C" int katz_attention_f16_mma(const void* Q, const void* K, const void* 
         KATZ_CHECK_ARG(kv_chunk_rows % ABN == 0 && kv_chunk_stride % 8 == 0, KATZ_ESIZE);
     }
     dim3 grid(ceil_div(Sq, ABM), H, B);
-    attention_d64_kernel<<<grid, ATHREADS, 0, (cudaStream_t)stream>>>(
-        (const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, Sq, Sk, ldq, ldk, ldv, ldo, bsq, bsk, bsv, bso,
+    launch_k(attention_d64_kernel, grid, ATHREADS, 0, (cudaStream_t)stream, (const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, Sq, Sk, ldq, ldk, ldv, ldo, bsq, bsk, bsv, bso,
         scale * 1.44269504088896340736f, kv_chunk_rows, kv_chunk_stride);
     KATZ_LAUNCH_RET();
 }

@@ -116,6 +116,9 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tc05_kernel(const __g
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // everything above (barriers, TMEM, descriptor prefetch) may overlap the previous kernel's tail; global memory waits
+    pdl_wait();
+    pdl_launch_dependents();
     const uint32_t tS0 = tmem_base, tO = tmem_base + 128;      // S at columns 0..127, O at 128..191
 
     if (warp == 0) {
@@ -398,6 +401,6 @@ extern "C" int katz_attention_f16(const void* Q, const void* K, const void* V, v
         attr = true;
     }
     dim3 grid((Sq + FA_BM - 1) / FA_BM, H, B);
-    attention_tc05_kernel<<<grid, FA_THREADS, FA_SMEM, (cudaStream_t)stream>>>(tq, tk, tv, p);
+    launch_k(attention_tc05_kernel, grid, FA_THREADS, FA_SMEM, (cudaStream_t)stream, tq, tk, tv, p);
     KATZ_LAUNCH_RET();
 }

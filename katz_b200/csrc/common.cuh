@@ -1,5 +1,6 @@
 // Shared device helpers for the katz_b200 kernels (sm_100a only).
 #pragma once
+#include <cstdlib>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -25,6 +26,39 @@
     } while (0)
 
 namespace katz {
+
+// ---- programmatic dependent launch -------------------------------------------------------------------------------------
+// Every kernel of the library is launched with programmatic stream serialisation allowed (KATZ_PDL=0 turns it off): the
+// next kernel's CTAs may become resident, and run whatever precedes pdl_wait() (barrier and TMEM set-up, descriptor
+// prefetch), while the tail of the previous kernel is still running. pdl_wait() returns once every kernel the launch
+// depends on has completed and its writes are visible, so each kernel calls it before its first global-memory access;
+// pdl_launch_dependents() lets the next kernel start that early part.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("KATZ_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);      // the caller reads cudaGetLastError()
+}
 
 __host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 __host__ __device__ inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }

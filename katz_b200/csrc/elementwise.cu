@@ -23,6 +23,8 @@ __device__ __forceinline__ float fast_gelu_mul_one(float x, float m) {
 
 __global__ void fast_gelu_mul_kernel(const __half2* __restrict__ x, const __half2* __restrict__ m, __half2* __restrict__ out,
                                      long long npairs) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < npairs; i += (long long)gridDim.x * blockDim.x) {
         float2 xv = __half22float2(x[i]), mv = __half22float2(m[i]);
         out[i] = __floats2half2_rn(fast_gelu_mul_one(xv.x, mv.x), fast_gelu_mul_one(xv.y, mv.y));
@@ -32,6 +34,8 @@ __global__ void fast_gelu_mul_kernel(const __half2* __restrict__ x, const __half
 // Unfused GEGLU of the reference torch path (activations.py:146-149): h, g = chunk(proj(x)); h * gelu(g), erf GELU,
 // gelu result and product each rounded to half as torch's fp16 ops do.
 __global__ void geglu_erf_kernel(const __half* __restrict__ hg, __half* __restrict__ out, long long M, int F, int ld) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     const int FP = F >> 1;
     const long long total = M * FP;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -53,6 +57,8 @@ struct IntakeArgs {
 };
 __global__ void residual_intake_kernel(const __half2* __restrict__ src, __half2* __restrict__ dst, IntakeArgs a,
                                        long long npairs) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < npairs; i += (long long)gridDim.x * blockDim.x) {
         float2 acc = make_float2(0.f, 0.f);
         for (int k = 0; k < a.n; ++k) {
@@ -70,6 +76,8 @@ __global__ void residual_intake_kernel(const __half2* __restrict__ src, __half2*
 // out[r, 0:half] = cos(t_r * f_i), out[r, half:dim] = sin(t_r * f_i), f_i = exp(-ln(10000) * i / half)
 __global__ void timestep_embedding_kernel(const float* __restrict__ t, __half* __restrict__ out, int rows, int dim,
                                           int ld_out) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     const int half_dim = dim >> 1;
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= rows * half_dim) return;
@@ -81,6 +89,8 @@ __global__ void timestep_embedding_kernel(const float* __restrict__ t, __half* _
 }
 
 __global__ void silu_kernel(const __half2* __restrict__ x, __half2* __restrict__ y, long long npairs) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < npairs; i += (long long)gridDim.x * blockDim.x) {
         float2 v = __half22float2(x[i]);
         y[i] = __floats2half2_rn(silu_f(v.x), silu_f(v.y));
@@ -89,6 +99,8 @@ __global__ void silu_kernel(const __half2* __restrict__ x, __half2* __restrict__
 
 __global__ void add_kernel(const __half2* __restrict__ a, const __half2* __restrict__ b, __half2* __restrict__ y,
                            long long npairs) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < npairs; i += (long long)gridDim.x * blockDim.x) {
         float2 u = __half22float2(a[i]), v = __half22float2(b[i]);
         y[i] = __floats2half2_rn(u.x + v.x, u.y + v.y);
@@ -97,6 +109,8 @@ __global__ void add_kernel(const __half2* __restrict__ a, const __half2* __restr
 
 // NCHW (C real channels) -> NHWC with the channel count padded to Cpad (zeros), and back.
 __global__ void nchw_to_nhwc_kernel(const __half* __restrict__ x, __half* __restrict__ y, int B, int C, int HW, int Cpad) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     long long total = (long long)B * HW * Cpad;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         int c = (int)(i % Cpad);
@@ -107,6 +121,8 @@ __global__ void nchw_to_nhwc_kernel(const __half* __restrict__ x, __half* __rest
     }
 }
 __global__ void nhwc_to_nchw_kernel(const __half* __restrict__ x, __half* __restrict__ y, int B, int C, int HW, int Cpad) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     long long total = (long long)B * C * HW;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         int hw = (int)(i % HW);
@@ -127,6 +143,8 @@ __global__ void nhwc_to_nchw_kernel(const __half* __restrict__ x, __half* __rest
 // fp32 scalar, so torch keeps the result in fp16), optionally written twice (batch-2 CFG input).
 __global__ void euler_scale_input_kernel(const __half* __restrict__ x, __half* __restrict__ out, long long n, float sigma,
                                          int copies, int mode) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     // sigma**2, + 1, ** 0.5 are three separately rounded fp32 operations in the reference: no fused multiply-add
     const float den = __fsqrt_rn(__fadd_rn(__fmul_rn(sigma, sigma), 1.0f));
     const float inv = __fdiv_rn(1.0f, den);
@@ -143,6 +161,8 @@ __global__ void euler_scale_input_kernel(const __half* __restrict__ x, __half* _
 __global__ void euler_cfg_step_kernel(__half* __restrict__ x, const __half* __restrict__ eps_uncond,
                                       const __half* __restrict__ eps_cond, long long n, float guidance, float sigma,
                                       float sigma_next, int mode) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     const float dt = __fsub_rn(sigma_next, sigma);
     const float sigma_mul = mode == 0 ? sigma : rh(sigma);
     const float inv_sigma = __fdiv_rn(1.0f, sigma);
@@ -165,6 +185,8 @@ __global__ void euler_cfg_step_kernel(__half* __restrict__ x, const __half* __re
 // y[r, :] = x1[r, :C1] ++ x2[r, :C2], 16-byte chunks (C1, C2 multiples of 8)
 __global__ void concat_channels_kernel(const uint4* __restrict__ x1, const uint4* __restrict__ x2, uint4* __restrict__ y,
                                        long long rows, int ch1, int ch2) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     const int ch = ch1 + ch2;
     const long long total = rows * ch;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -176,6 +198,8 @@ __global__ void concat_channels_kernel(const uint4* __restrict__ x1, const uint4
 
 // Nearest-neighbour 2x upsample of an NHWC tensor (Upsample2D's F.interpolate, upsampling.py:165-172), 16-byte chunks.
 __global__ void upsample2x_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int B, int H, int W, int ch) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     const long long total = (long long)B * (2 * H) * (2 * W) * ch;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         int c = (int)(i % ch);
@@ -202,7 +226,7 @@ extern "C" int katz_fast_gelu_mul_f16(const void* x, const void* m, void* out, l
     KATZ_CHECK_ARG(x && m && out, KATZ_EINVAL);
     KATZ_CHECK_ARG(n > 0 && n % 2 == 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(((uintptr_t)x & 3) == 0 && ((uintptr_t)m & 3) == 0 && ((uintptr_t)out & 3) == 0, KATZ_EALIGN);
-    fast_gelu_mul_kernel<<<ew_grid(n / 2, 256), 256, 0, (cudaStream_t)stream>>>((const __half2*)x, (const __half2*)m,
+    launch_k(fast_gelu_mul_kernel, ew_grid(n / 2, 256), 256, 0, (cudaStream_t)stream, (const __half2*)x, (const __half2*)m,
                                                                               (__half2*)out, n / 2);
     KATZ_LAUNCH_RET();
 }
@@ -211,7 +235,7 @@ extern "C" int katz_geglu_erf_f16(const void* hg, void* out, long long M, int F,
     KATZ_CHECK_ARG(hg && out, KATZ_EINVAL);
     KATZ_CHECK_ARG(M > 0 && F > 0 && F % 2 == 0 && ld % 2 == 0 && ld >= 2 * F, KATZ_ESIZE);
     KATZ_CHECK_ARG(((uintptr_t)hg & 3) == 0 && ((uintptr_t)out & 3) == 0, KATZ_EALIGN);
-    geglu_erf_kernel<<<ew_grid(M * (F / 2), 256), 256, 0, (cudaStream_t)stream>>>((const __half*)hg, (__half*)out, M, F, ld);
+    launch_k(geglu_erf_kernel, ew_grid(M * (F / 2), 256), 256, 0, (cudaStream_t)stream, (const __half*)hg, (__half*)out, M, F, ld);
     KATZ_LAUNCH_RET();
 }
 
@@ -227,7 +251,7 @@ extern "C" int katz_residual_intake_f16(const void* src, void* dst, const void* 
         a.r[i] = (const __half*)residuals[i];
         a.scale[i] = scales[i];
     }
-    residual_intake_kernel<<<ew_grid(n / 2, 256), 256, 0, (cudaStream_t)stream>>>((const __half2*)src, (__half2*)dst, a, n / 2);
+    launch_k(residual_intake_kernel, ew_grid(n / 2, 256), 256, 0, (cudaStream_t)stream, (const __half2*)src, (__half2*)dst, a, n / 2);
     KATZ_LAUNCH_RET();
 }
 
@@ -235,21 +259,21 @@ extern "C" int katz_timestep_embedding_f16(const float* t, void* out, int rows, 
     KATZ_CHECK_ARG(t && out, KATZ_EINVAL);
     KATZ_CHECK_ARG(rows > 0 && dim > 0 && dim % 2 == 0 && ld_out >= dim, KATZ_ESIZE);
     int n = rows * (dim / 2);
-    timestep_embedding_kernel<<<ceil_div(n, 128), 128, 0, (cudaStream_t)stream>>>(t, (__half*)out, rows, dim, ld_out);
+    launch_k(timestep_embedding_kernel, ceil_div(n, 128), 128, 0, (cudaStream_t)stream, t, (__half*)out, rows, dim, ld_out);
     KATZ_LAUNCH_RET();
 }
 
 extern "C" int katz_silu_f16(const void* x, void* y, long long n, void* stream) {
     KATZ_CHECK_ARG(x && y, KATZ_EINVAL);
     KATZ_CHECK_ARG(n > 0 && n % 2 == 0, KATZ_ESIZE);
-    silu_kernel<<<ew_grid(n / 2, 256), 256, 0, (cudaStream_t)stream>>>((const __half2*)x, (__half2*)y, n / 2);
+    launch_k(silu_kernel, ew_grid(n / 2, 256), 256, 0, (cudaStream_t)stream, (const __half2*)x, (__half2*)y, n / 2);
     KATZ_LAUNCH_RET();
 }
 
 extern "C" int katz_add_f16(const void* a, const void* b, void* y, long long n, void* stream) {
     KATZ_CHECK_ARG(a && b && y, KATZ_EINVAL);
     KATZ_CHECK_ARG(n > 0 && n % 2 == 0, KATZ_ESIZE);
-    add_kernel<<<ew_grid(n / 2, 256), 256, 0, (cudaStream_t)stream>>>((const __half2*)a, (const __half2*)b, (__half2*)y, n / 2);
+    launch_k(add_kernel, ew_grid(n / 2, 256), 256, 0, (cudaStream_t)stream, (const __half2*)a, (const __half2*)b, (__half2*)y, n / 2);
     KATZ_LAUNCH_RET();
 }
 
@@ -259,7 +283,7 @@ extern "C" int katz_concat_channels_f16(const void* x1, const void* x2, void* y,
     KATZ_CHECK_ARG(rows > 0 && C1 > 0 && C2 > 0 && C1 % 8 == 0 && C2 % 8 == 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(aligned16(x1) && aligned16(x2) && aligned16(y), KATZ_EALIGN);
     long long n = rows * ((C1 + C2) / 8);
-    concat_channels_kernel<<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((const uint4*)x1, (const uint4*)x2, (uint4*)y,
+    launch_k(concat_channels_kernel, ew_grid(n, 256), 256, 0, (cudaStream_t)stream, (const uint4*)x1, (const uint4*)x2, (uint4*)y,
                                                                             rows, C1 / 8, C2 / 8);
     KATZ_LAUNCH_RET();
 }
@@ -269,7 +293,7 @@ extern "C" int katz_upsample_nearest2x_nhwc_f16(const void* x, void* y, int B, i
     KATZ_CHECK_ARG(B > 0 && H > 0 && W > 0 && C > 0 && C % 8 == 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(aligned16(x) && aligned16(y), KATZ_EALIGN);
     long long n = (long long)B * 4 * H * W * (C / 8);
-    upsample2x_kernel<<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((const uint4*)x, (uint4*)y, B, H, W, C / 8);
+    launch_k(upsample2x_kernel, ew_grid(n, 256), 256, 0, (cudaStream_t)stream, (const uint4*)x, (uint4*)y, B, H, W, C / 8);
     KATZ_LAUNCH_RET();
 }
 
@@ -277,7 +301,7 @@ extern "C" int katz_nchw_to_nhwc_f16(const void* x, void* y, int B, int C, int H
     KATZ_CHECK_ARG(x && y, KATZ_EINVAL);
     KATZ_CHECK_ARG(B > 0 && C > 0 && HW > 0 && Cpad >= C, KATZ_ESIZE);
     long long n = (long long)B * HW * Cpad;
-    nchw_to_nhwc_kernel<<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((const __half*)x, (__half*)y, B, C, HW, Cpad);
+    launch_k(nchw_to_nhwc_kernel, ew_grid(n, 256), 256, 0, (cudaStream_t)stream, (const __half*)x, (__half*)y, B, C, HW, Cpad);
     KATZ_LAUNCH_RET();
 }
 
@@ -285,7 +309,7 @@ extern "C" int katz_nhwc_to_nchw_f16(const void* x, void* y, int B, int C, int H
     KATZ_CHECK_ARG(x && y, KATZ_EINVAL);
     KATZ_CHECK_ARG(B > 0 && C > 0 && HW > 0 && Cpad >= C, KATZ_ESIZE);
     long long n = (long long)B * HW * C;
-    nhwc_to_nchw_kernel<<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((const __half*)x, (__half*)y, B, C, HW, Cpad);
+    launch_k(nhwc_to_nchw_kernel, ew_grid(n, 256), 256, 0, (cudaStream_t)stream, (const __half*)x, (__half*)y, B, C, HW, Cpad);
     KATZ_LAUNCH_RET();
 }
 
@@ -293,7 +317,7 @@ extern "C" int katz_euler_scale_input(const void* x, void* out, long long n, flo
                                       void* stream) {
     KATZ_CHECK_ARG(x && out, KATZ_EINVAL);
     KATZ_CHECK_ARG(n > 0 && copies >= 1, KATZ_ESIZE);
-    euler_scale_input_kernel<<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((const __half*)x, (__half*)out, n, sigma, copies, mode);
+    launch_k(euler_scale_input_kernel, ew_grid(n, 256), 256, 0, (cudaStream_t)stream, (const __half*)x, (__half*)out, n, sigma, copies, mode);
     KATZ_LAUNCH_RET();
 }
 
@@ -301,7 +325,7 @@ extern "C" int katz_euler_cfg_step(void* x, const void* eps_uncond, const void* 
                                    float sigma, float sigma_next, int mode, void* stream) {
     KATZ_CHECK_ARG(x && eps_uncond, KATZ_EINVAL);
     KATZ_CHECK_ARG(n > 0 && sigma != 0.f, KATZ_ESIZE);
-    euler_cfg_step_kernel<<<ew_grid(n, 256), 256, 0, (cudaStream_t)stream>>>((__half*)x, (const __half*)eps_uncond,
+    launch_k(euler_cfg_step_kernel, ew_grid(n, 256), 256, 0, (cudaStream_t)stream, (__half*)x, (const __half*)eps_uncond,
                                                                            (const __half*)eps_cond, n, guidance, sigma, sigma_next, mode);
     KATZ_LAUNCH_RET();
 }

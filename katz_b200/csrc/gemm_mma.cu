@@ -34,6 +34,8 @@ struct IgemmParams {
 
 template <bool CONV>
 __global__ void __launch_bounds__(NTHREADS) igemm_kernel(const IgemmParams p) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int warp_m = warp & 1, warp_n = warp >> 1;
@@ -231,9 +233,9 @@ static int launch_igemm(const IgemmParams& p, bool conv, cudaStream_t st) {
     dim3 grid(ceil_div(p.N, BN), ceil_div(p.M, BM));
     if (grid.y > 65535) return KATZ_ESIZE;
     if (conv)
-        igemm_kernel<true><<<grid, NTHREADS, IGEMM_SMEM, st>>>(p);
+        launch_k(igemm_kernel<true>, grid, NTHREADS, IGEMM_SMEM, st, p);
     else
-        igemm_kernel<false><<<grid, NTHREADS, IGEMM_SMEM, st>>>(p);
+        launch_k(igemm_kernel<false>, grid, NTHREADS, IGEMM_SMEM, st, p);
     KATZ_LAUNCH_RET();
 }
 

@@ -165,6 +165,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // everything above (barriers, TMEM, descriptor prefetch) may overlap the previous kernel's tail; global memory waits
+    pdl_wait();
+    pdl_launch_dependents();
 
     if (warp == 0) {
         // ------------------------------------------------------------------------------------ TMA producer
@@ -509,7 +512,7 @@ static int launch_tc05(const CUtensorMap& a, const CUtensorMap& b, const CUtenso
     }
     const int total = p.m_tiles * p.n_tiles;
     const int grid = total < sm_count() ? total : sm_count();
-    tc05_gemm_kernel<BN, STAGES, GEGLU><<<grid, TC_THREADS, smem, st>>>(a, b, c, r, p);
+    launch_k(tc05_gemm_kernel<BN, STAGES, GEGLU>, grid, TC_THREADS, smem, st, a, b, c, r, p);
     KATZ_LAUNCH_RET();
 }
 

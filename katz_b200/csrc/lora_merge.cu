@@ -154,6 +154,8 @@ template <typename T>
 __global__ void __launch_bounds__(LM_THREADS, 1) lora_merge_kernel(const katz_lora_layer* __restrict__ layers,
                                                                    const int* __restrict__ tile_start, int n_layers,
                                                                    int total_tiles, float sign, int counts_in_smem) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     using Cfg = LmCfg<T>;
     constexpr int TM = Cfg::TM, NST = Cfg::NST;
     constexpr int ES = sizeof(T);
@@ -372,6 +374,8 @@ __global__ void __launch_bounds__(LM_THREADS, 1) lora_merge_f16_tc05_kernel(cons
                                                                            const int* __restrict__ tile_start, int n_layers,
                                                                            int total_tiles, float sign, int counts_in_smem,
                                                                            int* __restrict__ status) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     using namespace tc05;
     using T = __half;
     using Cfg = LmCfg<__half>;
@@ -601,6 +605,8 @@ __global__ void __launch_bounds__(WS_THREADS, 1) lora_merge_f16_ws_kernel(const 
                                                                          const int* __restrict__ tile_start, int n_layers,
                                                                          int total_tiles, float sign,
                                                                          int* __restrict__ status, int CH) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     using namespace tc05;
     using T = __half;
     extern __shared__ unsigned char smem_raw[];
@@ -882,7 +888,7 @@ extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_til
         }
         int* status = tc05_status_device_ptr();
         if (!status) return KATZ_ENOTREADY;
-        lora_merge_f16_ws_kernel<<<grid, WS_THREADS, WS_SMEM, st>>>(d_layers, reinterpret_cast<const CUtensorMap*>(d_tile_maps),
+        launch_k(lora_merge_f16_ws_kernel, grid, WS_THREADS, WS_SMEM, st, d_layers, reinterpret_cast<const CUtensorMap*>(d_tile_maps),
                                                                     d_tile_start, n_layers, total_tiles, sign, status,
                                                                     (flags & KATZ_LORA_NO_ADAPTERS) ? 1 : WS_CHUNK);
     } else if (w_dtype == KATZ_DTYPE_F16 && use_tc05) {
@@ -895,12 +901,12 @@ extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_til
         }
         int* status = tc05_status_device_ptr();
         if (!status) return KATZ_ENOTREADY;
-        lora_merge_f16_tc05_kernel<<<grid, LM_THREADS, LmCfg<__half>::SMEM + 1024, st>>>(d_layers, d_tile_start, n_layers,
+        launch_k(lora_merge_f16_tc05_kernel, grid, LM_THREADS, LmCfg<__half>::SMEM + 1024, st, d_layers, d_tile_start, n_layers,
                                                                                           total_tiles, sign, in_smem, status);
     } else if (w_dtype == KATZ_DTYPE_F16)
-        lora_merge_kernel<__half><<<grid, LM_THREADS, LmCfg<__half>::SMEM, st>>>(d_layers, d_tile_start, n_layers, total_tiles, sign, in_smem);
+        launch_k(lora_merge_kernel<__half>, grid, LM_THREADS, LmCfg<__half>::SMEM, st, d_layers, d_tile_start, n_layers, total_tiles, sign, in_smem);
     else
-        lora_merge_kernel<float><<<grid, LM_THREADS, LmCfg<float>::SMEM, st>>>(d_layers, d_tile_start, n_layers, total_tiles, sign, in_smem);
+        launch_k(lora_merge_kernel<float>, grid, LM_THREADS, LmCfg<float>::SMEM, st, d_layers, d_tile_start, n_layers, total_tiles, sign, in_smem);
     KATZ_LAUNCH_RET();
 }
 

@@ -18,6 +18,8 @@ constexpr int GN_MAXG = 64;
 
 __global__ void __launch_bounds__(GN_THREADS) gn_stats_nhwc_kernel(const __half* __restrict__ x, float* __restrict__ partial,
                                                                    int HW, int C, int G, int rows_per_slab) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     // per-thread partials parked in shared memory and summed per group in a FIXED order: the statistics, and with them
     // every GroupNorm output, are bit-reproducible from run to run (no floating-point atomics)
     __shared__ float2 s_part[GN_MAXP][GN_THREADS];
@@ -64,6 +66,8 @@ __global__ void __launch_bounds__(GN_THREADS) gn_apply_nhwc_kernel(const __half*
                                                                    const __half* __restrict__ gamma,
                                                                    const __half* __restrict__ beta, int HW, int C, int G,
                                                                    int rows_per_slab, float eps, int act) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     __shared__ float s_mean[GN_MAXG], s_rstd[GN_MAXG];
     const int slab = blockIdx.x, b = blockIdx.y;
     const int tid = threadIdx.x;
@@ -128,6 +132,8 @@ __global__ void __launch_bounds__(GN_THREADS) gn_apply_nhwc_kernel(const __half*
 __global__ void gn_stats_v8_kernel(const __half* __restrict__ x, float* __restrict__ partial, int HW, int C, int G,
                                    int rows_per_slab, int R, float* __restrict__ mr_out, unsigned int* __restrict__ tickets,
                                    double n_total, float eps) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     extern __shared__ float s_dyn[];    // [blockDim][16]: 8 channel sums then 8 channel sums of squares
     const int slab = blockIdx.x, b = blockIdx.y, nslab = gridDim.x;
     const int NC = C >> 3, cpg = C / G;
@@ -239,6 +245,8 @@ __global__ void gn_apply_v8_kernel(const __half* __restrict__ x, __half* __restr
                                    int unused_, const __half* __restrict__ gamma, const __half* __restrict__ beta, int HW,
                                    int C, int G, int rows_per_slab, int R, double n_total, float eps, int act,
                                    const double* __restrict__ dsums) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     extern __shared__ float s_dyn[];    // [C] scale, [C] shift
     __shared__ float s_mean[GN_MAXG], s_rstd[GN_MAXG];
     const int slab = blockIdx.x, b = blockIdx.y;
@@ -303,6 +311,8 @@ __global__ void gn_apply_v8_kernel(const __half* __restrict__ x, __half* __restr
 // Folds the per-slab partials of one shard into [B, G, 2] fp64 sums (fixed order): the quantity that is summed across
 // ranks when the latent is row-split.
 __global__ void gn_fold_kernel(const float* __restrict__ partial, int nslab, int G, double* __restrict__ sums) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     const int b = blockIdx.x, g = threadIdx.x;
     if (g >= G) return;
     double s = 0.0, q = 0.0;
@@ -319,6 +329,8 @@ __global__ void gn_fold_kernel(const float* __restrict__ partial, int nslab, int
 __global__ void __launch_bounds__(1024) gn_nchw_kernel(const __half* __restrict__ x, __half* __restrict__ y,
                                                        const __half* __restrict__ gamma, const __half* __restrict__ beta,
                                                        int HW, int C, int G, float eps, int act) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     __shared__ double s_a[32], s_b[32];
     __shared__ float s_mean, s_rstd;
     const int g = blockIdx.x, b = blockIdx.y, cpg = C / G;
@@ -366,6 +378,8 @@ constexpr int LN_MAXCH = 10;  // 16-byte chunks per lane: C <= 32 * 10 * 8 = 256
 __global__ void __launch_bounds__(256) layer_norm_kernel(const __half* __restrict__ x, __half* __restrict__ y,
                                                          const __half* __restrict__ gamma, const __half* __restrict__ beta,
                                                          int rows, int C, float eps) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -484,15 +498,15 @@ extern "C" int katz_group_norm_nhwc_f16(const void* x, void* y, const void* gamm
         }
         const GnScratch sc = gn_carve(scratch, B, G);
         const double n_total = (double)HW * (C / G);
-        gn_stats_v8_kernel<<<grid, threads, threads * 64, st>>>((const __half*)x, sc.partial, HW, C, G, rows, R, sc.mr, sc.tickets,
+        launch_k(gn_stats_v8_kernel, grid, threads, threads * 64, st, (const __half*)x, sc.partial, HW, C, G, rows, R, sc.mr, sc.tickets,
                                                                 n_total, eps);
-        gn_apply_v8_kernel<<<grid, threads, 2 * C * 4, st>>>((const __half*)x, (__half*)y, sc.mr, 0, (const __half*)gamma,
+        launch_k(gn_apply_v8_kernel, grid, threads, 2 * C * 4, st, (const __half*)x, (__half*)y, sc.mr, 0, (const __half*)gamma,
                                                              (const __half*)beta, HW, C, G, rows, R, n_total, eps, act, nullptr);
         KATZ_LAUNCH_RET();
     }
     float* partial = gn_carve(scratch, B, G).partial;      // the ticket counters at the head of the scratch stay untouched
-    gn_stats_nhwc_kernel<<<grid, GN_THREADS, 0, st>>>((const __half*)x, partial, HW, C, G, rows);
-    gn_apply_nhwc_kernel<<<grid, GN_THREADS, 0, st>>>((const __half*)x, (__half*)y, partial, nslab,
+    launch_k(gn_stats_nhwc_kernel, grid, GN_THREADS, 0, st, (const __half*)x, partial, HW, C, G, rows);
+    launch_k(gn_apply_nhwc_kernel, grid, GN_THREADS, 0, st, (const __half*)x, (__half*)y, partial, nslab,
                                                       (const __half*)gamma, (const __half*)beta, HW, C, G, rows, eps, act);
     KATZ_LAUNCH_RET();
 }
@@ -524,9 +538,9 @@ extern "C" int katz_group_norm_stats_nhwc_f16(const void* x, double* sums, int B
     const int nslab = ceil_div(HW, rows);
     cudaStream_t st = (cudaStream_t)stream;
     const GnScratch sc = gn_carve(scratch, B, G);
-    gn_stats_v8_kernel<<<dim3(nslab, B), threads, threads * 64, st>>>((const __half*)x, sc.partial, HW, C, G, rows, R, nullptr,
+    launch_k(gn_stats_v8_kernel, dim3(nslab, B), threads, threads * 64, st, (const __half*)x, sc.partial, HW, C, G, rows, R, nullptr,
                                                                       nullptr, 0.0, 0.f);
-    gn_fold_kernel<<<B, GN_MAXG, 0, st>>>(sc.partial, nslab, G, sums);
+    launch_k(gn_fold_kernel, B, GN_MAXG, 0, st, sc.partial, nslab, G, sums);
     KATZ_LAUNCH_RET();
 }
 
@@ -541,8 +555,7 @@ extern "C" int katz_group_norm_apply_nhwc_f16(const void* x, void* y, const doub
     if (rc) return rc;
     const int rows = gn_rows_per_slab(HW, B);
     const int nslab = ceil_div(HW, rows);
-    gn_apply_v8_kernel<<<dim3(nslab, B), threads, 2 * C * 4, (cudaStream_t)stream>>>(
-        (const __half*)x, (__half*)y, nullptr, 0, (const __half*)gamma, (const __half*)beta, HW, C, G, rows, R, n_total, eps, act,
+    launch_k(gn_apply_v8_kernel, dim3(nslab, B), threads, 2 * C * 4, (cudaStream_t)stream, (const __half*)x, (__half*)y, nullptr, 0, (const __half*)gamma, (const __half*)beta, HW, C, G, rows, R, n_total, eps, act,
         sums);
     KATZ_LAUNCH_RET();
 }
@@ -553,7 +566,7 @@ extern "C" int katz_group_norm_nchw_f16(const void* x, void* y, const void* gamm
     KATZ_CHECK_ARG(B > 0 && HW > 0 && C > 0 && G > 0 && C % G == 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(B <= 65535, KATZ_ESIZE);
     KATZ_CHECK_ARG(act == 0 || act == 1, KATZ_EINVAL);
-    gn_nchw_kernel<<<dim3(G, B), 1024, 0, (cudaStream_t)stream>>>((const __half*)x, (__half*)y, (const __half*)gamma,
+    launch_k(gn_nchw_kernel, dim3(G, B), 1024, 0, (cudaStream_t)stream, (const __half*)x, (__half*)y, (const __half*)gamma,
                                                                   (const __half*)beta, HW, C, G, eps, act);
     KATZ_LAUNCH_RET();
 }
@@ -565,8 +578,7 @@ extern "C" int katz_layer_norm_f16(const void* x, void* y, const void* gamma, co
     KATZ_CHECK_ARG(C % 8 == 0 && C <= 32 * LN_MAXCH * 8, KATZ_ESIZE);
     KATZ_CHECK_ARG(aligned16(x) && aligned16(y) && aligned16(gamma) && aligned16(beta), KATZ_EALIGN);
     const int rows_per_cta = 8;
-    layer_norm_kernel<<<ceil_div(rows, rows_per_cta), rows_per_cta * 32, 0, (cudaStream_t)stream>>>(
-        (const __half*)x, (__half*)y, (const __half*)gamma, (const __half*)beta, rows, C, eps);
+    launch_k(layer_norm_kernel, ceil_div(rows, rows_per_cta), rows_per_cta * 32, 0, (cudaStream_t)stream, (const __half*)x, (__half*)y, (const __half*)gamma, (const __half*)beta, rows, C, eps);
     KATZ_LAUNCH_RET();
 }
 
@@ -632,9 +644,9 @@ extern "C" int katz_group_norm_nhwc_f16_noalloc(const void* x, void* y, const vo
     // zero by themselves, so nothing left by an earlier call is used
     const GnScratch sc = gn_carve(scratch, B, G);
     const double n_total = (double)HW * (C / G);
-    gn_stats_v8_kernel<<<dim3(nslab, B), threads, threads * 64, st>>>((const __half*)x, sc.partial, HW, C, G, rows, R, sc.mr,
+    launch_k(gn_stats_v8_kernel, dim3(nslab, B), threads, threads * 64, st, (const __half*)x, sc.partial, HW, C, G, rows, R, sc.mr,
                                                                       sc.tickets, n_total, eps);
-    gn_apply_v8_kernel<<<dim3(nslab, B), threads, 2 * C * 4, st>>>((const __half*)x, (__half*)y, sc.mr, 0, (const __half*)gamma,
+    launch_k(gn_apply_v8_kernel, dim3(nslab, B), threads, 2 * C * 4, st, (const __half*)x, (__half*)y, sc.mr, 0, (const __half*)gamma,
                                                                    (const __half*)beta, HW, C, G, rows, R, n_total, eps, act,
                                                                    nullptr);
     KATZ_LAUNCH_RET();
