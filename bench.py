@@ -184,6 +184,9 @@ def main():
                     help="launch the dominant linear GEMM shapes between cudaProfilerStart/Stop and exit")
     ap.add_argument("--profile-merge", action="store_true",
                     help="run ONE LoRA merge over a reduced layer set between cudaProfilerStart/Stop and exit")
+    ap.add_argument("--parallel", default="auto", choices=["auto", "rows"],
+                    help="N > 1: 'auto' splits the CFG batch over two halves of the ranks and the latent rows inside a half; "
+                         "'rows' splits latent rows only")
     ap.add_argument("--latent", type=int, default=128, help="latent height = width (128 = 1024^2 images)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "katz" else max(args.warmup, 0)
@@ -290,8 +293,9 @@ def main():
     h_out = torch.empty(B, 4, HW, HW, dtype=torch.float16).pin_memory()
 
     if world > 1:
-        from katz_b200.latent_parallel import RowParallelStep
-        step = RowParallelStep(unet, B, HW, HW, rank, world)
+        from katz_b200.latent_parallel import CfgRowParallelStep
+        # batch halves first (the reference's own 2-GPU mode), latent rows inside a half; --parallel rows = rows only
+        step = CfgRowParallelStep(unet, B, HW, HW, rank, world, split_cfg=(args.parallel == "auto"))
     else:
         step = GraphedStep(unet, B, HW, HW)
     step.run(sample=h_sample, timestep=h_t, encoder_hidden_states=h_ctx, text_embeds=h_te, time_ids=h_ti)
@@ -304,7 +308,7 @@ def main():
 
     # ---- device-resident timing
     for _ in range(args.warmup):
-        step.graph.replay()
+        step.replay()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -313,7 +317,7 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        step.graph.replay()
+        step.replay()
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1) / args.steps
@@ -351,7 +355,7 @@ def main():
         barrier()
         e2e_ms = e0.elapsed_time(e1) / args.steps
     h2d = sum(t.numel() * t.element_size() for t in (h_sample, h_ctx, h_te, h_ti, h_t))
-    d2h = h_out.numel() * h_out.element_size() // (world if world > 1 else 1)
+    d2h = h_out.numel() * h_out.element_size()
 
     if world > 1:
         t = torch.tensor([ms, e2e_ms], device=dev)
@@ -391,7 +395,9 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": "SDXL UNet step, batch 2 (CFG), latent %dx%d, 1 rank-64 LoRA merged (configs[1])" % (HW, HW),
-                       "latent_parallel": world, "l2": "inputs larger than L2: 5.1 GB of weights streamed per step",
+                       "latent_parallel": world,
+                       "parallelism": ("1 GPU" if world == 1 else "cfg%d x rows%d" % (step.halves, step.rows_world)),
+                       "l2": "inputs larger than L2: 5.1 GB of weights streamed per step",
                        "timing": "CUDA-graph replay, CUDA events, max over ranks"},
             "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": step.launches_per_step * args.steps,

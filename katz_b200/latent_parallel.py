@@ -144,5 +144,79 @@ class RowParallelStep:
         self.launches_per_step = self._inner.launches_per_step
         self.static = self._inner.static
 
+    def replay(self):
+        return self._inner.replay()
+
     def run(self, **tensors):
         return self._inner.run(**tensors)
+
+
+def cfg_rows_layout(batch, world, rank, split_cfg=True):
+    """How `world` ranks share a step of `batch` samples: (halves, rows_world, half, row_rank, local_batch).
+
+    With an even batch (classifier-free guidance: unconditional and conditional halves) and an even world the batch is
+    split first — each half of the ranks runs one half of the batch, the reference's own 2-GPU mode
+    (sdxl_unet_server.py:41,199-215), with no exchange inside the step — and only the ranks of one half row-split the
+    latent among themselves. An odd batch or an odd world falls back to the pure row split."""
+    if world < 1 or not (0 <= rank < world):
+        raise KatzError("bad rank/world: %s/%s" % (rank, world))
+    halves = 2 if (split_cfg and batch % 2 == 0 and world % 2 == 0) else 1
+    rows_world = world // halves
+    return halves, rows_world, rank // rows_world, rank % rows_world, batch // halves
+
+
+def assemble_halves(gathered, halves, rows_world, out=None):
+    """gathered: [world, local_batch, ...] (an all-gather of every rank's result, each already whole in rows) ->
+    [batch, ...]: half h of the batch is what the first rank of half h holds."""
+    world, lb = gathered.shape[0], gathered.shape[1]
+    if out is None:
+        out = torch.empty((halves * lb,) + tuple(gathered.shape[2:]), dtype=gathered.dtype, device=gathered.device)
+    for h in range(halves):
+        out[h * lb:(h + 1) * lb].copy_(gathered[h * rows_world])
+    return out
+
+
+class CfgRowParallelStep:
+    """CUDA-graph step shared by `world` ranks: batch halves first, latent rows inside a half (cfg_rows_layout). Same
+    interface as engine.GraphedStep; every rank passes the same full-batch inputs and receives the whole prediction."""
+
+    def __init__(self, unet, batch, height, width, rank, world, text_len=77, warmup=2, split_cfg=True):
+        from .engine import GraphedStep
+        self.rank, self.world = rank, world
+        self.halves, self.rows_world, self.half, self.row_rank, self.local_batch = cfg_rows_layout(batch, world, rank, split_cfg)
+        row_group = None
+        if self.halves > 1 and self.rows_world > 1:
+            # every rank creates every group, in the same order
+            groups = [dist.new_group(list(range(h * self.rows_world, (h + 1) * self.rows_world))) for h in range(self.halves)]
+            row_group = groups[self.half]
+        if self.rows_world > 1:
+            self._inner = RowParallelStep(unet, self.local_batch, height, width, self.row_rank, self.rows_world,
+                                          text_len=text_len, group=row_group, warmup=warmup)
+        else:
+            unet.rp = None
+            self._inner = GraphedStep(unet, self.local_batch, height, width, text_len=text_len, warmup=warmup)
+        self.graph = self._inner.graph
+        self.launches_per_step = self._inner.launches_per_step
+        self.static = self._inner.static
+        self.out = None
+        self._gathered = None
+        if self.halves > 1:
+            c = unet.cfg["out_channels"]
+            self._gathered = torch.empty((world, self.local_batch, c, height, width), dtype=torch.float16, device=unet.device)
+            self.out = torch.empty((batch, c, height, width), dtype=torch.float16, device=unet.device)
+
+    def replay(self):
+        """Run the step on whatever the static input buffers hold, then assemble the batch halves."""
+        return self._finish(self._inner.replay())
+
+    def run(self, **tensors):
+        lb, h = self.local_batch, self.half
+        local = {k: (v if (k == "timestep" or self.halves == 1) else v[h * lb:(h + 1) * lb]) for k, v in tensors.items()}
+        return self._finish(self._inner.run(**local))
+
+    def _finish(self, o):
+        lb = self.local_batch
+        if self.halves == 1:
+            return o
+        dist.all_gather_into_tensor(self._gathered.view((self.world * lb,) + tuple(self._gathered.shape[2:])), o.contiguous())
+        return assemble_halves(self._gathered, self.halves, self.rows_world, out=self.out)

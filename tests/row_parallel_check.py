@@ -41,9 +41,22 @@ def main():
     ok = err <= 1e-2 and rel <= 2e-3
     print("rank %d/%d row-split vs single-GPU: max-abs %.3e rel-l2 %.3e %s" % (rank, world, err, rel, "OK" if ok else "MISMATCH"),
           flush=True)
+    # the graphed step that splits the batch halves first and the rows inside a half
+    from katz_b200.latent_parallel import CfgRowParallelStep
+    unet.rp = None
+    ref2 = unet(sample, t, **kw)[0]
+    step = CfgRowParallelStep(unet, sample.shape[0], cfg["sample_size"], cfg["sample_size"], rank, world, text_len=ctx.shape[1])
+    out2 = step.run(sample=sample, timestep=t, encoder_hidden_states=ctx, text_embeds=te, time_ids=ti)
+    torch.cuda.synchronize()
+    err2 = float((out2.float() - ref2.float()).abs().max())
+    rel2 = float((out2.float() - ref2.float()).norm() / ref2.float().norm())
+    ok2 = err2 <= 1e-2 and rel2 <= 2e-3
+    print("rank %d/%d cfg%d x rows%d graphed step vs single-GPU: max-abs %.3e rel-l2 %.3e %s"
+          % (rank, world, step.halves, step.rows_world, err2, rel2, "OK" if ok2 else "MISMATCH"), flush=True)
     dist.barrier()
-    dist.destroy_process_group()
-    sys.exit(0 if ok else 1)
+    torch.cuda.synchronize()
+    # NCCL communicators captured in live CUDA graphs do not tear down cleanly: leave without destroying the group
+    os._exit(0 if (ok and ok2) else 1)
 
 
 if __name__ == "__main__":

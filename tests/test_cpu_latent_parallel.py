@@ -146,3 +146,21 @@ def test_single_rank_is_identity():
     t, b = rp.exchange_halo(x)
     assert float(t.abs().max()) == 0 and float(b.abs().max()) == 0
     assert torch.equal(rp.gather_rows(x), x) and torch.equal(rp.shard_rows(x), x)
+
+
+def test_cfg_rows_layout_and_assembly():
+    """Batch halves first, rows inside a half: the bookkeeping of the multi-GPU step, on CPU tensors."""
+    from katz_b200.latent_parallel import assemble_halves, cfg_rows_layout
+    assert cfg_rows_layout(2, 1, 0) == (1, 1, 0, 0, 2)
+    assert cfg_rows_layout(2, 2, 1) == (2, 1, 1, 0, 1)
+    assert cfg_rows_layout(2, 8, 5) == (2, 4, 1, 1, 1)
+    assert cfg_rows_layout(2, 8, 5, split_cfg=False) == (1, 8, 0, 5, 2)
+    assert cfg_rows_layout(3, 4, 2) == (1, 4, 0, 2, 3)          # odd batch: rows only
+    assert cfg_rows_layout(2, 3, 2) == (1, 3, 0, 2, 2)          # odd world: rows only
+    with pytest.raises(Exception):
+        cfg_rows_layout(2, 2, 2)
+    world, lb = 4, 1
+    per_half = [torch.full((lb, 4, 8, 8), float(h + 1)) for h in range(2)]
+    gathered = torch.stack([per_half[r // 2] for r in range(world)])       # every rank of a half holds that half, whole
+    out = assemble_halves(gathered, 2, 2)
+    assert out.shape == (2, 4, 8, 8) and float(out[0].mean()) == 1.0 and float(out[1].mean()) == 2.0
