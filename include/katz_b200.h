@@ -147,12 +147,13 @@ int katz_linear_f16(const void* A, int lda, const void* W, void* C, int ldc, int
  * fp16 tensors round. Same shape rules as katz_linear_f16, F % 16 == 0. */
 int katz_linear_geglu_f16(const void* A, int lda, const void* W, void* C, int ldc, int M, int F, int K, const void* bias,
                           void* stream);
-/* 3x3, stride 1, padding 1 NHWC convolution on the tcgen05 path (nn.Conv2d of ResnetBlock2D, resnet.py:378,408).
- * X[B,Hin,W,Cin], W[Cout,3,3,Cin], Y[B,Hout,W,Cout] with Hout = Hin + 2*pad_h - 2: pad_h = 1 is the usual padding,
- * pad_h = 0 is for a row shard whose input already carries its halo rows (latent-row parallelism). Needs Cin % 64 == 0, Cout % 8 == 0 and W a power of two >= 8 or a
- * multiple of 128. Epilogue as katz_conv2d_nhwc_f16_mma. */
-int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int B, int Hin, int Wd, int Cin, int Cout, int pad_h,
-                          const void* bias, const void* rowvec, int ld_rowvec, const void* residual, int act,
+/* 3x3 NHWC convolution, stride 1 or 2, horizontal padding 1, on the tcgen05 path (nn.Conv2d of ResnetBlock2D,
+ * resnet.py:378,408; Downsample2D, downsampling.py). X[B,Hin,Win,Cin], W[Cout,3,3,Cin], Y[B,Hout,Wout,Cout] with
+ * Hout = (Hin + 2*pad_h - 3)/stride + 1 and Wout = (Win - 1)/stride + 1: pad_h = 1 is the usual padding, pad_h = 0 is for
+ * a row shard whose input already carries its halo rows (latent-row parallelism). Needs Cin % 64 == 0, Cout % 8 == 0
+ * and Wout a power of two >= 8 or a multiple of 128 (stride 2: Win even). Epilogue as katz_conv2d_nhwc_f16_mma. */
+int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int B, int Hin, int Win, int Cin, int Cout, int stride,
+                          int pad_h, const void* bias, const void* rowvec, int ld_rowvec, const void* residual, int act,
                           float out_scale, void* stream);
 /* Status word of the tcgen05 kernels: 0, or which bounded device-side wait gave up (1 producer, 2 MMA issuer,
  * 3 epilogue). Reading it synchronises the device; clear it before the next launch. */

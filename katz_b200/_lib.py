@@ -69,7 +69,7 @@ SIGNATURES = {
     "katz_linear_f16_mma": (_I, [_V, _I, _V, _V, _I, _I, _I, _I, _V, _V, _I, _I, _V, _I, _I, _F, _V]),
     "katz_linear_f16": (_I, [_V, _I, _V, _V, _I, _I, _I, _I, _V, _V, _I, _I, _V, _I, _I, _F, _V]),
     "katz_linear_geglu_f16": (_I, [_V, _I, _V, _V, _I, _I, _I, _I, _V, _V]),
-    "katz_conv3x3_nhwc_f16": (_I, [_V, _V, _V, _I, _I, _I, _I, _I, _I, _V, _V, _I, _V, _I, _F, _V]),
+    "katz_conv3x3_nhwc_f16": (_I, [_V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _V, _V, _I, _V, _I, _F, _V]),
     "katz_tc05_status": (_I, []),
     "katz_tc05_clear_status": (_I, []),
     "katz_upsample_nearest2x_nhwc_f16": (_I, [_V, _V, _I, _I, _I, _I, _V]),

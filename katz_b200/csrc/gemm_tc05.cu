@@ -46,7 +46,7 @@ struct Tc05Params {
     int geglu_F;            // > 0: GEGLU mode, weight has 2F rows
     int rows_img;           // rows of one image of the output tensor map (M for a linear layer, H*W for a convolution)
     // convolution geometry (stride 1, output size = input size)
-    int conv, H, W, TW, TH, tiles_w, tiles_h, cin_chunks, ksize, pad_h, pad_w;   // H, W: OUTPUT size
+    int conv, H, W, TW, TH, tiles_w, tiles_h, cin_chunks, ksize, pad_h, pad_w, stride;   // H, W: OUTPUT size
     int* status;
 };
 
@@ -197,7 +197,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                         const int tap = kt / p.cin_chunks;
                         const int cc = kt - tap * p.cin_chunks;
                         const int ky = tap / p.ksize, kx = tap - ky * p.ksize;
-                        tma_load_4d(sa, &tmA, cc * TBK, cw0 + kx - p.pad_w, ch0 + ky - p.pad_h, cb, fb);
+                        // the tensor map walks the input with the convolution's stride: TW x TH pixels per box
+                        tma_load_4d(sa, &tmA, cc * TBK, cw0 * p.stride + kx - p.pad_w, ch0 * p.stride + ky - p.pad_h, cb, fb);
                     } else {
                         tma_load_2d(sa, &tmA, kt * TBK, m0, fb);
                     }
@@ -471,13 +472,15 @@ static int encode_out(CUtensorMap* map, const void* base, int N, long long rows_
     return r == CUDA_SUCCESS ? 0 : KATZ_EINVAL;
 }
 
-static int encode_nhwc(CUtensorMap* map, const void* base, int B, int H, int W, int C, int TW, int TH) {
+// Input of the implicit-GEMM convolution: boxes of TW x TH pixels x 64 channels. With stride 2 the map's traversal stride
+// picks every second pixel (the box then spans 2 TW x 2 TH pixels of the tensor and still delivers TW x TH).
+static int encode_nhwc(CUtensorMap* map, const void* base, int B, int H, int W, int C, int TW, int TH, int stride) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return KATZ_ENOTREADY;
     cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)B};
     cuuint64_t strides[3] = {(cuuint64_t)C * 2, (cuuint64_t)W * C * 2, (cuuint64_t)H * W * C * 2};
-    cuuint32_t box[4] = {(cuuint32_t)TBK, (cuuint32_t)TW, (cuuint32_t)TH, 1};
-    cuuint32_t es[4] = {1, 1, 1, 1};
+    cuuint32_t box[4] = {(cuuint32_t)TBK, (cuuint32_t)(TW * stride), (cuuint32_t)(TH * stride), 1};
+    cuuint32_t es[4] = {1, (cuuint32_t)stride, (cuuint32_t)stride, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, es,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -627,13 +630,15 @@ extern "C" int katz_linear_geglu_f16(const void* A, int lda, const void* W, void
     return linear_common(A, lda, W, C, ldc, M, F, K, bias, nullptr, 0, 0, nullptr, 0, 0, 1.0f, F, stream);
 }
 
-extern "C" int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int B, int Hin, int Wd, int Cin, int Cout,
-                                     int pad_h, const void* bias, const void* rowvec, int ld_rowvec, const void* residual, int act,
-                                     float out_scale, void* stream) {
+extern "C" int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int B, int Hin, int Win, int Cin, int Cout,
+                                     int stride, int pad_h, const void* bias, const void* rowvec, int ld_rowvec,
+                                     const void* residual, int act, float out_scale, void* stream) {
     KATZ_CHECK_ARG(X && W && Y, KATZ_EINVAL);
-    KATZ_CHECK_ARG(B > 0 && Hin > 0 && Wd > 0 && Cin > 0 && Cout > 0, KATZ_ESIZE);
-    KATZ_CHECK_ARG(pad_h == 0 || pad_h == 1, KATZ_EINVAL);
-    const int H = Hin + 2 * pad_h - 2;   // output rows
+    KATZ_CHECK_ARG(B > 0 && Hin > 0 && Win > 0 && Cin > 0 && Cout > 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG((pad_h == 0 || pad_h == 1) && (stride == 1 || stride == 2), KATZ_EINVAL);
+    KATZ_CHECK_ARG(Hin + 2 * pad_h >= 3 && (stride == 1 || Win % 2 == 0), KATZ_ESIZE);
+    const int H = (Hin + 2 * pad_h - 3) / stride + 1;   // output rows
+    const int Wd = (Win + 2 - 3) / stride + 1;          // output columns
     KATZ_CHECK_ARG(H > 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(Cin % TBK == 0 && Cout % 8 == 0, KATZ_ESIZE);
     const int TW = Wd < 128 ? Wd : 128;
@@ -644,14 +649,14 @@ extern "C" int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int 
     KATZ_CHECK_ARG(!rowvec || (aligned16(rowvec) && ld_rowvec % 8 == 0), KATZ_EALIGN);
     KATZ_CHECK_ARG(!residual || aligned16(residual), KATZ_EALIGN);
     CUtensorMap ta, tb;
-    int rc = encode_nhwc(&ta, X, B, Hin, Wd, Cin, TW, TH);
+    int rc = encode_nhwc(&ta, X, B, Hin, Win, Cin, TW, TH, stride);
     if (rc) return rc;
     Tc05Params p{};
     p.C = (__half*)Y; p.bias = (const __half*)bias; p.rowvec = (const __half*)rowvec; p.residual = (const __half*)residual;
     p.M = B * H * Wd; p.N = Cout; p.K = 9 * Cin; p.ldc = Cout; p.ldr = Cout; p.ld_rowvec = ld_rowvec; p.rows_per_batch = H * Wd;
     p.act = act; p.out_scale = out_scale;
     p.conv = 1; p.H = H; p.W = Wd; p.TW = TW; p.TH = TH; p.tiles_w = Wd / TW; p.tiles_h = ceil_div(H, TH);
-    p.cin_chunks = Cin / TBK; p.ksize = 3; p.pad_h = pad_h; p.pad_w = 1;
+    p.cin_chunks = Cin / TBK; p.ksize = 3; p.pad_h = pad_h; p.pad_w = 1; p.stride = stride;
     p.m_tiles = B * p.tiles_w * p.tiles_h;
     p.rows_img = H * Wd;
     const int bn = pick_bn(p.m_tiles, Cout, false);

@@ -136,12 +136,13 @@ def conv2d(x, w, bias=None, ksize=3, stride=1, pad=1, upsample=False, x2=None, r
         out = torch.empty((B, Hout, Wout, Cout), dtype=torch.float16, device=x.device)
     if residual is not None and (tuple(residual.shape) != (B, Hout, Wout, Cout) or not residual.is_contiguous()):
         raise KatzError("conv2d: bad residual")
-    tw = min(Win, 128)
-    if (_use_tc05() and ksize == 3 and stride == 1 and pad == 1 and ph in (0, 1) and x2 is None and C1 % 64 == 0
-            and Cout % 8 == 0 and tw >= 8 and (tw & (tw - 1)) == 0 and Win % tw == 0 and _al16(x) and _al16(w) and _al16(out)
+    tw = min(Wout, 128)
+    if (_use_tc05() and ksize == 3 and stride in (1, 2) and pad == 1 and ph in (0, 1) and x2 is None and C1 % 64 == 0
+            and Cout % 8 == 0 and tw >= 8 and (tw & (tw - 1)) == 0 and Wout % tw == 0 and (stride == 1 or Win % 2 == 0)
+            and _al16(x) and _al16(w) and _al16(out)
             and _al16(bias) and _al16(residual) and (rowvec is None or (_al16(rowvec) and rowvec.stride(0) % 8 == 0))):
         src = upsample_nearest2x(x) if upsample else x
-        call("katz_conv3x3_nhwc_f16", _p(src), _p(w), _p(out), B, Hin, Win, C1, Cout, ph, _p(bias), _p(rowvec),
+        call("katz_conv3x3_nhwc_f16", _p(src), _p(w), _p(out), B, Hin, Win, C1, Cout, stride, ph, _p(bias), _p(rowvec),
              rowvec.stride(0) if rowvec is not None else 0, _p(residual), act, float(out_scale), _stream())
         return out
     call("katz_conv2d_nhwc_f16_mma", _p(x), _p(x2), _p(w), _p(out), B, Hin, Win, C1, C2, Cout, ksize, stride, ph, pad,

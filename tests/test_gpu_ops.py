@@ -246,11 +246,13 @@ def test_linear_tcgen05_strided_views(cuda_device, monkeypatch):
     assert float(big[:, :N].abs().max()) == 0
 
 
-@pytest.mark.parametrize("B,H,W,Cin,Cout,up", [(2, 16, 16, 64, 128, False), (2, 32, 32, 128, 320, False),
-                                               (1, 128, 128, 64, 64, False), (2, 64, 64, 320, 640, False),
-                                               (1, 6, 16, 64, 64, False), (1, 16, 16, 128, 128, True),
-                                               (1, 8, 256, 64, 64, False)])
-def test_conv3x3_tcgen05(cuda_device, B, H, W, Cin, Cout, up, monkeypatch):
+@pytest.mark.parametrize("B,H,W,Cin,Cout,up,stride", [(2, 16, 16, 64, 128, False, 1), (2, 32, 32, 128, 320, False, 1),
+                                                      (1, 128, 128, 64, 64, False, 1), (2, 64, 64, 320, 640, False, 1),
+                                                      (1, 6, 16, 64, 64, False, 1), (1, 16, 16, 128, 128, True, 1),
+                                                      (1, 8, 256, 64, 64, False, 1), (2, 32, 32, 64, 128, False, 2),
+                                                      (2, 128, 128, 320, 320, False, 2), (1, 64, 64, 640, 640, False, 2),
+                                                      (1, 10, 16, 64, 64, False, 2)])
+def test_conv3x3_tcgen05(cuda_device, B, H, W, Cin, Cout, up, stride, monkeypatch):
     monkeypatch.setenv("KATZ_GEMM", "tc05")
     from katz_b200 import ops
     g = torch.Generator().manual_seed(12)
@@ -258,11 +260,11 @@ def test_conv3x3_tcgen05(cuda_device, B, H, W, Cin, Cout, up, monkeypatch):
     w = (torch.randn(Cout, Cin, 3, 3, generator=g) / (9 * Cin) ** 0.5).half().cuda()
     bias = torch.randn(Cout, generator=g).half().cuda()
     xin = F.interpolate(x.float(), scale_factor=2.0, mode="nearest") if up else x.float()
-    ref = F.conv2d(xin, w.float(), bias.float(), padding=1)
+    ref = F.conv2d(xin, w.float(), bias.float(), padding=1, stride=stride)
     temb = torch.randn(B, Cout, generator=g).half().cuda()
     res = torch.randn(ref.shape, generator=g).half().cuda()
     ref = ref + temb.float()[:, :, None, None] + res.float()
-    out = ops.conv2d(x.permute(0, 2, 3, 1).contiguous(), w.permute(0, 2, 3, 1).contiguous(), bias, upsample=up,
+    out = ops.conv2d(x.permute(0, 2, 3, 1).contiguous(), w.permute(0, 2, 3, 1).contiguous(), bias, upsample=up, stride=stride,
                      rowvec=temb, residual=res.permute(0, 2, 3, 1).contiguous())
     assert ops.tc05_status() == 0
     assert _rel(out.permute(0, 3, 1, 2), ref) < 2e-3
