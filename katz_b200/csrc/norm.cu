@@ -375,6 +375,7 @@ __global__ void __launch_bounds__(1024) gn_nchw_kernel(const __half* __restrict_
 
 constexpr int LN_MAXCH = 10;  // 16-byte chunks per lane: C <= 32 * 10 * 8 = 2560
 
+template <int MAXCH>
 __global__ void __launch_bounds__(256) layer_norm_kernel(const __half* __restrict__ x, __half* __restrict__ y,
                                                          const __half* __restrict__ gamma, const __half* __restrict__ beta,
                                                          int rows, int C, float eps) {
@@ -385,29 +386,46 @@ __global__ void __launch_bounds__(256) layer_norm_kernel(const __half* __restric
     if (row >= rows) return;
     const int nch = C >> 3;
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * C);
-    float v[LN_MAXCH][8];
+    // one warp per row; every global load of the row, of gamma and of beta is requested before anything is consumed
+    uint4 xv[MAXCH], gv[MAXCH], bv[MAXCH];
+#pragma unroll
+    for (int i = 0; i < MAXCH; ++i) {
+        const int ch = lane + i * 32;
+        if (ch < nch) xv[i] = xr[ch];
+    }
+#pragma unroll
+    for (int i = 0; i < MAXCH; ++i) {
+        const int ch = lane + i * 32;
+        if (ch < nch) {
+            gv[i] = __ldg(reinterpret_cast<const uint4*>(gamma) + ch);
+            bv[i] = __ldg(reinterpret_cast<const uint4*>(beta) + ch);
+        }
+    }
+    float v[MAXCH][8];
     float s = 0.f;
 #pragma unroll
-    for (int i = 0; i < LN_MAXCH; ++i) {
-        int ch = lane + i * 32;
+    for (int i = 0; i < MAXCH; ++i) {
+        const int ch = lane + i * 32;
         if (ch < nch) {
-            uint4 u = xr[ch];
-            float2 a = unpack_half2(u.x), b2 = unpack_half2(u.y), c = unpack_half2(u.z), d = unpack_half2(u.w);
-            v[i][0] = a.x; v[i][1] = a.y; v[i][2] = b2.x; v[i][3] = b2.y;
-            v[i][4] = c.x; v[i][5] = c.y; v[i][6] = d.x; v[i][7] = d.y;
+            const uint32_t w[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w};
 #pragma unroll
-            for (int e = 0; e < 8; ++e) s += v[i][e];
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = unpack_half2(w[e]);
+                v[i][2 * e] = f.x;
+                v[i][2 * e + 1] = f.y;
+                s += f.x + f.y;
+            }
         }
     }
     const float mean = warp_sum(s) / (float)C;
     float q = 0.f;
 #pragma unroll
-    for (int i = 0; i < LN_MAXCH; ++i) {
-        int ch = lane + i * 32;
+    for (int i = 0; i < MAXCH; ++i) {
+        const int ch = lane + i * 32;
         if (ch < nch) {
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                float d = v[i][e] - mean;
+                const float d = v[i][e] - mean;
                 q += d * d;
             }
         }
@@ -415,24 +433,17 @@ __global__ void __launch_bounds__(256) layer_norm_kernel(const __half* __restric
     const float rstd = rsqrtf(warp_sum(q) / (float)C + eps);
     uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * C);
 #pragma unroll
-    for (int i = 0; i < LN_MAXCH; ++i) {
-        int ch = lane + i * 32;
+    for (int i = 0; i < MAXCH; ++i) {
+        const int ch = lane + i * 32;
         if (ch < nch) {
-            float o[8];
-            uint4 g4 = reinterpret_cast<const uint4*>(gamma)[ch];
-            uint4 b4 = reinterpret_cast<const uint4*>(beta)[ch];
-            float2 g0 = unpack_half2(g4.x), g1 = unpack_half2(g4.y), g2 = unpack_half2(g4.z), g3 = unpack_half2(g4.w);
-            float2 b0 = unpack_half2(b4.x), b1 = unpack_half2(b4.y), b2 = unpack_half2(b4.z), b3 = unpack_half2(b4.w);
-            float gg[8] = {g0.x, g0.y, g1.x, g1.y, g2.x, g2.y, g3.x, g3.y};
-            float bb[8] = {b0.x, b0.y, b1.x, b1.y, b2.x, b2.y, b3.x, b3.y};
+            const uint32_t gw[4] = {gv[i].x, gv[i].y, gv[i].z, gv[i].w}, bw[4] = {bv[i].x, bv[i].y, bv[i].z, bv[i].w};
+            uint32_t o[4];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) o[e] = (v[i][e] - mean) * rstd * gg[e] + bb[e];
-            uint4 u;
-            u.x = pack_half2(o[0], o[1]);
-            u.y = pack_half2(o[2], o[3]);
-            u.z = pack_half2(o[4], o[5]);
-            u.w = pack_half2(o[6], o[7]);
-            yr[ch] = u;
+            for (int e = 0; e < 4; ++e) {
+                const float2 gg = unpack_half2(gw[e]), bb = unpack_half2(bw[e]);
+                o[e] = pack_half2((v[i][2 * e] - mean) * rstd * gg.x + bb.x, (v[i][2 * e + 1] - mean) * rstd * gg.y + bb.y);
+            }
+            yr[ch] = make_uint4(o[0], o[1], o[2], o[3]);
         }
     }
 }
@@ -577,8 +588,13 @@ extern "C" int katz_layer_norm_f16(const void* x, void* y, const void* gamma, co
     KATZ_CHECK_ARG(rows > 0 && C > 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(C % 8 == 0 && C <= 32 * LN_MAXCH * 8, KATZ_ESIZE);
     KATZ_CHECK_ARG(aligned16(x) && aligned16(y) && aligned16(gamma) && aligned16(beta), KATZ_EALIGN);
-    const int rows_per_cta = 8;
-    launch_k(layer_norm_kernel, ceil_div(rows, rows_per_cta), rows_per_cta * 32, 0, (cudaStream_t)stream, (const __half*)x, (__half*)y, (const __half*)gamma, (const __half*)beta, rows, C, eps);
+    const int rows_per_cta = 4;       // 4 warps per CTA: 2048 rows spread over more SMs than with 8
+    if (C <= 32 * 5 * 8)
+        launch_k(layer_norm_kernel<5>, ceil_div(rows, rows_per_cta), rows_per_cta * 32, 0, (cudaStream_t)stream, (const __half*)x,
+                 (__half*)y, (const __half*)gamma, (const __half*)beta, rows, C, eps);
+    else
+        launch_k(layer_norm_kernel<LN_MAXCH>, ceil_div(rows, rows_per_cta), rows_per_cta * 32, 0, (cudaStream_t)stream,
+                 (const __half*)x, (__half*)y, (const __half*)gamma, (const __half*)beta, rows, C, eps);
     KATZ_LAUNCH_RET();
 }
 
