@@ -182,6 +182,8 @@ def main():
                     help="run ONE eager UNet step between cudaProfilerStart/Stop and exit (for `ncu --profile-from-start off`)")
     ap.add_argument("--profile-gemm", action="store_true",
                     help="launch the dominant linear GEMM shapes between cudaProfilerStart/Stop and exit")
+    ap.add_argument("--profile-attn", action="store_true",
+                    help="run the two self-attention shapes of the step under cudaProfilerStart/Stop (for ncu) and exit")
     ap.add_argument("--profile-merge", action="store_true",
                     help="run ONE LoRA merge over a reduced layer set between cudaProfilerStart/Stop and exit")
     ap.add_argument("--parallel", default="auto", choices=["auto", "rows"],
@@ -234,6 +236,26 @@ def main():
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
         print(json.dumps({"profiled": "linear GEMMs", "shapes": shapes, "kernel": ops.gemm_kernel_name()}))
+        return
+    if args.profile_attn:
+        # self-attention of the 32x32 level (20 heads, 1024 tokens) and of the 64x64 level (10 heads, 4096 tokens)
+        shapes = [(2, 20, 1024), (2, 10, 4096)]
+        bufs = []
+        for (Bq, Hh, S) in shapes:
+            qkv = torch.randn(Bq, S, 3 * Hh * 64, device=dev).half()
+            bufs.append((qkv, Hh, torch.empty(Bq, S, Hh * 64, dtype=torch.float16, device=dev)))
+        for qkv, Hh, o in bufs:
+            C = Hh * 64
+            ops.attention(qkv[:, :, :C], qkv[:, :, C:2 * C], qkv[:, :, 2 * C:], Hh, out=o)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        for qkv, Hh, o in bufs:
+            C = Hh * 64
+            for _ in range(2):
+                ops.attention(qkv[:, :, :C], qkv[:, :, C:2 * C], qkv[:, :, 2 * C:], Hh, out=o)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"profiled": "self-attention", "shapes": shapes}))
         return
     # ---- model: random-init SDXL UNet (seed 0), weights drawn on the device
     sd = init_state_dict(unet_param_shapes(cfg), seed=0, dtype=torch.float16, device=dev, generator_device=dev)
