@@ -117,14 +117,19 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t* r, unsigned char*
     }
 }
 
-template <int BN, int STAGES, bool GEGLU>
+// PAIR: two CTAs of a cluster share every tcgen05.mma (cta_group::2, M = 256): each loads its own 128-row A tile and HALF
+// of the B tile, the leader issues the instruction for both, each CTA's TMEM receives its own 128 rows and each runs its
+// own epilogue. Per k-step a CTA then takes 16 + BN/2 x 128 B from L2 instead of 16 + BN x 128 B; the main loop is bound
+// by that delivery, not by the tensor pipe. No load is multicast; only completion signals cross the pair.
+template <int BN, int STAGES, bool GEGLU, bool PAIR>
 __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                   const __grid_constant__ CUtensorMap tmB,
                                                                   const __grid_constant__ CUtensorMap tmC,
                                                                   const __grid_constant__ CUtensorMap tmR,
                                                                   const Tc05Params p) {
+    static_assert(!(GEGLU && PAIR), "the GEGLU tile keeps both weight halves in one CTA");
     constexpr int A_BYTES = TBM * TBK * 2;
-    constexpr int B_BYTES = BN * TBK * 2;
+    constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * TBK * 2;      // this CTA's part of the B tile
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr int BN_OUT = GEGLU ? BN / 2 : BN;      // output columns per tile
     extern __shared__ unsigned char smem_raw[];
@@ -139,7 +144,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KT = p.K / TBK;
-    const int total_tiles = p.m_tiles * p.n_tiles;
+    // PAIR: a work item is a pair of vertically adjacent tiles; CTA rank r of cluster c takes the r-th tile of items
+    // c, c + clusters, ... Without pairs an item is one tile and every CTA is its own "cluster".
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0;
+    const int item0 = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int item_stride = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    const int total_tiles = (PAIR ? (p.m_tiles + 1) / 2 : p.m_tiles) * p.n_tiles;      // work items
 
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmA);
@@ -150,7 +160,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tfull0 + 8 * b, 1);
-            mbar_init(tempty0 + 8 * b, EPI_WARPS);    // one arrival per epilogue warp
+            mbar_init(tempty0 + 8 * b, EPI_WARPS * (PAIR ? 2 : 1));    // one arrival per epilogue warp (of both CTAs)
         }
         for (int b = 0; b < EPI_BOXES; ++b) mbar_init(smem_u32(bars + 2 * STAGES + 4 + b), 1);   // residual boxes
         tma_prefetch_desc(&tmC);
@@ -158,11 +168,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_pair(smem_u32(tmem_slot), TMEM_COLS);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+            tmem_relinquish();
+        }
     }
     fence_before_sync();
     __syncthreads();
+    if (PAIR) cluster_sync_all();      // the peer's barriers are initialised before anything signals them
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     // everything above (barriers, TMEM, descriptor prefetch) may overlap the previous kernel's tail; global memory waits
@@ -174,8 +190,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
         if (elect_one()) {
             bool ok = true;
             uint32_t it = 0, issued = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
+            for (int tile = item0; tile < total_tiles && ok; tile += item_stride) {
+                const int mi = tile / p.n_tiles, nt = tile - mi * p.n_tiles;
+                const int mt = PAIR ? 2 * mi + (int)rank : mi;      // past the last tile for the odd one out: loads zeros
                 int m0 = mt * TBM, cb = 0, ch0 = 0, cw0 = 0;
                 if (p.conv) {
                     const int tpi = p.tiles_w * p.tiles_h;
@@ -190,41 +207,59 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { ok = false; break; }
-                    const uint32_t fb = full0 + 8 * s;
-                    mbar_expect_tx(fb, STAGE_BYTES);
                     const uint32_t sa = smem_base + s * STAGE_BYTES;
-                    if (p.conv) {
-                        const int tap = kt / p.cin_chunks;
-                        const int cc = kt - tap * p.cin_chunks;
-                        const int ky = tap / p.ksize, kx = tap - ky * p.ksize;
-                        // the tensor map walks the input with the convolution's stride: TW x TH pixels per box
-                        tma_load_4d(sa, &tmA, cc * TBK, cw0 * p.stride + kx - p.pad_w, ch0 * p.stride + ky - p.pad_h, cb, fb);
+                    if constexpr (PAIR) {
+                        // both CTAs' bytes are counted on the leader's barrier, which the leader arms for both
+                        const uint32_t fb = mapa_shared(full0 + 8 * s, 0);
+                        if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
+                        if (p.conv) {
+                            const int tap = kt / p.cin_chunks;
+                            const int cc = kt - tap * p.cin_chunks;
+                            const int ky = tap / p.ksize, kx = tap - ky * p.ksize;
+                            tma_load_4d_pair(sa, &tmA, cc * TBK, cw0 * p.stride + kx - p.pad_w, ch0 * p.stride + ky - p.pad_h, cb, fb);
+                        } else {
+                            tma_load_2d_pair(sa, &tmA, kt * TBK, m0, fb);
+                        }
+                        tma_load_2d_pair(sa + A_BYTES, &tmB, kt * TBK, n0 + (int)rank * (BN / 2), fb);
                     } else {
-                        tma_load_2d(sa, &tmA, kt * TBK, m0, fb);
-                    }
-                    if (GEGLU) {
-                        tma_load_2d(sa + A_BYTES, &tmB, kt * TBK, n0, fb);
-                        tma_load_2d(sa + A_BYTES + B_BYTES / 2, &tmB, kt * TBK, p.geglu_F + n0, fb);
-                    } else {
-                        tma_load_2d(sa + A_BYTES, &tmB, kt * TBK, n0, fb);
+                        const uint32_t fb = full0 + 8 * s;
+                        mbar_expect_tx(fb, STAGE_BYTES);
+                        if (p.conv) {
+                            const int tap = kt / p.cin_chunks;
+                            const int cc = kt - tap * p.cin_chunks;
+                            const int ky = tap / p.ksize, kx = tap - ky * p.ksize;
+                            // the tensor map walks the input with the convolution's stride: TW x TH pixels per box
+                            tma_load_4d(sa, &tmA, cc * TBK, cw0 * p.stride + kx - p.pad_w, ch0 * p.stride + ky - p.pad_h, cb, fb);
+                        } else {
+                            tma_load_2d(sa, &tmA, kt * TBK, m0, fb);
+                        }
+                        if (GEGLU) {
+                            tma_load_2d(sa + A_BYTES, &tmB, kt * TBK, n0, fb);
+                            tma_load_2d(sa + A_BYTES + B_BYTES / 2, &tmB, kt * TBK, p.geglu_F + n0, fb);
+                        } else {
+                            tma_load_2d(sa + A_BYTES, &tmB, kt * TBK, n0, fb);
+                        }
                     }
                     issued = it + 1;
                 }
             }
             if (!ok) {
                 atomicExch(p.status, 1);
-                // let copies already in flight land before the CTA's shared memory is released
-                const uint32_t first = issued > (uint32_t)STAGES ? issued - STAGES : 0;
-                for (uint32_t j = first; j < issued; ++j) mbar_wait(full0 + 8 * (j % STAGES), (j / STAGES) & 1);
+                // let copies already in flight land before the CTA's shared memory is released (a pair's peer waits in
+                // the cluster barrier of the teardown instead: its copies are counted on the leader's barriers)
+                if (!PAIR || rank == 0) {
+                    const uint32_t first = issued > (uint32_t)STAGES ? issued - STAGES : 0;
+                    for (uint32_t j = first; j < issued; ++j) mbar_wait(full0 + 8 * (j % STAGES), (j / STAGES) & 1);
+                }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------------------------ MMA issuer
-        if (elect_one()) {
-            constexpr uint32_t idesc = idesc_f16(TBM, BN);
+        if ((!PAIR || rank == 0) && elect_one()) {
+            constexpr uint32_t idesc = idesc_f16(PAIR ? 2 * TBM : TBM, BN);
             bool ok = true;
             uint32_t it = 0, t = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+            for (int tile = item0; tile < total_tiles && ok; tile += item_stride, ++t) {
                 const uint32_t buf = t & 1;
                 if (!mbar_wait(tempty0 + 8 * buf, ((t >> 1) & 1) ^ 1)) { ok = false; break; }
                 fence_after_sync();
@@ -239,11 +274,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
 #pragma unroll
                     for (int k = 0; k < TBK / 16; ++k) {
                         // +32 bytes per 16-element K step inside the 128-byte swizzle row (encoded >> 4)
-                        umma_f16(tacc, ad + 2 * k, bd + 2 * k, idesc, (kt | k) != 0);
+                        if (PAIR) umma_f16_pair(tacc, ad + 2 * k, bd + 2 * k, idesc, (kt | k) != 0);
+                        else umma_f16(tacc, ad + 2 * k, bd + 2 * k, idesc, (kt | k) != 0);
                     }
-                    umma_commit(empty0 + 8 * s);   // stage reusable once these MMAs have read it
+                    // stage reusable once these MMAs have read it (in both CTAs of a pair)
+                    if (PAIR) umma_commit_pair(empty0 + 8 * s, 3);
+                    else umma_commit(empty0 + 8 * s);
                 }
-                if (ok) umma_commit(tfull0 + 8 * buf);
+                if (ok) {
+                    if (PAIR) umma_commit_pair(tfull0 + 8 * buf, 3);
+                    else umma_commit(tfull0 + 8 * buf);
+                }
             }
             if (!ok) atomicExch(p.status, 2);
         }
@@ -267,9 +308,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
         const uint32_t swz = (uint32_t)((lane >> 1) & 3);      // 64-byte swizzle: 16-byte chunk index ^ ((row >> 1) & 3)
         bool ok = true;
         uint32_t t = 0, g = 0;                  // tiles done by the CTA, chunks (boxes) done by this warp
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+        for (int tile = item0; tile < total_tiles && ok; tile += item_stride, ++t) {
             const uint32_t buf = t & 1;
-            const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
+            const int mi = tile / p.n_tiles, nt = tile - mi * p.n_tiles;
+            const int mt = PAIR ? 2 * mi + (int)rank : mi;
             const int n0 = nt * BN_OUT;
             // coordinates of this warp's 32 rows in the output tensor map {N, rows per image, images}
             int y0, z0;
@@ -283,10 +325,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                 y0 = mt * TBM + q * 32;
                 z0 = 0;
             }
-            const bool rows_in = y0 < p.rows_img;      // warp-uniform: do any of this warp's 32 rows exist?
-            const __half* bias_p = p.bias ? p.bias + n0 : nullptr;
+            // warp-uniform: do any of this warp's 32 rows exist? (a pair's odd tile out lies past the last tile)
+            const bool rows_in = mt < p.m_tiles && y0 < p.rows_img;
+            const __half* bias_p = (p.bias && rows_in) ? p.bias + n0 : nullptr;
             const __half* aux_p = nullptr;             // gate bias (GEGLU) or the image's row vector
-            if (GEGLU) {
+            if (!rows_in) {
+                // nothing to load
+            } else if (GEGLU) {
                 if (p.bias) aux_p = p.bias + p.geglu_F + n0;
             } else if (p.rowvec) {
                 aux_p = p.rowvec + (size_t)(p.conv ? z0 : (mt * TBM) / p.rows_per_batch) * p.ld_rowvec + n0;
@@ -411,16 +456,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
             // this warp is done reading the accumulator buffer
             fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_cluster(mapa_shared(tempty0 + 8 * buf, 0));      // the leader's MMA thread waits for both CTAs
+                else mbar_arrive(tempty0 + 8 * buf);
+            }
         }
         if (lane == 0) bulk_wait<0>();          // every store has left shared memory and reached global memory
     }
     // ---------------------------------------------------------------------------------------- teardown
     fence_before_sync();
     __syncthreads();
+    if (PAIR) cluster_sync_all();      // neither CTA leaves (or frees TMEM) while the other may still signal it or read its tiles
     if (warp == 1) {
         fence_after_sync();
-        tmem_dealloc(tmem_base, TMEM_COLS);
+        if (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+        else tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 
@@ -497,25 +547,48 @@ static int sm_count() {
     return n;
 }
 
-template <int BN, int STAGES, bool GEGLU>
+template <int BN, int STAGES, bool GEGLU, bool PAIR>
 static constexpr int tc05_smem() {
-    return STAGES * (TBM * TBK * 2 + BN * TBK * 2) + EPI_BOXES * BOX_BYTES + (2 * STAGES + 4 + EPI_BOXES) * 8 + 16 + 1024;
+    return STAGES * (TBM * TBK * 2 + (PAIR ? BN / 2 : BN) * TBK * 2) + EPI_BOXES * BOX_BYTES + (2 * STAGES + 4 + EPI_BOXES) * 8 + 16 +
+           1024;
 }
 
-template <int BN, int STAGES, bool GEGLU>
+template <int BN, int STAGES, bool GEGLU, bool PAIR>
 static int launch_tc05(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const CUtensorMap& r,
                        const Tc05Params& p, cudaStream_t st) {
     static bool attr = false;
-    constexpr int smem = tc05_smem<BN, STAGES, GEGLU>();
+    static int max_ctas = 0;
+    constexpr int smem = tc05_smem<BN, STAGES, GEGLU, PAIR>();
     static_assert(smem <= 232448, "shared memory budget");
+    auto kernel = tc05_gemm_kernel<BN, STAGES, GEGLU, PAIR>;
     if (!attr) {
-        cudaError_t e = cudaFuncSetAttribute(tc05_gemm_kernel<BN, STAGES, GEGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
+        max_ctas = sm_count();
+        if (PAIR) {
+            // how many CTA pairs the device can hold at once (a pair sits on two SMs of one TPC)
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3(2 * sm_count());
+            cfg.blockDim = dim3(TC_THREADS);
+            cfg.dynamicSmemBytes = smem;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = 2;
+            at[0].val.clusterDim.y = 1;
+            at[0].val.clusterDim.z = 1;
+            cfg.attrs = at;
+            cfg.numAttrs = 1;
+            int clusters = 0;
+            e = cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg);
+            if (e != cudaSuccess || clusters <= 0) return e != cudaSuccess ? (int)e : KATZ_ENOTREADY;
+            max_ctas = 2 * clusters;
+        }
         attr = true;
     }
-    const int total = p.m_tiles * p.n_tiles;
-    const int grid = total < sm_count() ? total : sm_count();
-    launch_k(tc05_gemm_kernel<BN, STAGES, GEGLU>, grid, TC_THREADS, smem, st, a, b, c, r, p);
+    const int items = (PAIR ? (p.m_tiles + 1) / 2 : p.m_tiles) * p.n_tiles;
+    const int per_item = PAIR ? 2 : 1;
+    const int grid = items * per_item < max_ctas ? items * per_item : max_ctas;
+    launch_k_cluster(kernel, grid, TC_THREADS, smem, st, PAIR ? 2 : 1, a, b, c, r, p);
     KATZ_LAUNCH_RET();
 }
 
@@ -532,6 +605,11 @@ int* tc05_status_device_ptr() { return status_ptr(); }
 
 // Tile width by wave efficiency: tiles of width bn cost ~bn per wave; pick the width with the least total cost.
 static int pick_bn(int m_tiles, int n_out, bool geglu) {
+    // KATZ_TC05_BN=128|160|256 forces a width (tuning runs); ignored where the width is not available
+    if (const char* e = getenv("KATZ_TC05_BN")) {
+        const int v = atoi(e);
+        if ((v == 128 || v == 256 || (v == 160 && !geglu))) return v;
+    }
     const int sms = sm_count();
     const int cand[3] = {256, 160, 128};
     int best = 128;
@@ -552,8 +630,19 @@ static int pick_bn(int m_tiles, int n_out, bool geglu) {
     return best;
 }
 
+// A CTA pair per 256 x BN tile where the shape has at least two row tiles (the GEGLU tile keeps both weight halves in one
+// CTA and stays single). KATZ_TC05_PAIR=0 turns pairs off.
+static bool use_pairs(const Tc05Params& p, bool geglu) {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("KATZ_TC05_PAIR");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on && !geglu && p.m_tiles >= 2;
+}
+
 template <bool GEGLU>
-static int dispatch(const CUtensorMap& a, const CUtensorMap& b, Tc05Params& p, int bn, int rows_per_image, int images,
+static int dispatch(const CUtensorMap& a, const CUtensorMap& b, Tc05Params& p, int bn, bool pair, int rows_per_image, int images,
                     cudaStream_t st) {
     p.status = status_ptr();
     if (!p.status) return KATZ_ENOTREADY;
@@ -562,11 +651,16 @@ static int dispatch(const CUtensorMap& a, const CUtensorMap& b, Tc05Params& p, i
     if (rc) return rc;
     rc = encode_out(&r, p.residual ? p.residual : p.C, p.N, rows_per_image, images, p.residual ? p.ldr : p.ldc);
     if (rc) return rc;
-    if (bn == 256) return launch_tc05<256, 4, GEGLU>(a, b, c, r, p, st);
     if constexpr (!GEGLU) {
-        if (bn == 160) return launch_tc05<160, 5, GEGLU>(a, b, c, r, p, st);
+        if (pair) {
+            if (bn == 256) return launch_tc05<256, 6, false, true>(a, b, c, r, p, st);
+            if (bn == 160) return launch_tc05<160, 7, false, true>(a, b, c, r, p, st);
+            return launch_tc05<128, 7, false, true>(a, b, c, r, p, st);
+        }
+        if (bn == 160) return launch_tc05<160, 5, false, false>(a, b, c, r, p, st);
     }
-    return launch_tc05<128, 6, GEGLU>(a, b, c, r, p, st);
+    if (bn == 256) return launch_tc05<256, 4, GEGLU, false>(a, b, c, r, p, st);
+    return launch_tc05<128, 6, GEGLU, false>(a, b, c, r, p, st);
 }
 
 }  // namespace katz
@@ -612,9 +706,11 @@ static int linear_common(const void* A, int lda, const void* W, void* C, int ldc
     const int out_w = geglu ? bn / 2 : bn;
     p.n_tiles = ceil_div(N_out, out_w);
     const uint64_t w_rows = geglu ? 2ull * geglu_F : (uint64_t)N_out;
-    rc = encode_2d(&tb, W, K, w_rows, (uint64_t)K * 2, TBK, geglu ? bn / 2 : bn);
+    const bool pair = use_pairs(p, geglu);
+    rc = encode_2d(&tb, W, K, w_rows, (uint64_t)K * 2, TBK, (geglu || pair) ? bn / 2 : bn);      // box rows: what one load brings
     if (rc) return rc;
-    return geglu ? dispatch<true>(ta, tb, p, bn, M, 1, (cudaStream_t)stream) : dispatch<false>(ta, tb, p, bn, M, 1, (cudaStream_t)stream);
+    return geglu ? dispatch<true>(ta, tb, p, bn, false, M, 1, (cudaStream_t)stream)
+                 : dispatch<false>(ta, tb, p, bn, pair, M, 1, (cudaStream_t)stream);
 }
 
 extern "C" int katz_linear_f16(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, int K,
@@ -661,7 +757,8 @@ extern "C" int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int 
     p.rows_img = H * Wd;
     const int bn = pick_bn(p.m_tiles, Cout, false);
     p.n_tiles = ceil_div(Cout, bn);
-    rc = encode_2d(&tb, W, (uint64_t)9 * Cin, Cout, (uint64_t)9 * Cin * 2, TBK, bn);
+    const bool pair = use_pairs(p, false);
+    rc = encode_2d(&tb, W, (uint64_t)9 * Cin, Cout, (uint64_t)9 * Cin * 2, TBK, pair ? bn / 2 : bn);
     if (rc) return rc;
-    return dispatch<false>(ta, tb, p, bn, H * Wd, B, (cudaStream_t)stream);
+    return dispatch<false>(ta, tb, p, bn, pair, H * Wd, B, (cudaStream_t)stream);
 }
