@@ -127,7 +127,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                                                                   const __grid_constant__ CUtensorMap tmC,
                                                                   const __grid_constant__ CUtensorMap tmR,
                                                                   const Tc05Params p) {
-    static_assert(!(GEGLU && PAIR), "the GEGLU tile keeps both weight halves in one CTA");
     constexpr int A_BYTES = TBM * TBK * 2;
     constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * TBK * 2;      // this CTA's part of the B tile
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -220,7 +219,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                         } else {
                             tma_load_2d_pair(sa, &tmA, kt * TBK, m0, fb);
                         }
-                        tma_load_2d_pair(sa + A_BYTES, &tmB, kt * TBK, n0 + (int)rank * (BN / 2), fb);
+                        // this CTA's half of the B tile: the upper columns, or in GEGLU mode the gate rows of the weight
+                        tma_load_2d_pair(sa + A_BYTES, &tmB, kt * TBK,
+                                         GEGLU ? (rank ? p.geglu_F + n0 : n0) : n0 + (int)rank * (BN / 2), fb);
                     } else {
                         const uint32_t fb = full0 + 8 * s;
                         mbar_expect_tx(fb, STAGE_BYTES);
@@ -630,15 +631,15 @@ static int pick_bn(int m_tiles, int n_out, bool geglu) {
     return best;
 }
 
-// A CTA pair per 256 x BN tile where the shape has at least two row tiles (the GEGLU tile keeps both weight halves in one
-// CTA and stays single). KATZ_TC05_PAIR=0 turns pairs off.
+// A CTA pair per 256 x BN tile where the shape has at least two row tiles. KATZ_TC05_PAIR=0 turns pairs off.
 static bool use_pairs(const Tc05Params& p, bool geglu) {
     static int on = -1;
     if (on < 0) {
         const char* e = getenv("KATZ_TC05_PAIR");
         on = (e && e[0] == '0') ? 0 : 1;
     }
-    return on && !geglu && p.m_tiles >= 2;
+    (void)geglu;
+    return on && p.m_tiles >= 2;
 }
 
 template <bool GEGLU>
@@ -651,12 +652,14 @@ static int dispatch(const CUtensorMap& a, const CUtensorMap& b, Tc05Params& p, i
     if (rc) return rc;
     rc = encode_out(&r, p.residual ? p.residual : p.C, p.N, rows_per_image, images, p.residual ? p.ldr : p.ldc);
     if (rc) return rc;
-    if constexpr (!GEGLU) {
-        if (pair) {
-            if (bn == 256) return launch_tc05<256, 6, false, true>(a, b, c, r, p, st);
+    if (pair) {
+        if (bn == 256) return launch_tc05<256, 6, GEGLU, true>(a, b, c, r, p, st);
+        if constexpr (!GEGLU) {
             if (bn == 160) return launch_tc05<160, 7, false, true>(a, b, c, r, p, st);
-            return launch_tc05<128, 7, false, true>(a, b, c, r, p, st);
         }
+        return launch_tc05<128, 7, GEGLU, true>(a, b, c, r, p, st);
+    }
+    if constexpr (!GEGLU) {
         if (bn == 160) return launch_tc05<160, 5, false, false>(a, b, c, r, p, st);
     }
     if (bn == 256) return launch_tc05<256, 4, GEGLU, false>(a, b, c, r, p, st);
@@ -709,7 +712,7 @@ static int linear_common(const void* A, int lda, const void* W, void* C, int ldc
     const bool pair = use_pairs(p, geglu);
     rc = encode_2d(&tb, W, K, w_rows, (uint64_t)K * 2, TBK, (geglu || pair) ? bn / 2 : bn);      // box rows: what one load brings
     if (rc) return rc;
-    return geglu ? dispatch<true>(ta, tb, p, bn, false, M, 1, (cudaStream_t)stream)
+    return geglu ? dispatch<true>(ta, tb, p, bn, pair, M, 1, (cudaStream_t)stream)
                  : dispatch<false>(ta, tb, p, bn, pair, M, 1, (cudaStream_t)stream);
 }
 
