@@ -31,7 +31,10 @@ constexpr int TBM = 128, TBK = 64;
 constexpr int TC_THREADS = 320;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: epilogue
 constexpr int TMEM_COLS = 512;    // two accumulator buffers at columns 0 and 256
 constexpr int BOX_BYTES = 32 * 64;    // epilogue box: 32 rows x 32 fp16 columns, 64-byte swizzle
-constexpr int EPI_WARPS = 8, EPI_BOXES = 2 * EPI_WARPS;      // two boxes per epilogue warp
+constexpr int EPI_WARPS = 8;
+// boxes per epilogue warp: one per chunk it handles in a tile (two warps share a tile's 32-column chunks), so a warp never
+// waits for a TMA store inside a tile
+__host__ __device__ constexpr int tc05_boxes_per_warp(int bn_out) { return (bn_out / 32 + 1) / 2; }
 
 struct Tc05Params {
     __half* C;
@@ -131,12 +134,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
     constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * TBK * 2;      // this CTA's part of the B tile
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr int BN_OUT = GEGLU ? BN / 2 : BN;      // output columns per tile
+    constexpr int NBW = tc05_boxes_per_warp(BN_OUT), EPI_BOXES = EPI_WARPS * NBW;
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte alignment: the swizzle pattern and the UMMA descriptors assume it
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* box_base = smem + STAGES * STAGE_BYTES;                 // 1024-byte aligned (stages are multiples of 1 KB)
     uint64_t* bars = reinterpret_cast<uint64_t*>(box_base + EPI_BOXES * BOX_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + EPI_BOXES);
+    static_assert(EPI_BOXES <= 32, "barrier area");
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
     const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
@@ -301,14 +306,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
         const int ew = warp - 2;                // epilogue warp 0..7
         const int q = warp & 3;                 // TMEM lane quarter this warp may read
         const int half = ew >> 2;               // which of the quarter's two warps: chunks half, half + 2, ...
-        unsigned char* boxes = box_base + ew * 2 * BOX_BYTES;
-        const uint32_t rfull0 = smem_u32(bars + 2 * STAGES + 4 + ew * 2);
+        unsigned char* boxes = box_base + ew * NBW * BOX_BYTES;
+        const uint32_t rfull0 = smem_u32(bars + 2 * STAGES + 4 + ew * NBW);
         constexpr int NCH = BN_OUT / 32;
         static_assert(BN_OUT % 32 == 0, "output tile width must be a multiple of the 32-column box");
         const bool has_res = p.residual != nullptr;
         const uint32_t swz = (uint32_t)((lane >> 1) & 3);      // 64-byte swizzle: 16-byte chunk index ^ ((row >> 1) & 3)
         bool ok = true;
-        uint32_t t = 0, g = 0;                  // tiles done by the CTA, chunks (boxes) done by this warp
+        uint32_t t = 0, rpar = 0;               // tiles done by the CTA; parity bit per residual box of this warp
         for (int tile = item0; tile < total_tiles && ok; tile += item_stride, ++t) {
             const uint32_t buf = t & 1;
             const int mi = tile / p.n_tiles, nt = tile - mi * p.n_tiles;
@@ -345,10 +350,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                 mbar_expect_tx(bar, BOX_BYTES);
                 tma_load_3d(smem_u32(boxes + b * BOX_BYTES), &tmR, n0 + c * 32, y0, z0, bar);
             };
-            const bool first_in = rows_in && half < NCH && n0 + half * 32 < p.N;
-            if (lane == 0 && has_res && first_in) {
-                bulk_wait_read<1>();            // the box was last stored two of this warp's chunks ago
-                request_residual(half, g & 1);
+            if (lane == 0) {
+                // every box of this warp was stored in the previous tile: those stores must have read shared memory before
+                // anything (a residual load, a thread of this warp) writes the boxes again. The wait overlaps the main loop.
+                bulk_wait_read<0>();
+                if (has_res && rows_in) {
+#pragma unroll
+                    for (int cc = 0; cc < NBW; ++cc) {
+                        const int c = 2 * cc + half;
+                        if (c < NCH && n0 + c * 32 < p.N) request_residual(c, cc);
+                    }
+                }
             }
             uint4 nb4[4], nv4[4];               // bias / aux values of the warp's next chunk
             if (!GEGLU) {
@@ -370,7 +382,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
             for (int cc = 0; cc < (NCH + 1) / 2; ++cc) {
                 const int c = 2 * cc + half;
                 if (!rows_in || c >= NCH || n0 + c * 32 >= p.N) break;      // nothing of this box (or of the rest) exists
-                const uint32_t b = g & 1;
+                const uint32_t b = cc;
                 unsigned char* rowp = boxes + b * BOX_BYTES + lane * 64;
                 uint32_t r[GEGLU ? 1 : 32];
                 uint4 cb4[4], cv4[4];
@@ -390,9 +402,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                     }
                 }
                 if (has_res) {
-                    ok = mbar_wait(rfull0 + 8 * b, (g >> 1) & 1);
-                } else {
-                    if (lane == 0) bulk_wait_read<1>();          // the store that last used this box has read it
+                    ok = mbar_wait(rfull0 + 8 * b, (rpar >> cc) & 1);
+                    rpar ^= 1u << cc;
                 }
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) {
@@ -446,12 +457,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                 if (lane == 0) {
                     tma_store_3d(&tmC, n0 + c * 32, y0, z0, smem_u32(boxes + b * BOX_BYTES));
                     bulk_commit();
-                    if (has_res && c + 2 < NCH && n0 + (c + 2) * 32 < p.N) {
-                        bulk_wait_read<1>();    // the other box's store (the warp's previous chunk) has read it
-                        request_residual(c + 2, (g + 1) & 1);
-                    }
                 }
-                ++g;
             }
             if (!ok) break;
             // this warp is done reading the accumulator buffer
@@ -550,8 +556,8 @@ static int sm_count() {
 
 template <int BN, int STAGES, bool GEGLU, bool PAIR>
 static constexpr int tc05_smem() {
-    return STAGES * (TBM * TBK * 2 + (PAIR ? BN / 2 : BN) * TBK * 2) + EPI_BOXES * BOX_BYTES + (2 * STAGES + 4 + EPI_BOXES) * 8 + 16 +
-           1024;
+    constexpr int boxes = EPI_WARPS * tc05_boxes_per_warp(GEGLU ? BN / 2 : BN);
+    return STAGES * (TBM * TBK * 2 + (PAIR ? BN / 2 : BN) * TBK * 2) + boxes * BOX_BYTES + (2 * STAGES + 4 + boxes) * 8 + 16 + 1024;
 }
 
 template <int BN, int STAGES, bool GEGLU, bool PAIR>
@@ -653,16 +659,17 @@ static int dispatch(const CUtensorMap& a, const CUtensorMap& b, Tc05Params& p, i
     rc = encode_out(&r, p.residual ? p.residual : p.C, p.N, rows_per_image, images, p.residual ? p.ldr : p.ldc);
     if (rc) return rc;
     if (pair) {
-        if (bn == 256) return launch_tc05<256, 6, GEGLU, true>(a, b, c, r, p, st);
+        // stage counts: what fits beside the epilogue boxes (8 KB to 64 KB) in 227 KB
+        if (bn == 256) return launch_tc05<256, GEGLU ? 6 : 5, GEGLU, true>(a, b, c, r, p, st);
         if constexpr (!GEGLU) {
-            if (bn == 160) return launch_tc05<160, 7, false, true>(a, b, c, r, p, st);
+            if (bn == 160) return launch_tc05<160, 6, false, true>(a, b, c, r, p, st);
         }
         return launch_tc05<128, 7, GEGLU, true>(a, b, c, r, p, st);
     }
     if constexpr (!GEGLU) {
-        if (bn == 160) return launch_tc05<160, 5, false, false>(a, b, c, r, p, st);
+        if (bn == 160) return launch_tc05<160, 4, false, false>(a, b, c, r, p, st);
     }
-    if (bn == 256) return launch_tc05<256, 4, GEGLU, false>(a, b, c, r, p, st);
+    if (bn == 256) return launch_tc05<256, GEGLU ? 4 : 3, GEGLU, false>(a, b, c, r, p, st);
     return launch_tc05<128, 6, GEGLU, false>(a, b, c, r, p, st);
 }
 
