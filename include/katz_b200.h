@@ -194,6 +194,26 @@ int katz_attention_f16(const void* Q, const void* K, const void* V, void* O, int
  * inside). */
 int katz_residual_intake_f16(const void* src, void* dst, const void* const* h_residuals, const float* h_scales,
                              int n_res, long long n, void* stream);
+/* ---- peer-memory all-gather (latent-row split over several GPUs, one process per GPU) ---------------------------------
+ * No reference counterpart: the reference's 2-GPU mode exchanges tensors through torch.distributed
+ * (sdxl_unet_server.py:199-215). Each process allocates one arena (katz_peer_arena_alloc: cudaMalloc, first
+ * katz_peer_ctrl_bytes() bytes are zeroed control words), exports it (katz_peer_ipc_export, a
+ * katz_peer_ipc_handle_bytes()-byte handle to send to the other processes by any means) and maps the others'
+ * (katz_peer_ipc_open). katz_peer_allgather copies `bytes` (multiple of 16) from `src` into
+ * arena[p] + dst_off + rank*bytes on EVERY rank p with plain stores over NVLink, then returns (in stream order) once
+ * every rank's block has arrived in this rank's arena. h_bases[world]: the arenas as mapped in this process, own arena at
+ * index `rank`. Every rank must issue the same sequence of calls; consecutive calls must use different dst_off. Waits
+ * are bounded: katz_peer_status(arena) is 0, or 100 + the rank whose block never arrived. */
+int katz_peer_ctrl_bytes(void);
+int katz_peer_arena_alloc(long long bytes, void** ptr);
+int katz_peer_arena_free(void* ptr);
+int katz_peer_ipc_handle_bytes(void);
+int katz_peer_ipc_export(void* ptr, void* handle_out);
+int katz_peer_ipc_open(const void* handle, void** ptr);
+int katz_peer_ipc_close(void* ptr);
+int katz_peer_allgather(const void* src, long long bytes, long long dst_off, const unsigned long long* h_bases, int rank,
+                        int world, void* stream);
+int katz_peer_status(const void* arena);
 /* get_timestep_embedding (diffusers/models/embeddings.py:26-66), flip_sin_to_cos, shift 0: out[rows, dim] fp16. */
 int katz_timestep_embedding_f16(const float* t, void* out, int rows, int dim, int ld_out, void* stream);
 int katz_silu_f16(const void* x, void* y, long long n, void* stream);

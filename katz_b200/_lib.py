@@ -79,6 +79,15 @@ SIGNATURES = {
     "katz_residual_intake_f16": (_I, [_V, _V, POINTER(c_void_p), POINTER(c_float), _I, _L, _V]),
     "katz_timestep_embedding_f16": (_I, [_V, _V, _I, _I, _I, _V]),
     "katz_silu_f16": (_I, [_V, _V, _L, _V]),
+    "katz_peer_ctrl_bytes": (_I, []),
+    "katz_peer_arena_alloc": (_I, [_L, POINTER(c_void_p)]),
+    "katz_peer_arena_free": (_I, [_V]),
+    "katz_peer_ipc_handle_bytes": (_I, []),
+    "katz_peer_ipc_export": (_I, [_V, _V]),
+    "katz_peer_ipc_open": (_I, [_V, POINTER(c_void_p)]),
+    "katz_peer_ipc_close": (_I, [_V]),
+    "katz_peer_allgather": (_I, [_V, _L, _L, POINTER(ctypes.c_ulonglong), _I, _I, _V]),
+    "katz_peer_status": (_I, [_V]),
     "katz_add_f16": (_I, [_V, _V, _V, _L, _V]),
     "katz_concat_channels_f16": (_I, [_V, _V, _V, _L, _I, _I, _V]),
     "katz_nchw_to_nhwc_f16": (_I, [_V, _V, _I, _I, _I, _I, _V]),

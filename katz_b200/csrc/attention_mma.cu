@@ -204,7 +204,8 @@ extern "C" int katz_attention_f16_mma(const void* Q, const void* K, const void* 
         KATZ_CHECK_ARG(kv_chunk_rows % ABN == 0 && kv_chunk_stride % 8 == 0, KATZ_ESIZE);
     }
     dim3 grid(ceil_div(Sq, ABM), H, B);
-    launch_k(attention_d64_kernel, grid, ATHREADS, 0, (cudaStream_t)stream, (const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, Sq, Sk, ldq, ldk, ldv, ldo, bsq, bsk, bsv, bso,
-        scale * 1.44269504088896340736f, kv_chunk_rows, kv_chunk_stride);
+    launch_k(attention_d64_kernel, grid, ATHREADS, 0, (cudaStream_t)stream, (const __half*)Q, (const __half*)K,
+             (const __half*)V, (__half*)O, Sq, Sk, ldq, ldk, ldv, ldo, bsq, bsk, bsv, bso, scale * 1.44269504088896340736f,
+             kv_chunk_rows, kv_chunk_stride);
     KATZ_LAUNCH_RET();
 }

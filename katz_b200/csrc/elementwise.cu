@@ -317,7 +317,8 @@ extern "C" int katz_euler_scale_input(const void* x, void* out, long long n, flo
                                       void* stream) {
     KATZ_CHECK_ARG(x && out, KATZ_EINVAL);
     KATZ_CHECK_ARG(n > 0 && copies >= 1, KATZ_ESIZE);
-    launch_k(euler_scale_input_kernel, ew_grid(n, 256), 256, 0, (cudaStream_t)stream, (const __half*)x, (__half*)out, n, sigma, copies, mode);
+    launch_k(euler_scale_input_kernel, ew_grid(n, 256), 256, 0, (cudaStream_t)stream, (const __half*)x, (__half*)out, n, sigma,
+             copies, mode);
     KATZ_LAUNCH_RET();
 }
 

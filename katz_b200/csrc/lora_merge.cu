@@ -904,9 +904,11 @@ extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_til
         launch_k(lora_merge_f16_tc05_kernel, grid, LM_THREADS, LmCfg<__half>::SMEM + 1024, st, d_layers, d_tile_start, n_layers,
                                                                                           total_tiles, sign, in_smem, status);
     } else if (w_dtype == KATZ_DTYPE_F16)
-        launch_k(lora_merge_kernel<__half>, grid, LM_THREADS, LmCfg<__half>::SMEM, st, d_layers, d_tile_start, n_layers, total_tiles, sign, in_smem);
+        launch_k(lora_merge_kernel<__half>, grid, LM_THREADS, LmCfg<__half>::SMEM, st, d_layers, d_tile_start, n_layers,
+                 total_tiles, sign, in_smem);
     else
-        launch_k(lora_merge_kernel<float>, grid, LM_THREADS, LmCfg<float>::SMEM, st, d_layers, d_tile_start, n_layers, total_tiles, sign, in_smem);
+        launch_k(lora_merge_kernel<float>, grid, LM_THREADS, LmCfg<float>::SMEM, st, d_layers, d_tile_start, n_layers,
+                 total_tiles, sign, in_smem);
     KATZ_LAUNCH_RET();
 }
 

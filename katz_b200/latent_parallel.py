@@ -14,6 +14,8 @@ is equal up to the order of the GroupNorm reduction.
 Collectives go through torch.distributed (NCCL on GPUs). The communication primitives at the top of `RowParallel`
 are backend-agnostic and are exercised with gloo on CPU tensors in the tests.
 """
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -27,6 +29,13 @@ class RowParallel:
         self.world = dist.get_world_size(group) if world is None else world
         if self.world < 1 or not (0 <= self.rank < self.world):
             raise KatzError("bad rank/world for RowParallel: %s/%s" % (self.rank, self.world))
+        self.peer = None          # peer.PeerArena: exchanges go over peer memory instead of torch.distributed
+        self._exchange = 0        # index of the next exchange within the step
+
+    def begin_step(self):
+        """Called at the start of every step: the exchanges of a step are numbered from zero (each has its own buffer in
+        the peer arena)."""
+        self._exchange = 0
 
     # ---- sharding -------------------------------------------------------------------------------------------------
     def rows_of(self, H):
@@ -60,6 +69,10 @@ class RowParallel:
         if self.world == 1:
             return t.unsqueeze(0)
         t = t.contiguous()
+        if self.peer is not None and t.is_cuda and (t.numel() * t.element_size()) % 16 == 0:
+            k = self._exchange
+            self._exchange += 1
+            return self.peer.allgather(t, k)
         # the concatenated form (dim 0 = P * t.shape[0]) is the one every backend accepts
         out = torch.empty((self.world * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
         dist.all_gather_into_tensor(out, t, group=self.group)
@@ -67,7 +80,9 @@ class RowParallel:
 
     def reduce_stats(self, sums):
         """In-place sum over ranks of the fp64 GroupNorm sums [B, G, 2]."""
-        if self.world > 1:
+        if self.world > 1 and self.peer is not None and sums.is_cuda:
+            sums.copy_(self.gather_shards(sums).sum(0))      # rank order: the same bits on every rank
+        elif self.world > 1:
             dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=self.group)
         return sums
 
@@ -138,7 +153,11 @@ class RowParallelStep:
         for lvl in range(len(unet.cfg["block_out_channels"])):
             if (height >> lvl) % world or ((height >> lvl) // world) % (2 if lvl < len(unet.cfg["block_out_channels"]) - 1 else 1):
                 raise KatzError("latent height %d cannot be row-split over %d ranks at every UNet level" % (height, world))
+        if world > 1 and unet.device.type == "cuda" and os.environ.get("KATZ_PEER", "1") != "0":
+            from .peer import PeerArena
+            rp.peer = PeerArena(rank, world, group=group, device=unet.device)
         unet.rp = rp
+        self.rp = rp
         self._inner = GraphedStep(unet, batch, height, width, text_len=text_len, warmup=warmup)
         self.graph = self._inner.graph
         self.launches_per_step = self._inner.launches_per_step

@@ -1,0 +1,89 @@
+"""Peer-memory arena for the exchanges of the latent-row split (katz_peer_* in include/katz_b200.h).
+
+One arena per rank, allocated by the library with cudaMalloc and mapped into the other processes of the group through
+CUDA IPC handles (exchanged once with torch.distributed). `allgather` pushes a local block into the same slot of every
+rank's arena and returns, in stream order, when every rank's block has arrived here: one small kernel instead of a NCCL
+collective. The reference has no counterpart (its 2-GPU mode exchanges through torch.distributed,
+sdxl_unet_server.py:199-215).
+"""
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from ._lib import KatzError
+
+
+class _Raw:
+    """Memory the library allocated, presented to torch through the CUDA array interface."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerArena:
+    def __init__(self, rank, world, group=None, device=None, nbytes=None):
+        if world < 2:
+            raise KatzError("a peer arena needs at least two ranks")
+        lib = _lib.load()
+        self.rank, self.world, self.group = rank, world, group
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.nbytes = int(nbytes if nbytes is not None else os.environ.get("KATZ_PEER_ARENA_BYTES", 1 << 30))
+        self.ctrl = lib.katz_peer_ctrl_bytes()
+        ptr = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.katz_peer_arena_alloc(self.nbytes, ctypes.byref(ptr)), "katz_peer_arena_alloc")
+            hb = lib.katz_peer_ipc_handle_bytes()
+            handle = ctypes.create_string_buffer(hb)
+            _lib.check(lib.katz_peer_ipc_export(ptr, handle), "katz_peer_ipc_export")
+            handles = [None] * world
+            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            self._ptr = ptr.value
+            self._opened = []
+            bases = []
+            for r in range(world):
+                if r == rank:
+                    bases.append(self._ptr)
+                    continue
+                p = ctypes.c_void_p()
+                _lib.check(lib.katz_peer_ipc_open(ctypes.create_string_buffer(handles[r], hb), ctypes.byref(p)),
+                           "katz_peer_ipc_open(rank %d)" % r)
+                self._opened.append(p.value)
+                bases.append(p.value)
+        self.bases = (ctypes.c_ulonglong * world)(*bases)
+        self.local = torch.as_tensor(_Raw(self._ptr, self.nbytes), device=self.device)      # uint8 view of this rank's arena
+        self._slots = []          # (offset, bytes) per call site of a step, in call order
+        self._cursor = (self.ctrl + 255) // 256 * 256
+        dist.barrier(group=group)     # every arena is mapped everywhere before anything is pushed
+
+    def slot(self, index, nbytes):
+        """Offset of the buffer of the index-th exchange of a step (assigned on first use, the same on every rank)."""
+        if index < len(self._slots):
+            off, size = self._slots[index]
+            if size != nbytes:
+                raise KatzError("exchange %d of the step changed size (%d -> %d bytes)" % (index, size, nbytes))
+            return off
+        if index != len(self._slots):
+            raise KatzError("exchanges must be numbered consecutively")
+        off = self._cursor
+        if off + nbytes > self.nbytes:
+            raise KatzError("peer arena of %d bytes is too small (KATZ_PEER_ARENA_BYTES)" % self.nbytes)
+        self._cursor = (off + nbytes + 255) // 256 * 256
+        self._slots.append((off, nbytes))
+        return off
+
+    def allgather(self, src, index):
+        """src: contiguous CUDA tensor whose byte size is a multiple of 16 -> [world, *src.shape] view of the arena."""
+        nb = src.numel() * src.element_size()
+        if nb % 16 or not src.is_contiguous() or src.data_ptr() % 16:
+            raise KatzError("peer all-gather needs a contiguous, 16-byte aligned block of a multiple of 16 bytes")
+        off = self.slot(index, self.world * nb)
+        st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        _lib.call("katz_peer_allgather", ctypes.c_void_p(src.data_ptr()), nb, off, self.bases, self.rank, self.world, st)
+        return self.local[off:off + self.world * nb].view(src.dtype).view((self.world,) + tuple(src.shape))
+
+    def status(self):
+        """0, or 100 + the rank whose block never arrived within the bounded wait. Synchronises the device."""
+        return _lib.load().katz_peer_status(ctypes.c_void_p(self._ptr))

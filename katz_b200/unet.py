@@ -353,6 +353,7 @@ class KatzUNet(_Net):
         kv = self._cross_kv(ctx)
         h = ops.nchw_to_nhwc(x, cpad=self.w.conv_cin_pad["conv_in.weight"])
         if self.rp is not None:
+            self.rp.begin_step()
             h = self.rp.shard_rows(h)          # every rank holds the whole latent; keep this rank's rows
         h = self._conv3x3(h, self._P("conv_in.weight"), self._P("conv_in.bias"))
         mid, res = self._down_and_mid(h, temb_all, kv)

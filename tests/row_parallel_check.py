@@ -53,10 +53,23 @@ def main():
     ok2 = err2 <= 1e-2 and rel2 <= 2e-3
     print("rank %d/%d cfg%d x rows%d graphed step vs single-GPU: max-abs %.3e rel-l2 %.3e %s"
           % (rank, world, step.halves, step.rows_world, err2, rel2, "OK" if ok2 else "MISMATCH"), flush=True)
+    # the pure row split as a graphed step: its exchanges go over the peer-memory arena
+    step3 = CfgRowParallelStep(unet, sample.shape[0], cfg["sample_size"], cfg["sample_size"], rank, world, text_len=ctx.shape[1],
+                               split_cfg=False)
+    out3 = step3.run(sample=sample, timestep=t, encoder_hidden_states=ctx, text_embeds=te, time_ids=ti)
+    torch.cuda.synchronize()
+    unet.rp = None
+    err3 = float((out3.float() - ref2.float()).abs().max())
+    rel3 = float((out3.float() - ref2.float()).norm() / ref2.float().norm())
+    peer = step3._inner.rp.peer
+    ok3 = err3 <= 1e-2 and rel3 <= 2e-3 and (peer is None or peer.status() == 0)
+    print("rank %d/%d rows%d graphed step over %s vs single-GPU: max-abs %.3e rel-l2 %.3e %s"
+          % (rank, world, step3.rows_world, "peer memory" if peer is not None else "NCCL", err3, rel3, "OK" if ok3 else "MISMATCH"),
+          flush=True)
     dist.barrier()
     torch.cuda.synchronize()
     # NCCL communicators captured in live CUDA graphs do not tear down cleanly: leave without destroying the group
-    os._exit(0 if (ok and ok2) else 1)
+    os._exit(0 if (ok and ok2 and ok3) else 1)
 
 
 if __name__ == "__main__":
