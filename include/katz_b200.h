@@ -97,8 +97,9 @@ int katz_group_norm_nhwc_f16(const void* x, void* y, const void* gamma, const vo
  * normalises the shard with the global sums and n_total = (total rows) * (C / G). Needs C % 8 == 0. */
 int katz_group_norm_stats_nhwc_f16(const void* x, double* sums, int B, int HW, int C, int G, void* scratch,
                                    long long scratch_bytes, void* stream);
-int katz_group_norm_apply_nhwc_f16(const void* x, void* y, const double* sums, const void* gamma, const void* beta, int B,
-                                   int HW, int C, int G, double n_total, float eps, int act, void* stream);
+int katz_group_norm_apply_nhwc_f16(const void* x, void* y, const double* sums, int n_parts, const void* gamma,
+                                   const void* beta, int B, int HW, int C, int G, double n_total, float eps, int act,
+                                   void* stream);
 /* katz_group_norm_nhwc_f16 for callers that cannot allocate device memory (no counterpart in the reference: its op
  * takes scratch from torch's allocator). A serving process that gave all device memory to another allocator at
  * start-up, or a plugin inside a runtime that forbids allocations after initialisation, has no buffer to pass as
@@ -194,13 +195,21 @@ int katz_attention_f16(const void* Q, const void* K, const void* V, void* O, int
  * inside). */
 int katz_residual_intake_f16(const void* src, void* dst, const void* const* h_residuals, const float* h_scales,
                              int n_res, long long n, void* stream);
+/* Latent-row split: the input of a row shard's 3x3 convolution in one pass. x[B,h,W,C] plus the all-gather of every
+ * rank's first and last row (edges[P][2][B][W][C], NULL when world == 1) -> out[B, h+top+bottom, W, C] with the
+ * neighbours' rows attached (zeros at the image edge), or with upsample = 1 (top = bottom = 1) -> out[B, 2h+2, 2W, C]:
+ * rows [1, 2h+3) of the nearest-2x upsample of the padded shard. No reference counterpart (the reference has no row
+ * split). */
+int katz_halo_assemble_f16(const void* x, const void* edges, void* out, int B, int h, int W, int C, int top, int bottom,
+                           int upsample, int rank, int world, void* stream);
 /* ---- peer-memory all-gather (latent-row split over several GPUs, one process per GPU) ---------------------------------
  * No reference counterpart: the reference's 2-GPU mode exchanges tensors through torch.distributed
  * (sdxl_unet_server.py:199-215). Each process allocates one arena (katz_peer_arena_alloc: cudaMalloc, first
  * katz_peer_ctrl_bytes() bytes are zeroed control words), exports it (katz_peer_ipc_export, a
  * katz_peer_ipc_handle_bytes()-byte handle to send to the other processes by any means) and maps the others'
- * (katz_peer_ipc_open). katz_peer_allgather copies `bytes` (multiple of 16) from `src` into
- * arena[p] + dst_off + rank*bytes on EVERY rank p with plain stores over NVLink, then returns (in stream order) once
+ * (katz_peer_ipc_open). katz_peer_allgather copies a block of `rows` rows of `row_bytes` bytes (multiple of 16;
+ * `src_pitch_bytes` apart in the source, so a column slice needs no contiguous copy) from `src` into
+ * arena[p] + dst_off + rank*rows*row_bytes, packed, on EVERY rank p with plain stores over NVLink, then returns (in stream order) once
  * every rank's block has arrived in this rank's arena. h_bases[world]: the arenas as mapped in this process, own arena at
  * index `rank`. Every rank must issue the same sequence of calls; consecutive calls must use different dst_off. Waits
  * are bounded: katz_peer_status(arena) is 0, or 100 + the rank whose block never arrived. */
@@ -211,8 +220,8 @@ int katz_peer_ipc_handle_bytes(void);
 int katz_peer_ipc_export(void* ptr, void* handle_out);
 int katz_peer_ipc_open(const void* handle, void** ptr);
 int katz_peer_ipc_close(void* ptr);
-int katz_peer_allgather(const void* src, long long bytes, long long dst_off, const unsigned long long* h_bases, int rank,
-                        int world, void* stream);
+int katz_peer_allgather(const void* src, long long rows, long long row_bytes, long long src_pitch_bytes, long long dst_off,
+                        const unsigned long long* h_bases, int rank, int world, void* stream);
 int katz_peer_status(const void* arena);
 /* get_timestep_embedding (diffusers/models/embeddings.py:26-66), flip_sin_to_cos, shift 0: out[rows, dim] fp16. */
 int katz_timestep_embedding_f16(const float* t, void* out, int rows, int dim, int ld_out, void* stream);

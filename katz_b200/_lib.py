@@ -59,7 +59,7 @@ SIGNATURES = {
     "katz_group_norm_scratch_bytes": (_L, [_I, _I, _I, _I]),
     "katz_group_norm_nhwc_f16": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _F, _I, _V, _L, _V]),
     "katz_group_norm_stats_nhwc_f16": (_I, [_V, _V, _I, _I, _I, _I, _V, _L, _V]),
-    "katz_group_norm_apply_nhwc_f16": (_I, [_V, _V, _V, _V, _V, _I, _I, _I, _I, ctypes.c_double, _F, _I, _V]),
+    "katz_group_norm_apply_nhwc_f16": (_I, [_V, _V, _V, _I, _V, _V, _I, _I, _I, _I, ctypes.c_double, _F, _I, _V]),
     "katz_group_norm_static_scratch_bytes": (_L, []),
     "katz_group_norm_nhwc_f16_noalloc": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _F, _I, _V]),
     "katz_group_norm_nchw_f16": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _F, _I, _V]),
@@ -79,6 +79,7 @@ SIGNATURES = {
     "katz_residual_intake_f16": (_I, [_V, _V, POINTER(c_void_p), POINTER(c_float), _I, _L, _V]),
     "katz_timestep_embedding_f16": (_I, [_V, _V, _I, _I, _I, _V]),
     "katz_silu_f16": (_I, [_V, _V, _L, _V]),
+    "katz_halo_assemble_f16": (_I, [_V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _V]),
     "katz_peer_ctrl_bytes": (_I, []),
     "katz_peer_arena_alloc": (_I, [_L, POINTER(c_void_p)]),
     "katz_peer_arena_free": (_I, [_V]),
@@ -86,7 +87,7 @@ SIGNATURES = {
     "katz_peer_ipc_export": (_I, [_V, _V]),
     "katz_peer_ipc_open": (_I, [_V, POINTER(c_void_p)]),
     "katz_peer_ipc_close": (_I, [_V]),
-    "katz_peer_allgather": (_I, [_V, _L, _L, POINTER(ctypes.c_ulonglong), _I, _I, _V]),
+    "katz_peer_allgather": (_I, [_V, _L, _L, _L, _L, POINTER(ctypes.c_ulonglong), _I, _I, _V]),
     "katz_peer_status": (_I, [_V]),
     "katz_add_f16": (_I, [_V, _V, _V, _L, _V]),
     "katz_concat_channels_f16": (_I, [_V, _V, _V, _L, _I, _I, _V]),
@@ -130,7 +131,7 @@ def check(code, what):
 
 
 # kernels launched per successful entry-point call (everything else launches one)
-_KERNELS_PER_CALL = {"katz_group_norm_nhwc_f16": 2, "katz_group_norm_stats_nhwc_f16": 2}
+_KERNELS_PER_CALL = {"katz_group_norm_nhwc_f16": 2}
 _launches = 0
 
 

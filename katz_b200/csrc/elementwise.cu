@@ -263,6 +263,50 @@ extern "C" int katz_timestep_embedding_f16(const float* t, void* out, int rows, 
     KATZ_LAUNCH_RET();
 }
 
+// Row shard [B, h, W, C] -> the input a 3x3 convolution of the shard reads: the neighbours' adjacent rows (zeros at the
+// image edge) attached above and / or below, optionally seen through a nearest 2x upsample (then rows [1, 2h+3) of the
+// upsampled padded shard, 2W wide: exactly what the 2h output rows read). One pass instead of an allocation, three
+// copies, an upsample and a slice copy. `edges` is the all-gather of every rank's first and last row, [P][2][B][W][C].
+__global__ void halo_assemble_kernel(const uint4* __restrict__ x, const uint4* __restrict__ edges, uint4* __restrict__ out,
+                                     int B, int h, int W, int ch, int Ho, int Wo, int top, int upsample, int rank, int world,
+                                     long long total) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % ch);
+        long long r = i / ch;
+        const int w = (int)(r % Wo);
+        r /= Wo;
+        const int j = (int)(r % Ho);
+        const int b = (int)(r / Ho);
+        const int sr = upsample ? (j + 1) / 2 - 1 : j - top;
+        const int sw = upsample ? w >> 1 : w;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (sr >= 0 && sr < h) {
+            v = x[(((long long)b * h + sr) * W + sw) * ch + c];
+        } else if (edges) {
+            const int p = sr < 0 ? rank - 1 : rank + 1, e = sr < 0 ? 1 : 0;      // the neighbour's last / first row
+            if (p >= 0 && p < world) v = edges[((((long long)p * 2 + e) * B + b) * W + sw) * ch + c];
+        }
+        out[i] = v;
+    }
+}
+
+extern "C" int katz_halo_assemble_f16(const void* x, const void* edges, void* out, int B, int h, int W, int C, int top,
+                                      int bottom, int upsample, int rank, int world, void* stream) {
+    KATZ_CHECK_ARG(x && out, KATZ_EINVAL);
+    KATZ_CHECK_ARG(B > 0 && h > 0 && W > 0 && C > 0 && C % 8 == 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG((top == 0 || top == 1) && (bottom == 0 || bottom == 1) && world >= 1 && rank >= 0 && rank < world, KATZ_EINVAL);
+    KATZ_CHECK_ARG(!upsample || (top == 1 && bottom == 1), KATZ_EINVAL);
+    KATZ_CHECK_ARG(world == 1 || edges, KATZ_EINVAL);
+    KATZ_CHECK_ARG(aligned16(x) && aligned16(out) && (!edges || aligned16(edges)), KATZ_EALIGN);
+    const int Ho = upsample ? 2 * h + 2 : h + top + bottom, Wo = upsample ? 2 * W : W;
+    const long long total = (long long)B * Ho * Wo * (C / 8);
+    launch_k(halo_assemble_kernel, ew_grid(total, 256), 256, 0, (cudaStream_t)stream, (const uint4*)x, (const uint4*)edges,
+             (uint4*)out, B, h, W, C / 8, Ho, Wo, top, upsample, rank, world, total);
+    KATZ_LAUNCH_RET();
+}
+
 extern "C" int katz_silu_f16(const void* x, void* y, long long n, void* stream) {
     KATZ_CHECK_ARG(x && y, KATZ_EINVAL);
     KATZ_CHECK_ARG(n > 0 && n % 2 == 0, KATZ_ESIZE);

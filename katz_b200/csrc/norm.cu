@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(GN_THREADS) gn_apply_nhwc_kernel(const __half*
 // one per CTA of the normalising pass.
 __global__ void gn_stats_v8_kernel(const __half* __restrict__ x, float* __restrict__ partial, int HW, int C, int G,
                                    int rows_per_slab, int R, float* __restrict__ mr_out, unsigned int* __restrict__ tickets,
-                                   double n_total, float eps) {
+                                   double n_total, float eps, double* __restrict__ dsum_out) {
     pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
     pdl_launch_dependents();
     extern __shared__ float s_dyn[];    // [blockDim][16]: 8 channel sums then 8 channel sums of squares
@@ -203,7 +203,7 @@ __global__ void gn_stats_v8_kernel(const __half* __restrict__ x, float* __restri
             __threadfence();
         }
     }
-    if (!mr_out) return;
+    if (!mr_out && !dsum_out) return;
     __shared__ int s_last;
     __syncthreads();
     if (tid == 0) s_last = atomicInc(tickets + b, (unsigned int)(nslab - 1)) == (unsigned int)(nslab - 1);
@@ -233,6 +233,12 @@ __global__ void gn_stats_v8_kernel(const __half* __restrict__ x, float* __restri
             s += s_part[(i * G + tid) * 2];
             q += s_part[(i * G + tid) * 2 + 1];
         }
+        if (dsum_out) {
+            // a shard of a row-split tensor: hand out the raw sums, the normalising pass adds the shards' sums
+            dsum_out[((size_t)b * G + tid) * 2] = s;
+            dsum_out[((size_t)b * G + tid) * 2 + 1] = q;
+            return;
+        }
         const double mean = s / n_total;
         double var = q / n_total - mean * mean;
         if (var < 0.0) var = 0.0;
@@ -244,7 +250,7 @@ __global__ void gn_stats_v8_kernel(const __half* __restrict__ x, float* __restri
 __global__ void gn_apply_v8_kernel(const __half* __restrict__ x, __half* __restrict__ y, const float* __restrict__ mr,
                                    const __half* __restrict__ gamma, const __half* __restrict__ beta, int HW,
                                    int C, int G, int rows_per_slab, int R, double n_total, float eps, int act,
-                                   const double* __restrict__ dsums) {
+                                   const double* __restrict__ dsums, int n_parts) {
     pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
     pdl_launch_dependents();
     extern __shared__ float s_dyn[];    // [C] scale, [C] shift
@@ -256,7 +262,13 @@ __global__ void gn_apply_v8_kernel(const __half* __restrict__ x, __half* __restr
         s_mean[tid] = mr[((size_t)b * G + tid) * 2];
         s_rstd[tid] = mr[((size_t)b * G + tid) * 2 + 1];
     } else if (tid < G) {
-        const double s = dsums[((size_t)b * G + tid) * 2], q = dsums[((size_t)b * G + tid) * 2 + 1];
+        // dsums: [n_parts][B][G][2], one part per shard of a row-split tensor, added in part order
+        double s = 0.0, q = 0.0;
+        for (int i = 0; i < n_parts; ++i) {
+            const double* d = dsums + (((size_t)i * gridDim.y + b) * G + tid) * 2;
+            s += d[0];
+            q += d[1];
+        }
         const double mean = s / n_total;
         double var = q / n_total - mean * mean;
         if (var < 0.0) var = 0.0;
@@ -509,10 +521,10 @@ extern "C" int katz_group_norm_nhwc_f16(const void* x, void* y, const void* gamm
         }
         const GnScratch sc = gn_carve(scratch, B, G);
         const double n_total = (double)HW * (C / G);
-        launch_k(gn_stats_v8_kernel, grid, threads, threads * 64, st, (const __half*)x, sc.partial, HW, C, G, rows, R, sc.mr, sc.tickets,
-                                                                n_total, eps);
+        launch_k(gn_stats_v8_kernel, grid, threads, threads * 64, st, (const __half*)x, sc.partial, HW, C, G, rows, R, sc.mr,
+                 sc.tickets, n_total, eps, nullptr);
         launch_k(gn_apply_v8_kernel, grid, threads, 2 * C * 4, st, (const __half*)x, (__half*)y, sc.mr, (const __half*)gamma,
-                                                             (const __half*)beta, HW, C, G, rows, R, n_total, eps, act, nullptr);
+                 (const __half*)beta, HW, C, G, rows, R, n_total, eps, act, nullptr, 0);
         KATZ_LAUNCH_RET();
     }
     float* partial = gn_carve(scratch, B, G).partial;      // the ticket counters at the head of the scratch stay untouched
@@ -549,15 +561,23 @@ extern "C" int katz_group_norm_stats_nhwc_f16(const void* x, double* sums, int B
     const int nslab = ceil_div(HW, rows);
     cudaStream_t st = (cudaStream_t)stream;
     const GnScratch sc = gn_carve(scratch, B, G);
+    if (B <= GN_MAX_TICKETS) {
+        // the CTA that finishes last for an image folds the partials into the fp64 sums: one kernel
+        launch_k(gn_stats_v8_kernel, dim3(nslab, B), threads, threads * 64, st, (const __half*)x, sc.partial, HW, C, G, rows, R,
+                 nullptr, sc.tickets, 0.0, 0.f, sums);
+        KATZ_LAUNCH_RET();
+    }
     launch_k(gn_stats_v8_kernel, dim3(nslab, B), threads, threads * 64, st, (const __half*)x, sc.partial, HW, C, G, rows, R, nullptr,
-                                                                      nullptr, 0.0, 0.f);
+             nullptr, 0.0, 0.f, nullptr);
     launch_k(gn_fold_kernel, B, GN_MAXG, 0, st, sc.partial, nslab, G, sums);
     KATZ_LAUNCH_RET();
 }
 
-extern "C" int katz_group_norm_apply_nhwc_f16(const void* x, void* y, const double* sums, const void* gamma, const void* beta,
-                                              int B, int HW, int C, int G, double n_total, float eps, int act, void* stream) {
+extern "C" int katz_group_norm_apply_nhwc_f16(const void* x, void* y, const double* sums, int n_parts, const void* gamma,
+                                              const void* beta, int B, int HW, int C, int G, double n_total, float eps, int act,
+                                              void* stream) {
     KATZ_CHECK_ARG(x && y && sums, KATZ_EINVAL);
+    KATZ_CHECK_ARG(n_parts >= 1 && n_parts <= 64, KATZ_ESIZE);
     KATZ_CHECK_ARG(B > 0 && B <= 65535 && HW > 0 && C > 0 && G > 0 && G <= GN_MAXG && C % G == 0 && n_total > 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(act == 0 || act == 1, KATZ_EINVAL);
     KATZ_CHECK_ARG(aligned16(x) && aligned16(y) && ((uintptr_t)sums & 7) == 0, KATZ_EALIGN);
@@ -567,7 +587,7 @@ extern "C" int katz_group_norm_apply_nhwc_f16(const void* x, void* y, const doub
     const int rows = gn_rows_per_slab(HW, B);
     const int nslab = ceil_div(HW, rows);
     launch_k(gn_apply_v8_kernel, dim3(nslab, B), threads, 2 * C * 4, (cudaStream_t)stream, (const __half*)x, (__half*)y, nullptr,
-             (const __half*)gamma, (const __half*)beta, HW, C, G, rows, R, n_total, eps, act, sums);
+             (const __half*)gamma, (const __half*)beta, HW, C, G, rows, R, n_total, eps, act, sums, n_parts);
     KATZ_LAUNCH_RET();
 }
 
@@ -661,9 +681,8 @@ extern "C" int katz_group_norm_nhwc_f16_noalloc(const void* x, void* y, const vo
     const GnScratch sc = gn_carve(scratch, B, G);
     const double n_total = (double)HW * (C / G);
     launch_k(gn_stats_v8_kernel, dim3(nslab, B), threads, threads * 64, st, (const __half*)x, sc.partial, HW, C, G, rows, R, sc.mr,
-                                                                      sc.tickets, n_total, eps);
+             sc.tickets, n_total, eps, nullptr);
     launch_k(gn_apply_v8_kernel, dim3(nslab, B), threads, 2 * C * 4, st, (const __half*)x, (__half*)y, sc.mr, (const __half*)gamma,
-                                                                   (const __half*)beta, HW, C, G, rows, R, n_total, eps, act,
-                                                                   nullptr);
+             (const __half*)beta, HW, C, G, rows, R, n_total, eps, act, nullptr, 0);
     KATZ_LAUNCH_RET();
 }

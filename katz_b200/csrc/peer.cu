@@ -26,13 +26,16 @@ struct PeerArgs {
     int rank, world;
 };
 
-__global__ void __launch_bounds__(256) peer_allgather_kernel(const uint4* __restrict__ src, long long n16, long long dst_off,
-                                                             PeerArgs a) {
+// The block is `rows` rows of `row16` 16-byte vectors, `pitch16` vectors apart in the source (a column slice of a wider
+// tensor is pushed without being made contiguous first); it lands packed.
+__global__ void __launch_bounds__(256) peer_allgather_kernel(const uint4* __restrict__ src, long long n16, int row16,
+                                                             long long pitch16, long long dst_off, PeerArgs a) {
     pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
     pdl_launch_dependents();
     const long long slot = dst_off + (long long)a.rank * n16 * 16;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) {
-        const uint4 v = src[i];
+        const long long r = i / row16;
+        const uint4 v = src[r * pitch16 + (i - r * row16)];
 #pragma unroll 1
         for (int p = 0; p < a.world; ++p) reinterpret_cast<uint4*>(a.base[p] + slot)[i] = v;
     }
@@ -117,12 +120,16 @@ extern "C" int katz_peer_ipc_close(void* ptr) {
     return e == cudaSuccess ? KATZ_OK : (int)e;
 }
 
-extern "C" int katz_peer_allgather(const void* src, long long bytes, long long dst_off, const unsigned long long* h_bases,
-                                   int rank, int world, void* stream) {
+extern "C" int katz_peer_allgather(const void* src, long long rows, long long row_bytes, long long src_pitch_bytes,
+                                   long long dst_off, const unsigned long long* h_bases, int rank, int world, void* stream) {
     KATZ_CHECK_ARG(src && h_bases, KATZ_EINVAL);
     KATZ_CHECK_ARG(world >= 1 && world <= PEER_MAX_RANKS && rank >= 0 && rank < world, KATZ_ESIZE);
-    KATZ_CHECK_ARG(bytes > 0 && bytes % 16 == 0 && dst_off >= PEER_CTRL_BYTES && dst_off % 16 == 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(rows > 0 && row_bytes > 0 && row_bytes % 16 == 0 && row_bytes < (1ll << 34) && src_pitch_bytes >= row_bytes &&
+                       src_pitch_bytes % 16 == 0,
+                   KATZ_ESIZE);
+    KATZ_CHECK_ARG(dst_off >= PEER_CTRL_BYTES && dst_off % 16 == 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(aligned16(src), KATZ_EALIGN);
+    const long long bytes = rows * row_bytes;
     PeerArgs a{};
     for (int p = 0; p < world; ++p) {
         KATZ_CHECK_ARG(h_bases[p] != 0 && (h_bases[p] & 255) == 0, KATZ_EALIGN);
@@ -134,7 +141,8 @@ extern "C" int katz_peer_allgather(const void* src, long long bytes, long long d
     long long ctas = (n16 + 1023) / 1024;      // four vectors per thread
     if (ctas > 64) ctas = 64;
     if (ctas < 1) ctas = 1;
-    launch_k(peer_allgather_kernel, dim3((unsigned)ctas), dim3(256), 0, (cudaStream_t)stream, (const uint4*)src, n16, dst_off, a);
+    launch_k(peer_allgather_kernel, dim3((unsigned)ctas), dim3(256), 0, (cudaStream_t)stream, (const uint4*)src, n16,
+             (int)(row_bytes / 16), src_pitch_bytes / 16, dst_off, a);
     KATZ_LAUNCH_RET();
 }
 

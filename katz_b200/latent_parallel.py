@@ -68,11 +68,11 @@ class RowParallel:
         """t: contiguous local shard -> [P, *t.shape], rank-major (the K/V all-gather and the final row gather)."""
         if self.world == 1:
             return t.unsqueeze(0)
-        t = t.contiguous()
-        if self.peer is not None and t.is_cuda and (t.numel() * t.element_size()) % 16 == 0:
+        if self.peer is not None and t.is_cuda and (t.shape[-1] * t.element_size()) % 16 == 0:
             k = self._exchange
             self._exchange += 1
-            return self.peer.allgather(t, k)
+            return self.peer.allgather(t, k)        # takes a column slice as it is
+        t = t.contiguous()
         # the concatenated form (dim 0 = P * t.shape[0]) is the one every backend accepts
         out = torch.empty((self.world * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
         dist.all_gather_into_tensor(out, t, group=self.group)
@@ -91,6 +91,29 @@ class RowParallel:
         g = self.gather_shards(x_local)                                     # [P, B, h, W, C]
         P, B, h, W, C = g.shape
         return g.permute(1, 0, 2, 3, 4).reshape(B, P * h, W, C).contiguous()
+
+    def gather_edges(self, x):
+        """[P, 2, B, W, C]: every rank's first and last row (None on a single rank)."""
+        if self.world == 1:
+            return None
+        B, h = x.shape[0], x.shape[1]
+        if B == 1 and h > 1 and self.peer is not None and x.is_cuda:
+            # rows 0 and h-1 of the single image: two rows at a constant pitch, pushed without packing them first
+            edges = x.as_strided((2, 1, x.shape[2], x.shape[3]), ((h - 1) * x.stride(1), x.stride(0), x.stride(2), x.stride(3)))
+            k = self._exchange
+            self._exchange += 1
+            return self.peer.allgather(edges.view(2, -1), k).view(self.world, 2, 1, x.shape[2], x.shape[3])
+        return self.gather_shards(torch.stack([x[:, 0], x[:, -1]]).contiguous())
+
+    def assemble(self, x, top=True, bottom=True, upsample=False):
+        """The input a 3x3 convolution of this shard reads: one kernel on the GPU (ops.halo_assemble)."""
+        if x.is_cuda and x.dtype == torch.float16:
+            from . import ops
+            return ops.halo_assemble(x.contiguous(), self.gather_edges(x), self.rank, self.world, top, bottom, upsample)
+        if upsample:
+            up = self.pad_rows(x).repeat_interleave(2, dim=1).repeat_interleave(2, dim=2)
+            return up[:, 1:2 * x.shape[1] + 3].contiguous()
+        return self.pad_rows(x, top, bottom)
 
     def pad_rows(self, x, top=True, bottom=True):
         """x [B, h, W, C] -> [B, h + top + bottom, W, C] with the neighbours' rows (zeros at image edges) attached."""
@@ -113,20 +136,22 @@ class RowParallel:
         if upsample:
             # exchange the rows before the upsample, upsample the padded shard, drop the outermost upsampled rows:
             # rows [1, 2h+3) of the upsampled padded shard are exactly the 2h+2 input rows the 2h output rows read
-            up = ops.upsample_nearest2x(self.pad_rows(x))
-            return ops.conv2d(up[:, 1:2 * h + 3].contiguous(), w, bias, stride=1, pad=1, pad_h=0, **epi)
+            return ops.conv2d(self.assemble(x, upsample=True), w, bias, stride=1, pad=1, pad_h=0, **epi)
         if stride == 2:
             if h % 2:
                 raise KatzError("a stride-2 convolution needs an even number of rows per rank (got %d)" % h)
-            return ops.conv2d(self.pad_rows(x, bottom=False), w, bias, stride=2, pad=1, pad_h=0, **epi)
-        return ops.conv2d(self.pad_rows(x), w, bias, stride=1, pad=1, pad_h=0, **epi)
+            return ops.conv2d(self.assemble(x, bottom=False), w, bias, stride=2, pad=1, pad_h=0, **epi)
+        return ops.conv2d(self.assemble(x), w, bias, stride=1, pad=1, pad_h=0, **epi)
 
     def group_norm(self, x, gamma, beta, groups, eps, act):
         from . import ops
         B, C = x.shape[0], x.shape[-1]
         rows_local = x.numel() // (B * C)
         sums = ops.group_norm_stats(x, groups)
-        self.reduce_stats(sums)
+        if self.peer is not None and self.world > 1:
+            sums = self.gather_shards(sums)          # [P, B, G, 2]: the normalising kernel adds the shards' sums itself
+        else:
+            self.reduce_stats(sums)
         return ops.group_norm_apply(x, sums, gamma, beta, groups, float(rows_local) * self.world * (C // groups), eps, act)
 
     def self_attention(self, qkv, C, heads):
@@ -134,7 +159,7 @@ class RowParallel:
         place by the attention kernel as P chunks."""
         from . import ops
         B, s, _ = qkv.shape
-        g = self.gather_shards(qkv[:, :, C:].contiguous())                  # [P, B, s, 2C]
+        g = self.gather_shards(qkv[:, :, C:])                               # [P, B, s, 2C]
         if s % 64 == 0:
             return ops.attention(qkv[:, :, :C], g[0][:, :, :C], g[0][:, :, C:], heads,
                                  kv_chunks=(self.world, s, B * s * 2 * C))

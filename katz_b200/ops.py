@@ -202,17 +202,19 @@ def group_norm_stats(x, groups):
 
 
 def group_norm_apply(x, sums, gamma, beta, groups, n_total, eps, act=ACT_NONE, out=None):
-    """Second half: normalise the shard with the (globally summed) statistics; n_total = elements per (batch, group)
-    over the WHOLE tensor."""
+    """Second half: normalise the shard with the statistics of the whole tensor; n_total = elements per (batch, group)
+    over the WHOLE tensor. sums: fp64 [B, G, 2] (already summed over the shards) or [P, B, G, 2] (one entry per shard,
+    added here in shard order)."""
     _f16(x, "x")
     B, C = x.shape[0], x.shape[-1]
     HW = x.numel() // (B * C)
-    if sums.dtype != torch.float64 or tuple(sums.shape) != (B, groups, 2) or not sums.is_contiguous():
-        raise KatzError("group_norm_apply: sums must be a contiguous fp64 [B, G, 2] tensor")
+    if sums.dtype != torch.float64 or not sums.is_contiguous() or tuple(sums.shape[-3:]) != (B, groups, 2) or sums.dim() not in (3, 4):
+        raise KatzError("group_norm_apply: sums must be a contiguous fp64 [B, G, 2] or [P, B, G, 2] tensor")
+    n_parts = sums.shape[0] if sums.dim() == 4 else 1
     if out is None:
         out = torch.empty_like(x)
-    call("katz_group_norm_apply_nhwc_f16", _p(x), _p(out), _p(sums), _p(gamma), _p(beta), B, HW, C, groups, float(n_total),
-         float(eps), act, _stream())
+    call("katz_group_norm_apply_nhwc_f16", _p(x), _p(out), _p(sums), n_parts, _p(gamma), _p(beta), B, HW, C, groups,
+         float(n_total), float(eps), act, _stream())
     return out
 
 
@@ -349,6 +351,21 @@ def concat_channels(a, b, out=None):
     if out is None:
         out = torch.empty(tuple(a.shape[:-1]) + (C1 + C2,), dtype=torch.float16, device=a.device)
     call("katz_concat_channels_f16", _p(a), _p(b), _p(out), rows, C1, C2, _stream())
+    return out
+
+
+def halo_assemble(x, edges, rank, world, top=True, bottom=True, upsample=False, out=None):
+    """x [B,h,W,C] + gathered edge rows [P,2,B,W,C] (None when world == 1) -> the padded (optionally 2x upsampled) input
+    of a row shard's 3x3 convolution."""
+    _f16(x, "x")
+    if not x.is_contiguous() or (edges is not None and not edges.is_contiguous()):
+        raise KatzError("halo_assemble: x and edges must be contiguous")
+    B, h, W, C = x.shape
+    shape = (B, 2 * h + 2, 2 * W, C) if upsample else (B, h + int(top) + int(bottom), W, C)
+    if out is None:
+        out = torch.empty(shape, dtype=torch.float16, device=x.device)
+    call("katz_halo_assemble_f16", _p(x), _p(edges), _p(out), B, h, W, C, int(top), int(bottom), 1 if upsample else 0, rank,
+         world, _stream())
     return out
 
 

@@ -75,13 +75,26 @@ class PeerArena:
         return off
 
     def allgather(self, src, index):
-        """src: contiguous CUDA tensor whose byte size is a multiple of 16 -> [world, *src.shape] view of the arena."""
-        nb = src.numel() * src.element_size()
-        if nb % 16 or not src.is_contiguous() or src.data_ptr() % 16:
-            raise KatzError("peer all-gather needs a contiguous, 16-byte aligned block of a multiple of 16 bytes")
+        """src: CUDA tensor, contiguous or a column slice [..., c0:c1] of a contiguous tensor, whose rows are multiples of
+        16 bytes -> [world, *src.shape] view of the arena (packed)."""
+        es = src.element_size()
+        if src.is_contiguous():
+            rows, row_bytes, pitch = 1, src.numel() * es, src.numel() * es
+        else:
+            # rows of src.shape[-1] elements at a constant pitch
+            lead = src.reshape(-1, src.shape[-1]) if src.dim() > 1 else None
+            ok = src.dim() >= 2 and src.stride(-1) == 1 and all(
+                src.stride(i) == src.stride(i + 1) * src.shape[i + 1] for i in range(src.dim() - 2))
+            if not ok or lead is None:
+                raise KatzError("peer all-gather needs a contiguous block or a column slice of one")
+            rows, row_bytes, pitch = src.numel() // src.shape[-1], src.shape[-1] * es, src.stride(-2) * es
+        if row_bytes % 16 or pitch % 16 or src.data_ptr() % 16:
+            raise KatzError("peer all-gather needs 16-byte aligned rows of a multiple of 16 bytes")
+        nb = rows * row_bytes
         off = self.slot(index, self.world * nb)
         st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        _lib.call("katz_peer_allgather", ctypes.c_void_p(src.data_ptr()), nb, off, self.bases, self.rank, self.world, st)
+        _lib.call("katz_peer_allgather", ctypes.c_void_p(src.data_ptr()), rows, row_bytes, pitch, off, self.bases, self.rank,
+                  self.world, st)
         return self.local[off:off + self.world * nb].view(src.dtype).view((self.world,) + tuple(src.shape))
 
     def status(self):

@@ -39,7 +39,7 @@ def test_argument_errors_need_no_device():
     e = _lib.LoraLayer()
     assert lib.katz_lora_layer_check(ctypes.byref(e), 0) < 0           # null W
     assert lib.katz_linear_f16_mma(None, 0, None, None, 0, 1, 1, 8, None, None, 0, 0, None, 0, 0, 1.0, None) == -1
-    assert lib.katz_group_norm_apply_nhwc_f16(None, None, None, None, None, 1, 1, 8, 1, 1.0, 1e-5, 0, None) == -1
+    assert lib.katz_group_norm_apply_nhwc_f16(None, None, None, 1, None, None, 1, 1, 8, 1, 1.0, 1e-5, 0, None) == -1
     assert lib.katz_attention_f16_mma(1, 1, 1, 1, 1, 1, 64, 64, 32, 64, 64, 64, 64, 0, 0, 0, 0, 0.125, 0, 0, None) == -3
     with pytest.raises(_lib.KatzError):
         _lib.check(-2, "x")

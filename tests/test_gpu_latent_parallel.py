@@ -103,3 +103,28 @@ def test_row_split_equals_single_gpu_on_all_gpus(cuda_device):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert r.stdout.count("OK") == 3 * n          # eager row split, batch halves x rows, graphed row split: every rank
+
+
+@pytest.mark.parametrize("B,P", [(1, 4), (2, 2)])
+def test_halo_assemble_equals_padded_slices(cuda_device, B, P):
+    """The one-pass kernel that builds a shard's convolution input (neighbour rows, zeros at the image edge, optional
+    nearest 2x upsample) against slicing the zero-padded whole tensor; the shards of P ranks are emulated on one GPU."""
+    from katz_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    H, W, C = 16, 8, 64
+    x = torch.randn(B, H, W, C, generator=g).half().cuda()
+    h = H // P
+    shards = [x[:, r * h:(r + 1) * h].contiguous() for r in range(P)]
+    edges = torch.stack([torch.stack([s[:, 0], s[:, -1]]) for s in shards]).contiguous()       # [P, 2, B, W, C]
+    zero = torch.zeros(B, 1, W, C, dtype=torch.float16, device="cuda")
+    xp = torch.cat([zero, x, zero], dim=1)
+    up = xp.repeat_interleave(2, dim=1).repeat_interleave(2, dim=2)
+    for r in range(P):
+        both = ops.halo_assemble(shards[r], edges, r, P)
+        assert torch.equal(both, xp[:, r * h:r * h + h + 2])
+        top_only = ops.halo_assemble(shards[r], edges, r, P, bottom=False)
+        assert torch.equal(top_only, xp[:, r * h:r * h + h + 1])
+        ups = ops.halo_assemble(shards[r], edges, r, P, upsample=True)
+        assert torch.equal(ups, up[:, 2 * r * h + 1:2 * r * h + 2 * h + 3])
+    alone = ops.halo_assemble(x, None, 0, 1)
+    assert torch.equal(alone, xp)
