@@ -19,7 +19,7 @@ namespace katz {
 
 constexpr int PEER_MAX_RANKS = 8;
 constexpr int PEER_CTRL_BYTES = 4096;
-constexpr unsigned int PEER_WAIT_LIMIT = 1u << 24;      // polls of about 100 ns each
+constexpr unsigned int PEER_WAIT_LIMIT = 1u << 21;      // polls of roughly a microsecond each: a second or two
 
 struct PeerArgs {
     unsigned long long base[PEER_MAX_RANKS];      // arena of every rank as mapped in THIS process
