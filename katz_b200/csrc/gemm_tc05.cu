@@ -628,7 +628,8 @@ static int pick_bn(int m_tiles, int n_out, bool geglu) {
         const long long tiles = (long long)m_tiles * ceil_div(n_out, out_w);
         const long long waves = (tiles + sms - 1) / sms;
         // per-tile time ~ MMA time (prop. to bn) + fixed overhead per tile (epilogue drain, barrier round trips)
-        const double cost = (double)waves * (bn + 24.0);
+        // (the GEGLU epilogue is several times heavier per tile: 72 fits the measured 128- and 256-wide launches)
+        const double cost = (double)waves * (bn + (geglu ? 72.0 : 24.0));
         if (cost < best_cost) {
             best_cost = cost;
             best = bn;
