@@ -251,7 +251,8 @@ def test_linear_tcgen05_strided_views(cuda_device, monkeypatch):
                                                       (1, 6, 16, 64, 64, False, 1), (1, 16, 16, 128, 128, True, 1),
                                                       (1, 8, 256, 64, 64, False, 1), (2, 32, 32, 64, 128, False, 2),
                                                       (2, 128, 128, 320, 320, False, 2), (1, 64, 64, 640, 640, False, 2),
-                                                      (1, 10, 16, 64, 64, False, 2)])
+                                                      (1, 10, 16, 64, 64, False, 2), (3, 16, 8, 64, 128, False, 1),
+                                                      (3, 16, 16, 128, 320, False, 2)])
 def test_conv3x3_tcgen05(cuda_device, B, H, W, Cin, Cout, up, stride, monkeypatch):
     monkeypatch.setenv("KATZ_GEMM", "tc05")
     from katz_b200 import ops
