@@ -612,18 +612,18 @@ int* tc05_status_device_ptr() { return status_ptr(); }
 
 // Tile width by wave efficiency: tiles of width bn cost ~bn per wave; pick the width with the least total cost.
 static int pick_bn(int m_tiles, int n_out, bool geglu) {
-    // KATZ_TC05_BN=128|160|256 forces a width (tuning runs); ignored where the width is not available
+    // KATZ_TC05_BN=96|128|160|256 forces a width (tuning runs); ignored where the width is not available
     if (const char* e = getenv("KATZ_TC05_BN")) {
         const int v = atoi(e);
-        if ((v == 128 || v == 256 || (v == 160 && !geglu))) return v;
+        if ((v == 128 || v == 256 || ((v == 160 || v == 96) && !geglu))) return v;
     }
     const int sms = sm_count();
-    const int cand[3] = {256, 160, 128};
+    const int cand[4] = {256, 160, 128, 96};     // 96: small M (batch 1, row shards), where wider tiles leave SMs idle
     int best = 128;
     double best_cost = 1e30;
-    for (int i = 0; i < 3; ++i) {
+    for (int i = 0; i < 4; ++i) {
         const int bn = cand[i];
-        if (geglu && bn == 160) continue;        // its 80 output columns are not a whole number of 32-column boxes
+        if (geglu && (bn == 160 || bn == 96)) continue;      // half of it is not a whole number of 32-column boxes
         const int out_w = geglu ? bn / 2 : bn;
         const long long tiles = (long long)m_tiles * ceil_div(n_out, out_w);
         const long long waves = (tiles + sms - 1) / sms;
@@ -664,11 +664,13 @@ static int dispatch(const CUtensorMap& a, const CUtensorMap& b, Tc05Params& p, i
         if (bn == 256) return launch_tc05<256, GEGLU ? 6 : 5, GEGLU, true>(a, b, c, r, p, st);
         if constexpr (!GEGLU) {
             if (bn == 160) return launch_tc05<160, 6, false, true>(a, b, c, r, p, st);
+            if (bn == 96) return launch_tc05<96, 8, false, true>(a, b, c, r, p, st);
         }
         return launch_tc05<128, 7, GEGLU, true>(a, b, c, r, p, st);
     }
     if constexpr (!GEGLU) {
         if (bn == 160) return launch_tc05<160, 4, false, false>(a, b, c, r, p, st);
+        if (bn == 96) return launch_tc05<96, 6, false, false>(a, b, c, r, p, st);
     }
     if (bn == 256) return launch_tc05<256, GEGLU ? 4 : 3, GEGLU, false>(a, b, c, r, p, st);
     return launch_tc05<128, 6, GEGLU, false>(a, b, c, r, p, st);

@@ -206,7 +206,7 @@ def test_small_kernels(cuda_device, golden_dir):
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 320, 640), (154, 640, 2048), (2, 1280, 320), (2048, 1280, 1280),
-                                   (8192, 5120, 640), (300, 72, 64), (4096, 640, 2560)])
+                                   (8192, 5120, 640), (300, 72, 64), (4096, 640, 2560), (1024, 1280, 1280), (512, 640, 640)])
 def test_linear_tcgen05(cuda_device, M, N, K, monkeypatch):
     monkeypatch.setenv("KATZ_GEMM", "tc05")
     from katz_b200 import ops
