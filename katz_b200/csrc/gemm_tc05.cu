@@ -185,9 +185,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
     if (PAIR) cluster_sync_all();      // the peer's barriers are initialised before anything signals them
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    // everything above (barriers, TMEM, descriptor prefetch) may overlap the previous kernel's tail; global memory waits
-    pdl_wait();
-    pdl_launch_dependents();
+    // Everything above (barriers, TMEM, descriptor prefetch) and each role's index arithmetic may overlap the previous
+    // kernel's tail: the roles call pdl_wait() themselves, right before their first global-memory access (the MMA
+    // thread touches none).
 
     if (warp == 0) {
         // ------------------------------------------------------------------------------------ TMA producer
@@ -212,6 +212,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { ok = false; break; }
                     const uint32_t sa = smem_base + s * STAGE_BYTES;
+                    if (it == 0) {
+                        pdl_wait();                 // the first load: the kernels this launch depends on are done
+                        pdl_launch_dependents();
+                    }
                     if constexpr (PAIR) {
                         // both CTAs' bytes are counted on the leader's barrier, which the leader arms for both
                         const uint32_t fb = mapa_shared(full0 + 8 * s, 0);
@@ -314,6 +318,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
         const uint32_t swz = (uint32_t)((lane >> 1) & 3);      // 64-byte swizzle: 16-byte chunk index ^ ((row >> 1) & 3)
         bool ok = true;
         uint32_t t = 0, rpar = 0;               // tiles done by the CTA; parity bit per residual box of this warp
+        pdl_wait();                             // bias, row vector and residual are global reads
         for (int tile = item0; tile < total_tiles && ok; tile += item_stride, ++t) {
             const uint32_t buf = t & 1;
             const int mi = tile / p.n_tiles, nt = tile - mi * p.n_tiles;
@@ -468,7 +473,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                 else mbar_arrive(tempty0 + 8 * buf);
             }
         }
-        if (lane == 0) bulk_wait<0>();          // every store has left shared memory and reached global memory
+        if (lane == 0) bulk_wait_read<0>();     // every store has read its box (the writes complete with the kernel)
     }
     // ---------------------------------------------------------------------------------------- teardown
     fence_before_sync();
