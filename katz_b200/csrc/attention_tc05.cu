@@ -116,15 +116,16 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tc05_kernel(const __g
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    // everything above (barriers, TMEM, descriptor prefetch) may overlap the previous kernel's tail; global memory waits
-    pdl_wait();
-    pdl_launch_dependents();
+    // Everything above (barriers, TMEM, descriptor prefetch) may overlap the previous kernel's tail: the producer and the
+    // softmax warps call pdl_wait() themselves before their first global-memory access (the MMA thread touches none).
     const uint32_t tS0 = tmem_base, tO = tmem_base + 128;      // S at columns 0..127, O at 128..191
 
     if (warp == 0) {
         // ------------------------------------------------------------------------------------ TMA producer
         if (elect_one()) {
             bool ok = true;
+            pdl_wait();
+            pdl_launch_dependents();
             mbar_expect_tx(q_full, FA_TILE);
             tma_load_4d_fa(sQ, &tmQ, h * FA_D, q0, b, 0, q_full);
             for (int j = 0; j < NT && ok; ++j) {
@@ -190,6 +191,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tc05_kernel(const __g
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
         float m_used = -INFINITY, l_sum = 0.f;
         bool ok = true;
+        pdl_wait();      // O is written at the end; nothing of this kernel may reach global memory before the previous one is done
         for (int j = 0; j < NT; ++j) {
             ok = mbar_wait(s_full, j & 1);
             ok = __all_sync(0xffffffffu, ok);
