@@ -188,4 +188,6 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2 and not os.environ.get("KATZ_REFERENCE_ROOT"):
+        raise SystemExit("usage: python tests/golden/make_golden.py <path of a checkout of the reference project>")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["KATZ_REFERENCE_ROOT"])
