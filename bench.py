@@ -184,6 +184,8 @@ def main():
                     help="launch the dominant linear GEMM shapes between cudaProfilerStart/Stop and exit")
     ap.add_argument("--profile-attn", action="store_true",
                     help="run the two self-attention shapes of the step under cudaProfilerStart/Stop (for ncu) and exit")
+    ap.add_argument("--compare-cublas", action="store_true",
+                    help="time the step's linear shapes against torch.addmm (cuBLAS) in CUDA graphs of 20 launches and exit")
     ap.add_argument("--profile-merge", action="store_true",
                     help="run ONE LoRA merge over a reduced layer set between cudaProfilerStart/Stop and exit")
     ap.add_argument("--parallel", default="auto", choices=["auto", "rows"],
@@ -236,6 +238,35 @@ def main():
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
         print(json.dumps({"profiled": "linear GEMMs", "shapes": shapes, "kernel": ops.gemm_kernel_name()}))
+        return
+    if args.compare_cublas:
+        def graph_time(fn, n=20):
+            for _ in range(3):
+                fn(0)
+            torch.cuda.synchronize()
+            gr, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+            with torch.cuda.stream(st):
+                fn(0)
+                with torch.cuda.graph(gr, stream=st):
+                    for i in range(n):
+                        fn(i)
+            torch.cuda.synchronize()
+            gr.replay()
+            return time_events(gr.replay, 3) * 1e3 / n
+        rows = []
+        for (M, N, K) in [(2048, 10240, 1280), (2048, 1280, 1280), (2048, 3840, 1280), (2048, 1280, 5120), (8192, 640, 640),
+                          (8192, 5120, 640), (1024, 1280, 1280), (8192, 8192, 4096)]:
+            nw = 6 if N * K < 3e7 else 2          # distinct weights per launch: they are cold in the step, too
+            x = torch.randn(M, K, device=dev).half()
+            ws = [(torch.randn(N, K, device=dev) * 0.03).half() for _ in range(nw)]
+            b = torch.randn(N, device=dev).half()
+            o = torch.empty(M, N, dtype=torch.float16, device=dev)
+            tk = graph_time(lambda i: ops.linear(x, ws[i % nw], b, out=o))
+            tc = graph_time(lambda i: torch.addmm(b, x, ws[i % nw].t(), out=o))
+            fl = 2.0 * M * N * K
+            rows.append({"shape": [M, N, K], "katz_us": round(tk, 1), "katz_tflops": round(fl / tk / 1e6),
+                         "cublas_us": round(tc, 1), "cublas_tflops": round(fl / tc / 1e6)})
+        print(json.dumps({"compared": "linear + bias, fp16, CUDA graph of 20 launches", "rows": rows}))
         return
     if args.profile_attn:
         # self-attention of the 32x32 level (20 heads, 1024 tokens) and of the 64x64 level (10 heads, 4096 tokens)
