@@ -88,9 +88,10 @@ __device__ __forceinline__ float gelu_erf_fast(float x) {
 
 __device__ __forceinline__ float rhalf(float v) { return __half2float(__float2half_rn(v)); }
 
-// One thread's 32 accumulator columns of a chunk -> its 64-byte row of the box: + bias + row vector (zeros when the
-// layer has none), SiLU, + residual (already in the box), * scale, rounded to fp16.
-template <bool ACT, bool RES>
+// One thread's 32 accumulator columns of a chunk -> its 64-byte row of the box: + bias, + row vector (AUX), SiLU (ACT),
+// + residual (RES, already in the box), * scale, rounded to fp16. The options are compile-time so that the body is
+// straight-line code without the conversions and additions of absent terms.
+template <bool ACT, bool RES, bool AUX>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t* r, unsigned char* rowp, uint32_t swz, const uint4* b4,
                                                const uint4* v4, float out_scale) {
 #pragma unroll
@@ -103,8 +104,13 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t* r, unsigned char*
         uint32_t ow[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const float2 bf = unpack_half2(bw[e]), vf = unpack_half2(vw[e]);
-            float v0 = (__uint_as_float(r[k * 8 + 2 * e]) + bf.x) + vf.x, v1 = (__uint_as_float(r[k * 8 + 2 * e + 1]) + bf.y) + vf.y;
+            const float2 bf = unpack_half2(bw[e]);
+            float v0 = __uint_as_float(r[k * 8 + 2 * e]) + bf.x, v1 = __uint_as_float(r[k * 8 + 2 * e + 1]) + bf.y;
+            if (AUX) {
+                const float2 vf = unpack_half2(vw[e]);
+                v0 += vf.x;
+                v1 += vf.y;
+            }
             if (ACT) {
                 v0 = silu_f(v0);
                 v1 = silu_f(v1);
@@ -449,12 +455,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                 } else {
                     tmem_ld_wait();
                     // act and residual are uniform over the launch: one branch per chunk picks a straight-line body
+                    // (SiLU only follows the tiny embedding GEMMs: it keeps the general body)
                     if (p.act == 1) {
-                        if (has_res) epilogue_chunk<true, true>(r, rowp, swz, cb4, cv4, p.out_scale);
-                        else epilogue_chunk<true, false>(r, rowp, swz, cb4, cv4, p.out_scale);
+                        if (has_res) epilogue_chunk<true, true, true>(r, rowp, swz, cb4, cv4, p.out_scale);
+                        else epilogue_chunk<true, false, true>(r, rowp, swz, cb4, cv4, p.out_scale);
+                    } else if (aux_p) {
+                        if (has_res) epilogue_chunk<false, true, true>(r, rowp, swz, cb4, cv4, p.out_scale);
+                        else epilogue_chunk<false, false, true>(r, rowp, swz, cb4, cv4, p.out_scale);
                     } else {
-                        if (has_res) epilogue_chunk<false, true>(r, rowp, swz, cb4, cv4, p.out_scale);
-                        else epilogue_chunk<false, false>(r, rowp, swz, cb4, cv4, p.out_scale);
+                        if (has_res) epilogue_chunk<false, true, false>(r, rowp, swz, cb4, cv4, p.out_scale);
+                        else epilogue_chunk<false, false, false>(r, rowp, swz, cb4, cv4, p.out_scale);
                     }
                 }
                 fence_proxy_async();            // this thread's row of the box -> visible to the TMA store
