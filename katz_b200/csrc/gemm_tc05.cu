@@ -161,21 +161,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
     const int item_stride = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     const int total_tiles = (PAIR ? (p.m_tiles + 1) / 2 : p.m_tiles) * p.n_tiles;      // work items
 
-    if (threadIdx.x == 0) {
-        tma_prefetch_desc(&tmA);
-        tma_prefetch_desc(&tmB);
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, 1);
+    // barrier set-up spread over the lanes of warp 0 (about forty barriers; one thread took half a microsecond)
+    if (warp == 0) {
+        constexpr int NBAR = 2 * STAGES + 4 + EPI_BOXES;
+        for (int i = lane; i < NBAR; i += 32) {
+            // full / empty / accumulator full / residual box: one arrival; accumulator free: one per epilogue warp (of
+            // both CTAs of a pair)
+            const bool acc_free = i >= 2 * STAGES + 2 && i < 2 * STAGES + 4;
+            mbar_init(smem_u32(bars + i), acc_free ? EPI_WARPS * (PAIR ? 2 : 1) : 1);
         }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(tfull0 + 8 * b, 1);
-            mbar_init(tempty0 + 8 * b, EPI_WARPS * (PAIR ? 2 : 1));    // one arrival per epilogue warp (of both CTAs)
-        }
-        for (int b = 0; b < EPI_BOXES; ++b) mbar_init(smem_u32(bars + 2 * STAGES + 4 + b), 1);   // residual boxes
-        tma_prefetch_desc(&tmC);
-        if (p.residual) tma_prefetch_desc(&tmR);
         fence_barrier_init();
+        if (lane == 0) {
+            tma_prefetch_desc(&tmA);
+            tma_prefetch_desc(&tmB);
+            tma_prefetch_desc(&tmC);
+            if (p.residual) tma_prefetch_desc(&tmR);
+        }
     }
     if (warp == 1) {
         if (PAIR) {
