@@ -24,12 +24,22 @@ namespace katz {
 
 using namespace tc05;
 
-constexpr int FA_BM = 128, FA_BN = 128, FA_D = 64, FA_ST = 2;
+// Key tile: 128 keys with two CTAs per SM. (64 keys with three CTAs per SM compiles too, -DKATZ_FA_BN=64, and measured
+// 25-40% slower: the per-tile barrier round trips do not shrink with the tile.)
+#ifndef KATZ_FA_BN
+#define KATZ_FA_BN 128
+#endif
+constexpr int FA_BM = 128, FA_BN = KATZ_FA_BN, FA_D = 64, FA_ST = 2;
+static_assert(FA_BN == 64 || FA_BN == 128, "key tile");
+constexpr int FA_CTAS_PER_SM = FA_BN == 64 ? 3 : 2;
 constexpr int FA_THREADS = 192;
-constexpr int FA_TILE = 128 * 128;                     // bytes of a 128-row x 64-half tile
-constexpr int FA_TMEM_COLS = 256;                      // S at columns 0..127, O at 128..191
-constexpr int FA_SMEM = FA_TILE * (1 + 2 * FA_ST + 2) + 256;     // Q, K ring, V ring, P (two 64-key sub-tiles), barriers
-static_assert(2 * (FA_SMEM + 1024) <= 228 * 1024, "two CTAs must fit one SM");
+constexpr int FA_TILE = 128 * 128;                     // bytes of a 128-row x 64-half tile (Q; one 64-key sub-tile of P)
+constexpr int FA_KV_TILE = FA_BN * 128;                // bytes of a key or value tile
+constexpr int FA_P_BYTES = FA_BM * FA_BN * 2;          // P: FA_BN / 64 sub-tiles of 128 rows x 64 keys
+constexpr int FA_TMEM_COLS = FA_BN == 64 ? 128 : 256;  // S at columns 0..FA_BN-1, O in the 64 columns after it
+constexpr int FA_SMEM = FA_TILE + 2 * FA_ST * FA_KV_TILE + FA_P_BYTES + 256;     // Q, K ring, V ring, P, barriers
+static_assert(FA_CTAS_PER_SM * (FA_SMEM + 1024) <= 228 * 1024, "the CTAs of one SM must fit its shared memory");
+static_assert(FA_CTAS_PER_SM * FA_TMEM_COLS <= 512, "and its tensor memory");
 constexpr float FA_RESCALE_THRESHOLD = 8.0f;           // log2 units
 
 int* tc05_status_device_ptr();   // defined next to the status word (gemm_tc05.cu)
@@ -66,7 +76,7 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 // kind::f16 instruction descriptor with an MN-major B operand (bit 16)
 __host__ __device__ constexpr uint32_t idesc_f16_bmn(int M, int N) { return idesc_f16(M, N) | (1u << 16); }
 
-__global__ void __launch_bounds__(FA_THREADS, 2) attention_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
+__global__ void __launch_bounds__(FA_THREADS, FA_CTAS_PER_SM) attention_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
                                                                        const __grid_constant__ CUtensorMap tmK,
                                                                        const __grid_constant__ CUtensorMap tmV, const FaParams p) {
     // the 128-byte swizzle wants 1024-byte aligned tiles; there is no room for alignment slack when two CTAs share an
@@ -77,9 +87,9 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tc05_kernel(const __g
         return;
     }
     const uint32_t sQ = smem_u32(smem);
-    const uint32_t sK0 = sQ + FA_TILE, sV0 = sK0 + FA_ST * FA_TILE, sP0 = sV0 + FA_ST * FA_TILE;   // sP: two 64-key sub-tiles
-    unsigned char* sP_gen = smem + FA_TILE * (1 + 2 * FA_ST);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FA_TILE * (1 + 2 * FA_ST + 2));
+    const uint32_t sK0 = sQ + FA_TILE, sV0 = sK0 + FA_ST * FA_KV_TILE, sP0 = sV0 + FA_ST * FA_KV_TILE;
+    unsigned char* sP_gen = smem + FA_TILE + 2 * FA_ST * FA_KV_TILE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sP_gen + FA_P_BYTES);
     // barrier map
     const uint32_t b0 = smem_u32(bars);
     const uint32_t q_full = b0, k_full = b0 + 8, k_empty = k_full + 8 * FA_ST, v_full = k_empty + 8 * FA_ST,
@@ -118,7 +128,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tc05_kernel(const __g
     const uint32_t tmem_base = *tmem_slot;
     // Everything above (barriers, TMEM, descriptor prefetch) may overlap the previous kernel's tail: the producer and the
     // softmax warps call pdl_wait() themselves before their first global-memory access (the MMA thread touches none).
-    const uint32_t tS0 = tmem_base, tO = tmem_base + 128;      // S at columns 0..127, O at 128..191
+    const uint32_t tS0 = tmem_base, tO = tmem_base + FA_BN;      // S at columns 0..FA_BN-1, O right after it
 
     if (warp == 0) {
         // ------------------------------------------------------------------------------------ TMA producer
@@ -134,11 +144,11 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tc05_kernel(const __g
                 const int key0 = j * FA_BN;
                 const int chunk = key0 / p.kv_chunk_rows, row = key0 - chunk * p.kv_chunk_rows;
                 if (!mbar_wait(k_empty + 8 * s, ph ^ 1)) { ok = false; break; }
-                mbar_expect_tx(k_full + 8 * s, FA_TILE);
-                tma_load_4d_fa(sK0 + s * FA_TILE, &tmK, h * FA_D, row, b, chunk, k_full + 8 * s);
+                mbar_expect_tx(k_full + 8 * s, FA_KV_TILE);
+                tma_load_4d_fa(sK0 + s * FA_KV_TILE, &tmK, h * FA_D, row, b, chunk, k_full + 8 * s);
                 if (!mbar_wait(v_empty + 8 * s, ph ^ 1)) { ok = false; break; }
-                mbar_expect_tx(v_full + 8 * s, FA_TILE);
-                tma_load_4d_fa(sV0 + s * FA_TILE, &tmV, h * FA_D, row, b, chunk, v_full + 8 * s);
+                mbar_expect_tx(v_full + 8 * s, FA_KV_TILE);
+                tma_load_4d_fa(sV0 + s * FA_KV_TILE, &tmV, h * FA_D, row, b, chunk, v_full + 8 * s);
             }
             if (!ok) atomicExch(p.status, 11);
         }
@@ -153,7 +163,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tc05_kernel(const __g
                 if (!mbar_wait(k_full + 8 * s, (j / FA_ST) & 1)) return false;
                 if (!mbar_wait(s_free, (j & 1) ^ 1)) return false;       // the softmax holds tile j-1's scores in registers
                 fence_after_sync();
-                const uint64_t ad = smem_desc_sw128(sQ), bd = smem_desc_sw128(sK0 + s * FA_TILE);
+                const uint64_t ad = smem_desc_sw128(sQ), bd = smem_desc_sw128(sK0 + s * FA_KV_TILE);
 #pragma unroll
                 for (int k = 0; k < FA_D / 16; ++k) umma_f16(tS0, ad + 2 * k, bd + 2 * k, idesc_qk, k != 0);
                 umma_commit(s_full);
@@ -170,7 +180,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tc05_kernel(const __g
                 if (!mbar_wait(p_full, j & 1)) { ok = false; break; }
                 if (!mbar_wait(v_full + 8 * s, (j / FA_ST) & 1)) { ok = false; break; }
                 fence_after_sync();
-                const uint32_t pa = sP0, va = sV0 + s * FA_TILE;
+                const uint32_t pa = sP0, va = sV0 + s * FA_KV_TILE;
 #pragma unroll
                 for (int k = 0; k < FA_BN / 16; ++k) {
                     // A = P: two 64-key sub-tiles, +32 B per 16-key step inside a sub-tile.
@@ -338,12 +348,12 @@ static FaEncodeFn fa_encode_fn() {
 
 // [chunks][B][rows][cols] view of a token-major buffer: box = 64 columns x 128 rows
 static int fa_encode(CUtensorMap* map, const void* base, int cols, long long rows, int B, int chunks, long long ld,
-                     long long bs, long long chunk_stride) {
+                     long long bs, long long chunk_stride, int box_rows) {
     FaEncodeFn enc = fa_encode_fn();
     if (!enc) return KATZ_ENOTREADY;
     cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)B, (cuuint64_t)chunks};
     cuuint64_t strides[3] = {(cuuint64_t)ld * 2, (cuuint64_t)bs * 2, (cuuint64_t)chunk_stride * 2};
-    cuuint32_t box[4] = {(cuuint32_t)FA_D, (cuuint32_t)FA_BN, 1, 1};
+    cuuint32_t box[4] = {(cuuint32_t)FA_D, (cuuint32_t)box_rows, 1, 1};
     cuuint32_t es[4] = {1, 1, 1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, es,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -381,11 +391,11 @@ extern "C" int katz_attention_f16(const void* Q, const void* K, const void* V, v
     const long long bsq_e = B > 1 ? bsq : (long long)Sq * ldq, bsk_e = B > 1 ? bsk : rows * ldk, bsv_e = B > 1 ? bsv : rows * ldv;
     KATZ_CHECK_ARG(bsq_e > 0 && bsk_e > 0 && bsv_e > 0, KATZ_ESIZE);
     CUtensorMap tq, tk, tv;
-    int rc = fa_encode(&tq, Q, H * 64, Sq, B, 1, ldq, bsq_e, bsq_e * B);
+    int rc = fa_encode(&tq, Q, H * 64, Sq, B, 1, ldq, bsq_e, bsq_e * B, FA_BM);
     if (rc) return rc;
-    rc = fa_encode(&tk, K, H * 64, rows, B, chunks, ldk, bsk_e, chunks > 1 ? cstride : bsk_e * B);
+    rc = fa_encode(&tk, K, H * 64, rows, B, chunks, ldk, bsk_e, chunks > 1 ? cstride : bsk_e * B, FA_BN);
     if (rc) return rc;
-    rc = fa_encode(&tv, V, H * 64, rows, B, chunks, ldv, bsv_e, chunks > 1 ? cstride : bsv_e * B);
+    rc = fa_encode(&tv, V, H * 64, rows, B, chunks, ldv, bsv_e, chunks > 1 ? cstride : bsv_e * B, FA_BN);
     if (rc) return rc;
     FaParams p{};
     p.O = (__half*)O; p.Sq = Sq; p.Sk = Sk; p.ldo = ldo; p.bso = bso;
