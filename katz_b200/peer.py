@@ -97,6 +97,18 @@ class PeerArena:
                   self.world, st)
         return self.local[off:off + self.world * nb].view(src.dtype).view((self.world,) + tuple(src.shape))
 
+    def close(self):
+        """Unmap the peers' arenas and free this rank's. Collective in effect: call it on every rank, after a
+        synchronisation, when no kernel that uses the arena is in flight or captured in a live CUDA graph."""
+        lib = _lib.load()
+        for p in self._opened:
+            lib.katz_peer_ipc_close(ctypes.c_void_p(p))
+        self._opened = []
+        if self._ptr:
+            self.local = None
+            lib.katz_peer_arena_free(ctypes.c_void_p(self._ptr))
+            self._ptr = 0
+
     def status(self):
         """0, or 100 + the rank whose block never arrived within the bounded wait. Synchronises the device."""
         return _lib.load().katz_peer_status(ctypes.c_void_p(self._ptr))
