@@ -437,9 +437,9 @@ def main():
                 "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"],
                 "peak_source": peaks["_source"] + " burst", "launch_ms": gemm_ms,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape, from the ncu capture summarised
-                # in profiles/tc05_gemm_linear_2048x10240x1280.md (31.55 MB + 8.04 MB; algorithmic bytes 73.4 MB, the
+                # in profiles/tc05_gemm_linear_2048x10240x1280.md (31.81 MB + 8.74 MB; algorithmic bytes 73.4 MB, the
                 # output is still in L2 when the launch ends)
-                "traffic": 39593216 if (M, N, K) == (2048, 10240, 1280) else None, "traffic_unit": "bytes"}
+                "traffic": 40551168 if (M, N, K) == (2048, 10240, 1280) else None, "traffic_unit": "bytes"}
 
     if rank == 0:
         step_tflops = flops["total"] / world / (ms * 1e-3) / 1e12
