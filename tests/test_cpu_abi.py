@@ -65,3 +65,16 @@ def test_euler_schedule_host_mirror(golden_dir):
     assert abs(s.init_noise_sigma - float(g["init_noise_sigma"])) < 1e-6
     with pytest.raises(NotImplementedError):
         EulerSchedule(beta_schedule="squaredcos_cap_v2")
+
+
+def test_binding_arity_matches_the_header():
+    """Every ctypes signature has as many arguments as the header's prototype (a drifted binding corrupts the call)."""
+    from katz_b200 import _lib
+    text = open(os.path.join(ROOT, "include", "katz_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    protos = dict(re.findall(r"\b(katz_[a-z0-9_]+)\s*\(([^;{]*?)\)\s*;", text, flags=re.S))
+    assert set(protos) == set(_lib.SIGNATURES)
+    for name, params in protos.items():
+        params = params.strip()
+        n = 0 if params in ("", "void") else len([p for p in params.split(",") if p.strip()])
+        assert n == len(_lib.SIGNATURES[name][1]), "%s: header has %d parameters, binding %d" % (name, n, len(_lib.SIGNATURES[name][1]))
