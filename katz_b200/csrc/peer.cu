@@ -79,7 +79,10 @@ extern "C" int katz_peer_arena_alloc(long long bytes, void** ptr) {
     KATZ_CHECK_ARG(bytes > PEER_CTRL_BYTES, KATZ_ESIZE);
     void* p = nullptr;
     cudaError_t e = cudaMalloc(&p, (size_t)bytes);
-    if (e != cudaSuccess) return (int)e;
+    if (e != cudaSuccess) {
+        cudaGetLastError();      // a failed allocation is the caller's to handle: do not leave it for the next launch check
+        return (int)e;
+    }
     e = cudaMemset(p, 0, PEER_CTRL_BYTES);
     if (e != cudaSuccess) return (int)e;
     *ptr = p;
@@ -98,7 +101,10 @@ extern "C" int katz_peer_ipc_export(void* ptr, void* handle_out) {
     KATZ_CHECK_ARG(ptr && handle_out, KATZ_EINVAL);
     cudaIpcMemHandle_t h;
     cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
-    if (e != cudaSuccess) return (int)e;
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return (int)e;
+    }
     memcpy(handle_out, &h, sizeof(h));
     return KATZ_OK;
 }
@@ -109,7 +115,10 @@ extern "C" int katz_peer_ipc_open(const void* handle, void** ptr) {
     memcpy(&h, handle, sizeof(h));
     void* p = nullptr;
     cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
-    if (e != cudaSuccess) return (int)e;
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return (int)e;
+    }
     *ptr = p;
     return KATZ_OK;
 }

@@ -180,7 +180,10 @@ class RowParallelStep:
                 raise KatzError("latent height %d cannot be row-split over %d ranks at every UNet level" % (height, world))
         if world > 1 and unet.device.type == "cuda" and os.environ.get("KATZ_PEER", "1") != "0":
             from .peer import PeerArena
-            rp.peer = PeerArena(rank, world, group=group, device=unet.device)
+            try:
+                rp.peer = PeerArena(rank, world, group=group, device=unet.device)
+            except KatzError:
+                rp.peer = None          # every rank reached the same verdict: the exchanges go through torch.distributed
         unet.rp = rp
         self.rp = rp
         self._inner = GraphedStep(unet, batch, height, width, text_len=text_len, warmup=warmup)

@@ -32,26 +32,37 @@ class PeerArena:
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.nbytes = int(nbytes if nbytes is not None else os.environ.get("KATZ_PEER_ARENA_BYTES", 1 << 30))
         self.ctrl = lib.katz_peer_ctrl_bytes()
+        # Every rank takes part in every collective below whatever happened locally, and all ranks reach the same verdict:
+        # a rank that cannot allocate, export or map sends that fact along instead of leaving the others waiting.
         ptr = ctypes.c_void_p()
+        self._ptr, self._opened = 0, []
         with torch.cuda.device(self.device):
-            _lib.check(lib.katz_peer_arena_alloc(self.nbytes, ctypes.byref(ptr)), "katz_peer_arena_alloc")
             hb = lib.katz_peer_ipc_handle_bytes()
             handle = ctypes.create_string_buffer(hb)
-            _lib.check(lib.katz_peer_ipc_export(ptr, handle), "katz_peer_ipc_export")
+            mine = None
+            if lib.katz_peer_arena_alloc(self.nbytes, ctypes.byref(ptr)) == 0:
+                self._ptr = ptr.value
+                if lib.katz_peer_ipc_export(ptr, handle) == 0:
+                    mine = bytes(handle.raw)
             handles = [None] * world
-            dist.all_gather_object(handles, bytes(handle.raw), group=group)
-            self._ptr = ptr.value
-            self._opened = []
-            bases = []
-            for r in range(world):
-                if r == rank:
-                    bases.append(self._ptr)
-                    continue
-                p = ctypes.c_void_p()
-                _lib.check(lib.katz_peer_ipc_open(ctypes.create_string_buffer(handles[r], hb), ctypes.byref(p)),
-                           "katz_peer_ipc_open(rank %d)" % r)
-                self._opened.append(p.value)
-                bases.append(p.value)
+            dist.all_gather_object(handles, mine, group=group)
+            bases, ok = [], all(h is not None for h in handles)
+            if ok:
+                for r in range(world):
+                    if r == rank:
+                        bases.append(self._ptr)
+                        continue
+                    p = ctypes.c_void_p()
+                    if lib.katz_peer_ipc_open(ctypes.create_string_buffer(handles[r], hb), ctypes.byref(p)) != 0:
+                        ok = False
+                        break
+                    self._opened.append(p.value)
+                    bases.append(p.value)
+            verdict = [None] * world
+            dist.all_gather_object(verdict, bool(ok), group=group)
+            if not all(verdict):
+                self.close()
+                raise KatzError("peer arenas could not be set up on every rank (allocation, IPC export or mapping failed)")
         self.bases = (ctypes.c_ulonglong * world)(*bases)
         self.local = torch.as_tensor(_Raw(self._ptr, self.nbytes), device=self.device)      # uint8 view of this rank's arena
         self._slots = []          # (offset, bytes) per call site of a step, in call order
@@ -106,6 +117,7 @@ class PeerArena:
         self._opened = []
         if self._ptr:
             self.local = None
+            torch.cuda.synchronize(self.device)
             lib.katz_peer_arena_free(ctypes.c_void_p(self._ptr))
             self._ptr = 0
 
