@@ -110,8 +110,12 @@ int katz_group_norm_apply_nhwc_f16(const void* x, void* y, const double* sums, i
  *   - The first call on each device looks up the array's device address (that device must be current); make that
  *     first call outside any stream capture.
  *   - All calls on a device share the one array: calls that may overlap on the GPU (different streams without an
- *     ordering between them) race. Nothing has to be cleared between calls — each call overwrites what it reads. */
+ *     ordering between them) race. Calls that are ordered need nothing cleared between them: each overwrites what it
+ *     reads and leaves the ticket counters at the head of the array at zero. After such a race, or after a launch
+ *     that was aborted, the counters may be left non-zero and later calls would then be wrong: call
+ *     katz_group_norm_static_scratch_reset(stream) (a 1 KiB memset in stream order; it allocates nothing either). */
 long long katz_group_norm_static_scratch_bytes(void);
+int katz_group_norm_static_scratch_reset(void* stream);
 int katz_group_norm_nhwc_f16_noalloc(const void* x, void* y, const void* gamma, const void* beta, int B, int HW, int C,
                                      int G, float eps, int act, void* stream);
 /* Same op for a channels-first tensor (the `channels_first` branch of group_norm.cu:162-206). */

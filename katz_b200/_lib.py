@@ -61,6 +61,7 @@ SIGNATURES = {
     "katz_group_norm_stats_nhwc_f16": (_I, [_V, _V, _I, _I, _I, _I, _V, _L, _V]),
     "katz_group_norm_apply_nhwc_f16": (_I, [_V, _V, _V, _I, _V, _V, _I, _I, _I, _I, ctypes.c_double, _F, _I, _V]),
     "katz_group_norm_static_scratch_bytes": (_L, []),
+    "katz_group_norm_static_scratch_reset": (_I, [_V]),
     "katz_group_norm_nhwc_f16_noalloc": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _F, _I, _V]),
     "katz_group_norm_nchw_f16": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _F, _I, _V]),
     "katz_fast_gelu_mul_f16": (_I, [_V, _V, _V, _L, _V]),

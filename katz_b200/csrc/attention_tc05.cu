@@ -157,6 +157,7 @@ __global__ void __launch_bounds__(FA_THREADS, FA_CTAS_PER_SM) attention_tc05_ker
         if (elect_one()) {
             constexpr uint32_t idesc_qk = idesc_f16(FA_BM, FA_BN);
             constexpr uint32_t idesc_pv = idesc_f16_bmn(FA_BM, FA_D);
+            pdl_wait();      // the bounded waits below must not count polls while the producer still waits for the dependency
             bool ok = mbar_wait(q_full, 0);
             auto issue_qk = [&](int j) -> bool {
                 const int s = j % FA_ST;
@@ -403,7 +404,8 @@ extern "C" int katz_attention_f16(const void* Q, const void* K, const void* V, v
     p.kv_chunk_rows = kv_chunk_rows;
     p.status = tc05_status_device_ptr();
     if (!p.status) return KATZ_ENOTREADY;
-    static bool attr = false;
+    static bool attr_dev[KATZ_MAX_DEVICES] = {false};
+    bool& attr = attr_dev[current_device_index()];
     if (!attr) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM);
         if (e != cudaSuccess) return (int)e;

@@ -88,6 +88,15 @@ inline void launch_k_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
     cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);      // the caller reads cudaGetLastError()
 }
 
+// One-time set-up that belongs to a DEVICE (cudaFuncSetAttribute, symbol addresses, occupancy queries) is cached per
+// device ordinal, not per process: a second GPU used from the same process gets its own set-up.
+constexpr int KATZ_MAX_DEVICES = 64;
+inline int current_device_index() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= KATZ_MAX_DEVICES) d = 0;
+    return d;
+}
+
 __host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 __host__ __device__ inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }
 

@@ -222,7 +222,8 @@ __global__ void __launch_bounds__(NTHREADS) igemm_kernel(const IgemmParams p) {
 }
 
 static int launch_igemm(const IgemmParams& p, bool conv, cudaStream_t st) {
-    static bool attr_set = false;
+    static bool attr_dev[KATZ_MAX_DEVICES] = {false};
+    bool& attr_set = attr_dev[current_device_index()];
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(igemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, IGEMM_SMEM);
         if (e != cudaSuccess) return (int)e;

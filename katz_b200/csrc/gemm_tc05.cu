@@ -276,6 +276,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
             constexpr uint32_t idesc = idesc_f16(PAIR ? 2 * TBM : TBM, BN);
             bool ok = true;
             uint32_t it = 0, t = 0;
+            // no global access here, but the bounded waits below count polls: they must not start counting while the
+            // kernels this launch depends on (which the producer waits for) may still run for a long time
+            pdl_wait();
             for (int tile = item0; tile < total_tiles && ok; tile += item_stride, ++t) {
                 const uint32_t buf = t & 1;
                 if (!mbar_wait(tempty0 + 8 * buf, ((t >> 1) & 1) ^ 1)) { ok = false; break; }
@@ -579,8 +582,11 @@ static constexpr int tc05_smem() {
 template <int BN, int STAGES, bool GEGLU, bool PAIR>
 static int launch_tc05(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const CUtensorMap& r,
                        const Tc05Params& p, cudaStream_t st) {
-    static bool attr = false;
-    static int max_ctas = 0;
+    static bool attr_dev[KATZ_MAX_DEVICES] = {false};
+    static int max_ctas_dev[KATZ_MAX_DEVICES] = {0};
+    const int dev_index = current_device_index();
+    bool& attr = attr_dev[dev_index];
+    int& max_ctas = max_ctas_dev[dev_index];
     constexpr int smem = tc05_smem<BN, STAGES, GEGLU, PAIR>();
     static_assert(smem <= 232448, "shared memory budget");
     auto kernel = tc05_gemm_kernel<BN, STAGES, GEGLU, PAIR>;
@@ -616,7 +622,8 @@ static int launch_tc05(const CUtensorMap& a, const CUtensorMap& b, const CUtenso
 }
 
 static int* status_ptr() {
-    static int* ptr = nullptr;
+    static int* ptr_dev[KATZ_MAX_DEVICES] = {nullptr};      // the symbol has one address per device
+    int*& ptr = ptr_dev[current_device_index()];
     if (!ptr) {
         void* p = nullptr;
         if (cudaGetSymbolAddress(&p, g_tc05_status) == cudaSuccess) ptr = (int*)p;

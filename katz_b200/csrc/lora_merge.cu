@@ -863,7 +863,8 @@ extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_til
     KATZ_CHECK_ARG(w_dtype == KATZ_DTYPE_F16 || w_dtype == KATZ_DTYPE_F32, KATZ_EINVAL);
     KATZ_CHECK_ARG(sign == 1.0f || sign == -1.0f, KATZ_EINVAL);
     cudaStream_t st = (cudaStream_t)stream;
-    static bool attr_set = false;
+    static bool attr_set_dev[KATZ_MAX_DEVICES] = {false};
+    bool& attr_set = attr_set_dev[current_device_index()];
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(lora_merge_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, LmCfg<__half>::SMEM);
         if (e != cudaSuccess) return (int)e;
@@ -880,7 +881,8 @@ extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_til
     }
     if (w_dtype == KATZ_DTYPE_F16 && use_tc05 && (flags & KATZ_LORA_UNIFORM_TILES) && d_tile_maps) {
         KATZ_CHECK_ARG((reinterpret_cast<uintptr_t>(d_tile_maps) & 63) == 0, KATZ_EALIGN);
-        static bool attr3 = false;
+        static bool attr3_dev[KATZ_MAX_DEVICES] = {false};
+        bool& attr3 = attr3_dev[current_device_index()];
         if (!attr3) {
             cudaError_t e = cudaFuncSetAttribute(lora_merge_f16_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WS_SMEM);
             if (e != cudaSuccess) return (int)e;
@@ -892,7 +894,8 @@ extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_til
                                                                     d_tile_start, n_layers, total_tiles, sign, status,
                                                                     (flags & KATZ_LORA_NO_ADAPTERS) ? 1 : WS_CHUNK);
     } else if (w_dtype == KATZ_DTYPE_F16 && use_tc05) {
-        static bool attr2 = false;
+        static bool attr2_dev[KATZ_MAX_DEVICES] = {false};
+        bool& attr2 = attr2_dev[current_device_index()];
         if (!attr2) {
             cudaError_t e = cudaFuncSetAttribute(lora_merge_f16_tc05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  LmCfg<__half>::SMEM + 1024);

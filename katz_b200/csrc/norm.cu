@@ -513,7 +513,8 @@ extern "C" int katz_group_norm_nhwc_f16(const void* x, void* y, const void* gamm
     if (C % 8 == 0 && NC <= 1024 && B <= GN_MAX_TICKETS && aligned16(x) && aligned16(y) && ((uintptr_t)scratch & 255) == 0) {
         const int R = NC >= 512 ? 1 : 512 / NC;
         const int threads = NC * R;
-        static bool attr = false;
+        static bool attr_dev[KATZ_MAX_DEVICES] = {false};
+        bool& attr = attr_dev[current_device_index()];
         if (!attr) {
             cudaFuncSetAttribute(gn_stats_v8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 * 64);
             cudaFuncSetAttribute(gn_apply_v8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 8192 * 4);
@@ -539,7 +540,8 @@ static int gn_v8_setup(int C, int* R, int* threads) {
     if (C % 8 != 0 || NC > 1024) return KATZ_ESIZE;
     *R = NC >= 512 ? 1 : 512 / NC;
     *threads = NC * (*R);
-    static bool attr = false;
+    static bool attr_dev[KATZ_MAX_DEVICES] = {false};
+    bool& attr = attr_dev[current_device_index()];
     if (!attr) {
         cudaFuncSetAttribute(gn_stats_v8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 * 64);
         cudaFuncSetAttribute(gn_apply_v8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 8192 * 4);
@@ -658,6 +660,17 @@ static float* gn_static_scratch_ptr(int* err) {
 }
 
 extern "C" long long katz_group_norm_static_scratch_bytes(void) { return GN_STATIC_SCRATCH_BYTES; }
+
+// The ticket counters at the head of the array come back to zero at the end of every call. Two calls that overlapped on
+// the GPU, or a launch that was aborted, can leave them elsewhere, and every later call would then fold its statistics
+// too early or never: this puts them back to zero, in stream order, without allocating.
+extern "C" int katz_group_norm_static_scratch_reset(void* stream) {
+    int err = 0;
+    float* scratch = gn_static_scratch_ptr(&err);
+    if (!scratch) return err;
+    cudaError_t e = cudaMemsetAsync(scratch, 0, 1024, (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : (int)e;
+}
 
 extern "C" int katz_group_norm_nhwc_f16_noalloc(const void* x, void* y, const void* gamma, const void* beta, int B, int HW,
                                                 int C, int G, float eps, int act, void* stream) {

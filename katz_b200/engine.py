@@ -12,6 +12,22 @@ from .ops import KatzError
 from .unet import NHWC
 
 
+def check_device_status(unet):
+    """The status words the kernels leave behind instead of hanging: tcgen05 pipeline waits (ops.tc05_status) and, when
+    the latent is row-split over peer memory, the all-gather's wait for a peer (PeerArena.status)."""
+    from . import ops
+    st = ops.tc05_status()
+    if st != 0:
+        raise KatzError("a bounded wait inside a tcgen05 kernel gave up (status %d): the step's result is not valid" % st)
+    rp = getattr(unet, "rp", None)
+    peer = getattr(rp, "peer", None) if rp is not None else None
+    if peer is not None:
+        ps = peer.status()
+        if ps != 0:
+            raise KatzError("a peer exchange timed out waiting for rank %d (status %d): the step's result is not valid"
+                            % (ps - 100, ps))
+
+
 class GraphedStep:
     """Static-input wrapper around `unet(...)` (+ optional in-process ControlNets).
 
@@ -21,7 +37,7 @@ class GraphedStep:
     """
 
     def __init__(self, unet, batch, height, width, text_len=77, controlnets=(), conditioning_scales=None,
-                 combine="sum", warmup=2):
+                 combine="sum", warmup=2, hoist=False):
         if combine not in ("sum", "mean"):
             raise KatzError("combine must be 'sum' or 'mean'")
         dev = unet.device
@@ -44,6 +60,19 @@ class GraphedStep:
         self.out = None
         self.graph = None
         self.launches_per_step = 0
+        # hoist: the step-invariant parts (text K/V projection of every net, conditioning embedding of every ControlNet;
+        # the reference recomputes both every step, sdxl_controlnet_server.py:87-100) live in persistent buffers that
+        # `refresh_hoisted` fills outside the graph; the captured step reads them.
+        self.hoist = bool(hoist)
+        self._hoisted = []          # (net, kv buffer or None, conditioning-embedding buffer or None)
+        self._hoist_epochs = None
+        if self.hoist:
+            s = self.static
+            for net in [unet] + self.controlnets:
+                kv = net._cross_kv(s["encoder_hidden_states"])
+                ce = net._cond_embedding(s["controlnet_cond"]) if net is not unet else None
+                self._hoisted.append((net, kv, ce))
+            self._hoist_epochs = [n.weights_epoch for n, _, _ in self._hoisted]
         self._capture(warmup)
 
     def _step(self):
@@ -62,8 +91,33 @@ class GraphedStep:
                          added_cond_kwargs=added, down_block_additional_residuals=down,
                          mid_block_additional_residual=mid, combine_scales=self.combine_scales)[0]
 
+    def _set_hoisted(self, on):
+        for net, kv, ce in self._hoisted:
+            net._hoisted_kv = kv if on else None
+            if ce is not None:
+                net._hoisted_cond = ce if on else None
+
+    def refresh_hoisted(self):
+        """Recompute the hoisted buffers from the static inputs (new prompt, new conditioning image, changed weights)."""
+        if not self.hoist:
+            return
+        s = self.static
+        for net, kv, ce in self._hoisted:
+            if kv is not None:
+                net._cross_kv(s["encoder_hidden_states"], out=kv)
+            if ce is not None:
+                net._cond_embedding(s["controlnet_cond"], out=ce)
+        self._hoist_epochs = [n.weights_epoch for n, _, _ in self._hoisted]
+
     def _capture(self, warmup):
         from . import _lib
+        self._set_hoisted(True)
+        try:
+            self._capture_inner(warmup, _lib)
+        finally:
+            self._set_hoisted(False)      # other callers of these nets keep the reference's per-step semantics
+
+    def _capture_inner(self, warmup, _lib):
         side = torch.cuda.Stream(device=self.unet.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -79,7 +133,10 @@ class GraphedStep:
         self.graph = g
 
     def replay(self):
-        """Run the step on whatever the static input buffers hold."""
+        """Run the step on whatever the static input buffers hold (a caller that wrote a new prompt or conditioning image
+        into them directly calls refresh_hoisted() first; changed weights are noticed here)."""
+        if self.hoist and self._hoist_epochs != [n.weights_epoch for n, _, _ in self._hoisted]:
+            self.refresh_hoisted()
         self.graph.replay()
         return self.out
 
@@ -88,7 +145,14 @@ class GraphedStep:
             if k not in self.static:
                 raise KatzError("unknown input %s" % k)
             self.static[k].copy_(v, non_blocking=True)
+        if self.hoist and ("encoder_hidden_states" in tensors or "controlnet_cond" in tensors):
+            self.refresh_hoisted()
         return self.replay()
+
+    def check(self):
+        """Raise if a bounded device-side wait of the tcgen05 kernels (or, row-split, of a peer exchange) ever gave up:
+        the step then ran on incomplete data. Synchronises the device; call it once per request, not per step."""
+        check_device_status(self.unet)
 
 
 class _GraphedCall:

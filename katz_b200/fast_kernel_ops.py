@@ -13,10 +13,15 @@ import torch
 from . import ops
 from .ops import ACT_NONE, ACT_SILU
 
+# The schemas torch infers from the reference's C++ signatures (group_norm.cuh:7-15, gelu.cuh:44): plain `Tensor`
+# arguments (weight and bias are NOT optional, `y` carries no alias annotation although it is written), registered for
+# every backend at once under CompositeExplicitAutograd as bind.cu:13-14 does.
+GROUP_NORM_SCHEMA = ("group_norm_fp16(Tensor x, Tensor y, float eps, int num_groups, str activation, Tensor weight, "
+                     "Tensor bias, bool affine, bool channels_last) -> ()")
+GELU_MUL_SCHEMA = "fast_gelu_mul_fp16(Tensor x, Tensor m) -> Tensor"
 _lib = torch.library.Library("fast_kernel", "DEF")
-_lib.define("group_norm_fp16(Tensor x, Tensor(a!) y, float eps, int num_groups, str activation, Tensor? weight, "
-            "Tensor? bias, bool affine, bool channels_last) -> ()")
-_lib.define("fast_gelu_mul_fp16(Tensor x, Tensor m) -> Tensor")
+_lib.define(GROUP_NORM_SCHEMA)
+_lib.define(GELU_MUL_SCHEMA)
 
 
 def _group_norm_fp16(x, y, eps, num_groups, activation, weight, bias, affine, channels_last):
@@ -55,5 +60,5 @@ def _fast_gelu_mul_fp16(x, m):
     return ops.fast_gelu_mul(x, m)
 
 
-_lib.impl("group_norm_fp16", _group_norm_fp16, "CUDA")
-_lib.impl("fast_gelu_mul_fp16", _fast_gelu_mul_fp16, "CUDA")
+_lib.impl("group_norm_fp16", _group_norm_fp16, "CompositeExplicitAutograd")
+_lib.impl("fast_gelu_mul_fp16", _fast_gelu_mul_fp16, "CompositeExplicitAutograd")

@@ -197,6 +197,15 @@ class RowParallelStep:
     def run(self, **tensors):
         return self._inner.run(**tensors)
 
+    def check(self):
+        """Raise KatzError if a tcgen05 wait or a peer exchange of this rank ever timed out (see engine.check_device_status).
+        The unet's `rp` may have been replaced since this step was built, so the step's own RowParallel is checked."""
+        from .engine import check_device_status
+
+        class _U:
+            rp = self.rp
+        check_device_status(_U)
+
 
 def cfg_rows_layout(batch, world, rank, split_cfg=True):
     """How `world` ranks share a step of `batch` samples: (halves, rows_world, half, row_rank, local_batch).
@@ -260,6 +269,10 @@ class CfgRowParallelStep:
         lb, h = self.local_batch, self.half
         local = {k: (v if (k == "timestep" or self.halves == 1) else v[h * lb:(h + 1) * lb]) for k, v in tensors.items()}
         return self._finish(self._inner.run(**local))
+
+    def check(self):
+        """Raise KatzError if a bounded device-side wait of this rank's step ever gave up."""
+        self._inner.check()
 
     def _finish(self, o):
         lb = self.local_batch

@@ -1,12 +1,9 @@
 """LoRA merge / restore / unmerge over a set of device-resident linears, one kernel launch per operation.
 
-Entry points mirror the reference's:
-  * `patch_on_lora(pipe, lora_state_dicts, ...)` — lora_utils.patch_on_lora (lora_utils.py:9-33): for every key of the
-    key map, `W[key] += up @ down * scale` with scale = fp16(20000/64).
-  * `KatzLoraPipelineMixin.patch_on_lora(lora_state_dict, lora_model_repos, default_unet_state_dict)` —
-    StableDiffusionXLControlNetPipelineKatz.patch_on_lora (pipeline_controlnet_sd_xl_katz.py:1730-1747): merge into a
-    pristine copy, then load.
-  * `LoraMerger.restore()` — `unet.load_state_dict(deepcopy(default_unet_state_dict))` (sdxl_unet_server.py:217).
+The reference's own entry points (`patch_on_lora(pipe, repos)` of lora_utils.py:9-33 and the pipeline method
+`patch_on_lora(lora_state_dict, repos, default_unet_state_dict)` of pipeline_controlnet_sd_xl_katz.py:1730-1747) live
+in katz_b200/lora_utils.py with the reference's argument lists; they delegate to the `LoraMerger` of this file, whose
+`restore()` is `unet.load_state_dict(deepcopy(default_unet_state_dict))` (sdxl_unet_server.py:217).
 
 The merger keeps the pristine weights W0 resident in HBM next to the live weights, so `merge` is a single streaming
 pass W_live = W0 + sum_i s_i * B_i A_i and `restore` is a bit-exact copy — the reference's copy semantics, without its
@@ -230,10 +227,11 @@ def load_key_map(path):
         return json.load(fr, object_pairs_hook=OrderedDict)
 
 
-def patch_on_lora(unet, merger, lora_state_dicts, key_maps, scale=REFERENCE_UNET_SCALE):
-    """lora_utils.patch_on_lora (lora_utils.py:9-33) for the UNet: every adapter's `up @ down * scale` is added to the
-    matching UNet linear. `lora_state_dicts` / `key_maps` are per-adapter lists (the reference reads them from the hub
-    and from ./lora_info_shm). Returns the adapters gathered on the device."""
+def merge_lora_state_dicts(unet, merger, lora_state_dicts, key_maps, scale=REFERENCE_UNET_SCALE):
+    """Merge LoRA state dicts (reference key names, gathered through reference-format key maps) into `unet` from the
+    pristine weights: the arithmetic of lora_utils.py:29-33 with the dicts and maps passed in instead of read from the
+    hub and from ./lora_info_shm. `lora_state_dicts` / `key_maps` may be per-adapter lists. Returns the adapters
+    gathered on the device."""
     if not isinstance(lora_state_dicts, (list, tuple)):
         lora_state_dicts, key_maps = [lora_state_dicts], [key_maps]
     adapters = [adapter_from_lora_state_dict(sd, km, merger.device, merger.dtype) for sd, km in zip(lora_state_dicts, key_maps)]

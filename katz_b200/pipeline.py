@@ -22,13 +22,13 @@ class KatzDenoiser:
     combine='mean' divides the sum by the number of nets (the service path, unet_2d_condition.py:1418-1439)."""
 
     def __init__(self, unet, height, width, controlnets=(), conditioning_scales=None, combine="sum", guidance_scale=5.0,
-                 schedule=None, text_len=77):
+                 schedule=None, text_len=77, hoist=False):
         self.unet = unet
         self.guidance_scale = float(guidance_scale)
         self.schedule = schedule or EulerSchedule()
         self.height, self.width = height, width
         self.step = GraphedStep(unet, 2, height, width, text_len=text_len, controlnets=controlnets,
-                                conditioning_scales=conditioning_scales, combine=combine)
+                                conditioning_scales=conditioning_scales, combine=combine, hoist=hoist)
 
     def prepare_latents(self, generator=None, seed=0):
         """`randn * init_noise_sigma` in fp16 (prepare_latents of the reference pipeline)."""
@@ -40,7 +40,7 @@ class KatzDenoiser:
         return (lat.to(self.unet.device) * self.schedule.init_noise_sigma).half()
 
     def denoise(self, latents, prompt_embeds, text_embeds, time_ids, controlnet_cond=None, num_inference_steps=50,
-                callback=None):
+                callback=None, check=False):
         """latents: fp16 [1,4,H,W] on the device (modified in place and returned). prompt_embeds [2,77,D], text_embeds
         [2,E], time_ids [2,6] ordered [negative, positive] as the reference concatenates them."""
         sch = self.schedule.set_timesteps(num_inference_steps)
@@ -52,6 +52,7 @@ class KatzDenoiser:
             if controlnet_cond is None:
                 raise KatzError("this denoiser was built with ControlNets: controlnet_cond is required")
             st["controlnet_cond"].copy_(controlnet_cond, non_blocking=True)
+        self.step.refresh_hoisted()       # hoist=True: text K/V and conditioning embeddings once per request
         sig, ts = sch.sigmas, sch.timesteps
         n = latents.numel()
         for i in range(num_inference_steps):
@@ -63,6 +64,8 @@ class KatzDenoiser:
             if callback is not None:
                 callback(i, latents)
         assert latents.numel() == n
+        if check:
+            self.step.check()      # one device synchronisation per request: did any bounded wait give up?
         return latents
 
 
@@ -92,4 +95,5 @@ class LoraRequestStream:
             e1.record()
             results.append((lat.clone(), e0, e1))
         torch.cuda.synchronize()
+        self.denoiser.step.check()
         return [(lat, a.elapsed_time(b)) for lat, a, b in results]

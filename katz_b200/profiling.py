@@ -1,0 +1,195 @@
+"""Small, self-contained workloads for kernel profilers and calibration runs.
+
+    python -m katz_b200.profiling gemm           # the step's dominant linear shapes, 3 launches each
+    python -m katz_b200.profiling attention      # the step's two self-attention shapes, 2 launches each
+    python -m katz_b200.profiling merge          # one LoRA merge over a 102-layer subset (0.7 GB of weights)
+    python -m katz_b200.profiling merge-fp32     # the same subset with fp32 weights and adapters
+    python -m katz_b200.profiling step [--batch B] [--latent HW]   # ONE eager UNet step
+    python -m katz_b200.profiling norms          # LayerNorm / GroupNorm launches of the step's shapes
+    python -m katz_b200.profiling compare-cublas # katz_linear_f16 against torch.addmm on the step's shapes (no profiler)
+
+Every mode but the last warms up, then brackets the launches of interest with cudaProfilerStart/Stop, so that
+`ncu --profile-from-start off` captures exactly those; each holds well under a few GB on the device (the `step` mode
+holds the 5.1 GB of UNet weights: capture it only with single-pass metrics). Each prints one JSON line.
+"""
+import argparse
+import json
+
+import torch
+
+
+def _time_events(fn, iters):
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def _bracket(fn):
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    fn()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+
+
+STEP_LINEAR_SHAPES = [(2048, 10240, 1280), (2048, 1280, 1280), (2048, 3840, 1280), (2048, 1280, 5120), (8192, 640, 640),
+                      (8192, 5120, 640), (8192, 640, 2560), (1024, 1280, 1280), (8192, 8192, 4096)]
+
+
+def gemm(dev, args):
+    from . import ops
+    shapes = [(2048, 10240, 1280), (2048, 1280, 1280), (8192, 640, 2560)]
+    sets = []
+    for (M, N, K) in shapes:
+        sets.append((torch.randn(M, K, device=dev).half(), (torch.randn(N, K, device=dev) * 0.03).half(),
+                     torch.empty(M, N, dtype=torch.float16, device=dev)))
+    for x, w, o in sets:
+        ops.linear(x, w, out=o)
+
+    def run():
+        for x, w, o in sets:
+            for _ in range(3):
+                ops.linear(x, w, out=o)
+    _bracket(run)
+    return {"profiled": "linear GEMMs, 3 launches each", "shapes": shapes, "kernel": ops.gemm_kernel_name(),
+            "tc05_status": ops.tc05_status()}
+
+
+def attention(dev, args):
+    from . import ops
+    shapes = [(2, 20, 1024), (2, 10, 4096)]
+    bufs = []
+    for (B, H, S) in shapes:
+        bufs.append((torch.randn(B, S, 3 * H * 64, device=dev).half(), H, torch.empty(B, S, H * 64, dtype=torch.float16, device=dev)))
+
+    def run(n):
+        for qkv, H, o in bufs:
+            C = H * 64
+            for _ in range(n):
+                ops.attention(qkv[:, :, :C], qkv[:, :, C:2 * C], qkv[:, :, 2 * C:], H, out=o)
+    run(1)
+    _bracket(lambda: run(2))
+    return {"profiled": "self-attention, 2 launches each", "shapes": shapes, "tc05_status": ops.tc05_status()}
+
+
+def _subset_merger(dev, dtype):
+    from collections import OrderedDict
+    from .lora import LoraMerger
+    from .params import SDXL_UNET_CONFIG, lora_target_keys, unet_param_shapes
+    shapes = unet_param_shapes(SDXL_UNET_CONFIG)
+    keys = [k for k in lora_target_keys(SDXL_UNET_CONFIG, include_proj=True) if k.startswith("down_blocks.2.attentions.0.")]
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+    W = OrderedDict((k, (torch.randn(shapes[k], generator=g, device=dev) * 0.02).to(dtype)) for k in keys)
+    ad = OrderedDict((k, ((torch.randn(w.shape[0], 64, generator=g, device=dev) * 0.01).to(dtype),
+                          (torch.randn(64, w.shape[1], generator=g, device=dev) / 64).to(dtype))) for k, w in W.items())
+    return LoraMerger(W), ad, keys
+
+
+def merge(dev, args, dtype=torch.float16):
+    merger, ad, keys = _subset_merger(dev, dtype)
+    for _ in range(2):
+        merger.merge(ad, 1.0)
+    _bracket(lambda: merger.merge(ad, 1.0))
+    return {"profiled": "one LoRA merge", "dtype": str(dtype), "layers": len(keys), "bytes": merger.algorithmic_bytes([64])}
+
+
+def merge_fp32(dev, args):
+    return merge(dev, args, torch.float32)
+
+
+def step(dev, args):
+    from . import _lib, ops
+    from .params import SDXL_UNET_CONFIG, init_state_dict, unet_param_shapes
+    from .unet import KatzUNet
+    cfg = SDXL_UNET_CONFIG
+    unet = KatzUNet(cfg, dev, init_state_dict(unet_param_shapes(cfg), seed=0, dtype=torch.float16, device=dev, generator_device=dev))
+    B, HW = args.batch, args.latent
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(B, 4, HW, HW, generator=g).half().to(dev)
+    ctx = torch.randn(B, 77, 2048, generator=g).half().to(dev)
+    added = {"text_embeds": torch.randn(B, 1280, generator=g).half().to(dev),
+             "time_ids": torch.tensor([[1024., 1024., 0., 0., 1024., 1024.]] * B).half().to(dev)}
+    t = torch.tensor([500.0], device=dev)
+    for _ in range(2):
+        unet(x, t, encoder_hidden_states=ctx, added_cond_kwargs=added)
+    n0 = _lib.launch_count()
+    _bracket(lambda: unet(x, t, encoder_hidden_states=ctx, added_cond_kwargs=added))
+    return {"profiled": "one eager UNet step", "batch": B, "latent": HW, "launches": _lib.launch_count() - n0,
+            "tc05_status": ops.tc05_status()}
+
+
+def norms(dev, args):
+    from . import ops
+    from .ops import ACT_SILU
+    ln = [(2048, 1280), (8192, 640)]
+    gn = [(2, 32 * 32, 1280), (2, 64 * 64, 640), (2, 128 * 128, 320), (2, 32 * 32, 2560)]
+    lnb = [(torch.randn(r, c, device=dev).half(), torch.ones(c, device=dev).half(), torch.zeros(c, device=dev).half()) for r, c in ln]
+    gnb = [(torch.randn(b, hw, c, device=dev).half(), torch.ones(c, device=dev).half(), torch.zeros(c, device=dev).half()) for b, hw, c in gn]
+
+    def run():
+        for x, g_, b_ in lnb:
+            ops.layer_norm(x, g_, b_)
+        for x, g_, b_ in gnb:
+            ops.group_norm_nhwc(x, g_, b_, 32, 1e-5, ACT_SILU)
+    run()
+    _bracket(run)
+    return {"profiled": "LayerNorm and GroupNorm launches", "layer_norm": ln, "group_norm": gn}
+
+
+def compare_cublas(dev, args):
+    """CUDA events around CUDA graphs of 20 launches, distinct weights per launch (they are cold in the step, too)."""
+    from . import ops
+
+    def graph_time(fn, n=20):
+        for _ in range(3):
+            fn(0)
+        torch.cuda.synchronize()
+        gr, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            fn(0)
+            with torch.cuda.graph(gr, stream=st):
+                for i in range(n):
+                    fn(i)
+        torch.cuda.synchronize()
+        gr.replay()
+        return _time_events(gr.replay, 5) * 1e3 / n
+    rows = []
+    for (M, N, K) in STEP_LINEAR_SHAPES:
+        nw = 6 if N * K < 3e7 else 2
+        x = torch.randn(M, K, device=dev).half()
+        ws = [(torch.randn(N, K, device=dev) * 0.03).half() for _ in range(nw)]
+        b = torch.randn(N, device=dev).half()
+        o = torch.empty(M, N, dtype=torch.float16, device=dev)
+        tk = graph_time(lambda i: ops.linear(x, ws[i % nw], b, out=o))
+        tc = graph_time(lambda i: torch.addmm(b, x, ws[i % nw].t(), out=o))
+        fl = 2.0 * M * N * K
+        rows.append({"shape": [M, N, K], "katz_us": round(tk, 1), "katz_tflops": round(fl / tk / 1e6),
+                     "cublas_us": round(tc, 1), "cublas_tflops": round(fl / tc / 1e6), "cublas_over_katz": round(tc / tk, 2)})
+    return {"compared": "linear + bias, fp16, CUDA graph of 20 launches", "rows": rows, "tc05_status": ops.tc05_status()}
+
+
+MODES = {"gemm": gemm, "attention": attention, "merge": merge, "merge-fp32": merge_fp32, "step": step, "norms": norms,
+         "compare-cublas": compare_cublas}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("mode", choices=sorted(MODES))
+    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--latent", type=int, default=128)
+    args = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        raise SystemExit("katz_b200.profiling needs a CUDA device")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    print(json.dumps(MODES[args.mode](dev, args)), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -66,6 +66,9 @@ def controlnet_server_loop(controlnet, device, dst_rank=0, latent_hw=(128, 128),
     served = 0
     while max_requests is None or served < max_requests:
         batch, steps, cond = _recv_request_header(device, cond_hw)
+        begin = getattr(controlnet, "begin_request", None)
+        if begin is not None:
+            begin()       # per-request hoisting contract: what the net cached for the last prompt / image is dropped
         pe, te, ti = _recv_embeddings(device, batch, dst_rank, text_len, cross_dim, pooled_dim)
         added = {"text_embeds": te, "time_ids": ti}
         x = torch.empty((batch, 4, latent_hw[0], latent_hw[1]), dtype=torch.float16, device=device)
@@ -104,14 +107,21 @@ def recv_controlnet_residuals(ranks, down_shapes, mid_shape, device):
 
 def unet_server_loop(unet, device, controlnet_parallel_rank=(), local_controlnet=None, block_out_channels=(320, 640, 1280),
                      latent_hw=(128, 128), cond_hw=(1024, 1024), text_len=77, cross_dim=2048, pooled_dim=1280,
-                     lora_hook=None, restore_hook=None, max_requests=None, verbose=False):
+                     lora_hook=None, restore_hook=None, request_hook=None, check_hook=None, max_requests=None, verbose=False):
     """sdxl_unet_server.py:96-220. `unet(sample, t, encoder_hidden_states=, added_cond_kwargs=,
     down_block_additional_residuals=, mid_block_additional_residual=, combine_scales=)` -> (prediction,).
+    request_hook() runs at the top of every request (`--lora-mode full`: patch_on_lora, sdxl_unet_server.py:99-100);
     lora_hook(status:int) -> bool is called every step until it returns True (async LoRA mode: `status` is the shm flag
-    sum received from rank 0); restore_hook() runs after each request."""
+    sum received from rank 0, sdxl_unet_server.py:153-181); restore_hook() runs after each request (:217); check_hook()
+    after it (did a bounded device-side wait give up during the request?)."""
     ranks = list(controlnet_parallel_rank)
     served = 0
     while max_requests is None or served < max_requests:
+        if request_hook is not None:
+            request_hook()
+        begin = getattr(unet, "begin_request", None)
+        if begin is not None:
+            begin()
         batch, steps, cond = _recv_request_header(device, cond_hw)
         pe, te, ti = _recv_embeddings(device, batch, 0, text_len, cross_dim, pooled_dim)
         added = {"text_embeds": te, "time_ids": ti}
@@ -144,10 +154,56 @@ def unet_server_loop(unet, device, controlnet_parallel_rank=(), local_controlnet
             dist.send(pred.contiguous(), dst=0)
         if restore_hook is not None:
             restore_hook()
+        if check_hook is not None:
+            check_hook()
         served += 1
         if verbose:
             print("UNet server: request %d done (%d steps)" % (served, steps))
     return served
+
+
+REFERENCE_LORA_REPOS = {0: [], 1: ["TheLastBen/Papercut_SDXL"],
+                        2: ["TheLastBen/William_Eggleston_Style_SDXL", "TheLastBen/Filmic"]}   # sdxl_unet_server.py:73-78
+
+
+def make_lora_hooks(pipe, lora_mode, load_lora_mode, lora_model_repos, device, shm_prefix="", shm_client=None):
+    """The three hooks of `unet_server_loop` for the reference's LoRA flags (sdxl_unet_server.py:24-38):
+
+      --lora-mode full                        request_hook: lora_utils.patch_on_lora(pipe, repos) before every request
+      --lora-mode sync --load-lora-mode async lora_hook: once the shm status equals 10 * len(repos) the adapters are
+                                              gathered from shared memory, summed element-wise over the repos as the
+                                              reference does (:169-173) and merged with pipe.patch_on_lora
+      any mode                                restore_hook: the pristine weights come back after the request (:217)
+
+    Returns (request_hook, lora_hook, restore_hook); a hook that the mode does not need is None."""
+    import json
+    import os
+    from .lora_utils import patch_on_lora
+    repos = list(lora_model_repos)
+    request_hook = lora_hook = None
+    if lora_mode == "full" and repos:
+        def request_hook():
+            patch_on_lora(pipe, repos)
+    elif lora_mode == "sync" and load_lora_mode == "async" and repos:
+        state = {"client": shm_client}
+
+        def lora_hook(status):
+            if status != 10 * len(repos):
+                return False
+            if state["client"] is None:
+                from .lora_shm import LoraShmClient
+                infos = []
+                for r in repos:
+                    with open(os.path.join(pipe.lora_info_dir, r.replace("/", "_") + ".json"), "r") as fr:
+                        infos.append(json.load(fr))
+                state["client"] = LoraShmClient(infos, prefix=shm_prefix)
+            summed = {}
+            for i in range(len(repos)):
+                for k, t in state["client"].gather(i, device).items():
+                    summed[k] = t if k not in summed else summed[k] + t
+            pipe.patch_on_lora(summed, repos, None)
+            return True
+    return request_hook, lora_hook, pipe.restore_unet
 
 
 def build_arg_parser(kind):
@@ -169,6 +225,12 @@ def build_arg_parser(kind):
     p.add_argument("--init-method", type=str, default="tcp://127.0.0.1:8000")
     p.add_argument("--state-dict", type=str, default=None, help="torch.save'd state dict with the reference's keys")
     p.add_argument("--max-requests", type=int, default=None)
+    if kind == "unet":
+        p.add_argument("--lora-info-dir", type=str, default="./lora_info_shm",
+                       help="folder of the reference's <repo>.json / <repo>_key_match_unet.json files")
+        p.add_argument("--lora-dir", type=str, default=None,
+                       help="--lora-mode full: folder holding <repo with / as _>.safetensors (the hub is not reachable)")
+        p.add_argument("--shm-prefix", type=str, default="", help="name prefix of the LoRA shared-memory segments")
     return p
 
 
@@ -197,8 +259,31 @@ def main(argv=None):
         net = KatzUNet(cfg, dev, sd)
         net.use_cuda_graph = True
         ranks = args.controlnet_parallel_rank if args.controlnet_parallel else []
-        unet_server_loop(net, dev, controlnet_parallel_rank=ranks, max_requests=args.max_requests, verbose=args.verbose)
+        hooks = unet_lora_hooks_from_args(net, args, dev)
+        from .engine import check_device_status
+        unet_server_loop(net, dev, controlnet_parallel_rank=ranks, request_hook=hooks[0], lora_hook=hooks[1],
+                         restore_hook=hooks[2], check_hook=lambda: check_device_status(net),
+                         max_requests=args.max_requests, verbose=args.verbose)
     dist.destroy_process_group()
+
+
+def unet_lora_hooks_from_args(unet, args, device, shm_client=None):
+    """What `main` passes to `unet_server_loop` for the parsed reference flags. `--lora-mode full` reads the adapters
+    from `--lora-dir` (safetensors files named after the repos)."""
+    import os
+    from .lora_utils import KatzPipe
+    repos = REFERENCE_LORA_REPOS[args.max_lora_num]
+    source = None
+    if args.lora_mode == "full" and repos:
+        if not args.lora_dir:
+            raise SystemExit("--lora-mode full needs --lora-dir (the hub is not reachable)")
+        from .lora_files import lora_state_dict
+
+        def source(repo):
+            return lora_state_dict(os.path.join(args.lora_dir, repo.replace("/", "_") + ".safetensors"))
+    pipe = KatzPipe(unet, lora_source=source, lora_info_dir=args.lora_info_dir)
+    return make_lora_hooks(pipe, args.lora_mode, args.load_lora_mode, repos, device, shm_prefix=args.shm_prefix,
+                           shm_client=shm_client)
 
 
 if __name__ == "__main__":

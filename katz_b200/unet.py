@@ -165,13 +165,22 @@ class _Net:
         self.w.alloc()
         self.dtype = torch.float16
         self.rp = None                 # latent_parallel.RowParallel when the latent is row-split across GPUs
-        self.cache_text_kv = False     # optional hoist of the step-invariant cross-attention K/V (off: reference semantics)
+        # Step-invariant hoisting of the cross-attention K/V projection (it depends on the prompt only). Two forms:
+        #  * eager calls: `cache_text_kv` keeps the projection of the last context tensor (off by default: the reference
+        #    recomputes it every step). The key is the tensor's address, shape and version, so a caller that starts a new
+        #    request calls begin_request() — a fresh tensor may reuse the old one's address. Never used during CUDA-graph
+        #    capture: a graph that omitted the projection could not follow a new prompt.
+        #  * CUDA graphs: engine.GraphedStep(hoist=True) computes the projection into a persistent buffer outside the graph
+        #    (`_hoisted_kv`), refreshes it when the prompt or the weights change, and the captured step reads the buffer.
+        self.cache_text_kv = False
         self._kv_cache_key = None
         self._kv_cache = None
+        self._hoisted_kv = None
+        self.weights_epoch = 0         # bumped whenever weights change (load_state_dict, LoRA merge / restore)
 
     # ---- state-dict surface (reference names)
     def load_state_dict(self, sd, strict=True):
-        self._kv_cache_key = None
+        self.invalidate_caches()
         return self.w.load(sd, strict=strict)
 
     def state_dict(self):
@@ -187,6 +196,12 @@ class _Net:
         return out
 
     def invalidate_caches(self):
+        """Call after anything that changes weights (a LoRA merge or restore writes the fused K/V weight buffer)."""
+        self._kv_cache_key = None
+        self.weights_epoch += 1
+
+    def begin_request(self):
+        """Start of a request in an eager serving loop: whatever was cached for the previous prompt / image is dropped."""
         self._kv_cache_key = None
 
     # ---- pieces
@@ -219,18 +234,21 @@ class _Net:
         temb_all = ops.linear(semb, self.w.fused["temb_w"], self.w.fused["temb_b"])
         return emb, temb_all
 
-    def _cross_kv(self, ctx):
-        """K/V projections of the text context for every transformer block at once: [B*S, sum 2C]."""
+    def _cross_kv(self, ctx, out=None):
+        """K/V projections of the text context for every transformer block at once: [B, S, sum 2C]."""
         if "cross_kv" not in self.w.fused:
             return None
-        if self.cache_text_kv:
-            key = (ctx.data_ptr(), tuple(ctx.shape), ctx._version)
+        if out is None and self._hoisted_kv is not None:
+            return self._hoisted_kv
+        use_cache = self.cache_text_kv and out is None and not torch.cuda.is_current_stream_capturing()
+        if use_cache:
+            key = (ctx.data_ptr(), tuple(ctx.shape), ctx._version, self.weights_epoch)
             if self._kv_cache_key == key:
                 return self._kv_cache
         B, S, D = ctx.shape
-        kv = ops.linear(ctx.reshape(B * S, D), self.w.fused["cross_kv"])
+        kv = ops.linear(ctx.reshape(B * S, D), self.w.fused["cross_kv"], out=None if out is None else out.view(B * S, -1))
         kv = kv.view(B, S, -1)
-        if self.cache_text_kv:
+        if use_cache:
             self._kv_cache_key, self._kv_cache = key, kv
         return kv
 
@@ -423,26 +441,36 @@ class KatzControlNet(_Net):
 
     def __init__(self, cfg, device="cuda", state_dict=None, conditioning_channels=3):
         super().__init__(cfg, controlnet_param_shapes(cfg, conditioning_channels), device)
-        self.cache_cond_embedding = False   # optional hoist of the step-invariant conditioning embedding
+        # the conditioning embedding depends on the image only: same two forms of hoisting as the text K/V (see _Net)
+        self.cache_cond_embedding = False
         self._cond_key = None
         self._cond_emb = None
+        self._hoisted_cond = None
         if state_dict is not None:
             self.load_state_dict(state_dict)
 
-    def _cond_embedding(self, cond):
-        """ControlNetConditioningEmbedding.forward (controlnet.py:113-127)."""
-        if self.cache_cond_embedding:
-            key = (cond.data_ptr(), tuple(cond.shape), cond._version)
+    def begin_request(self):
+        super().begin_request()
+        self._cond_key = None
+
+    def _cond_embedding(self, cond, out=None):
+        """ControlNetConditioningEmbedding.forward (controlnet.py:113-127) up to, not including, its conv_out."""
+        if out is None and self._hoisted_cond is not None:
+            return self._hoisted_cond
+        use_cache = self.cache_cond_embedding and out is None and not torch.cuda.is_current_stream_capturing()
+        if use_cache:
+            key = (cond.data_ptr(), tuple(cond.shape), cond._version, self.weights_epoch)
             if key == self._cond_key:
                 return self._cond_emb
         P = self._P
         p = "controlnet_cond_embedding"
         h = ops.nchw_to_nhwc(cond.to(device=self.device, dtype=torch.float16), cpad=self.w.conv_cin_pad[p + ".conv_in.weight"])
         h = ops.conv2d(h, P(p + ".conv_in.weight"), P(p + ".conv_in.bias"), act=ACT_SILU)
-        for i in range(2 * (len(CONTROLNET_COND_CHANNELS) - 1)):
+        n = 2 * (len(CONTROLNET_COND_CHANNELS) - 1)
+        for i in range(n):
             h = ops.conv2d(h, P("%s.blocks.%d.weight" % (p, i)), P("%s.blocks.%d.bias" % (p, i)),
-                           stride=2 if i % 2 == 1 else 1, act=ACT_SILU)
-        if self.cache_cond_embedding:
+                           stride=2 if i % 2 == 1 else 1, act=ACT_SILU, out=out if i == n - 1 else None)
+        if use_cache:
             self._cond_key, self._cond_emb = key, h
         return h
 

@@ -138,7 +138,7 @@ def transformer_2d(sd, p, x, ctx, heads, n_layers, groups):
 
 def time_and_aug_embedding(sd, cfg, timestep, text_embeds, time_ids, batch, dtype):
     """get_time_embed + TimestepEmbedding + text_time get_aug_embed (unet_2d_condition.py:997-1075,1147-1165)."""
-    t = torch.as_tensor(timestep, dtype=torch.float32).reshape(-1).expand(batch)
+    t = torch.as_tensor(timestep, dtype=torch.float32, device=text_embeds.device).reshape(-1).expand(batch)
     t_emb = timestep_embedding(t, cfg["block_out_channels"][0]).to(dtype)
     emb = _linear(sd, "time_embedding.linear_2", F.silu(_linear(sd, "time_embedding.linear_1", t_emb)))
     tid = timestep_embedding(time_ids.flatten().float(), cfg["addition_time_embed_dim"])

@@ -71,8 +71,8 @@ def test_tiny_controlnet_and_intake(tiny):
     assert len(down) == 9
     for d, r in zip(down, rdown):
         assert d.shape == r.shape
-        assert _maxabs(d, r) <= 1e-2 and _rel_l2(d, r) <= 4e-3, (_maxabs(d, r), _rel_l2(d, r))
-    assert _rel_l2(mid, rmid) <= 4e-3
+        assert _maxabs(d, r) <= 1e-2 and _rel_l2(d, r) <= 2e-3, (_maxabs(d, r), _rel_l2(d, r))
+    assert _rel_l2(mid, rmid) <= 2e-3
     out = tiny["unet"](sample.cuda(), torch.tensor(500.0), encoder_hidden_states=ctx.cuda(), added_cond_kwargs=added,
                        down_block_additional_residuals=down, mid_block_additional_residual=mid, return_dict=False)[0]
     assert _maxabs(out, ref) <= 1e-2 and _rel_l2(out, ref) <= 2e-3, (_maxabs(out, ref), _rel_l2(out, ref))
@@ -86,7 +86,7 @@ def test_tiny_controlnet_and_intake(tiny):
 
 def test_tiny_unet_with_lora_merged_then_restored(tiny):
     """Configuration 2 in small: one LoRA merged into every targeted linear, step, restore, step."""
-    from katz_b200.lora import LoraMerger, patch_on_lora, synthetic_key_map
+    from katz_b200.lora import LoraMerger, merge_lora_state_dicts, synthetic_key_map
     from oracle import lora_oracle, unet_oracle
     cfg, unet = tiny["cfg"], tiny["unet"]
     sample, ctx, te, ti, cond = tiny["inputs"]
@@ -103,7 +103,7 @@ def test_tiny_unet_with_lora_merged_then_restored(tiny):
     added = {"text_embeds": te.cuda(), "time_ids": ti.cuda()}
     args = (sample.cuda(), torch.tensor(500.0))
     before = unet(*args, encoder_hidden_states=ctx.cuda(), added_cond_kwargs=added)[0]
-    patch_on_lora(unet, merger, lora_sd, km, scale=1.0)
+    merge_lora_state_dicts(unet, merger, lora_sd, km, scale=1.0)
     merged_sd = dict(tiny["sd"])
     ad = {k: (lora_sd[km[k]["lora_up_key"]], lora_sd[km[k]["lora_down_key"]]) for k in keys}
     merged_sd.update(lora_oracle.merge_set({k: tiny["sd"][k] for k in keys}, [ad], [1.0]))
