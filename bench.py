@@ -295,7 +295,7 @@ def main():
     del sd
     keys = lora_target_keys(cfg, include_proj=True)     # the reference's 722-entry target set
     targets = unet.lora_targets(keys)
-    merger = LoraMerger(targets)
+    merger = LoraMerger(targets, on_change=unet.invalidate_caches)
     lora = make_lora(targets, 64, 100, dev)
 
     # ---- LoRA merge: HBM-bound pass, timed alone (weights 4.4 GB >> L2)

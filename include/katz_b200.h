@@ -75,6 +75,10 @@ int katz_lora_table_check(const katz_lora_layer* h_layers, int n_layers, int w_d
 #define KATZ_LORA_UNIFORM_TILES 1
 /* KATZ_LORA_NO_ADAPTERS additionally promises n_lora == 0 in every layer (a pure restore): a scheduling hint only. */
 #define KATZ_LORA_NO_ADAPTERS 2
+/* KATZ_LORA_UNIFORM_TILES_2 (instead of KATZ_LORA_UNIFORM_TILES) promises at most TWO adapters per layer, each of rank at
+ * most 64, with scale[1] == scale[0] wherever a layer has two: the same kernel accumulates both rank-r products in one
+ * tensor-memory tile (the sum of the products is rounded once, where the reference rounds after each adapter). */
+#define KATZ_LORA_UNIFORM_TILES_2 4
 int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_tile_start, int n_layers, int total_tiles, int w_dtype,
                     float sign, int max_tiles_per_layer, int flags, const void* d_tile_maps, void* stream);
 
@@ -152,6 +156,32 @@ int katz_linear_f16(const void* A, int lda, const void* W, void* C, int ldc, int
  * fp16 tensors round. Same shape rules as katz_linear_f16, F % 16 == 0. */
 int katz_linear_geglu_f16(const void* A, int lda, const void* W, void* C, int ldc, int M, int F, int K, const void* bias,
                           void* stream);
+
+/* LayerNorm folded into the linear layer that consumes it (nn.LayerNorm before to_q/to_k/to_v, attn2.to_q and the GEGLU
+ * projection: diffusers/models/attention.py:195,225,253 followed by attention_processor.py:1256-1258 / activations.py:145).
+ * LN(x) W^T = rstd * (x W'^T) - rstd * mean * c1 + c2 with W' = W diag(gamma), c1[n] = sum_k W'[n,k] and
+ * c2[n] = sum_k W[n,k] beta[k] + bias[n]: the GEMM reads the RAW rows x and the epilogue applies the two row scalars.
+ *  - katz_ln_fold_f16 prepares W' (fp16, [N,K]) and c12 ([N] pairs of fp32 (c1, c2)) from W, gamma, beta (bias optional). Run
+ *    it whenever W changes (a LoRA merge or restore).
+ *  - A producer call passes extras.stats_out: float2 [ceil(N/32)][M], per 32-column chunk of its output and row the
+ *    (sum, sum of squares) of the fp16 values it stored.
+ *  - The consumer call passes W' as W and extras.ln_stats (= the producer's stats_out, ln_slots = its chunk count, which must
+ *    cover exactly this call's K columns), ln_c12 and ln_eps; bias, rowvec, residual must be NULL, act 0, out_scale 1.
+ * Both may be set in one call. The same shapes and alignments as katz_linear_f16 / katz_linear_geglu_f16. */
+typedef struct katz_linear_extras {
+    const void* ln_stats;
+    const void* ln_c12;
+    int ln_slots;
+    float ln_eps;
+    void* stats_out;
+} katz_linear_extras;
+int katz_ln_fold_f16(const void* W, const void* gamma, const void* beta, const void* bias, void* Wf, void* c12, int N, int K,
+                     void* stream);
+int katz_linear_ex_f16(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, int K, const void* bias,
+                       const void* rowvec, int ld_rowvec, int rows_per_batch, const void* residual, int ldr, int act,
+                       float out_scale, const katz_linear_extras* ex, void* stream);
+int katz_linear_geglu_ex_f16(const void* A, int lda, const void* W, void* C, int ldc, int M, int F, int K, const void* bias,
+                             const katz_linear_extras* ex, void* stream);
 /* 3x3 NHWC convolution, stride 1 or 2, horizontal padding 1, on the tcgen05 path (nn.Conv2d of ResnetBlock2D,
  * resnet.py:378,408; Downsample2D, downsampling.py). X[B,Hin,Win,Cin], W[Cout,3,3,Cin], Y[B,Hout,Wout,Cout] with
  * Hout = (Hin + 2*pad_h - 3)/stride + 1 and Wout = (Win - 1)/stride + 1: pad_h = 1 is the usual padding, pad_h = 0 is for

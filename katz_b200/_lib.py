@@ -46,6 +46,12 @@ class LoraLayer(Structure):
 
 _V, _I, _L, _F = c_void_p, c_int, c_longlong, c_float
 
+
+class LinearExtras(Structure):
+    """Mirror of `struct katz_linear_extras`."""
+    _fields_ = [("ln_stats", c_void_p), ("ln_c12", c_void_p), ("ln_slots", c_int), ("ln_eps", c_float), ("stats_out", c_void_p)]
+
+
 # name -> (restype, argtypes). Every symbol include/katz_b200.h declares must be listed here; a test checks it.
 SIGNATURES = {
     "katz_abi_version": (_I, []),
@@ -70,6 +76,9 @@ SIGNATURES = {
     "katz_linear_f16_mma": (_I, [_V, _I, _V, _V, _I, _I, _I, _I, _V, _V, _I, _I, _V, _I, _I, _F, _V]),
     "katz_linear_f16": (_I, [_V, _I, _V, _V, _I, _I, _I, _I, _V, _V, _I, _I, _V, _I, _I, _F, _V]),
     "katz_linear_geglu_f16": (_I, [_V, _I, _V, _V, _I, _I, _I, _I, _V, _V]),
+    "katz_ln_fold_f16": (_I, [_V, _V, _V, _V, _V, _V, _I, _I, _V]),
+    "katz_linear_ex_f16": (_I, [_V, _I, _V, _V, _I, _I, _I, _I, _V, _V, _I, _I, _V, _I, _I, _F, POINTER(LinearExtras), _V]),
+    "katz_linear_geglu_ex_f16": (_I, [_V, _I, _V, _V, _I, _I, _I, _I, _V, POINTER(LinearExtras), _V]),
     "katz_conv3x3_nhwc_f16": (_I, [_V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _V, _V, _I, _V, _I, _F, _V]),
     "katz_tc05_status": (_I, []),
     "katz_tc05_clear_status": (_I, []),

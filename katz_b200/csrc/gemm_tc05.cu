@@ -51,6 +51,17 @@ struct Tc05Params {
     // convolution geometry (stride 1, output size = input size)
     int conv, H, W, TW, TH, tiles_w, tiles_h, cin_chunks, ksize, pad_h, pad_w, stride;   // H, W: OUTPUT size
     int* status;
+    // LayerNorm folded into this GEMM (kernel template LN): A holds the RAW rows x, W holds W * diag(gamma); the epilogue
+    // turns acc = x W'^T into rstd * acc - rstd * mean * c1 + c2 with c1[n] = sum_k W'[n,k], c2[n] = sum_k W[n,k] beta[k] (+
+    // bias). Row statistics come as partial (sum, sum of squares) per 32-column chunk of the producer's output:
+    // ln_stats[slot][M] (float2), ln_slots slots covering the K columns of x.
+    const float2* ln_stats;
+    const float2* ln_c12;       // (c1[n], c2[n]) interleaved: one 16-byte load brings both vectors for two columns
+    int ln_slots;
+    float ln_eps;
+    // this GEMM's own output feeds a folded LayerNorm: per 32-column chunk and row, (sum, sum of squares) of the fp16 values
+    // stored, written to stats_out[chunk][M]
+    float2* stats_out;
 };
 
 __device__ int g_tc05_status = 0;
@@ -71,19 +82,66 @@ __device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t* r) {
                  : "memory");
 }
 
+// Packed fp32 arithmetic (sm_100: one instruction works on two fp32 lanes held in a 64-bit register pair). The GEGLU
+// epilogue is bound by instruction issue, so its polynomial runs two gate values per instruction.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{\n"
+        ".reg .b64 ra, rb, rc, rd;\n"
+        "mov.b64 ra, {%2, %3};\n"
+        "mov.b64 rb, {%4, %5};\n"
+        "mov.b64 rc, {%6, %7};\n"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n"
+        "mov.b64 {%0, %1}, rd;\n"
+        "}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n"
+        ".reg .b64 ra, rb, rd;\n"
+        "mov.b64 ra, {%2, %3};\n"
+        "mov.b64 rb, {%4, %5};\n"
+        "mul.rn.f32x2 rd, ra, rb;\n"
+        "mov.b64 {%0, %1}, rd;\n"
+        "}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n"
+        ".reg .b64 ra, rb, rd;\n"
+        "mov.b64 ra, {%2, %3};\n"
+        "mov.b64 rb, {%4, %5};\n"
+        "add.rn.f32x2 rd, ra, rb;\n"
+        "mov.b64 {%0, %1}, rd;\n"
+        "}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+
 // Exact-form GELU x * Phi(x) with erf from Abramowitz & Stegun 7.1.26 (|error| <= 1.5e-7 on erf, far below the fp16
 // rounding that follows): 1 - erf(z) = (a1 t + ... + a5 t^5) exp(-z^2), t = 1 / (1 + p z), z = |x| / sqrt(2).
-// About 15 instructions against erff's 30; the GEGLU epilogue is instruction-issue bound.
-__device__ __forceinline__ float gelu_erf_fast(float x) {
-    const float ax = fabsf(x);
-    const float t = __frcp_rn(fmaf(ax, 0.3275911f * 0.70710678f, 1.0f));
-    float h = fmaf(t, 0.5f * 1.061405429f, 0.5f * -1.453152027f);
-    h = fmaf(t, h, 0.5f * 1.421413741f);
-    h = fmaf(t, h, 0.5f * -0.284496736f);
-    h = fmaf(t, h, 0.5f * 0.254829592f);
-    h = h * t * exp2f(x * x * (-0.5f * 1.4426950408889634f));      // 0.5 * (1 - erf(z))
-    const float r = x * h;                                          // x * Phi(-|x|)
-    return x >= 0.f ? x - r : r;
+// Two values at a time: ten packed instructions, four special-function ones (two reciprocals, two exp2) and four
+// scalar ones for the pair, against erff's thirty per value.
+__device__ __forceinline__ float2 gelu_erf_fast2(float2 x) {
+    const float2 ax = make_float2(fabsf(x.x), fabsf(x.y));
+    const float2 den = fma2(ax, make_float2(0.3275911f * 0.70710678f, 0.3275911f * 0.70710678f), make_float2(1.0f, 1.0f));
+    const float2 t = make_float2(__frcp_rn(den.x), __frcp_rn(den.y));
+    float2 h = fma2(t, make_float2(0.5f * 1.061405429f, 0.5f * 1.061405429f), make_float2(0.5f * -1.453152027f, 0.5f * -1.453152027f));
+    h = fma2(t, h, make_float2(0.5f * 1.421413741f, 0.5f * 1.421413741f));
+    h = fma2(t, h, make_float2(0.5f * -0.284496736f, 0.5f * -0.284496736f));
+    h = fma2(t, h, make_float2(0.5f * 0.254829592f, 0.5f * 0.254829592f));
+    const float2 xx = mul2(mul2(x, x), make_float2(-0.5f * 1.4426950408889634f, -0.5f * 1.4426950408889634f));
+    const float2 e = make_float2(exp2f(xx.x), exp2f(xx.y));
+    const float2 r = mul2(x, mul2(mul2(h, t), e));          // x * Phi(-|x|): the sign of x
+    // x >= 0: x - r (r >= 0); x < 0: r (r < 0)  ==  max(x, 0) - |r|
+    return make_float2(fmaxf(x.x, 0.f) - fabsf(r.x), fmaxf(x.y, 0.f) - fabsf(r.y));
 }
 
 __device__ __forceinline__ float rhalf(float v) { return __half2float(__float2half_rn(v)); }
@@ -91,9 +149,10 @@ __device__ __forceinline__ float rhalf(float v) { return __half2float(__float2ha
 // One thread's 32 accumulator columns of a chunk -> its 64-byte row of the box: + bias, + row vector (AUX), SiLU (ACT),
 // + residual (RES, already in the box), * scale, rounded to fp16. The options are compile-time so that the body is
 // straight-line code without the conversions and additions of absent terms.
-template <bool ACT, bool RES, bool AUX>
+template <bool ACT, bool RES, bool AUX, bool STATS = false>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t* r, unsigned char* rowp, uint32_t swz, const uint4* b4,
-                                               const uint4* v4, float out_scale) {
+                                               const uint4* v4, float out_scale, float2* sums = nullptr) {
+    float2 s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         uint4* cell = reinterpret_cast<uint4*>(rowp + (((uint32_t)k ^ swz) << 4));
@@ -120,9 +179,38 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t* r, unsigned char*
                 v0 += a.x;
                 v1 += a.y;
             }
-            ow[e] = pack_half2(v0 * out_scale, v1 * out_scale);
+            v0 *= out_scale;
+            v1 *= out_scale;
+            if (STATS) {
+                // row statistics for a LayerNorm folded into the next GEMM, from the fp32 values (their fp16 rounding moves
+                // a 1280-term sum by parts in 1e5): two packed instructions per pair of columns
+                const float2 v = make_float2(v0, v1);
+                s1 = add2(s1, v);
+                s2 = fma2(v, v, s2);
+            }
+            ow[e] = pack_half2(v0, v1);
         }
         *cell = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+    if (STATS) *sums = make_float2(s1.x + s1.y, s2.x + s2.y);
+}
+
+// LayerNorm-folded epilogue of one chunk: out = half(acc * rstd + (c2[n] - rstd * mean * c1[n])). c12 holds (c1, c2) per
+// column; it is the same for every row (warp-uniform addresses: broadcast loads that stay in L1).
+__device__ __forceinline__ void epilogue_chunk_ln(const uint32_t* r, unsigned char* rowp, uint32_t swz, const float2* c12,
+                                                  int ncols, float rstd, float nrm) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        uint32_t ow[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int col = k * 8 + 2 * e;
+            const float4 cc = col < ncols ? __ldg(reinterpret_cast<const float4*>(c12 + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float v0 = fmaf(__uint_as_float(r[col]), rstd, fmaf(nrm, cc.x, cc.y));
+            const float v1 = fmaf(__uint_as_float(r[col + 1]), rstd, fmaf(nrm, cc.z, cc.w));
+            ow[e] = pack_half2(v0, v1);
+        }
+        *reinterpret_cast<uint4*>(rowp + (((uint32_t)k ^ swz) << 4)) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
 }
 
@@ -130,7 +218,7 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t* r, unsigned char*
 // of the B tile, the leader issues the instruction for both, each CTA's TMEM receives its own 128 rows and each runs its
 // own epilogue. Per k-step a CTA then takes 16 + BN/2 x 128 B from L2 instead of 16 + BN x 128 B; the main loop is bound
 // by that delivery, not by the tensor pipe. No load is multicast; only completion signals cross the pair.
-template <int BN, int STAGES, bool GEGLU, bool PAIR>
+template <int BN, int STAGES, bool GEGLU, bool PAIR, bool LN>
 __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                   const __grid_constant__ CUtensorMap tmB,
                                                                   const __grid_constant__ CUtensorMap tmC,
@@ -348,6 +436,34 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
             }
             // warp-uniform: do any of this warp's 32 rows exist? (a pair's odd tile out lies past the last tile)
             const bool rows_in = mt < p.m_tiles && y0 < p.rows_img;
+            // global output row of this thread (linear layers and convolutions alike: images are stored one after another)
+            const long long grow = (long long)z0 * p.rows_img + y0 + lane;
+            const bool row_in = rows_in && (y0 + lane) < p.rows_img;
+            float ln_rstd = 1.f, ln_nrm = 0.f;
+            if constexpr (LN) {
+                // fold this row's partial sums (one float2 per 32-column chunk of x, rows contiguous per chunk): the loads
+                // overlap the tile's main loop
+                float s1 = 0.f, s2 = 0.f;
+                if (row_in) {
+                    const float2* sp = p.ln_stats + grow;
+                    for (int c0 = 0; c0 < p.ln_slots; c0 += 8) {      // eight loads in flight at a time
+                        float2 v[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u)
+                            v[u] = c0 + u < p.ln_slots ? __ldg(sp + (size_t)(c0 + u) * p.M) : make_float2(0.f, 0.f);
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            s1 += v[u].x;
+                            s2 += v[u].y;
+                        }
+                    }
+                }
+                const float inv_n = 1.0f / (float)p.K;
+                const float mean = s1 * inv_n;
+                const float var = fmaxf(fmaf(-mean, mean, s2 * inv_n), 0.f);
+                ln_rstd = rsqrtf(var + p.ln_eps);
+                ln_nrm = -ln_rstd * mean;
+            }
             const __half* bias_p = (p.bias && rows_in) ? p.bias + n0 : nullptr;
             const __half* aux_p = nullptr;             // gate bias (GEGLU) or the image's row vector
             if (!rows_in) {
@@ -427,40 +543,65 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                     break;
                 }
                 if constexpr (GEGLU) {
-                    // the gate's erf makes this epilogue instruction-bound: a rolled loop over 8-column groups keeps the
-                    // code small enough for the instruction cache (fully unrolled it ran 2.5x slower)
-                    uint4 b4 = load_vec(bias_p, c * 32), g4 = load_vec(aux_p, c * 32);
+                    // The gate's erf makes this epilogue instruction-bound: packed fp32 arithmetic (two values per
+                    // instruction) and a rolled loop over 16-column groups, which keeps the code inside the instruction
+                    // cache (fully unrolled it ran 2.5x slower).
 #pragma unroll 1
-                    for (int k = 0; k < 4; ++k) {
-                        const int col = c * 32 + k * 8;
-                        uint32_t v8[8], g8[8];
-                        tmem_ld_32x8(tacc + col, v8);
-                        tmem_ld_32x8(tacc + BN / 2 + col, g8);
-                        const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w}, gw[4] = {g4.x, g4.y, g4.z, g4.w};
-                        if (k < 3) {
-                            b4 = load_vec(bias_p, col + 8);
-                            g4 = load_vec(aux_p, col + 8);
-                        }
+                    for (int k2 = 0; k2 < 2; ++k2) {
+                        const int col = c * 32 + k2 * 16;
+                        uint32_t v16[16], g16[16];
+                        tmem_ld_32x16(tacc + col, v16);
+                        tmem_ld_32x16(tacc + BN / 2 + col, g16);
+                        const uint4 bA = load_vec(bias_p, col), bB = load_vec(bias_p, col + 8);
+                        const uint4 gA = load_vec(aux_p, col), gB = load_vec(aux_p, col + 8);
+                        const uint32_t bw[8] = {bA.x, bA.y, bA.z, bA.w, bB.x, bB.y, bB.z, bB.w};
+                        const uint32_t gw[8] = {gA.x, gA.y, gA.z, gA.w, gB.x, gB.y, gB.z, gB.w};
                         tmem_ld_wait();
-                        uint32_t ow[4];
+                        uint32_t ow[8];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
+                        for (int e = 0; e < 8; ++e) {
                             // activations.py:146-149 on fp16 tensors: proj output, gelu and product each round to half.
                             // The product of two halfs is exact in fp32, so its rounding is the half2 multiply.
-                            const float2 bf = unpack_half2(bw[e]), gb = unpack_half2(gw[e]);
-                            const __half2 vh = __floats2half2_rn(__uint_as_float(v8[2 * e]) + bf.x, __uint_as_float(v8[2 * e + 1]) + bf.y);
-                            const float2 gr = __half22float2(
-                                __floats2half2_rn(__uint_as_float(g8[2 * e]) + gb.x, __uint_as_float(g8[2 * e + 1]) + gb.y));
-                            const __half2 oh = __hmul2(vh, __floats2half2_rn(gelu_erf_fast(gr.x), gelu_erf_fast(gr.y)));
+                            float2 vv, gg;
+                            if constexpr (LN) {
+                                const int nn = n0 + col + 2 * e;
+                                const bool in = nn < p.N;
+                                const float4 cv = in ? __ldg(reinterpret_cast<const float4*>(p.ln_c12 + nn)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                                const float4 cg = in ? __ldg(reinterpret_cast<const float4*>(p.ln_c12 + p.geglu_F + nn)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                                const float2 rs = make_float2(ln_rstd, ln_rstd), nm = make_float2(ln_nrm, ln_nrm);
+                                vv = fma2(make_float2(__uint_as_float(v16[2 * e]), __uint_as_float(v16[2 * e + 1])), rs,
+                                          fma2(nm, make_float2(cv.x, cv.z), make_float2(cv.y, cv.w)));
+                                gg = fma2(make_float2(__uint_as_float(g16[2 * e]), __uint_as_float(g16[2 * e + 1])), rs,
+                                          fma2(nm, make_float2(cg.x, cg.z), make_float2(cg.y, cg.w)));
+                            } else {
+                                vv = add2(make_float2(__uint_as_float(v16[2 * e]), __uint_as_float(v16[2 * e + 1])), unpack_half2(bw[e]));
+                                gg = add2(make_float2(__uint_as_float(g16[2 * e]), __uint_as_float(g16[2 * e + 1])), unpack_half2(gw[e]));
+                            }
+                            const __half2 vh = __floats2half2_rn(vv.x, vv.y);
+                            const float2 gr = __half22float2(__floats2half2_rn(gg.x, gg.y));
+                            const float2 ge = gelu_erf_fast2(gr);
+                            const __half2 oh = __hmul2(vh, __floats2half2_rn(ge.x, ge.y));
                             ow[e] = *reinterpret_cast<const uint32_t*>(&oh);
                         }
-                        *reinterpret_cast<uint4*>(rowp + (((uint32_t)k ^ swz) << 4)) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                        *reinterpret_cast<uint4*>(rowp + (((uint32_t)(2 * k2) ^ swz) << 4)) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                        *reinterpret_cast<uint4*>(rowp + (((uint32_t)(2 * k2 + 1) ^ swz) << 4)) = make_uint4(ow[4], ow[5], ow[6], ow[7]);
                     }
                 } else {
                     tmem_ld_wait();
                     // act and residual are uniform over the launch: one branch per chunk picks a straight-line body
                     // (SiLU only follows the tiny embedding GEMMs: it keeps the general body)
-                    if (p.act == 1) {
+                    if constexpr (LN) {
+                        const int ncols = p.N - (n0 + c * 32);
+                        epilogue_chunk_ln(r, rowp, swz, p.ln_c12 + n0 + c * 32, ncols < 32 ? ncols : 32, ln_rstd, ln_nrm);
+                    } else if (p.stats_out != nullptr) {
+                        // this output feeds a folded LayerNorm: per row, (sum, sum of squares) of this chunk's 32 values
+                        // (columns past N come from zero operands and zero vectors: they add nothing). Launches with a
+                        // row vector or an activation do not ask for statistics.
+                        float2 sums;
+                        if (has_res) epilogue_chunk<false, true, false, true>(r, rowp, swz, cb4, cv4, p.out_scale, &sums);
+                        else epilogue_chunk<false, false, false, true>(r, rowp, swz, cb4, cv4, p.out_scale, &sums);
+                        if (row_in) p.stats_out[(size_t)((n0 >> 5) + c) * p.M + grow] = sums;
+                    } else if (p.act == 1) {
                         if (has_res) epilogue_chunk<true, true, true>(r, rowp, swz, cb4, cv4, p.out_scale);
                         else epilogue_chunk<true, false, true>(r, rowp, swz, cb4, cv4, p.out_scale);
                     } else if (aux_p) {
@@ -579,7 +720,7 @@ static constexpr int tc05_smem() {
     return STAGES * (TBM * TBK * 2 + (PAIR ? BN / 2 : BN) * TBK * 2) + boxes * BOX_BYTES + (2 * STAGES + 4 + boxes) * 8 + 16 + 1024;
 }
 
-template <int BN, int STAGES, bool GEGLU, bool PAIR>
+template <int BN, int STAGES, bool GEGLU, bool PAIR, bool LN = false>
 static int launch_tc05(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const CUtensorMap& r,
                        const Tc05Params& p, cudaStream_t st) {
     static bool attr_dev[KATZ_MAX_DEVICES] = {false};
@@ -589,7 +730,7 @@ static int launch_tc05(const CUtensorMap& a, const CUtensorMap& b, const CUtenso
     int& max_ctas = max_ctas_dev[dev_index];
     constexpr int smem = tc05_smem<BN, STAGES, GEGLU, PAIR>();
     static_assert(smem <= 232448, "shared memory budget");
-    auto kernel = tc05_gemm_kernel<BN, STAGES, GEGLU, PAIR>;
+    auto kernel = tc05_gemm_kernel<BN, STAGES, GEGLU, PAIR, LN>;
     if (!attr) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
@@ -672,7 +813,7 @@ static bool use_pairs(const Tc05Params& p, bool geglu) {
     return on && p.m_tiles >= 2;
 }
 
-template <bool GEGLU>
+template <bool GEGLU, bool LN = false>
 static int dispatch(const CUtensorMap& a, const CUtensorMap& b, Tc05Params& p, int bn, bool pair, int rows_per_image, int images,
                     cudaStream_t st) {
     p.status = status_ptr();
@@ -684,24 +825,68 @@ static int dispatch(const CUtensorMap& a, const CUtensorMap& b, Tc05Params& p, i
     if (rc) return rc;
     if (pair) {
         // stage counts: what fits beside the epilogue boxes (8 KB to 64 KB) in 227 KB
-        if (bn == 256) return launch_tc05<256, GEGLU ? 6 : 5, GEGLU, true>(a, b, c, r, p, st);
+        if (bn == 256) return launch_tc05<256, GEGLU ? 6 : 5, GEGLU, true, LN>(a, b, c, r, p, st);
         if constexpr (!GEGLU) {
-            if (bn == 160) return launch_tc05<160, 6, false, true>(a, b, c, r, p, st);
-            if (bn == 96) return launch_tc05<96, 8, false, true>(a, b, c, r, p, st);
+            if (bn == 160) return launch_tc05<160, 6, false, true, LN>(a, b, c, r, p, st);
+            if (bn == 96) return launch_tc05<96, 8, false, true, LN>(a, b, c, r, p, st);
         }
-        return launch_tc05<128, 7, GEGLU, true>(a, b, c, r, p, st);
+        return launch_tc05<128, 7, GEGLU, true, LN>(a, b, c, r, p, st);
     }
     if constexpr (!GEGLU) {
-        if (bn == 160) return launch_tc05<160, 4, false, false>(a, b, c, r, p, st);
-        if (bn == 96) return launch_tc05<96, 6, false, false>(a, b, c, r, p, st);
+        if (bn == 160) return launch_tc05<160, 4, false, false, LN>(a, b, c, r, p, st);
+        if (bn == 96) return launch_tc05<96, 6, false, false, LN>(a, b, c, r, p, st);
     }
-    if (bn == 256) return launch_tc05<256, GEGLU ? 4 : 3, GEGLU, false>(a, b, c, r, p, st);
-    return launch_tc05<128, 6, GEGLU, false>(a, b, c, r, p, st);
+    if (bn == 256) return launch_tc05<256, GEGLU ? 4 : 3, GEGLU, false, LN>(a, b, c, r, p, st);
+    return launch_tc05<128, 6, GEGLU, false, LN>(a, b, c, r, p, st);
+}
+
+// W' = W diag(gamma) (fp16), c12[n] = (sum_k W'[n,k], sum_k W[n,k] beta[k] + bias[n]) in fp32: the per-weight constants of a
+// LayerNorm folded into the linear layer that consumes it. One warp per output row.
+__global__ void __launch_bounds__(256) ln_fold_kernel(const __half* __restrict__ W, const __half* __restrict__ gamma,
+                                                      const __half* __restrict__ beta, const __half* __restrict__ bias,
+                                                      __half* __restrict__ Wf, float2* __restrict__ c12, int N, int K) {
+    pdl_wait();
+    // writes weights that later kernels may fetch before their own dependency wait: no early release of dependents
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + warp;
+    if (n >= N) return;
+    const __half* w = W + (size_t)n * K;
+    __half* wf = Wf + (size_t)n * K;
+    float s1 = 0.f, s2 = 0.f;
+    for (int k = lane * 8; k < K; k += 256) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(w + k);
+        const uint4 gv = __ldg(reinterpret_cast<const uint4*>(gamma + k));
+        const uint4 bv = __ldg(reinterpret_cast<const uint4*>(beta + k));
+        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w}, gw[4] = {gv.x, gv.y, gv.z, gv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 wf2 = unpack_half2(ww[e]), g2 = unpack_half2(gw[e]), b2 = unpack_half2(bw[e]);
+            ow[e] = pack_half2(wf2.x * g2.x, wf2.y * g2.y);
+            const float2 o2 = unpack_half2(ow[e]);          // the folded weight as the GEMM will read it
+            s1 += o2.x + o2.y;
+            s2 = fmaf(wf2.x, b2.x, fmaf(wf2.y, b2.y, s2));
+        }
+        *reinterpret_cast<uint4*>(wf + k) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    if (lane == 0) c12[n] = make_float2(s1, s2 + (bias ? __half2float(bias[n]) : 0.f));
 }
 
 }  // namespace katz
 
 using namespace katz;
+
+extern "C" int katz_ln_fold_f16(const void* W, const void* gamma, const void* beta, const void* bias, void* Wf, void* c12,
+                                int N, int K, void* stream) {
+    KATZ_CHECK_ARG(W && gamma && beta && Wf && c12, KATZ_EINVAL);
+    KATZ_CHECK_ARG(N > 0 && K > 0 && K % 8 == 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG(aligned16(W) && aligned16(gamma) && aligned16(beta) && aligned16(Wf) && ((uintptr_t)c12 & 7) == 0, KATZ_EALIGN);
+    launch_k(ln_fold_kernel, ceil_div(N, 8), 256, 0, (cudaStream_t)stream, (const __half*)W, (const __half*)gamma,
+             (const __half*)beta, (const __half*)bias, (__half*)Wf, (float2*)c12, N, K);
+    KATZ_LAUNCH_RET();
+}
 
 extern "C" int katz_tc05_status(void) {
     int v = -1;
@@ -716,7 +901,7 @@ extern "C" int katz_tc05_clear_status(void) {
 
 static int linear_common(const void* A, int lda, const void* W, void* C, int ldc, int M, int N_out, int K, const void* bias,
                          const void* rowvec, int ld_rowvec, int rows_per_batch, const void* residual, int ldr, int act,
-                         float out_scale, int geglu_F, void* stream) {
+                         float out_scale, int geglu_F, void* stream, const katz_linear_extras* ex = nullptr) {
     KATZ_CHECK_ARG(A && W && C, KATZ_EINVAL);
     KATZ_CHECK_ARG(M > 0 && N_out > 0 && K > 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(K % TBK == 0 && N_out % 8 == 0, KATZ_ESIZE);
@@ -745,8 +930,42 @@ static int linear_common(const void* A, int lda, const void* W, void* C, int ldc
     const bool pair = use_pairs(p, geglu);
     rc = encode_2d(&tb, W, K, w_rows, (uint64_t)K * 2, TBK, (geglu || pair) ? bn / 2 : bn);      // box rows: what one load brings
     if (rc) return rc;
+    bool ln = false;
+    if (ex) {
+        if (ex->stats_out) {
+            KATZ_CHECK_ARG(((uintptr_t)ex->stats_out & 7) == 0, KATZ_EALIGN);
+            p.stats_out = reinterpret_cast<float2*>(ex->stats_out);
+        }
+        if (ex->ln_stats) {
+            // the folded LayerNorm replaces bias, row vector, activation and residual of this call
+            KATZ_CHECK_ARG(ex->ln_c12 && ex->ln_slots > 0 && !bias && !rowvec && !residual && act == 0 && out_scale == 1.0f, KATZ_EINVAL);
+            KATZ_CHECK_ARG(((uintptr_t)ex->ln_stats & 7) == 0 && aligned16(ex->ln_c12), KATZ_EALIGN);
+            p.ln_stats = reinterpret_cast<const float2*>(ex->ln_stats);
+            p.ln_c12 = reinterpret_cast<const float2*>(ex->ln_c12);
+            p.ln_slots = ex->ln_slots;
+            p.ln_eps = ex->ln_eps;
+            ln = true;
+        }
+    }
+    if (ln)
+        return geglu ? dispatch<true, true>(ta, tb, p, bn, pair, M, 1, (cudaStream_t)stream)
+                     : dispatch<false, true>(ta, tb, p, bn, pair, M, 1, (cudaStream_t)stream);
     return geglu ? dispatch<true>(ta, tb, p, bn, pair, M, 1, (cudaStream_t)stream)
                  : dispatch<false>(ta, tb, p, bn, pair, M, 1, (cudaStream_t)stream);
+}
+
+extern "C" int katz_linear_ex_f16(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, int K,
+                                  const void* bias, const void* rowvec, int ld_rowvec, int rows_per_batch,
+                                  const void* residual, int ldr, int act, float out_scale, const katz_linear_extras* ex,
+                                  void* stream) {
+    return linear_common(A, lda, W, C, ldc, M, N, K, bias, rowvec, ld_rowvec, rows_per_batch, residual, ldr, act, out_scale, 0,
+                         stream, ex);
+}
+
+extern "C" int katz_linear_geglu_ex_f16(const void* A, int lda, const void* W, void* C, int ldc, int M, int F, int K,
+                                        const void* bias, const katz_linear_extras* ex, void* stream) {
+    KATZ_CHECK_ARG(F > 0 && F % 16 == 0, KATZ_ESIZE);
+    return linear_common(A, lda, W, C, ldc, M, F, K, bias, nullptr, 0, 0, nullptr, 0, 0, 1.0f, F, stream, ex);
 }
 
 extern "C" int katz_linear_f16(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, int K,

@@ -154,8 +154,9 @@ template <typename T>
 __global__ void __launch_bounds__(LM_THREADS, 1) lora_merge_kernel(const katz_lora_layer* __restrict__ layers,
                                                                    const int* __restrict__ tile_start, int n_layers,
                                                                    int total_tiles, float sign, int counts_in_smem) {
+    // Writes weights, which later kernels may fetch before their own dependency wait: dependents are released only by this
+    // kernel's completion (no griddepcontrol.launch_dependents).
     pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
-    pdl_launch_dependents();
     using Cfg = LmCfg<T>;
     constexpr int TM = Cfg::TM, NST = Cfg::NST;
     constexpr int ES = sizeof(T);
@@ -374,8 +375,9 @@ __global__ void __launch_bounds__(LM_THREADS, 1) lora_merge_f16_tc05_kernel(cons
                                                                            const int* __restrict__ tile_start, int n_layers,
                                                                            int total_tiles, float sign, int counts_in_smem,
                                                                            int* __restrict__ status) {
+    // Writes weights, which later kernels may fetch before their own dependency wait: dependents are released only by this
+    // kernel's completion (no griddepcontrol.launch_dependents).
     pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
-    pdl_launch_dependents();
     using namespace tc05;
     using T = __half;
     using Cfg = LmCfg<__half>;
@@ -557,12 +559,19 @@ __global__ void __launch_bounds__(LM_THREADS, 1) lora_merge_f16_tc05_kernel(cons
 //     async copies into the layouts tcgen05.mma reads.
 // A W stage is reused once the TMA store has read it (cp.async.bulk.wait_group.read), so loads of tiles j+1..j+3, the
 // product of tile j+1 and the write-back of tile j are in flight together.
-constexpr int WS_NW = 4;                        // W ring
+// MAXL = adapters per layer the launch can take (1 or 2: one rank <= 64 product per adapter and tile, all accumulated in
+// the tile's TMEM accumulator; the adapters of a layer share one scale). With two adapters the B buffers double and the W
+// ring gives up a stage to make room.
 constexpr int WS_NA = 3;                        // A ring
 constexpr int WS_W_BYTES = 32768;
 constexpr int WS_A_BYTES = 16384;
 constexpr int WS_B_BYTES = 16384;
-constexpr int WS_SMEM = WS_NW * WS_W_BYTES + WS_NA * WS_A_BYTES + 2 * WS_B_BYTES + 1024;
+template <int MAXL>
+struct WsCfg {
+    static constexpr int NW = MAXL == 1 ? 4 : 3;                 // W ring
+    static constexpr int NB = 2 * MAXL;                          // B buffers: two bands in flight x adapters
+    static constexpr int SMEM = NW * WS_W_BYTES + WS_NA * WS_A_BYTES + NB * WS_B_BYTES + 1024;
+};
 constexpr int WS_THREADS = 320;
 constexpr int WS_PRODUCERS = 128;
 constexpr int WS_CHUNK = 4;                     // consecutive tiles per CTA turn
@@ -574,12 +583,14 @@ struct WsTile {
 };
 
 // One role's view of the layer that owns the current tile; the table entry is re-read only when the layer changes.
+template <int MAXL>
 struct WsLayer {
     int li = -1, start = 0, end = 0;
-    int in_f = 0, out_f = 0, n_lora = 0, rank = 0, tiles_n = 1;
+    int in_f = 0, out_f = 0, n_lora = 0, tiles_n = 1;
+    int rank[MAXL];
     float scale = 0.f;
-    const __half* B = nullptr;
-    const __half* A = nullptr;
+    const __half* B[MAXL];
+    const __half* A[MAXL];
     bool has_w0 = false;
     __device__ __forceinline__ void seek(const katz_lora_layer* __restrict__ layers, const int* tile_start, int n_layers,
                                          int total_tiles, int tile) {
@@ -590,31 +601,39 @@ struct WsLayer {
         const katz_lora_layer* L = layers + li;
         in_f = L->in_features;
         out_f = L->out_features;
-        n_lora = L->n_lora;
-        rank = L->rank[0];
+        n_lora = min(L->n_lora, MAXL);
         scale = L->scale[0];
-        B = reinterpret_cast<const __half*>(L->B[0]);
-        A = reinterpret_cast<const __half*>(L->A[0]);
+#pragma unroll
+        for (int a = 0; a < MAXL; ++a) {
+            rank[a] = L->rank[a];
+            B[a] = reinterpret_cast<const __half*>(L->B[a]);
+            A[a] = reinterpret_cast<const __half*>(L->A[a]);
+        }
         has_w0 = L->W0 != nullptr;
         tiles_n = (in_f + 127) >> 7;
     }
 };
 
+template <int MAXL>
 __global__ void __launch_bounds__(WS_THREADS, 1) lora_merge_f16_ws_kernel(const katz_lora_layer* __restrict__ layers,
                                                                          const CUtensorMap* __restrict__ maps,
                                                                          const int* __restrict__ tile_start, int n_layers,
                                                                          int total_tiles, float sign,
                                                                          int* __restrict__ status, int CH) {
+    // This kernel writes weights that the next kernels read as operands they may fetch before their own dependency wait:
+    // its dependents are released only by its completion (no griddepcontrol.launch_dependents here).
     pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
-    pdl_launch_dependents();
     using namespace tc05;
     using T = __half;
+    constexpr int WS_NW = WsCfg<MAXL>::NW, WS_NB = WsCfg<MAXL>::NB;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* smem_a = smem + WS_NW * WS_W_BYTES;
     unsigned char* smem_b = smem_a + WS_NA * WS_A_BYTES;
     __shared__ WsTile s_tile[WS_NW];
-    __shared__ int4 s_ab[WS_NA];                 // {n_lora, rank, B buffer, first tile of a band} for the A stage's tile
+    // per A stage: {adapters of the tile, rank of this stage's adapter, B buffer, bit 0: first tile of a band, bit 1: first
+    // adapter of the tile, bit 2: last adapter of the tile}
+    __shared__ int4 s_ab[WS_NA];
     __shared__ __align__(8) uint64_t s_bars[2 * WS_NW + 2 * WS_NA + 2 + 4];
     __shared__ uint32_t s_tmem;
     __shared__ int s_start[WS_MAX_LAYERS_SMEM];
@@ -636,7 +655,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) lora_merge_f16_ws_kernel(const 
             mbar_init(aempty0 + 8 * s, 1);                 // tcgen05.commit
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(bempty0 + 8 * b, 1);         // tcgen05.commit at the end of the band that used the buffer
+            mbar_init(bempty0 + 8 * b, 1);         // tcgen05.commit at the end of the band that used the buffers
             mbar_init(dfull0 + 8 * b, 1);          // delta accumulator ready (tcgen05.commit)
             mbar_init(dempty0 + 8 * b, 4);         // delta accumulator read (one arrival per fold warp)
         }
@@ -715,7 +734,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) lora_merge_f16_ws_kernel(const 
     } else if (warp == 4) {
         // ------------------------------------------------------------------------------------ W loader (one thread)
         if (elect_one()) {
-            WsLayer lay;
+            WsLayer<MAXL> lay;
             for (int j = 0, tile; (tile = tile_of(j)) >= 0; ++j) {
                 const int s = j % WS_NW;
                 if (!mbar_wait(wempty0 + 8 * s, ((j / WS_NW) & 1) ^ 1)) { ok = false; break; }
@@ -740,47 +759,50 @@ __global__ void __launch_bounds__(WS_THREADS, 1) lora_merge_f16_ws_kernel(const 
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------------------------------ MMA issuer (one thread)
+        // Driven by what the adapter warps publish per A stage: one stage per (tile, adapter), or one empty stage for a
+        // tile without adapters. The products of a tile's adapters accumulate in the same TMEM tile.
         if (elect_one()) {
-            int prev_bs = -1;
-            for (int j = 0, tile; (tile = tile_of(j)) >= 0; ++j) {
-                const int s = j % WS_NA, b = j & 1;
-                if (!mbar_wait(afull0 + 8 * s, (j / WS_NA) & 1)) { ok = false; break; }
+            int ja = 0, bands_seen = 0;
+            for (int j = 0, tile; (tile = tile_of(j)) >= 0 && ok; ++j) {
+                const int b = j & 1;
                 if (!mbar_wait(dempty0 + 8 * b, ((j >> 1) & 1) ^ 1)) { ok = false; break; }
-                const int4 info = s_ab[s];
-                if (info.x > 0) {
-                    if (info.w) {
-                        if (prev_bs >= 0) umma_commit(bempty0 + 8 * prev_bs);     // the previous band's products are done
-                        prev_bs = info.z;
-                    }
-                    fence_proxy_async();          // async-copy writes of B/A -> tensor-core reads
-                    fence_after_sync();
-                    const uint32_t sBa = smem_u32(smem_b + info.z * WS_B_BYTES), sAa = smem_u32(smem_a + s * WS_A_BYTES);
-                    const int kpad = (info.y + 15) & ~15;
-                    constexpr uint32_t idesc = idesc_f16(128, 64) | (1u << 16);     // B operand MN-major
+                for (bool last = false; !last; ++ja) {
+                    const int s = ja % WS_NA;
+                    if (!mbar_wait(afull0 + 8 * s, (ja / WS_NA) & 1)) { ok = false; break; }
+                    const int4 info = s_ab[s];
+                    last = (info.w & 4) != 0;
+                    if (info.x > 0) {
+                        // a new band starts: once everything issued so far is complete, the previous band's B buffers are free
+                        if ((info.w & 3) == 3 && bands_seen++ > 0) umma_commit(bempty0 + 8 * ((info.z / MAXL) ^ 1));
+                        fence_proxy_async();          // async-copy writes of B/A -> tensor-core reads
+                        fence_after_sync();
+                        const uint32_t sBa = smem_u32(smem_b + info.z * WS_B_BYTES), sAa = smem_u32(smem_a + s * WS_A_BYTES);
+                        const int kpad = (info.y + 15) & ~15;
+                        const bool first = (info.w & 2) != 0;
+                        constexpr uint32_t idesc = idesc_f16(128, 64) | (1u << 16);     // B operand MN-major
 #pragma unroll
-                    for (int nb = 0; nb < 2; ++nb)
-                        for (int ks = 0; ks < kpad / 16; ++ks)
-                            umma_f16(tmem_base + b * 128 + nb * 64, smem_desc_sw128(sBa) + 2 * ks,
-                                     smem_desc_sw128(sAa + nb * 8192 + ks * 2048), idesc, ks != 0);
+                        for (int nb = 0; nb < 2; ++nb)
+                            for (int ks = 0; ks < kpad / 16; ++ks)
+                                umma_f16(tmem_base + b * 128 + nb * 64, smem_desc_sw128(sBa) + 2 * ks,
+                                         smem_desc_sw128(sAa + nb * 8192 + ks * 2048), idesc, !(first && ks == 0));
+                    }
+                    if (last) umma_commit(dfull0 + 8 * b);      // with no MMA outstanding this arrives at once (plain restore tiles)
+                    umma_commit(aempty0 + 8 * s);
                 }
-                umma_commit(dfull0 + 8 * b);      // with no MMA outstanding these arrive at once (plain restore tiles)
-                umma_commit(aempty0 + 8 * s);
             }
             if (!ok) atomicExch(status, 32);
         }
     } else {
         // ------------------------------------------------------------------------------------ adapter tiles (128 threads)
         const int pt = tid - 192;
-        WsLayer lay;
-        int band = -1, prev_li = -1, prev_row0 = -1;      // bands with an adapter so far; B buffer = band & 1
-        for (int j = 0, tile; (tile = tile_of(j)) >= 0; ++j) {
-            const int s = j % WS_NA;
-            if (!mbar_wait(aempty0 + 8 * s, ((j / WS_NA) & 1) ^ 1)) { ok = false; break; }
+        WsLayer<MAXL> lay;
+        int band = -1, prev_li = -1, prev_row0 = -1;      // bands with an adapter so far; B buffers = (band & 1) * MAXL + adapter
+        int ja = 0;
+        for (int j = 0, tile; (tile = tile_of(j)) >= 0 && ok; ++j) {
             lay.seek(layers, tile_start, n_layers, total_tiles, tile);
             const int rel = tile - lay.start, tm = rel / lay.tiles_n;
             const int row0 = tm * 128, col0 = (rel - tm * lay.tiles_n) * 128;
-            const int rank = lay.rank, kpad = (rank + 15) & ~15;
-            const uint32_t fb = afull0 + 8 * s;
+            const int nsub = lay.n_lora > 0 ? lay.n_lora : 1;
             bool new_band = false;
             if (lay.n_lora > 0) {
                 new_band = lay.li != prev_li || row0 != prev_row0;
@@ -788,42 +810,54 @@ __global__ void __launch_bounds__(WS_THREADS, 1) lora_merge_f16_ws_kernel(const 
                 prev_row0 = row0;
                 if (new_band) {
                     ++band;
-                    // the buffer is free once the products of the band before last are complete
+                    // the buffers are free once the products of the band before last are complete
                     if (!mbar_wait(bempty0 + 8 * (band & 1), ((band >> 1) & 1) ^ 1)) { ok = false; break; }
+                }
+            }
+#pragma unroll 1
+            for (int a = 0; a < nsub; ++a, ++ja) {
+                const int s = ja % WS_NA;
+                if (!mbar_wait(aempty0 + 8 * s, ((ja / WS_NA) & 1) ^ 1)) { ok = false; break; }
+                const int rank = lay.n_lora > 0 ? lay.rank[a < MAXL ? a : 0] : 0, kpad = (rank + 15) & ~15;
+                const __half* Bm = lay.B[a < MAXL ? a : 0];
+                const __half* Am = lay.A[a < MAXL ? a : 0];
+                const int bbuf = (band & 1) * MAXL + a;
+                const uint32_t fb = afull0 + 8 * s;
+                if (lay.n_lora > 0 && new_band) {
                     const int rows = min(128, lay.out_f - row0);
                     const int c = pt & 7;
                     if (c < (kpad >> 3)) {
-                        const uint32_t sB = smem_u32(smem_b + (band & 1) * WS_B_BYTES);
+                        const uint32_t sB = smem_u32(smem_b + bbuf * WS_B_BYTES);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const int r = (pt >> 3) + 16 * i;
                             const bool in = (c * 8) < rank && r < rows;
-                            const T* src = in ? lay.B + (size_t)(row0 + r) * rank + c * 8 : lay.B;
+                            const T* src = in ? Bm + (size_t)(row0 + r) * rank + c * 8 : Bm;
                             cp_async16(sB + b_off<T>(r, c), src, in ? 16 : 0);
                         }
                     }
                 }
-            }
-            if (pt == 0) {
-                s_ab[s] = make_int4(lay.n_lora, rank, band & 1, new_band ? 1 : 0);
-                mbar_arrive(fb);
-            }
-            if (lay.n_lora > 0) {
-                const int cols = min(128, lay.in_f - col0);
-                const int c = pt & 15;
-                const bool col_in = (c * 8) < cols;
-                const uint32_t sA = smem_u32(smem_a + s * WS_A_BYTES);
-                const T* src0 = lay.A + col0 + c * 8;
+                if (pt == 0) {
+                    s_ab[s] = make_int4(lay.n_lora, rank, bbuf, (new_band ? 1 : 0) | (a == 0 ? 2 : 0) | (a == nsub - 1 ? 4 : 0));
+                    mbar_arrive(fb);
+                }
+                if (lay.n_lora > 0) {
+                    const int cols = min(128, lay.in_f - col0);
+                    const int c = pt & 15;
+                    const bool col_in = (c * 8) < cols;
+                    const uint32_t sA = smem_u32(smem_a + s * WS_A_BYTES);
+                    const T* src0 = Am + col0 + c * 8;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int r = (pt >> 4) + 8 * i;
-                    if (r < kpad) {
-                        const bool in = r < rank && col_in;
-                        cp_async16(sA + a_off<T, true>(r, c), in ? src0 + (size_t)r * lay.in_f : lay.A, in ? 16 : 0);
+                    for (int i = 0; i < 8; ++i) {
+                        const int r = (pt >> 4) + 8 * i;
+                        if (r < kpad) {
+                            const bool in = r < rank && col_in;
+                            cp_async16(sA + a_off<T, true>(r, c), in ? src0 + (size_t)r * lay.in_f : Am, in ? 16 : 0);
+                        }
                     }
                 }
+                cp_async_mbar_arrive_noinc(fb);
             }
-            cp_async_mbar_arrive_noinc(fb);
         }
         if (!ok && lane == 0) atomicExch(status, 34);
         cp_async_wait<0>();
@@ -879,20 +913,27 @@ extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_til
         const char* e = getenv("KATZ_LORA_MMA");
         use_tc05 = (e && e[0] == '1') ? 0 : 1;
     }
-    if (w_dtype == KATZ_DTYPE_F16 && use_tc05 && (flags & KATZ_LORA_UNIFORM_TILES) && d_tile_maps) {
+    if (w_dtype == KATZ_DTYPE_F16 && use_tc05 && (flags & (KATZ_LORA_UNIFORM_TILES | KATZ_LORA_UNIFORM_TILES_2)) && d_tile_maps) {
         KATZ_CHECK_ARG((reinterpret_cast<uintptr_t>(d_tile_maps) & 63) == 0, KATZ_EALIGN);
         static bool attr3_dev[KATZ_MAX_DEVICES] = {false};
         bool& attr3 = attr3_dev[current_device_index()];
         if (!attr3) {
-            cudaError_t e = cudaFuncSetAttribute(lora_merge_f16_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WS_SMEM);
+            cudaError_t e = cudaFuncSetAttribute(lora_merge_f16_ws_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, WsCfg<1>::SMEM);
+            if (e != cudaSuccess) return (int)e;
+            e = cudaFuncSetAttribute(lora_merge_f16_ws_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, WsCfg<2>::SMEM);
             if (e != cudaSuccess) return (int)e;
             attr3 = true;
         }
         int* status = tc05_status_device_ptr();
         if (!status) return KATZ_ENOTREADY;
-        launch_k(lora_merge_f16_ws_kernel, grid, WS_THREADS, WS_SMEM, st, d_layers, reinterpret_cast<const CUtensorMap*>(d_tile_maps),
-                                                                    d_tile_start, n_layers, total_tiles, sign, status,
-                                                                    (flags & KATZ_LORA_NO_ADAPTERS) ? 1 : WS_CHUNK);
+        const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(d_tile_maps);
+        const int ch = (flags & KATZ_LORA_NO_ADAPTERS) ? 1 : WS_CHUNK;
+        if (flags & KATZ_LORA_UNIFORM_TILES)
+            launch_k(lora_merge_f16_ws_kernel<1>, grid, WS_THREADS, WsCfg<1>::SMEM, st, d_layers, maps, d_tile_start, n_layers,
+                     total_tiles, sign, status, ch);
+        else
+            launch_k(lora_merge_f16_ws_kernel<2>, grid, WS_THREADS, WsCfg<2>::SMEM, st, d_layers, maps, d_tile_start, n_layers,
+                     total_tiles, sign, status, ch);
     } else if (w_dtype == KATZ_DTYPE_F16 && use_tc05) {
         static bool attr2_dev[KATZ_MAX_DEVICES] = {false};
         bool& attr2 = attr2_dev[current_device_index()];

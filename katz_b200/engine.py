@@ -98,7 +98,10 @@ class GraphedStep:
                 net._hoisted_cond = ce if on else None
 
     def refresh_hoisted(self):
-        """Recompute the hoisted buffers from the static inputs (new prompt, new conditioning image, changed weights)."""
+        """Recompute the hoisted buffers from the static inputs (new prompt, new conditioning image, changed weights), and
+        whatever the nets derive from their weights. Callers that replay `self.graph` directly call this once per request."""
+        for net in [self.unet] + self.controlnets:
+            net.ensure_folds()
         if not self.hoist:
             return
         s = self.static
@@ -118,6 +121,8 @@ class GraphedStep:
             self._set_hoisted(False)      # other callers of these nets keep the reference's per-step semantics
 
     def _capture_inner(self, warmup, _lib):
+        for net in [self.unet] + self.controlnets:
+            net.ensure_folds()
         side = torch.cuda.Stream(device=self.unet.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -137,6 +142,8 @@ class GraphedStep:
         into them directly calls refresh_hoisted() first; changed weights are noticed here)."""
         if self.hoist and self._hoist_epochs != [n.weights_epoch for n, _, _ in self._hoisted]:
             self.refresh_hoisted()
+        for net in [self.unet] + self.controlnets:
+            net.ensure_folds()        # LayerNorm-folded weights follow LoRA merges / restores (a no-op otherwise)
         self.graph.replay()
         return self.out
 
@@ -175,6 +182,7 @@ class _GraphedCall:
             self.mid = [st(m) for m in mids]
         self.combine_scales = combine_scales
         self.copy_in(sample, timestep, ctx, added, down, mid)
+        unet.ensure_folds()
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -223,5 +231,6 @@ def graphed_unet_call(unet, sample, timestep, ctx, added, down, mid, combine_sca
         unet._graphs[key] = gc
     else:
         gc.copy_in(sample, timestep, ctx, added, down, mid)
+    unet.ensure_folds()
     gc.graph.replay()
     return gc.out

@@ -15,10 +15,24 @@ import ctypes
 import json
 from collections import OrderedDict
 
+import numpy as np
 import torch
 
 from . import _lib
 from ._lib import KATZ_DTYPE_F16, KATZ_DTYPE_F32, KatzError, LoraLayer, LORA_MAX_ADAPTERS
+
+# numpy view of `struct katz_lora_layer` (128 bytes): the host table is filled column by column
+_LAYER_DTYPE = np.dtype([("W", "<u8"), ("W0", "<u8"), ("B", "<u8", (LORA_MAX_ADAPTERS,)), ("A", "<u8", (LORA_MAX_ADAPTERS,)),
+                         ("rank", "<i4", (LORA_MAX_ADAPTERS,)), ("scale", "<f4", (LORA_MAX_ADAPTERS,)), ("out_features", "<i4"),
+                         ("in_features", "<i4"), ("n_lora", "<i4"), ("reserved_", "<i4")])
+assert _LAYER_DTYPE.itemsize == ctypes.sizeof(LoraLayer)
+
+
+class RegisteredAdapter:
+    """An adapter validated once against a LoraMerger's target set (LoraMerger.register_adapter)."""
+
+    def __init__(self, merger, adapter, up_ptr, down_ptr, rank):
+        self.merger, self.adapter, self.up_ptr, self.down_ptr, self.rank = merger, adapter, up_ptr, down_ptr, rank
 
 REFERENCE_UNET_SCALE = float(torch.tensor(20000.0 / 64.0, dtype=torch.float16))  # lora_utils.py:22
 
@@ -36,9 +50,13 @@ class LoraMerger:
 
     weights: OrderedDict key -> CUDA tensor [out, in] (contiguous rows; views into fused buffers are fine).
     keep_pristine: clone every target weight once (W0) so restore is a copy and merge never accumulates error.
+    on_change: callable run after every merge / restore launch; pass the model's `invalidate_caches` (KatzUNet.lora_merger
+    does) so that whatever the model derives from its weights follows them.
     """
 
-    def __init__(self, weights, keep_pristine=True):
+    def __init__(self, weights, keep_pristine=True, on_change=None):
+        self.on_change = on_change      # called after every launch that rewrites the weights (a model passes its
+        #                                 invalidate_caches, so storage derived from the weights is rebuilt before the next step)
         if not weights:
             raise KatzError("no target weights")
         self.keys = list(weights.keys())
@@ -68,6 +86,16 @@ class LoraMerger:
         # the host table lives in the pinned staging buffer itself, so an upload is one asynchronous copy
         self._h_pinned = torch.empty(ctypes.sizeof(LoraLayer) * n, dtype=torch.uint8).pin_memory()
         self._h_table = (LoraLayer * n).from_address(self._h_pinned.data_ptr())
+        self._np_table = np.frombuffer((ctypes.c_char * (ctypes.sizeof(LoraLayer) * n)).from_address(self._h_pinned.data_ptr()),
+                                       dtype=_LAYER_DTYPE, count=n)
+        self._shapes = [tuple(w.shape) for w in self.weights.values()]
+        self._np_table["W"] = np.array([w.data_ptr() for w in self.weights.values()], np.uint64)
+        self._np_table["out_features"] = [sh[0] for sh in self._shapes]
+        self._np_table["in_features"] = [sh[1] for sh in self._shapes]
+        self._np_table["reserved_"] = 0
+        self._w0_ptr = np.zeros(n, np.uint64)
+        if self.pristine is not None:
+            self._w0_ptr = np.array([self.pristine[k].data_ptr() for k in self.keys], np.uint64)
         self._d_table = torch.empty(ctypes.sizeof(self._h_table), dtype=torch.uint8, device=self.device)
         self._keepalive = []
         self._d_maps = None        # TMA tensor maps of the fp16 fast path (two per layer), encoded on first use
@@ -80,6 +108,7 @@ class LoraMerger:
         """Record the current live weights as W0 (gen_unet_state_dict.py:54-58 plays this role in the reference)."""
         self.pristine = OrderedDict((k, w.clone()) for k, w in self.weights.items())
         self._d_maps = None
+        self._w0_ptr = np.array([self.pristine[k].data_ptr() for k in self.keys], np.uint64)
 
     def algorithmic_bytes(self, ranks):
         """Bytes one merge pass must move: read + write of every W, plus each adapter's A and B once."""
@@ -89,8 +118,43 @@ class LoraMerger:
         return 2 * wb + ab
 
     # -- table --------------------------------------------------------------------------------------------------
+    def _adapter_arrays(self, ad):
+        """Per-layer arrays (up pointers, down pointers, ranks) of one adapter, validated against the target set. A
+        `RegisteredAdapter` carries them ready-made."""
+        if isinstance(ad, RegisteredAdapter):
+            if ad.merger is not self:
+                raise KatzError("this adapter was registered with another LoraMerger")
+            return ad.up_ptr, ad.down_ptr, ad.rank
+        n = len(self.keys)
+        up_ptr, down_ptr, rank = np.zeros(n, np.uint64), np.zeros(n, np.uint64), np.zeros(n, np.int32)
+        dt, dev = self.dtype, self.device
+        get = ad.get
+        for i, k in enumerate(self.keys):
+            pair = get(k)
+            if pair is None:
+                continue
+            up, down = pair
+            if up.dtype != dt or down.dtype != dt or up.device != dev or down.device != dev:
+                raise KatzError("adapter tensors for %s must be %s on %s" % (k, dt, dev))
+            if not up.is_contiguous() or not down.is_contiguous():
+                raise KatzError("adapter tensors for %s must be contiguous" % k)
+            r = down.shape[0]
+            o, c = self._shapes[i]
+            if up.shape != (o, r) or down.shape != (r, c):
+                raise KatzError("adapter shapes for %s do not match W%s: up%s down%s" % (k, (o, c), tuple(up.shape), tuple(down.shape)))
+            up_ptr[i], down_ptr[i], rank[i] = up.data_ptr(), down.data_ptr(), r
+        return up_ptr, down_ptr, rank
+
+    def register_adapter(self, ad):
+        """Validate an adapter once and keep its table columns: a serving loop that switches between a fixed pool of
+        adapters passes the returned handle to merge() and pays no per-layer host work per switch. The handle keeps
+        the tensors alive; do not replace tensors inside `ad` afterwards."""
+        up_ptr, down_ptr, rank = self._adapter_arrays(ad)
+        return RegisteredAdapter(self, ad, up_ptr, down_ptr, rank)
+
     def _fill(self, adapters, scales, use_pristine):
-        """adapters: list of dict key -> (up [out,r], down [r,in]) on this device, same dtype as W."""
+        """adapters: list of dict key -> (up [out,r], down [r,in]) on this device, same dtype as W (or handles from
+        register_adapter). The table is written as whole numpy columns into the pinned staging buffer."""
         if len(adapters) > LORA_MAX_ADAPTERS:
             raise KatzError("at most %d adapters per merge" % LORA_MAX_ADAPTERS)
         if use_pristine and self.pristine is None:
@@ -98,42 +162,37 @@ class LoraMerger:
         lib = _lib.load()
         if self._upload_done is not None:
             self._upload_done.synchronize()
-        keep = []
-        uniform = True
-        for i, k in enumerate(self.keys):
-            w = self.weights[k]
-            e = self._h_table[i]
-            e.W = w.data_ptr()
-            e.W0 = self.pristine[k].data_ptr() if use_pristine else None
-            e.out_features, e.in_features = w.shape
-            n = 0
-            for ad, s in zip(adapters, scales):
-                if k not in ad:
-                    continue
-                up, down = ad[k]
-                if up.dtype != self.dtype or down.dtype != self.dtype or up.device != self.device or down.device != self.device:
-                    raise KatzError("adapter tensors for %s must be %s on %s" % (k, self.dtype, self.device))
-                if not up.is_contiguous() or not down.is_contiguous():
-                    raise KatzError("adapter tensors for %s must be contiguous" % k)
-                r = down.shape[0]
-                if up.shape != (w.shape[0], r) or down.shape != (r, w.shape[1]):
-                    raise KatzError("adapter shapes for %s do not match W%s: up%s down%s" % (k, tuple(w.shape), tuple(up.shape), tuple(down.shape)))
-                e.B[n] = up.data_ptr()
-                e.A[n] = down.data_ptr()
-                e.rank[n] = r
-                e.scale[n] = float(s[k]) if isinstance(s, dict) else float(s)
-                keep.append((up, down))
-                n += 1
-            e.n_lora = n
-            if n > 1 or (n == 1 and e.rank[0] > 64):
-                uniform = False
+        n = len(self.keys)
+        tab = self._np_table
+        tab["W0"] = self._w0_ptr if use_pristine else 0
+        slot = np.zeros(n, np.int64)             # next free adapter slot of every layer
+        cols = {f: np.zeros((n, LORA_MAX_ADAPTERS), tab[f].dtype) for f in ("B", "A", "rank", "scale")}
+        rows = np.arange(n)
+        for ad, s in zip(adapters, scales):
+            up_ptr, down_ptr, rank = self._adapter_arrays(ad)
+            has = rank > 0
+            if isinstance(s, dict):
+                sc = np.array([float(s.get(k, 0.0)) for k in self.keys], np.float32)
+            else:
+                sc = np.full(n, float(s), np.float32)
+            r, c = rows[has], slot[has]
+            cols["B"][r, c], cols["A"][r, c], cols["rank"][r, c], cols["scale"][r, c] = up_ptr[has], down_ptr[has], rank[has], sc[has]
+            slot[has] += 1
+        for f, v in cols.items():
+            tab[f] = v
+        tab["n_lora"] = slot
         bad = ctypes.c_int(-1)
-        rc = lib.katz_lora_table_check(self._h_table, len(self.keys), self.code, ctypes.byref(bad))
+        rc = lib.katz_lora_table_check(self._h_table, n, self.code, ctypes.byref(bad))
         if rc != 0:
             _lib.check(rc, "katz_lora_table_check(%s)" % self.keys[bad.value])
-        self._keepalive = keep
-        # flags: bit 0 promises at most one adapter per layer of rank <= 64 (the fast path), bit 1 no adapter at all
-        self._flags = (1 if uniform else 0) | (2 if not keep else 0)
+        self._keepalive = list(adapters)
+        rk, sc, nl = cols["rank"], cols["scale"], slot
+        any_adapter = bool((nl > 0).any())
+        uniform = bool((nl <= 1).all() and (rk[:, 0] <= 64).all())                 # at most one adapter of rank <= 64 per layer
+        uniform2 = bool((nl <= 2).all() and (rk[:, :2] <= 64).all() and ((nl < 2) | (sc[:, 0] == sc[:, 1])).all())
+        # flags: bit 0 promises at most one adapter per layer of rank <= 64 (the fast path), bit 1 no adapter at all, bit 2
+        # at most two adapters of rank <= 64 with one scale per layer (the same kernel, both products in one accumulator)
+        self._flags = (1 if uniform else (4 if uniform2 else 0)) | (2 if not any_adapter else 0)
         self._d_table.copy_(self._h_pinned, non_blocking=True)
         self._upload_done = torch.cuda.Event()
         self._upload_done.record(torch.cuda.current_stream(self.device))
@@ -165,6 +224,8 @@ class LoraMerger:
                                        self._flags, ctypes.c_void_p(maps.data_ptr() if maps is not None else None), st),
                    "katz_lora_merge")
         _lib.note_launches(1)
+        if self.on_change is not None:
+            self.on_change()
 
     # -- operations ---------------------------------------------------------------------------------------------
     def replay(self):

@@ -49,7 +49,7 @@ class KatzLoraPipelineMixin:
         if self._lora_merger is None or self._lora_keys != keys:
             if self._lora_merger is not None and self._lora_merger.merged:
                 raise KatzError("the LoRA target set changed while adapters are merged; restore first")
-            self._lora_merger = LoraMerger(self.unet.lora_targets(keys))
+            self._lora_merger = LoraMerger(self.unet.lora_targets(keys), on_change=self.unet.invalidate_caches)
             self._lora_keys = keys
             self._pristine_src = None
         return self._lora_merger

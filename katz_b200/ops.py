@@ -61,17 +61,72 @@ def tc05_status():
     return _lib.load().katz_tc05_status()
 
 
-def feed_forward_geglu(x, w, bias, out=None):
+class LnFold:
+    """A LayerNorm folded into the linear layer that consumes it: `wf` = W diag(gamma) (fp16), `c12` = per output column
+    (sum_k W'[n,k], sum_k W[n,k] beta[k] + bias[n]) in fp32, `eps` the norm's epsilon. Built by `ln_fold`."""
+
+    def __init__(self, wf, c12, eps):
+        self.wf, self.c12, self.eps = wf, c12, float(eps)
+
+
+def ln_fold(w, gamma, beta, bias=None, eps=1e-5, out=None):
+    """(Re)compute the folded constants of LayerNorm(gamma, beta) followed by linear(w, bias). Pass `out` (an LnFold) to
+    refresh it in place after `w` changed."""
+    _f16(w, "w"), _f16(gamma, "gamma"), _f16(beta, "beta")
+    if not w.is_contiguous() or w.dim() != 2 or gamma.numel() != w.shape[1] or beta.numel() != w.shape[1]:
+        raise KatzError("ln_fold: w must be a contiguous [N, K] tensor and gamma/beta [K]")
+    N, K = w.shape
+    if out is None:
+        out = LnFold(torch.empty_like(w), torch.empty((N, 2), dtype=torch.float32, device=w.device), eps)
+    call("katz_ln_fold_f16", _p(w), _p(gamma), _p(beta), _p(bias), _p(out.wf), _p(out.c12), N, K, _stream())
+    return out
+
+
+def ln_fusable(M, K, N):
+    """Whether `linear(layer_norm(x), w)` with x [M, K], w [N, K] can run as one folded GEMM on the tcgen05 path."""
+    return _use_tc05() and K % 64 == 0 and N % 8 == 0
+
+
+def _extras(x, ln, ln_stats, stats_out, M, K, N):
+    from ._lib import LinearExtras
+    ex = LinearExtras()
+    keep = []
+    if ln is not None:
+        if ln_stats is None or ln_stats.dtype != torch.float32 or not ln_stats.is_contiguous() or ln_stats.dim() != 3 \
+                or ln_stats.shape[1] != M or ln_stats.shape[2] != 2 or ln_stats.shape[0] != (K + 31) // 32:
+            raise KatzError("folded LayerNorm needs the producer's statistics [ceil(K/32), M, 2] fp32")
+        ex.ln_stats, ex.ln_c12, ex.ln_slots, ex.ln_eps = ln_stats.data_ptr(), ln.c12.data_ptr(), ln_stats.shape[0], ln.eps
+    if stats_out is True:
+        stats_out = torch.empty(((N + 31) // 32, M, 2), dtype=torch.float32, device=x.device)
+    if stats_out is not None:
+        if stats_out.dtype != torch.float32 or not stats_out.is_contiguous() or tuple(stats_out.shape) != ((N + 31) // 32, M, 2):
+            raise KatzError("stats_out must be a contiguous fp32 [ceil(N/32), M, 2] tensor")
+        ex.stats_out = stats_out.data_ptr()
+    return ex, stats_out
+
+
+def feed_forward_geglu(x, w, bias, out=None, ln=None, ln_stats=None):
     """GEGLU feed-forward projection: x[M,K], w[2F,K] (the unsplit `proj`), bias[2F] -> [M,F] = h * gelu(g).
-    One fused tcgen05 GEMM when the shape allows, else GEMM + gating kernel."""
-    _f16(x, "x"), _f16(w, "w")
+    One fused tcgen05 GEMM when the shape allows, else GEMM + gating kernel. With `ln` (an LnFold whose `wf` replaces `w`;
+    `bias` is already inside it) and `ln_stats` (the row statistics of x) x is the input of the LayerNorm."""
+    _f16(x, "x")
+    if ln is not None:
+        w, bias = ln.wf, None
+    _f16(w, "w")
     M, K = x.shape
     F = w.shape[0] // 2
     if out is None:
         out = torch.empty((M, F), dtype=torch.float16, device=x.device)
-    if (_use_tc05() and os.environ.get("KATZ_FUSED_GEGLU", "1") == "1" and K % 64 == 0 and F % 16 == 0
-            and x.stride(1) == 1 and x.stride(0) % 8 == 0 and w.is_contiguous() and _al16(x) and _al16(w) and _al16(out)
-            and _al16(bias) and out.stride(0) % 8 == 0):
+    fused_ok = (_use_tc05() and os.environ.get("KATZ_FUSED_GEGLU", "1") == "1" and K % 64 == 0 and F % 16 == 0
+                and x.stride(1) == 1 and x.stride(0) % 8 == 0 and w.is_contiguous() and _al16(x) and _al16(w) and _al16(out)
+                and _al16(bias) and out.stride(0) % 8 == 0)
+    if ln is not None:
+        if not fused_ok:
+            raise KatzError("feed_forward_geglu: this shape cannot take a folded LayerNorm")
+        ex, _ = _extras(x, ln, ln_stats, None, M, K, 2 * F)
+        call("katz_linear_geglu_ex_f16", _p(x), x.stride(0), _p(w), _p(out), out.stride(0), M, F, K, None, ctypes.byref(ex), _stream())
+        return out
+    if fused_ok:
         call("katz_linear_geglu_f16", _p(x), x.stride(0), _p(w), _p(out), out.stride(0), M, F, K, _p(bias), _stream())
         return out
     return geglu_erf(linear(x, w, bias), out=out)
@@ -86,10 +141,17 @@ def upsample_nearest2x(x, out=None):
     return out
 
 
-def linear(x, w, bias=None, residual=None, act=ACT_NONE, rowvec=None, rows_per_batch=0, out=None, out_scale=1.0):
+def linear(x, w, bias=None, residual=None, act=ACT_NONE, rowvec=None, rows_per_batch=0, out=None, out_scale=1.0,
+           ln=None, ln_stats=None, stats_out=None):
     """out[M,N] = x[M,K] @ w[N,K]^T (+bias) (+rowvec[m // rows_per_batch]) -> act -> (+residual) * out_scale.
-    `x`, `residual`, `out` may be row-strided 2-D views (unit column stride)."""
-    _f16(x, "x"), _f16(w, "w")
+    `x`, `residual`, `out` may be row-strided 2-D views (unit column stride).
+    Folded LayerNorm: with `ln` (an LnFold; its `wf` replaces `w` and holds the bias) and `ln_stats` the call computes
+    linear(layer_norm(x)); with `stats_out=True` (or a buffer) it also returns the row statistics of its own output for the
+    next folded LayerNorm: `(out, stats)`."""
+    _f16(x, "x")
+    if ln is not None:
+        w, bias = ln.wf, None
+    _f16(w, "w")
     if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
         raise KatzError("linear: shape mismatch x%s w%s" % (tuple(x.shape), tuple(w.shape)))
     if x.stride(1) != 1 or not w.is_contiguous():
@@ -102,8 +164,16 @@ def linear(x, w, bias=None, residual=None, act=ACT_NONE, rowvec=None, rows_per_b
         raise KatzError("linear: bad out")
     if residual is not None and (residual.shape != (M, N) or residual.stride(1) != 1):
         raise KatzError("linear: bad residual")
-    name = ("katz_linear_f16" if (_use_tc05() and _tc05_linear_ok(x, w, bias, residual, rowvec, out)
-                                  and _tc05_rowvec_ok(rowvec, rows_per_batch)) else "katz_linear_f16_mma")
+    tc05 = _use_tc05() and _tc05_linear_ok(x, w, bias, residual, rowvec, out) and _tc05_rowvec_ok(rowvec, rows_per_batch)
+    if ln is not None or stats_out is not None:
+        if not tc05:
+            raise KatzError("linear: this shape cannot take a folded LayerNorm / emit row statistics (tcgen05 path only)")
+        ex, stats = _extras(x, ln, ln_stats, stats_out, M, K, N)
+        call("katz_linear_ex_f16", _p(x), x.stride(0), _p(w), _p(out), out.stride(0), M, N, K, _p(bias), _p(rowvec),
+             rowvec.stride(0) if rowvec is not None else 0, rows_per_batch, _p(residual),
+             residual.stride(0) if residual is not None else 0, act, float(out_scale), ctypes.byref(ex), _stream())
+        return (out, stats) if stats is not None else out
+    name = "katz_linear_f16" if tc05 else "katz_linear_f16_mma"
     call(name, _p(x), x.stride(0), _p(w), _p(out), out.stride(0), M, N, K, _p(bias), _p(rowvec),
          rowvec.stride(0) if rowvec is not None else 0, rows_per_batch, _p(residual),
          residual.stride(0) if residual is not None else 0, act, float(out_scale), _stream())

@@ -75,7 +75,9 @@ class LoraRequestStream:
     merge pass `W = W0 + s*B*A` regardless of what was merged before."""
 
     def __init__(self, denoiser, merger, adapters, scale=1.0):
-        self.denoiser, self.merger, self.adapters, self.scale = denoiser, merger, list(adapters), scale
+        self.denoiser, self.merger, self.scale = denoiser, merger, scale
+        # validated once: a switch then costs one table upload and one merge launch, no per-layer host work
+        self.adapters = [merger.register_adapter(a) for a in adapters]
         self.current = None
 
     def run(self, lora_ids, request_inputs, num_inference_steps=50, seed=0):

@@ -11,6 +11,7 @@ The computation follows `_down_forward` -> ControlNet residual add -> `_up_forwa
 residuals and the mid residual. Activations are NHWC fp16 end to end ([B, H, W, C] is also the [B, H*W, C] token
 layout, so Transformer2DModel's permutes disappear); NCHW appears only at the model boundary.
 """
+import os
 from collections import OrderedDict
 
 import torch
@@ -177,6 +178,17 @@ class _Net:
         self._kv_cache = None
         self._hoisted_kv = None
         self.weights_epoch = 0         # bumped whenever weights change (load_state_dict, LoRA merge / restore)
+        # LayerNorms of the transformer blocks folded into the GEMMs that consume them (ops.LnFold per block: norm1 -> fused
+        # q/k/v, norm2 -> attn2.to_q, norm3 -> GEGLU projection). The folded weights are DERIVED storage: the reference
+        # keys keep addressing the plain weights (LoRA merges and state_dict() see those) and ensure_folds() re-derives
+        # after every change. OFF by default: it removes 210 of the SDXL step's 957 launches but the step gets SLOWER
+        # (19.2 -> 20.4 ms on a B200). With programmatic dependent launch a stand-alone LayerNorm runs in the shadow of the
+        # next GEMM's set-up (a block of six GEMMs takes 146 us with or without the three LayerNorm launches between them),
+        # while the statistics and the per-column correction lengthen the GEMM epilogues, which are on the critical path of
+        # the single-wave launches (+12 us per block). It also costs 2.4 GB for the folded copies.
+        self.fuse_ln = os.environ.get("KATZ_FUSED_LN", "0") == "1"
+        self._folds = {}
+        self._folds_epoch = -1
 
     # ---- state-dict surface (reference names)
     def load_state_dict(self, sd, strict=True):
@@ -195,6 +207,11 @@ class _Net:
             out[k] = self.w.t[k]
         return out
 
+    def lora_merger(self, keys, keep_pristine=True):
+        """A LoraMerger over this model's linears `keys` that tells the model whenever it rewrites them."""
+        from .lora import LoraMerger
+        return LoraMerger(self.lora_targets(keys), keep_pristine=keep_pristine, on_change=self.invalidate_caches)
+
     def invalidate_caches(self):
         """Call after anything that changes weights (a LoRA merge or restore writes the fused K/V weight buffer)."""
         self._kv_cache_key = None
@@ -203,6 +220,25 @@ class _Net:
     def begin_request(self):
         """Start of a request in an eager serving loop: whatever was cached for the previous prompt / image is dropped."""
         self._kv_cache_key = None
+
+    def ensure_folds(self):
+        """Re-derive the LayerNorm-folded weights if any weight changed since they were built (a few GB of streaming, about a
+        millisecond for SDXL). Called at the start of every eager step and before every graph replay; never inside a
+        capture (the kernels would be baked into the graph)."""
+        if not self.fuse_ln or self._folds_epoch == self.weights_epoch:
+            return
+        if torch.cuda.is_current_stream_capturing():
+            raise KatzError("weights changed during CUDA-graph capture: call ensure_folds() before capturing")
+        P = self._P
+        blocks = sorted(k[: -len(".norm1.weight")] for k in self.w.shapes if k.endswith(".norm1.weight") and ".transformer_blocks." in k)
+        for b in blocks:
+            old = self._folds.get(b, (None, None, None))
+            qkv = ops.ln_fold(self.w.fused[b + ".attn1.qkv"], P(b + ".norm1.weight"), P(b + ".norm1.bias"), None, 1e-5, out=old[0])
+            q = ops.ln_fold(P(b + ".attn2.to_q.weight"), P(b + ".norm2.weight"), P(b + ".norm2.bias"), None, 1e-5, out=old[1])
+            ff = ops.ln_fold(P(b + ".ff.net.0.proj.weight"), P(b + ".norm3.weight"), P(b + ".norm3.bias"),
+                             P(b + ".ff.net.0.proj.bias"), 1e-5, out=old[2])
+            self._folds[b] = (qkv, q, ff)
+        self._folds_epoch = self.weights_epoch
 
     # ---- pieces
     def _P(self, k):
@@ -288,6 +324,35 @@ class _Net:
         B, H, W, C = x.shape
         M = B * H * W
         h = self._gn(x, P(p + ".norm.weight"), P(p + ".norm.bias"), 1e-6, ACT_NONE)
+        # LayerNorm folded into its consumer: every GEMM whose output a LayerNorm reads also leaves that output's row
+        # statistics, and the consumer applies them in its epilogue (no LayerNorm kernel, no normalised copy of the rows)
+        fused = self.fuse_ln and self._folds_epoch == self.weights_epoch and ops.ln_fusable(M, C, C)
+        if not fused:
+            return self._transformer_unfused(p, x, h, kv, heads, n_layers)
+        h, st = ops.linear(h.view(M, C), P(p + ".proj_in.weight"), P(p + ".proj_in.bias"), stats_out=True)
+        for i in range(n_layers):
+            b = "%s.transformer_blocks.%d" % (p, i)
+            f_qkv, f_q, f_ff = self._folds[b]
+            qkv = ops.linear(h, f_qkv.wf, ln=f_qkv, ln_stats=st).view(B, H * W, 3 * C)
+            a = self._self_attention(qkv, C, heads)
+            h, st = ops.linear(a.view(M, C), P(b + ".attn1.to_out.0.weight"), P(b + ".attn1.to_out.0.bias"), residual=h, stats_out=True)
+            q = ops.linear(h, f_q.wf, ln=f_q, ln_stats=st).view(B, H * W, C)
+            off = self.w.cross_kv_offset[b]
+            a = ops.attention(q, kv[:, :, off:off + C], kv[:, :, off + C:off + 2 * C], heads)
+            h, st = ops.linear(a.view(M, C), P(b + ".attn2.to_out.0.weight"), P(b + ".attn2.to_out.0.bias"), residual=h, stats_out=True)
+            f = ops.feed_forward_geglu(h, f_ff.wf, None, ln=f_ff, ln_stats=st)
+            if i + 1 < n_layers:
+                h, st = ops.linear(f, P(b + ".ff.net.2.weight"), P(b + ".ff.net.2.bias"), residual=h, stats_out=True)
+            else:
+                h = ops.linear(f, P(b + ".ff.net.2.weight"), P(b + ".ff.net.2.bias"), residual=h)
+        out = ops.linear(h, P(p + ".proj_out.weight"), P(p + ".proj_out.bias"), residual=x.view(M, C))
+        return out.view(B, H, W, C)
+
+    def _transformer_unfused(self, p, x, h, kv, heads, n_layers):
+        """The same blocks with stand-alone LayerNorm kernels (shapes the folded path declines, KATZ_FUSED_LN=0)."""
+        P = self._P
+        B, H, W, C = x.shape
+        M = B * H * W
         h = ops.linear(h.view(M, C), P(p + ".proj_in.weight"), P(p + ".proj_in.bias"))
         for i in range(n_layers):
             b = "%s.transformer_blocks.%d" % (p, i)
@@ -366,6 +431,8 @@ class KatzUNet(_Net):
 
     def down_forward(self, x, timestep, ctx, te, ti):
         """`_down_forward` (unet_2d_condition.py:1127-1252) on NHWC tensors."""
+        if not torch.cuda.is_current_stream_capturing():
+            self.ensure_folds()
         B = x.shape[0]
         emb, temb_all = self._embeddings(timestep, te, ti, B)
         kv = self._cross_kv(ctx)
@@ -479,6 +546,8 @@ class KatzControlNet(_Net):
         """`_controlnet_forward` (controlnet.py:687-847): returns (list of 9 down residuals, mid residual), each already
         multiplied by `conditioning_scale`; NCHW like the reference unless `nhwc_out`."""
         P = self._P
+        if not torch.cuda.is_current_stream_capturing():
+            self.ensure_folds()
         x, ctx, te, ti = self._prep_inputs(sample, encoder_hidden_states, added_cond_kwargs)
         B = x.shape[0]
         emb, temb_all = self._embeddings(timestep, te, ti, B)

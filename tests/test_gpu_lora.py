@@ -143,3 +143,43 @@ def test_merge_fast_path_odd_ranks_and_layers_without_adapter(cuda_device, rank)
     for k in W:
         assert torch.equal(Wg[k].cpu(), W[k]), k
     assert ops.tc05_status() == 0
+
+
+def test_two_adapters_fast_path_ragged_shapes_missing_second_adapter_and_registered_handles(cuda_device):
+    """Two adapters per layer (ranks 64 and 32, one scale) run on the warp-specialised kernel with both products in one
+    accumulator: ragged edge tiles, a layer the second adapter does not touch, a layer neither touches, a second merge
+    from the pristine weights, and the pre-validated handles a serving loop uses."""
+    from katz_b200 import ops
+    from katz_b200.lora import LoraMerger
+    from oracle import lora_oracle
+    shapes = [(320, 320), (640, 2048), (200, 136), (1280, 1280), (384, 1280), (5120, 640)]
+    W, ad1 = _make(shapes, 64, torch.float16, 21)
+    _, ad2 = _make(shapes, 32, torch.float16, 22)
+    del ad2["layer1.weight"]
+    del ad1["layer4.weight"], ad2["layer4.weight"]
+    Wg = _cuda(W)
+    m = LoraMerger(Wg)
+    h1, h2 = m.register_adapter(_cuda(ad1)), m.register_adapter(_cuda(ad2))
+    ref = lora_oracle.merge_set(W, [ad1, ad2], [0.5, 0.5])
+    for rep in range(2):
+        m.merge([h1, h2], [0.5, 0.5])
+        assert m._flags & 4                       # the two-adapter fast path was taken
+        for k in W:
+            d = (Wg[k].cpu().float() - ref[k].float()).abs()
+            assert float(d.max()) <= 2 ** -8 * float(ref[k].float().abs().max()), (rep, k)
+        assert torch.equal(Wg["layer4.weight"].cpu(), W["layer4.weight"])
+    m.merge([h2], [2.0])                          # back to one adapter: whatever was merged is replaced
+    ref1 = lora_oracle.merge_set(W, [ad2], [2.0])
+    for k in W:
+        d = (Wg[k].cpu().float() - ref1[k].float()).abs()
+        assert float(d.max()) <= 2 ** -9 * float(ref1[k].float().abs().max()), k
+    m.merge([h1, h2], [1.0, 0.5])                 # different scales: the general kernel
+    assert not (m._flags & 5)
+    ref2 = lora_oracle.merge_set(W, [ad1, ad2], [1.0, 0.5])
+    for k in W:
+        d = (Wg[k].cpu().float() - ref2[k].float()).abs()
+        assert float(d.max()) <= 2 ** -8 * float(ref2[k].float().abs().max()), k
+    m.restore()
+    for k in W:
+        assert torch.equal(Wg[k].cpu(), W[k]), k
+    assert ops.tc05_status() == 0

@@ -331,3 +331,60 @@ def test_attention_tcgen05_large_logits_rescale(cuda_device, monkeypatch):
     out = ops.attention(q, k, v, H)
     assert ops.tc05_status() == 0
     assert float((out.float() - ref).abs().max()) < 8e-3
+
+
+@pytest.mark.parametrize("M,C,N,row_shift", [(2048, 1280, 3840, 0.0), (8192, 640, 1920, 3.0), (2048, 1280, 1280, -1.5), (300, 64, 192, 0.5)])
+def test_layer_norm_folded_into_linear(cuda_device, M, C, N, row_shift):
+    """nn.LayerNorm followed by nn.Linear as ONE GEMM on the raw rows (LN(x) W^T = rstd (x W'^T) - rstd mean c1 + c2): the
+    producer GEMM leaves the rows' (sum, sum of squares) per 32-column chunk, the consumer applies them. Against fp32 torch
+    on the same fp16 inputs, and against the unfused pair of kernels (whose extra fp16 rounding of the normalised rows the
+    folded form does not have)."""
+    from katz_b200 import ops
+    g = torch.Generator().manual_seed(31)
+    a = torch.randn(M, C, generator=g).half().cuda()
+    wp = (torch.randn(C, C, generator=g) / C ** 0.5).half().cuda()
+    bp = torch.randn(C, generator=g).half().cuda()
+    res = (torch.randn(M, C, generator=g) * 2 + row_shift).half().cuda()      # rows with a mean that is not small
+    gamma = (1 + 0.2 * torch.randn(C, generator=g)).half().cuda()
+    beta = (0.2 * torch.randn(C, generator=g)).half().cuda()
+    w = (torch.randn(N, C, generator=g) / C ** 0.5).half().cuda()
+    bias = torch.randn(N, generator=g).half().cuda()
+    # producer: x = a wp^T + bp + res, with the statistics of the fp16 x it stored
+    x, st = ops.linear(a, wp, bp, residual=res, stats_out=True)
+    assert torch.equal(x, ops.linear(a, wp, bp, residual=res))                # emitting statistics changes nothing else
+    xf = x.float()
+    s1 = st[:, :, 0].sum(0)
+    s2 = st[:, :, 1].sum(0)
+    assert torch.allclose(s1, xf.sum(1), rtol=1e-5, atol=1e-2) and torch.allclose(s2, (xf * xf).sum(1), rtol=1e-5, atol=1e-2)
+    fold = ops.ln_fold(w, gamma, beta, bias)
+    out = ops.linear(x, fold.wf, ln=fold, ln_stats=st)
+    ref = F.linear(F.layer_norm(xf, (C,), gamma.float(), beta.float(), 1e-5), w.float(), bias.float())
+    unfused = ops.linear(ops.layer_norm(x, gamma, beta), w, bias)
+    e_fold = float((out.float() - ref).norm() / ref.norm())
+    e_unf = float((unfused.float() - ref).norm() / ref.norm())
+    assert e_fold <= 1e-3 and e_fold <= 2.0 * e_unf + 1e-4, (e_fold, e_unf)
+    assert float((out.float() - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
+    assert ops.tc05_status() == 0
+
+
+@pytest.mark.parametrize("M,C,Fw", [(2048, 1280, 5120), (8192, 640, 2560), (256, 128, 512)])
+def test_layer_norm_folded_into_geglu(cuda_device, M, C, Fw):
+    from katz_b200 import ops
+    g = torch.Generator().manual_seed(32)
+    a = torch.randn(M, C, generator=g).half().cuda()
+    wp = (torch.randn(C, C, generator=g) / C ** 0.5).half().cuda()
+    res = (torch.randn(M, C, generator=g) + 1.0).half().cuda()
+    gamma = (1 + 0.2 * torch.randn(C, generator=g)).half().cuda()
+    beta = (0.2 * torch.randn(C, generator=g)).half().cuda()
+    w = (torch.randn(2 * Fw, C, generator=g) / C ** 0.5).half().cuda()
+    bias = torch.randn(2 * Fw, generator=g).half().cuda()
+    x, st = ops.linear(a, wp, None, residual=res, stats_out=True)
+    fold = ops.ln_fold(w, gamma, beta, bias)
+    out = ops.feed_forward_geglu(x, fold.wf, None, ln=fold, ln_stats=st)
+    hg = F.linear(F.layer_norm(x.float(), (C,), gamma.float(), beta.float(), 1e-5), w.float(), bias.float())
+    ref = hg[:, :Fw] * F.gelu(hg[:, Fw:])
+    unfused = ops.feed_forward_geglu(ops.layer_norm(x, gamma, beta), w, bias)
+    e_fold = float((out.float() - ref).norm() / ref.norm())
+    e_unf = float((unfused.float() - ref).norm() / ref.norm())
+    assert e_fold <= 1.5e-3 and e_fold <= 2.0 * e_unf + 1e-4, (e_fold, e_unf)
+    assert ops.tc05_status() == 0

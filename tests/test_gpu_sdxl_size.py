@@ -88,7 +88,7 @@ def sdxl(cuda_device):
     del sd
     keys = lora_target_keys(CFG, include_proj=True)
     assert len(keys) == 722
-    merger = LoraMerger(unet.lora_targets(keys))
+    merger = LoraMerger(unet.lora_targets(keys), on_change=unet.invalidate_caches)
     return dict(unet=unet, sd16=sd16, keys=keys, merger=merger, inputs=_inputs())
 
 
@@ -265,6 +265,7 @@ def _denoise_first_steps(den, latents, ctx, te, ti, cond, steps):
     st["text_embeds"].copy_(te)
     st["time_ids"].copy_(ti)
     st["controlnet_cond"].copy_(cond)
+    den.step.refresh_hoisted()
     sig, ts = den.schedule.sigmas, den.schedule.timesteps
     for i in range(steps):
         ops.euler_scale_input(latents, float(sig[i]), copies=2, out=st["sample"])

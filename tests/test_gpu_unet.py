@@ -125,3 +125,36 @@ def test_unet_requires_added_cond_kwargs(tiny):
     sample, ctx, te, ti, cond = tiny["inputs"]
     with pytest.raises(ValueError):
         tiny["unet"](sample.cuda(), torch.tensor(1.0), encoder_hidden_states=ctx.cuda(), added_cond_kwargs={"text_embeds": te})
+
+
+def test_tiny_unet_step_with_layer_norms_folded_into_their_gemms(tiny):
+    """`fuse_ln`: every transformer LayerNorm applied in the epilogue of the GEMM that consumes it (off by default: slower on
+    the SDXL step, see KatzUNet). Same oracle, same bounds; a LoRA merge must reach the folded copies of the weights."""
+    from katz_b200.params import lora_target_keys
+    from oracle import unet_oracle
+    sample, ctx, te, ti, cond = tiny["inputs"]
+    unet = tiny["unet"]
+    with torch.no_grad():
+        ref = unet_oracle.unet_step(_f32(tiny["sd"]), tiny["cfg"], sample.float(), 500.0, ctx.float(), te.float(), ti.float())
+    kw = dict(encoder_hidden_states=ctx.cuda(), added_cond_kwargs={"text_embeds": te.cuda(), "time_ids": ti.cuda()})
+    plain = unet(sample.cuda(), torch.tensor(500.0), **kw)[0].clone()
+    unet.fuse_ln = True
+    try:
+        out = unet(sample.cuda(), torch.tensor(500.0), **kw)[0].clone()
+        assert unet._folds and _maxabs(out, ref) <= 1e-2 and _rel_l2(out, ref) <= 2e-3, (_maxabs(out, ref), _rel_l2(out, ref))
+        assert _rel_l2(out, plain) <= 2e-3 and not torch.equal(out, plain)      # a different rounding sequence, the same result
+        keys = lora_target_keys(tiny["cfg"], include_proj=True)
+        merger = unet.lora_merger(keys)
+        g = torch.Generator().manual_seed(5)
+        ad = {k: ((torch.randn(w.shape[0], 8, generator=g) * 0.05).half().cuda(), (torch.randn(8, w.shape[1], generator=g) / 8).half().cuda())
+              for k, w in unet.lora_targets(keys).items()}
+        merger.merge(ad, 1.0)
+        merged = unet(sample.cuda(), torch.tensor(500.0), **kw)[0].clone()
+        unet.fuse_ln = False
+        merged_plain = unet(sample.cuda(), torch.tensor(500.0), **kw)[0].clone()
+        assert _rel_l2(merged, merged_plain) <= 2e-3 and _rel_l2(merged, out) > 1e-2
+        merger.restore()
+        unet.fuse_ln = True
+        assert torch.equal(unet(sample.cuda(), torch.tensor(500.0), **kw)[0], out)
+    finally:
+        unet.fuse_ln = False
