@@ -82,49 +82,6 @@ __device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t* r) {
                  : "memory");
 }
 
-// Packed fp32 arithmetic (sm_100: one instruction works on two fp32 lanes held in a 64-bit register pair). The GEGLU
-// epilogue is bound by instruction issue, so its polynomial runs two gate values per instruction.
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
-    float2 d;
-    asm("{\n"
-        ".reg .b64 ra, rb, rc, rd;\n"
-        "mov.b64 ra, {%2, %3};\n"
-        "mov.b64 rb, {%4, %5};\n"
-        "mov.b64 rc, {%6, %7};\n"
-        "fma.rn.f32x2 rd, ra, rb, rc;\n"
-        "mov.b64 {%0, %1}, rd;\n"
-        "}"
-        : "=f"(d.x), "=f"(d.y)
-        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
-    return d;
-}
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
-    float2 d;
-    asm("{\n"
-        ".reg .b64 ra, rb, rd;\n"
-        "mov.b64 ra, {%2, %3};\n"
-        "mov.b64 rb, {%4, %5};\n"
-        "mul.rn.f32x2 rd, ra, rb;\n"
-        "mov.b64 {%0, %1}, rd;\n"
-        "}"
-        : "=f"(d.x), "=f"(d.y)
-        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-    return d;
-}
-__device__ __forceinline__ float2 add2(float2 a, float2 b) {
-    float2 d;
-    asm("{\n"
-        ".reg .b64 ra, rb, rd;\n"
-        "mov.b64 ra, {%2, %3};\n"
-        "mov.b64 rb, {%4, %5};\n"
-        "add.rn.f32x2 rd, ra, rb;\n"
-        "mov.b64 {%0, %1}, rd;\n"
-        "}"
-        : "=f"(d.x), "=f"(d.y)
-        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-    return d;
-}
-
 // Exact-form GELU x * Phi(x) with erf from Abramowitz & Stegun 7.1.26 (|error| <= 1.5e-7 on erf, far below the fp16
 // rounding that follows): 1 - erf(z) = (a1 t + ... + a5 t^5) exp(-z^2), t = 1 / (1 + p z), z = |x| / sqrt(2).
 // Two values at a time: ten packed instructions, four special-function ones (two reciprocals, two exp2) and four

@@ -71,8 +71,66 @@ def tiny_inputs(cfg, seed=1, batch=2):
     return sample, ctx, text_embeds, time_ids, cond
 
 
+def kohya_names():
+    """Synthetic kohya-ss LoRA module names with the structure of an SDXL adapter (SGM block numbering for the UNet, both
+    text encoders): every block position, two transformer layers per attention, resnet convolutions, time-embedding
+    projections, shortcuts, down/upsamplers. Names only: no file of any adapter is reproduced."""
+    names = []
+    attn = ["attn1_to_q", "attn1_to_k", "attn1_to_v", "attn1_to_out_0", "attn2_to_q", "attn2_to_k", "attn2_to_v", "attn2_to_out_0",
+            "ff_net_0_proj", "ff_net_2"]
+    res = ["in_layers_2", "emb_layers_1", "out_layers_3"]
+
+    def transformer(prefix):
+        return [prefix + "_proj_in", prefix + "_proj_out"] + ["%s_transformer_blocks_%d_%s" % (prefix, j, leaf) for j in range(2) for leaf in attn]
+    for n in (1, 2, 4, 5, 7, 8):
+        names += ["lora_unet_input_blocks_%d_0_%s" % (n, leaf) for leaf in res]
+        if n in (4, 7):
+            names.append("lora_unet_input_blocks_%d_0_skip_connection" % n)
+        if n >= 4:
+            names += transformer("lora_unet_input_blocks_%d_1" % n)
+    names += ["lora_unet_input_blocks_3_0_op", "lora_unet_input_blocks_6_0_op"]
+    for m in (0, 2):
+        names += ["lora_unet_middle_block_%d_%s" % (m, leaf) for leaf in res]
+    names += transformer("lora_unet_middle_block_1")
+    for n in range(9):
+        names += ["lora_unet_output_blocks_%d_0_%s" % (n, leaf) for leaf in res + ["skip_connection"]]
+        if n < 6:
+            names += transformer("lora_unet_output_blocks_%d_1" % n)
+    names += ["lora_unet_output_blocks_2_2_conv", "lora_unet_output_blocks_5_2_conv"]
+    for te in ("lora_te1", "lora_te2"):
+        for i in (0, 11):
+            names += ["%s_text_model_encoder_layers_%d_self_attn_%s_proj" % (te, i, p) for p in ("q", "k", "v", "out")]
+            names += ["%s_text_model_encoder_layers_%d_mlp_fc%d" % (te, i, f) for f in (1, 2)]
+    return names
+
+
+def kohya_state_dict(names):
+    """One-element tensors whose VALUE identifies the entry, so a renamed dict can be matched back to its source."""
+    sd = {}
+    for i, n in enumerate(names):
+        sd[n + ".lora_down.weight"] = torch.full((1,), float(2 * i))
+        sd[n + ".lora_up.weight"] = torch.full((1,), float(2 * i + 1))
+        sd[n + ".alpha"] = torch.tensor(float(i % 7 + 1))
+    return sd
+
+
+def kohya_fixture(out_dir):
+    """kohya_keys.json: what the reference's own conversion (lora_conversion_utils.py:23-287, as LoraLoaderMixin.lora_state_dict
+    chains it, loaders/lora.py:290-305) makes of kohya_names(): {kohya tensor key: diffusers key} and the alphas."""
+    import types
+    from diffusers.loaders.lora_conversion_utils import _convert_kohya_lora_to_diffusers, _maybe_map_sgm_blocks_to_diffusers
+    sd = kohya_state_dict(kohya_names())
+    by_value = {float(v): k for k, v in sd.items() if not k.endswith(".alpha")}
+    new_sd, alphas = _convert_kohya_lora_to_diffusers(_maybe_map_sgm_blocks_to_diffusers(dict(sd), types.SimpleNamespace(layers_per_block=2)))
+    mapping = {by_value[float(v)]: k for k, v in new_sd.items()}
+    assert len(mapping) == len(by_value)
+    with open(os.path.join(out_dir, "kohya_keys.json"), "w") as fw:
+        json.dump({"keys": mapping, "alphas": alphas}, fw, indent=0, sort_keys=True)
+
+
 def main(ref_root):
     diffusers = _import_reference(ref_root)
+    kohya_fixture(HERE)
     from diffusers import ControlNetModel, EulerDiscreteScheduler, UNet2DConditionModel
     from diffusers.models.lora import LoRACompatibleLinear, LoRALinearLayer
     from katz_b200.params import (SDXL_UNET_CONFIG, TINY_UNET_CONFIG, controlnet_param_shapes, init_state_dict,

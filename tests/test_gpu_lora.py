@@ -183,3 +183,30 @@ def test_two_adapters_fast_path_ragged_shapes_missing_second_adapter_and_registe
     for k in W:
         assert torch.equal(Wg[k].cpu(), W[k]), k
     assert ops.tc05_status() == 0
+
+
+def test_adapter_file_staged_and_copied_asynchronously_then_merged(cuda_device, tmp_path):
+    """File -> pinned staging -> asynchronous copy on a side stream -> merge, the overlap the reference gets from loader
+    processes (pipeline_controlnet_sd_xl_katz.py:1522-1558): the merge waits for the copy's event, nothing else does."""
+    from katz_b200.lora import LoraMerger, adapter_from_lora_state_dict, synthetic_key_map
+    from katz_b200.lora_files import lora_state_dict, stage_pinned, to_device_async, write_safetensors
+    from oracle import lora_oracle
+    shapes = [(640, 640), (5120, 640), (1280, 2048)]
+    W, ad = _make(shapes, 16, torch.float16, 41)
+    km = synthetic_key_map(list(W.keys()))
+    sd = OrderedDict()
+    for k, (up, down) in ad.items():
+        sd[km[k]["lora_up_key"]], sd[km[k]["lora_down_key"]] = up, down
+    path = str(tmp_path / "adapter.safetensors")
+    write_safetensors(path, sd)
+    staged = stage_pinned(lora_state_dict(path)[0])
+    assert all(t.is_pinned() for t in staged.values())
+    dev_sd, ev = to_device_async(staged, cuda_device)
+    Wg = _cuda(W)
+    m = LoraMerger(Wg)
+    torch.cuda.current_stream().wait_event(ev)
+    m.merge(adapter_from_lora_state_dict(dev_sd, km, cuda_device, torch.float16), 1.0)
+    ref = lora_oracle.merge_set(W, [ad], [1.0])
+    for k in W:
+        d = (Wg[k].cpu().float() - ref[k].float()).abs()
+        assert float(d.max()) <= 2 ** -9 * float(ref[k].float().abs().max()), k
