@@ -6,7 +6,7 @@
 //     ahead across tile boundaries;
 //   * warp 1, one elected thread: tcgen05.mma kind::f16 (128 x BN x 16 per instruction), fp32 accumulators in TMEM,
 //     two accumulator buffers so tile i+1's main loop overlaps tile i's epilogue;
-//   * warps 2-9: epilogue, two warps per TMEM lane quarter taking alternate 32-column chunks. tcgen05.ld brings a
+//   * warps 2-13: epilogue, three warps per TMEM lane quarter taking every third 32-column chunk. tcgen05.ld brings a
 //     32-row x 32-column block into registers with one row per thread; bias / per-batch row vector / SiLU / residual /
 //     scale are applied there, and the block moves to and from global memory as a 32 x 64-byte TMA box (residual in,
 //     result out) staged in swizzled shared memory.
@@ -28,13 +28,14 @@ namespace katz {
 using namespace tc05;
 
 constexpr int TBM = 128, TBK = 64;
-constexpr int TC_THREADS = 320;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: epilogue
+constexpr int TC_THREADS = 448;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-13: epilogue
 constexpr int TMEM_COLS = 512;    // two accumulator buffers at columns 0 and 256
 constexpr int BOX_BYTES = 32 * 64;    // epilogue box: 32 rows x 32 fp16 columns, 64-byte swizzle
-constexpr int EPI_WARPS = 8;
-// boxes per epilogue warp: one per chunk it handles in a tile (two warps share a tile's 32-column chunks), so a warp never
-// waits for a TMA store inside a tile
-__host__ __device__ constexpr int tc05_boxes_per_warp(int bn_out) { return (bn_out / 32 + 1) / 2; }
+constexpr int EPI_WARPS = 12;
+constexpr int EPI_PER_Q = EPI_WARPS / 4;      // epilogue warps per TMEM lane quarter: they take every EPI_PER_Q-th 32-column chunk
+// boxes per epilogue warp: one per chunk it handles in a tile (the warps of a lane quarter share a tile's 32-column chunks),
+// so a warp never waits for a TMA store inside a tile
+__host__ __device__ constexpr int tc05_boxes_per_warp(int bn_out) { return (bn_out / 32 + EPI_PER_Q - 1) / EPI_PER_Q; }
 
 struct Tc05Params {
     __half* C;
@@ -192,7 +193,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
     unsigned char* box_base = smem + STAGES * STAGE_BYTES;                 // 1024-byte aligned (stages are multiples of 1 KB)
     uint64_t* bars = reinterpret_cast<uint64_t*>(box_base + EPI_BOXES * BOX_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + EPI_BOXES);
-    static_assert(EPI_BOXES <= 32, "barrier area");
+    static_assert(EPI_BOXES <= 48, "barrier area");
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
     const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
@@ -355,7 +356,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
         }
     } else {
         // ------------------------------------------------------------------------------------ epilogue
-        // Eight warps: two per TMEM lane quarter, taking alternate 32-column chunks of the tile. Thread = tile row. A
+        // Twelve warps: three per TMEM lane quarter, taking every third 32-column chunk of the tile (the epilogue of a
+        // single-tile launch is pure latency after the last MMA, and two warps per scheduler hid little of it). Thread = tile row. A
         // chunk of the warp's 32 rows is one 32 x 64-byte box: the residual box arrives by TMA (requested one of the
         // warp's chunks ahead: the first while the tile's main loop is still running), each thread updates its own
         // row of the box in shared memory, and the box leaves by TMA store, which clips rows past M (or past the
@@ -364,7 +366,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
         // epilogue slower than the main loop; so did per-element branches on the launch-uniform options.)
         const int ew = warp - 2;                // epilogue warp 0..7
         const int q = warp & 3;                 // TMEM lane quarter this warp may read
-        const int half = ew >> 2;               // which of the quarter's two warps: chunks half, half + 2, ...
+        const int half = ew >> 2;               // which of the quarter's EPI_PER_Q warps: chunks half, half + EPI_PER_Q, ...
         unsigned char* boxes = box_base + ew * NBW * BOX_BYTES;
         const uint32_t rfull0 = smem_u32(bars + 2 * STAGES + 4 + ew * NBW);
         constexpr int NCH = BN_OUT / 32;
@@ -445,7 +447,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                 if (has_res && rows_in) {
 #pragma unroll
                     for (int cc = 0; cc < NBW; ++cc) {
-                        const int c = 2 * cc + half;
+                        const int c = EPI_PER_Q * cc + half;
                         if (c < NCH && n0 + c * 32 < p.N) request_residual(c, cc);
                     }
                 }
@@ -467,8 +469,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
             fence_after_sync();
             const uint32_t tacc = tmem_base + buf * 256 + ((uint32_t)(q * 32) << 16);
 #pragma unroll
-            for (int cc = 0; cc < (NCH + 1) / 2; ++cc) {
-                const int c = 2 * cc + half;
+            for (int cc = 0; cc < NBW; ++cc) {
+                const int c = EPI_PER_Q * cc + half;
                 if (!rows_in || c >= NCH || n0 + c * 32 >= p.N) break;      // nothing of this box (or of the rest) exists
                 const uint32_t b = cc;
                 unsigned char* rowp = boxes + b * BOX_BYTES + lane * 64;
@@ -481,11 +483,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                         cb4[k] = nb4[k];
                         cv4[k] = nv4[k];
                     }
-                    if (c + 2 < NCH) {
+                    if (c + EPI_PER_Q < NCH) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            nb4[k] = load_vec(bias_p, (c + 2) * 32 + k * 8);
-                            nv4[k] = load_vec(aux_p, (c + 2) * 32 + k * 8);
+                            nb4[k] = load_vec(bias_p, (c + EPI_PER_Q) * 32 + k * 8);
+                            nv4[k] = load_vec(aux_p, (c + EPI_PER_Q) * 32 + k * 8);
                         }
                     }
                 }
@@ -782,7 +784,7 @@ static int dispatch(const CUtensorMap& a, const CUtensorMap& b, Tc05Params& p, i
     if (rc) return rc;
     if (pair) {
         // stage counts: what fits beside the epilogue boxes (8 KB to 64 KB) in 227 KB
-        if (bn == 256) return launch_tc05<256, GEGLU ? 6 : 5, GEGLU, true, LN>(a, b, c, r, p, st);
+        if (bn == 256) return launch_tc05<256, GEGLU ? 5 : 4, GEGLU, true, LN>(a, b, c, r, p, st);
         if constexpr (!GEGLU) {
             if (bn == 160) return launch_tc05<160, 6, false, true, LN>(a, b, c, r, p, st);
             if (bn == 96) return launch_tc05<96, 8, false, true, LN>(a, b, c, r, p, st);
@@ -793,8 +795,8 @@ static int dispatch(const CUtensorMap& a, const CUtensorMap& b, Tc05Params& p, i
         if (bn == 160) return launch_tc05<160, 4, false, false, LN>(a, b, c, r, p, st);
         if (bn == 96) return launch_tc05<96, 6, false, false, LN>(a, b, c, r, p, st);
     }
-    if (bn == 256) return launch_tc05<256, GEGLU ? 4 : 3, GEGLU, false, LN>(a, b, c, r, p, st);
-    return launch_tc05<128, 6, GEGLU, false, LN>(a, b, c, r, p, st);
+    if (bn == 256) return launch_tc05<256, 3, GEGLU, false, LN>(a, b, c, r, p, st);
+    return launch_tc05<128, GEGLU ? 6 : 5, GEGLU, false, LN>(a, b, c, r, p, st);
 }
 
 // W' = W diag(gamma) (fp16), c12[n] = (sum_k W'[n,k], sum_k W[n,k] beta[k] + bias[n]) in fp32: the per-weight constants of a

@@ -355,7 +355,9 @@ def test_layer_norm_folded_into_linear(cuda_device, M, C, N, row_shift):
     xf = x.float()
     s1 = st[:, :, 0].sum(0)
     s2 = st[:, :, 1].sum(0)
-    assert torch.allclose(s1, xf.sum(1), rtol=1e-5, atol=1e-2) and torch.allclose(s2, (xf * xf).sum(1), rtol=1e-5, atol=1e-2)
+    # the statistics are taken from the fp32 values before their fp16 rounding: the sums agree with those of the stored rows up
+    # to that rounding (2^-11 relative per element, random sign)
+    assert torch.allclose(s1, xf.sum(1), rtol=1e-3, atol=0.25) and torch.allclose(s2, (xf * xf).sum(1), rtol=2e-3, atol=0.5)
     fold = ops.ln_fold(w, gamma, beta, bias)
     out = ops.linear(x, fold.wf, ln=fold, ln_stats=st)
     ref = F.linear(F.layer_norm(xf, (C,), gamma.float(), beta.float(), 1e-5), w.float(), bias.float())
