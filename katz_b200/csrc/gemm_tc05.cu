@@ -235,16 +235,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
     }
     fence_before_sync();
     __syncthreads();
-    if (PAIR) cluster_sync_all();      // the peer's barriers are initialised before anything signals them
+    // The peer's barriers must be initialised before anything signals them. The cluster barrier's round trip (most of a
+    // microsecond in a trace) is split: every thread arrives here, and each role waits right before its first access to
+    // the peer, after whatever else it has to wait for (the producer: the previous kernel).
+    if (PAIR) cluster_arrive_relaxed();      // warp 0 issued fence.mbarrier_init.release.cluster after its initialisations
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     // Everything above (barriers, TMEM, descriptor prefetch) and each role's index arithmetic may overlap the previous
-    // kernel's tail: the roles call pdl_wait() themselves, right before their first global-memory access (the MMA
-    // thread touches none).
+    // kernel's tail: the roles call pdl_wait() themselves, before their first global-memory access.
 
     if (warp == 0) {
         // ------------------------------------------------------------------------------------ TMA producer
-        if (elect_one()) {
+        const bool elected = elect_one();
+        if (elected) {
+            pdl_wait();                 // the kernels this launch depends on are done (overlaps the cluster barrier)
+            pdl_launch_dependents();
+        }
+        if (PAIR) cluster_wait();
+        if (elected) {
             bool ok = true;
             uint32_t it = 0, issued = 0;
             for (int tile = item0; tile < total_tiles && ok; tile += item_stride) {
@@ -265,10 +273,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { ok = false; break; }
                     const uint32_t sa = smem_base + s * STAGE_BYTES;
-                    if (it == 0) {
-                        pdl_wait();                 // the first load: the kernels this launch depends on are done
-                        pdl_launch_dependents();
-                    }
                     if constexpr (PAIR) {
                         // both CTAs' bytes are counted on the leader's barrier, which the leader arms for both
                         const uint32_t fb = mapa_shared(full0 + 8 * s, 0);
@@ -318,6 +322,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------------------------ MMA issuer
+        if (PAIR) cluster_wait();
         if ((!PAIR || rank == 0) && elect_one()) {
             constexpr uint32_t idesc = idesc_f16(PAIR ? 2 * TBM : TBM, BN);
             bool ok = true;
@@ -375,7 +380,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
         const uint32_t swz = (uint32_t)((lane >> 1) & 3);      // 64-byte swizzle: 16-byte chunk index ^ ((row >> 1) & 3)
         bool ok = true;
         uint32_t t = 0, rpar = 0;               // tiles done by the CTA; parity bit per residual box of this warp
+        if (ew == EPI_WARPS - 1 && lane == 0 && item0 < total_tiles) {
+            // The weights of the CTA's first tile go to L2 now: they are cold in HBM (5 GB of weights stream through a 126 MB
+            // L2 every step), and loads that have to come from DRAM kept the tensor pipe waiting after the dependency had
+            // resolved. The prefetch needs no dependency (it only warms L2, the point of coherence) and is issued from an
+            // epilogue thread, idle until the first tile is done: each request costs its issuer about 40 ns, which the
+            // producer thread cannot spare.
+            const int pn0 = (item0 % p.n_tiles) * BN_OUT;
+            const int kmax = KT < 64 ? KT : 64;
+            for (int kt = 0; kt < kmax; ++kt) {
+                if constexpr (PAIR) {
+                    tma_prefetch_l2_2d(&tmB, kt * TBK, GEGLU ? (rank ? p.geglu_F + pn0 : pn0) : pn0 + (int)rank * (BN / 2));
+                } else {
+                    tma_prefetch_l2_2d(&tmB, kt * TBK, pn0);
+                    if (GEGLU) tma_prefetch_l2_2d(&tmB, kt * TBK, p.geglu_F + pn0);
+                }
+            }
+        }
         pdl_wait();                             // bias, row vector and residual are global reads
+        if (PAIR) cluster_wait();
         for (int tile = item0; tile < total_tiles && ok; tile += item_stride, ++t) {
             const uint32_t buf = t & 1;
             const int mi = tile / p.n_tiles, nt = tile - mi * p.n_tiles;
@@ -579,12 +602,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                 }
             }
             if (!ok) break;
-            // this warp is done reading the accumulator buffer
-            fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-                if (PAIR) mbar_arrive_cluster(mapa_shared(tempty0 + 8 * buf, 0));      // the leader's MMA thread waits for both CTAs
-                else mbar_arrive(tempty0 + 8 * buf);
+            // this warp is done reading the accumulator buffer: tell the MMA thread, which waits for it before the tile
+            // after next reuses the buffer. Nobody waits for the arrivals of a CTA's last two tiles, and the release at
+            // cluster scope cost a microsecond at the very end of a single-tile launch: those are skipped.
+            if (tile + 2 * item_stride < total_tiles) {
+                fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if (PAIR) mbar_arrive_cluster(mapa_shared(tempty0 + 8 * buf, 0));      // the leader's MMA thread waits for both CTAs
+                    else mbar_arrive(tempty0 + 8 * buf);
+                }
             }
         }
         if (lane == 0) bulk_wait_read<0>();     // every store has read its box (the writes complete with the kernel)
@@ -592,7 +619,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
     // ---------------------------------------------------------------------------------------- teardown
     fence_before_sync();
     __syncthreads();
-    if (PAIR) cluster_sync_all();      // neither CTA leaves (or frees TMEM) while the other may still signal it or read its tiles
+    if (PAIR) {      // neither CTA leaves (or frees TMEM) while the other may still signal it or read its tiles
+        cluster_arrive_relaxed();
+        cluster_wait();
+    }
     if (warp == 1) {
         fence_after_sync();
         if (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS);
