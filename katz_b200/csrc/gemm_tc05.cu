@@ -121,32 +121,20 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t* r, unsigned char*
         uint32_t ow[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const float2 bf = unpack_half2(bw[e]);
-            float v0 = __uint_as_float(r[k * 8 + 2 * e]) + bf.x, v1 = __uint_as_float(r[k * 8 + 2 * e + 1]) + bf.y;
-            if (AUX) {
-                const float2 vf = unpack_half2(vw[e]);
-                v0 += vf.x;
-                v1 += vf.y;
-            }
-            if (ACT) {
-                v0 = silu_f(v0);
-                v1 = silu_f(v1);
-            }
-            if (RES) {
-                const float2 a = unpack_half2(rw[e]);
-                v0 += a.x;
-                v1 += a.y;
-            }
-            v0 *= out_scale;
-            v1 *= out_scale;
+            // packed fp32 arithmetic: one instruction per pair of columns for each of the additions and the scaling (the
+            // epilogue of a single-wave launch is bound by instruction issue: three warps share a scheduler)
+            float2 v = add2(make_float2(__uint_as_float(r[k * 8 + 2 * e]), __uint_as_float(r[k * 8 + 2 * e + 1])), unpack_half2(bw[e]));
+            if (AUX) v = add2(v, unpack_half2(vw[e]));
+            if (ACT) v = make_float2(silu_f(v.x), silu_f(v.y));
+            if (RES) v = add2(v, unpack_half2(rw[e]));
+            v = mul2(v, make_float2(out_scale, out_scale));
             if (STATS) {
                 // row statistics for a LayerNorm folded into the next GEMM, from the fp32 values (their fp16 rounding moves
-                // a 1280-term sum by parts in 1e5): two packed instructions per pair of columns
-                const float2 v = make_float2(v0, v1);
+                // a 1280-term sum by parts in 1e5)
                 s1 = add2(s1, v);
                 s2 = fma2(v, v, s2);
             }
-            ow[e] = pack_half2(v0, v1);
+            ow[e] = pack_half2(v.x, v.y);
         }
         *cell = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
