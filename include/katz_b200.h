@@ -87,6 +87,14 @@ int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_tile_start, in
  * and pass the device copy to katz_lora_merge. No reference counterpart (the reference merges layer by layer in
  * PyTorch, lora_utils.py:29-33). */
 int katz_lora_encode_tile_maps(const katz_lora_layer* h_layers, int n_layers, void* h_maps);
+/* The fast paths for either weight type. fp32 weights with fp32 adapters (the reference's CPU-runnable configuration,
+ * lora_utils.py:29-33 on fp32 tensors): KATZ_LORA_UNIFORM_TILES, maps from katz_lora_encode_tile_maps_dtype(KATZ_DTYPE_F32) and a
+ * `d_tile_start` / `total_tiles` counted in tiles of katz_lora_fast_tile_rows x katz_lora_fast_tile_cols (128 x 64 for fp32,
+ * 128 x 128 for fp16, which equals katz_lora_tile_rows x katz_lora_tile_cols there) select the kernel that forms the rank-r
+ * product from three bf16 terms per operand on the tensor cores (fp32-accurate to parts in 1e-7). */
+int katz_lora_fast_tile_rows(int w_dtype);
+int katz_lora_fast_tile_cols(int w_dtype);
+int katz_lora_encode_tile_maps_dtype(const katz_lora_layer* h_layers, int n_layers, int w_dtype, void* h_maps);
 
 /* -------------------------------------------------------------------------------------- fast_kernel drop-ins ---- */
 /* fast_kernel::group_norm_fp16 (fast_kernel/csrc/group_norm.cuh:7-15, group_norm.cu:224-274), channels-last input.

@@ -62,6 +62,9 @@ SIGNATURES = {
     "katz_lora_table_check": (_I, [POINTER(LoraLayer), _I, _I, POINTER(c_int)]),
     "katz_lora_merge": (_I, [_V, _V, _I, _I, _I, _F, _I, _I, _V, _V]),
     "katz_lora_encode_tile_maps": (_I, [POINTER(LoraLayer), _I, _V]),
+    "katz_lora_fast_tile_rows": (_I, [_I]),
+    "katz_lora_fast_tile_cols": (_I, [_I]),
+    "katz_lora_encode_tile_maps_dtype": (_I, [POINTER(LoraLayer), _I, _I, _V]),
     "katz_group_norm_scratch_bytes": (_L, [_I, _I, _I, _I]),
     "katz_group_norm_nhwc_f16": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _F, _I, _V, _L, _V]),
     "katz_group_norm_stats_nhwc_f16": (_I, [_V, _V, _I, _I, _I, _I, _V, _L, _V]),

@@ -871,6 +871,9 @@ __global__ void __launch_bounds__(WS_THREADS, 1) lora_merge_f16_ws_kernel(const 
 }
 
 int* tc05_status_device_ptr();   // gemm_tc05.cu
+// lora_merge_f32.cu: the fp32 fast path (tiles of 128 x 64, bf16x3 products on tcgen05)
+int lora_merge_f32_ws_launch(const katz_lora_layer* d_layers, const void* d_tile_maps, const int* d_tile_start, int n_layers,
+                             int total_tiles, float sign, int no_adapters, int grid, cudaStream_t st);
 
 static int lm_sm_count() {
     static int n = 0;
@@ -888,6 +891,9 @@ using namespace katz;
 
 extern "C" int katz_lora_tile_rows(int w_dtype) { return w_dtype == KATZ_DTYPE_F16 ? LmCfg<__half>::TM : LmCfg<float>::TM; }
 extern "C" int katz_lora_tile_cols(void) { return LM_TN; }
+// Tile geometry of the TMA-tiled fast paths (KATZ_LORA_UNIFORM_TILES*): 128 x 128 for fp16 weights, 128 x 64 for fp32.
+extern "C" int katz_lora_fast_tile_rows(int w_dtype) { (void)w_dtype; return 128; }
+extern "C" int katz_lora_fast_tile_cols(int w_dtype) { return w_dtype == KATZ_DTYPE_F16 ? 128 : 64; }
 
 extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_tile_start, int n_layers, int total_tiles,
                                int w_dtype, float sign, int max_tiles_per_layer, int flags, const void* d_tile_maps,
@@ -912,6 +918,12 @@ extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_til
     if (use_tc05 < 0) {
         const char* e = getenv("KATZ_LORA_MMA");
         use_tc05 = (e && e[0] == '1') ? 0 : 1;
+    }
+    if (w_dtype == KATZ_DTYPE_F32 && use_tc05 && (flags & KATZ_LORA_UNIFORM_TILES) && d_tile_maps) {
+        // fp32 fast path: d_tile_start / total_tiles count tiles of katz_lora_fast_tile_rows x katz_lora_fast_tile_cols
+        KATZ_CHECK_ARG((reinterpret_cast<uintptr_t>(d_tile_maps) & 63) == 0, KATZ_EALIGN);
+        return lora_merge_f32_ws_launch(d_layers, d_tile_maps, d_tile_start, n_layers, total_tiles, sign,
+                                        (flags & KATZ_LORA_NO_ADAPTERS) ? 1 : 0, grid, st);
     }
     if (w_dtype == KATZ_DTYPE_F16 && use_tc05 && (flags & (KATZ_LORA_UNIFORM_TILES | KATZ_LORA_UNIFORM_TILES_2)) && d_tile_maps) {
         KATZ_CHECK_ARG((reinterpret_cast<uintptr_t>(d_tile_maps) & 63) == 0, KATZ_EALIGN);
@@ -959,7 +971,18 @@ extern "C" int katz_lora_merge(const katz_lora_layer* d_layers, const int* d_til
 // Tensor maps of the fast path, two per layer (128 bytes each): [2i] the pristine copy W0 (W when there is none), [2i+1]
 // the live W; 128-row x 64-column boxes with the 128-byte swizzle. They depend only on the weight pointers and shapes,
 // so a caller encodes them once and keeps them in device memory.
+static int encode_tile_maps(const katz_lora_layer* h_layers, int n_layers, int w_dtype, void* h_maps);
+
 extern "C" int katz_lora_encode_tile_maps(const katz_lora_layer* h_layers, int n_layers, void* h_maps) {
+    return encode_tile_maps(h_layers, n_layers, KATZ_DTYPE_F16, h_maps);
+}
+
+extern "C" int katz_lora_encode_tile_maps_dtype(const katz_lora_layer* h_layers, int n_layers, int w_dtype, void* h_maps) {
+    KATZ_CHECK_ARG(w_dtype == KATZ_DTYPE_F16 || w_dtype == KATZ_DTYPE_F32, KATZ_EINVAL);
+    return encode_tile_maps(h_layers, n_layers, w_dtype, h_maps);
+}
+
+static int encode_tile_maps(const katz_lora_layer* h_layers, int n_layers, int w_dtype, void* h_maps) {
     KATZ_CHECK_ARG(h_layers && h_maps, KATZ_EINVAL);
     KATZ_CHECK_ARG(n_layers > 0, KATZ_ESIZE);
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -978,15 +1001,16 @@ extern "C" int katz_lora_encode_tile_maps(const katz_lora_layer* h_layers, int n
     for (int i = 0; i < n_layers; ++i) {
         const katz_lora_layer& L = h_layers[i];
         KATZ_CHECK_ARG(L.W && aligned16(L.W) && (!L.W0 || aligned16(L.W0)), KATZ_EALIGN);
-        KATZ_CHECK_ARG(L.out_features > 0 && L.in_features > 0 && L.in_features % 8 == 0, KATZ_ESIZE);
+        const bool f32 = w_dtype == KATZ_DTYPE_F32;
+        KATZ_CHECK_ARG(L.out_features > 0 && L.in_features > 0 && L.in_features % (f32 ? 4 : 8) == 0, KATZ_ESIZE);
         cuuint64_t dims[2] = {(cuuint64_t)L.in_features, (cuuint64_t)L.out_features};
-        cuuint64_t strides[1] = {(cuuint64_t)L.in_features * 2};
-        cuuint32_t box[2] = {64, 128};
+        cuuint64_t strides[1] = {(cuuint64_t)L.in_features * (f32 ? 4 : 2)};
+        cuuint32_t box[2] = {f32 ? 32u : 64u, 128};      // 128 bytes per box row either way
         cuuint32_t es[2] = {1, 1};
         for (int k = 0; k < 2; ++k) {
             void* base = (k == 0 && L.W0) ? const_cast<void*>(L.W0) : L.W;
             CUtensorMap tmp;
-            CUresult r = enc(&tmp, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CUresult r = enc(&tmp, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r != CUDA_SUCCESS) return KATZ_EINVAL;
             memcpy(out + 2 * i + k, &tmp, sizeof(CUtensorMap));      // the caller's buffer need not be 64-byte aligned

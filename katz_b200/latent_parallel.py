@@ -167,6 +167,30 @@ class RowParallel:
         return ops.attention(qkv[:, :, :C], kv[:, :, :C], kv[:, :, C:], heads)
 
 
+def peer_arena_bytes(cfg, batch, height, width):
+    """Arena size for one step's exchanges: every exchange has its own buffer (so none is acknowledged), and the
+    self-attention K/V gathers dominate: per transformer layer 2 (K, V) x batch x tokens x channels fp16, whatever the number
+    of ranks. 25% and 64 MiB on top for halo rows, GroupNorm sums and alignment; KATZ_PEER_ARENA_BYTES overrides."""
+    if os.environ.get("KATZ_PEER_ARENA_BYTES"):
+        return int(os.environ["KATZ_PEER_ARENA_BYTES"])
+    total = 0
+    boc = cfg["block_out_channels"]
+    layers = cfg["transformer_layers_per_block"]
+    h, w = height, width
+    per_level = []
+    for bi, btype in enumerate(cfg["down_block_types"]):
+        per_level.append((boc[bi], h * w, layers[bi] if btype == "CrossAttnDownBlock2D" else 0))
+        if bi != len(boc) - 1:
+            h, w = h // 2, w // 2
+    n_res = cfg["layers_per_block"]
+    for bi, (c, tokens, n) in enumerate(per_level):
+        blocks = n_res + (n_res + 1)                       # the down block's and the mirrored up block's attentions
+        if bi == len(per_level) - 1:
+            blocks += 1                                    # the mid block
+        total += blocks * n * 2 * batch * tokens * c * 2
+    return int(total * 1.25) + (64 << 20)
+
+
 class RowParallelStep:
     """CUDA-graph step of a row-split UNet: same interface as engine.GraphedStep. Every rank passes the same inputs
     and receives the whole prediction."""
@@ -181,7 +205,8 @@ class RowParallelStep:
         if world > 1 and unet.device.type == "cuda" and os.environ.get("KATZ_PEER", "1") != "0":
             from .peer import PeerArena
             try:
-                rp.peer = PeerArena(rank, world, group=group, device=unet.device)
+                rp.peer = PeerArena(rank, world, group=group, device=unet.device,
+                                    nbytes=peer_arena_bytes(unet.cfg, batch, height, width))
             except KatzError:
                 rp.peer = None          # every rank reached the same verdict: the exchanges go through torch.distributed
         unet.rp = rp

@@ -79,6 +79,17 @@ class LoraMerger:
             total += n
         self.total_tiles = total
         self.d_tile_start = torch.tensor(starts, dtype=torch.int32, device=self.device)
+        # the TMA-tiled fast paths count tiles in their own geometry (the same as above for fp16, 128 x 64 for fp32)
+        fr, fc = lib.katz_lora_fast_tile_rows(self.code), lib.katz_lora_fast_tile_cols(self.code)
+        fstarts, ftotal, self.max_tiles_per_layer_fast = [], 0, 0
+        for w in self.weights.values():
+            fstarts.append(ftotal)
+            n = -(-w.shape[0] // fr) * -(-w.shape[1] // fc)
+            self.max_tiles_per_layer_fast = max(self.max_tiles_per_layer_fast, n)
+            ftotal += n
+        self.total_tiles_fast = ftotal
+        self.d_tile_start_fast = self.d_tile_start if (fr, fc) == (self.tile_rows, self.tile_cols) else \
+            torch.tensor(fstarts, dtype=torch.int32, device=self.device)
         self.pristine = None
         if keep_pristine:
             self.snapshot_pristine()
@@ -199,8 +210,6 @@ class LoraMerger:
 
     def _tile_maps(self):
         """Device copy of the per-layer tensor maps (they depend only on the weight and pristine pointers)."""
-        if self.dtype != torch.float16:
-            return None
         if self._d_maps is None:
             n = len(self.keys)
             table = (LoraLayer * n)()
@@ -210,18 +219,23 @@ class LoraMerger:
                 table[i].W0 = self.pristine[k].data_ptr() if self.pristine is not None else None
                 table[i].out_features, table[i].in_features = w.shape
             host = torch.empty(n * 256, dtype=torch.uint8)
-            _lib.check(_lib.load().katz_lora_encode_tile_maps(table, n, ctypes.c_void_p(host.data_ptr())),
-                       "katz_lora_encode_tile_maps")
+            _lib.check(_lib.load().katz_lora_encode_tile_maps_dtype(table, n, self.code, ctypes.c_void_p(host.data_ptr())),
+                       "katz_lora_encode_tile_maps_dtype")
             self._d_maps = host.to(self.device)
         return self._d_maps
 
     def _launch(self, sign):
         lib = _lib.load()
-        maps = self._tile_maps() if self._flags else None
+        # fast paths: fp16 with at most two adapters of rank <= 64 per layer, fp32 with at most one
+        fast = bool(self._flags & 1) or (self.dtype == torch.float16 and bool(self._flags & 4))
+        maps = self._tile_maps() if fast else None
+        flags = self._flags if fast else (self._flags & 2)
+        starts, total, mx = ((self.d_tile_start_fast, self.total_tiles_fast, self.max_tiles_per_layer_fast) if fast else
+                             (self.d_tile_start, self.total_tiles, self.max_tiles_per_layer))
         st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        _lib.check(lib.katz_lora_merge(ctypes.c_void_p(self._d_table.data_ptr()), ctypes.c_void_p(self.d_tile_start.data_ptr()),
-                                       len(self.keys), self.total_tiles, self.code, float(sign), self.max_tiles_per_layer,
-                                       self._flags, ctypes.c_void_p(maps.data_ptr() if maps is not None else None), st),
+        _lib.check(lib.katz_lora_merge(ctypes.c_void_p(self._d_table.data_ptr()), ctypes.c_void_p(starts.data_ptr()),
+                                       len(self.keys), total, self.code, float(sign), mx,
+                                       flags, ctypes.c_void_p(maps.data_ptr() if maps is not None else None), st),
                    "katz_lora_merge")
         _lib.note_launches(1)
         if self.on_change is not None:

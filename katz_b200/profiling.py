@@ -7,6 +7,8 @@
     python -m katz_b200.profiling step [--batch B] [--latent HW]   # ONE eager UNet step
     python -m katz_b200.profiling norms          # LayerNorm / GroupNorm launches of the step's shapes
     python -m katz_b200.profiling compare-cublas # katz_linear_f16 against torch.addmm on the step's shapes (no profiler)
+    python -m katz_b200.profiling families [--batch B] [--latent HW]   # time share per kernel family of one eager step, CUDA
+                                                 # events around every op (also under torchrun: the row-split step, rank 0 reports)
 
 Every mode but the last warms up, then brackets the launches of interest with cudaProfilerStart/Stop, so that
 `ncu --profile-from-start off` captures exactly those; each holds well under a few GB on the device (the `step` mode
@@ -174,7 +176,87 @@ def compare_cublas(dev, args):
     return {"compared": "linear + bias, fp16, CUDA graph of 20 launches", "rows": rows, "tc05_status": ops.tc05_status()}
 
 
-MODES = {"gemm": gemm, "attention": attention, "merge": merge, "merge-fp32": merge_fp32, "step": step, "norms": norms,
+def families(dev, args):
+    """Time share per kernel family of ONE eager UNet step: CUDA events (with a synchronisation) around every call of the op
+    layer, so launch gaps are excluded and absolute times are those of isolated kernels; the SHARES say where a step goes.
+    Under torchrun every rank runs the row-split step (cfg x rows as bench.py splits it) and rank 0 prints."""
+    import collections
+    import os
+    import torch.distributed as dist
+    from . import latent_parallel, ops
+    from .params import SDXL_UNET_CONFIG, init_state_dict, unet_param_shapes
+    from .unet import KatzUNet
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = SDXL_UNET_CONFIG
+    unet = KatzUNet(cfg, dev, init_state_dict(unet_param_shapes(cfg), seed=0, dtype=torch.float16, device=dev, generator_device=dev))
+    B, HW = args.batch, args.latent
+    halves, rows_world, half, row_rank, lb = latent_parallel.cfg_rows_layout(B, world, rank)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(B, 4, HW, HW, generator=g).half().to(dev)[half * lb:(half + 1) * lb]
+    ctx = torch.randn(B, 77, 2048, generator=g).half().to(dev)[half * lb:(half + 1) * lb]
+    added = {"text_embeds": torch.randn(B, 1280, generator=g).half().to(dev)[half * lb:(half + 1) * lb],
+             "time_ids": torch.tensor([[1024., 1024., 0., 0., 1024., 1024.]] * lb).half().to(dev)}
+    t = torch.tensor([500.0], device=dev)
+    if rows_world > 1:
+        grp = None
+        if halves > 1:
+            groups = [dist.new_group(list(range(h * rows_world, (h + 1) * rows_world))) for h in range(halves)]
+            grp = groups[half]
+        rp = latent_parallel.RowParallel(row_rank, rows_world, grp)
+        if os.environ.get("KATZ_PEER", "1") != "0":
+            from .peer import PeerArena
+            rp.peer = PeerArena(row_rank, rows_world, group=grp, device=dev)
+        unet.rp = rp
+    for _ in range(2):
+        unet(x, t, encoder_hidden_states=ctx, added_cond_kwargs=added)
+    torch.cuda.synchronize()
+    rec = collections.OrderedDict()
+
+    def wrap(mod, name, family):
+        fn = getattr(mod, name)
+
+        def f(*a, **k):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            r = fn(*a, **k)
+            e1.record()
+            torch.cuda.synchronize()
+            ent = rec.setdefault(family, [0, 0.0])
+            ent[0] += 1
+            ent[1] += e0.elapsed_time(e1) * 1e3
+            return r
+        setattr(mod, name, f)
+    for name, fam in (("linear", "linear GEMM"), ("feed_forward_geglu", "GEGLU GEMM"), ("conv2d", "convolution"), ("attention", "attention"),
+                      ("layer_norm", "LayerNorm"), ("group_norm_nhwc", "GroupNorm"), ("group_norm_stats", "GroupNorm"),
+                      ("group_norm_apply", "GroupNorm"), ("halo_assemble", "halo assemble"), ("concat_channels", "concat"),
+                      ("upsample_nearest2x", "upsample")):
+        wrap(ops, name, fam)
+    if unet.rp is not None and unet.rp.peer is not None:
+        wrap(unet.rp.peer, "allgather", "peer all-gather")
+    if world > 1:
+        dist.barrier()
+    unet(x, t, encoder_hidden_states=ctx, added_cond_kwargs=added)
+    torch.cuda.synchronize()
+    total = sum(v[1] for v in rec.values())
+    out = {"profiled": "kernel families of one eager step (isolated launches, CUDA events)", "world": world, "split": "cfg%d x rows%d" % (halves, rows_world),
+           "local_batch": lb, "latent": HW, "total_us": round(total, 1),
+           "families": [{"family": k, "calls": v[0], "us": round(v[1], 1), "share": round(v[1] / total, 4)} for k, v in
+                        sorted(rec.items(), key=lambda kv: -kv[1][1])]}
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+        if rank != 0:
+            os._exit(0)
+        print(json.dumps(out), flush=True)
+        os._exit(0)
+    return out
+
+
+MODES = {"families": families, "gemm": gemm, "attention": attention, "merge": merge, "merge-fp32": merge_fp32, "step": step, "norms": norms,
          "compare-cublas": compare_cublas}
 
 
@@ -186,7 +268,8 @@ def main(argv=None):
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("katz_b200.profiling needs a CUDA device")
-    dev = torch.device("cuda", 0)
+    import os
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
     print(json.dumps(MODES[args.mode](dev, args)), flush=True)
 
