@@ -261,6 +261,10 @@ def main():
                     help="N > 1: 'auto' splits the CFG batch over two halves of the ranks and the latent rows inside a half; "
                          "'rows' splits latent rows only")
     ap.add_argument("--latent", type=int, default=128, help="latent height = width (128 = 1024^2 images)")
+    ap.add_argument("--stream", default=None, metavar="REQUESTS:STEPS",
+                    help="also run a stream of requests (configs[4]: one ControlNet, one LoRA per request drawn from a pool of 16 "
+                         "rank-64 adapters, so consecutive requests force a switch): e.g. 4:10 = four requests of ten Euler "
+                         "steps. 1 GPU. Adds `request_stream` to the line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "katz" else max(args.warmup, 0)
 
@@ -498,6 +502,40 @@ def main():
             del W32, m32, l32
             torch.cuda.empty_cache()
 
+    stream_leg = None
+    if rank == 0 and world == 1 and args.stream:
+        from katz_b200.pipeline import KatzDenoiser, LoraRequestStream
+        n_req, n_steps = (int(v) for v in args.stream.split(":"))
+        merger.restore()
+        cn = KatzControlNet(cfg, dev, init_state_dict(controlnet_param_shapes(cfg), seed=1, dtype=torch.float16, device=dev,
+                                                     generator_device=dev))
+        den = KatzDenoiser(unet, HW, HW, controlnets=[cn], conditioning_scales=[0.5], guidance_scale=5.0)
+        pool = [make_lora(targets, 64, 100 + i, dev) for i in range(16)]
+        ids = torch.randint(0, 16, (n_req,), generator=torch.Generator().manual_seed(0)).tolist()
+        rs = LoraRequestStream(den, merger, pool, scale=1.0)
+        gi = torch.Generator().manual_seed(1)
+        req = dict(prompt_embeds=torch.randn(2, 77, 2048, generator=gi).half().to(dev), text_embeds=torch.randn(2, 1280, generator=gi).half().to(dev),
+                   time_ids=torch.tensor([[8.0 * HW, 8.0 * HW, 0., 0., 8.0 * HW, 8.0 * HW]] * 2).half().to(dev),
+                   controlnet_cond=torch.rand(2, 3, 8 * HW, 8 * HW, generator=gi).half().to(dev))
+        rs.run(ids[:1], lambda i: req, num_inference_steps=2)                   # warm-up
+        t0 = time.time()
+        res = rs.run(ids, lambda i: req, num_inference_steps=n_steps)
+        wall = time.time() - t0
+        lat = sorted(ms_ for _, ms_ in res)
+        per_step = sum(lat) / len(lat) / n_steps
+        stream_leg = {"workload": "stream of requests at %dx%d pixels: 1 ControlNet (scale 0.5), CFG 5.0, one rank-64 LoRA per request "
+                                  "from a pool of 16 (switch = one merge pass from the pristine weights), Euler (configs[4])" % (8 * HW, 8 * HW),
+                      "requests": n_req, "steps_per_request": n_steps, "lora_ids": ids, "ms_per_request_median": lat[len(lat) // 2],
+                      "ms_per_request_max": lat[-1], "ms_per_step": per_step, "images_per_s": n_req / wall,
+                      "ms_per_50_step_request_extrapolated": per_step * 50 if n_steps != 50 else None,
+                      "images_per_s_50_steps_extrapolated": 1e3 / (per_step * 50) if n_steps != 50 else None,
+                      "launches_per_step": den.step.launches_per_step + 2}
+        tc05 = max(tc05, ops.tc05_status())
+        ok_all = ok_all and tc05 == 0
+        del den, rs, pool, cn
+        merger.merge(lora, 1.0)
+        torch.cuda.empty_cache()
+
     if rank == 0:
         step_tflops = flops["total"] / world / (ms * 1e-3) / 1e12
         line = {
@@ -520,7 +558,7 @@ def main():
                               "peak_source": peaks["_source"] + " sustained", "flop_per_step": flops["total"],
                               "note": "per-GPU algorithmic FLOPs of the whole step / step time"},
             "lora_merge": merge1, "lora_merge_2adapters": merge2, "lora_merge_fp32": merge32,
-            "controlnet_step": cn_leg, "torch_gpu_baseline": tgb,
+            "controlnet_step": cn_leg, "torch_gpu_baseline": tgb, "request_stream": stream_leg,
         }
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1

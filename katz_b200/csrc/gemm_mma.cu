@@ -39,7 +39,7 @@ __global__ void __launch_bounds__(NTHREADS) igemm_kernel(const IgemmParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int warp_m = warp & 1, warp_n = warp >> 1;
-    const int bm = blockIdx.y * BM, bn = blockIdx.x * BN;
+    const int bm = blockIdx.x * BM, bn = blockIdx.y * BN;      // row tiles on x: a 2048 x 2048 image has more than 65535 of them
     const int Cin = p.C1 + p.C2;
 
     // ---- loader bookkeeping: each thread moves two A chunks and two W chunks of 16 B per stage
@@ -231,7 +231,7 @@ static int launch_igemm(const IgemmParams& p, bool conv, cudaStream_t st) {
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
-    dim3 grid(ceil_div(p.N, BN), ceil_div(p.M, BM));
+    dim3 grid(ceil_div(p.M, BM), ceil_div(p.N, BN));
     if (grid.y > 65535) return KATZ_ESIZE;
     if (conv)
         launch_k(igemm_kernel<true>, grid, NTHREADS, IGEMM_SMEM, st, p);
