@@ -265,6 +265,8 @@ int katz_peer_ipc_close(void* ptr);
 int katz_peer_allgather(const void* src, long long rows, long long row_bytes, long long src_pitch_bytes, long long dst_off,
                         const unsigned long long* h_bases, int rank, int world, void* stream);
 int katz_peer_status(const void* arena);
+/* Put the status word back to zero (for instance after a warm-up during which the ranks were not yet in step). */
+int katz_peer_clear_status(void* arena);
 /* get_timestep_embedding (diffusers/models/embeddings.py:26-66), flip_sin_to_cos, shift 0: out[rows, dim] fp16. */
 int katz_timestep_embedding_f16(const float* t, void* out, int rows, int dim, int ld_out, void* stream);
 int katz_silu_f16(const void* x, void* y, long long n, void* stream);

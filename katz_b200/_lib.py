@@ -102,6 +102,7 @@ SIGNATURES = {
     "katz_peer_ipc_close": (_I, [_V]),
     "katz_peer_allgather": (_I, [_V, _L, _L, _L, _L, POINTER(ctypes.c_ulonglong), _I, _I, _V]),
     "katz_peer_status": (_I, [_V]),
+    "katz_peer_clear_status": (_I, [_V]),
     "katz_add_f16": (_I, [_V, _V, _V, _L, _V]),
     "katz_concat_channels_f16": (_I, [_V, _V, _V, _L, _I, _I, _V]),
     "katz_nchw_to_nhwc_f16": (_I, [_V, _V, _I, _I, _I, _I, _V]),

@@ -155,6 +155,13 @@ extern "C" int katz_peer_allgather(const void* src, long long rows, long long ro
     KATZ_LAUNCH_RET();
 }
 
+// Back to zero (after a warm-up in which the ranks were not yet in step, say). Synchronous.
+extern "C" int katz_peer_clear_status(void* arena) {
+    KATZ_CHECK_ARG(arena, KATZ_EINVAL);
+    cudaError_t e = cudaMemset(reinterpret_cast<unsigned int*>(arena) + 2, 0, sizeof(unsigned int));
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
 extern "C" int katz_peer_status(const void* arena) {
     KATZ_CHECK_ARG(arena, KATZ_EINVAL);
     unsigned int v = 0;

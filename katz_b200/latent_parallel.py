@@ -211,7 +211,15 @@ class RowParallelStep:
                 rp.peer = None          # every rank reached the same verdict: the exchanges go through torch.distributed
         unet.rp = rp
         self.rp = rp
+        if world > 1 and dist.is_initialized():
+            dist.barrier(group=group)      # start the warm-up steps together: an exchange waits only a second or two for a peer
         self._inner = GraphedStep(unet, batch, height, width, text_len=text_len, warmup=warmup)
+        if rp.peer is not None:
+            # whatever skew the ranks had while they warmed up and captured is not the step's: from here on a time-out counts
+            torch.cuda.synchronize()
+            dist.barrier(group=group)
+            rp.peer.clear_status()
+            dist.barrier(group=group)
         self.graph = self._inner.graph
         self.launches_per_step = self._inner.launches_per_step
         self.static = self._inner.static

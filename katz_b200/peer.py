@@ -121,6 +121,10 @@ class PeerArena:
             lib.katz_peer_arena_free(ctypes.c_void_p(self._ptr))
             self._ptr = 0
 
+    def clear_status(self):
+        """Forget a time-out recorded so far (the ranks of a job are not in step while they warm up and capture)."""
+        _lib.check(_lib.load().katz_peer_clear_status(ctypes.c_void_p(self._ptr)), "katz_peer_clear_status")
+
     def status(self):
         """0, or 100 + the rank whose block never arrived within the bounded wait. Synchronises the device."""
         return _lib.load().katz_peer_status(ctypes.c_void_p(self._ptr))
