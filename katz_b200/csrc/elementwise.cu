@@ -31,6 +31,26 @@ __global__ void fast_gelu_mul_kernel(const __half2* __restrict__ x, const __half
     }
 }
 
+// The same on 16-byte packs of eight halves (the reference op moves packs of that size, elementwise.cuh:113-124);
+// the launcher takes it when the three pointers are 16-byte aligned, and leaves the tail (n % 8) to the pair kernel.
+__global__ void fast_gelu_mul_v8_kernel(const uint4* __restrict__ x, const uint4* __restrict__ m, uint4* __restrict__ out,
+                                        long long npacks) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < npacks; i += (long long)gridDim.x * blockDim.x) {
+        uint4 xv = x[i], mv = m[i], o;
+        const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+        const __half2* mh = reinterpret_cast<const __half2*>(&mv);
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float2 a = __half22float2(xh[k]), b = __half22float2(mh[k]);
+            oh[k] = __floats2half2_rn(fast_gelu_mul_one(a.x, b.x), fast_gelu_mul_one(a.y, b.y));
+        }
+        out[i] = o;
+    }
+}
+
 // Unfused GEGLU of the reference torch path (activations.py:146-149): h, g = chunk(proj(x)); h * gelu(g), erf GELU,
 // gelu result and product each rounded to half as torch's fp16 ops do.
 __global__ void geglu_erf_kernel(const __half* __restrict__ hg, __half* __restrict__ out, long long M, int F, int ld) {
@@ -226,8 +246,15 @@ extern "C" int katz_fast_gelu_mul_f16(const void* x, const void* m, void* out, l
     KATZ_CHECK_ARG(x && m && out, KATZ_EINVAL);
     KATZ_CHECK_ARG(n > 0 && n % 2 == 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(((uintptr_t)x & 3) == 0 && ((uintptr_t)m & 3) == 0 && ((uintptr_t)out & 3) == 0, KATZ_EALIGN);
-    launch_k(fast_gelu_mul_kernel, ew_grid(n / 2, 256), 256, 0, (cudaStream_t)stream, (const __half2*)x, (const __half2*)m,
-                                                                              (__half2*)out, n / 2);
+    long long done = 0;
+    if ((((uintptr_t)x | (uintptr_t)m | (uintptr_t)out) & 15) == 0 && n >= 8) {
+        done = n & ~7ll;
+        launch_k(fast_gelu_mul_v8_kernel, ew_grid(done / 8, 256), 256, 0, (cudaStream_t)stream, (const uint4*)x, (const uint4*)m,
+                 (uint4*)out, done / 8);
+        if (done == n) KATZ_LAUNCH_RET();
+    }
+    launch_k(fast_gelu_mul_kernel, ew_grid((n - done) / 2, 256), 256, 0, (cudaStream_t)stream, (const __half2*)((const __half*)x + done),
+             (const __half2*)((const __half*)m + done), (__half2*)((__half*)out + done), (n - done) / 2);
     KATZ_LAUNCH_RET();
 }
 

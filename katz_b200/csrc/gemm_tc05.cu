@@ -753,11 +753,6 @@ int* tc05_status_device_ptr() { return status_ptr(); }
 
 // Tile width by wave efficiency: tiles of width bn cost ~bn per wave; pick the width with the least total cost.
 static int pick_bn(int m_tiles, int n_out, bool geglu) {
-    // KATZ_TC05_BN=96|128|160|256 forces a width (tuning runs); ignored where the width is not available
-    if (const char* e = getenv("KATZ_TC05_BN")) {
-        const int v = atoi(e);
-        if ((v == 128 || v == 256 || ((v == 160 || v == 96) && !geglu))) return v;
-    }
     const int sms = sm_count();
     const int cand[4] = {256, 160, 128, 96};     // 96: small M (batch 1, row shards), where wider tiles leave SMs idle
     int best = 128;

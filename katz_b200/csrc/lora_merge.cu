@@ -625,7 +625,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) lora_merge_f16_ws_kernel(const 
     pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
     using namespace tc05;
     using T = __half;
-    constexpr int WS_NW = WsCfg<MAXL>::NW, WS_NB = WsCfg<MAXL>::NB;
+    constexpr int WS_NW = WsCfg<MAXL>::NW;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* smem_a = smem + WS_NW * WS_W_BYTES;

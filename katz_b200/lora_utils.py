@@ -14,8 +14,15 @@ What differs, and why: hub files are not reachable, so where the reference calls
 `LoraLoaderMixin.lora_state_dict(repo)` the pipe supplies `lora_source(repo) -> (lora_state_dict, network_alphas)`;
 the pristine weights stay resident on the device inside the merger, so a `default_unet_state_dict` argument is only
 copied in when it is a different dict from the one seen last (and it is never modified, where the reference adds into
-it); the text-encoder part of the reference functions (lora_utils.py:36-54) belongs to the text encoders, which are
-outside this path, and is skipped with a note when the pipe has none.
+it).
+
+The text-encoder part of both reference functions (lora_utils.py:36-54, ...katz.py:1749-1767) is here too:
+`state_dict[key] += up @ down` (no scale) over `<repo>_key_match_text_encoder.json` and `..._text_encoder_2.json`, into
+whatever `pipe.text_encoder` / `pipe.text_encoder_2` hold — an `nn.Module` whose `state_dict()` tensors are its live
+parameters, or a plain dict of CUDA tensors. The reference hard-codes the one repo that ships text-encoder layers; here a
+repo takes part when its key-map file exists. As in the reference the text encoders are ADDED into and never restored
+by `restore_unet`; `restore_text_encoders()` is there for a caller that wants them back. A pipe without text encoders
+skips the part with a note.
 """
 import os
 from collections import OrderedDict
@@ -36,6 +43,48 @@ class KatzLoraPipelineMixin:
     _lora_merger = None
     _lora_keys = None
     _pristine_src = None
+    _te_mergers = None
+
+    def _text_encoder_weights(self, which, keys):
+        te = getattr(self, which, None)
+        if te is None:
+            return None
+        sd = te if isinstance(te, dict) else te.state_dict()
+        missing = [k for k in keys if k not in sd]
+        if missing:
+            raise KatzError("%s has no weight %s (%d of %d keys missing)" % (which, missing[0], len(missing), len(keys)))
+        return OrderedDict((k, sd[k]) for k in keys)
+
+    def patch_text_encoders(self, lora_state_dict, repo):
+        """`text_encoder[_2].state_dict()[key] += up @ down` for every key of the repo's two text-encoder key maps
+        (lora_utils.py:36-54): an additive merge into the live weights, scale 1. Returns the number of layers merged."""
+        merged = 0
+        for which in ("text_encoder", "text_encoder_2"):
+            path = _repo_file(self.lora_info_dir, repo, "_key_match_%s.json" % which)
+            if not os.path.exists(path):
+                continue
+            km = load_key_map(path)
+            weights = self._text_encoder_weights(which, list(km))
+            if weights is None:
+                print("patch_on_lora: no %s on this pipe; its LoRA layers of %s are not applied" % (which, repo))
+                continue
+            if self._te_mergers is None:
+                self._te_mergers = {}
+            m = self._te_mergers.get(which)
+            if m is None or m.keys != list(km):
+                m = self._te_mergers[which] = LoraMerger(weights)
+            adapter = adapter_from_lora_state_dict(lora_state_dict, km, m.device, m.dtype)
+            if m.merged:
+                m.merge_in_place(adapter, 1.0)
+            else:
+                m.merge(adapter, 1.0)
+            merged += len(km)
+        return merged
+
+    def restore_text_encoders(self):
+        """The text encoders return to the weights they had before the first patch, bit-exactly."""
+        for m in (self._te_mergers or {}).values():
+            m.restore()
 
     def lora_key_map(self, repo):
         path = _repo_file(self.lora_info_dir, repo, "_key_match_unet.json")
@@ -78,8 +127,8 @@ class KatzLoraPipelineMixin:
         adapter = adapter_from_lora_state_dict(lora_state_dict, km, merger.device, merger.dtype)
         merger.merge(adapter, REFERENCE_UNET_SCALE)
         self.unet.invalidate_caches()
-        if getattr(self, "text_encoder", None) is None and "TheLastBen/Filmic" in lora_model_repos:
-            print("patch_on_lora: no text encoders on this pipe; the text-encoder LoRA of TheLastBen/Filmic is not applied")
+        for repo in lora_model_repos:
+            self.patch_text_encoders(lora_state_dict, repo)
 
     def restore_unet(self, default_unet_state_dict=None):
         """The UNet returns to the pristine weights, bit-exactly (one copy pass)."""
@@ -91,10 +140,12 @@ class KatzLoraPipelineMixin:
 
 
 class KatzPipe(KatzLoraPipelineMixin):
-    """The slice of the reference pipeline object this path touches: `pipe.unet`, optional `pipe.controlnet`."""
+    """The slice of the reference pipeline object this path touches: `pipe.unet`, optional `pipe.controlnet` and
+    `pipe.text_encoder` / `pipe.text_encoder_2` (modules or dicts of CUDA weights) for the text-encoder LoRA layers."""
 
-    def __init__(self, unet, controlnet=None, lora_source=None, lora_info_dir=None):
+    def __init__(self, unet, controlnet=None, lora_source=None, lora_info_dir=None, text_encoder=None, text_encoder_2=None):
         self.unet, self.controlnet = unet, controlnet
+        self.text_encoder, self.text_encoder_2 = text_encoder, text_encoder_2
         self.lora_source = lora_source
         if lora_info_dir is not None:
             self.lora_info_dir = lora_info_dir
@@ -114,9 +165,10 @@ def patch_on_lora(pipe, lora_model_repos):
     key_maps = [pipe.lora_key_map(r) for r in lora_model_repos]
     keys = list(OrderedDict((k, None) for km in key_maps for k in km))
     merger = pipe.lora_merger(keys)
-    adapters = []
+    adapters, dicts = [], []
     for repo, km in zip(lora_model_repos, key_maps):
         lora_state_dict, _network_alphas = pipe.lora_source(repo)
+        dicts.append(lora_state_dict)
         adapters.append(adapter_from_lora_state_dict(lora_state_dict, km, merger.device, merger.dtype))
     scales = [REFERENCE_UNET_SCALE] * len(adapters)
     if merger.merged:
@@ -124,5 +176,5 @@ def patch_on_lora(pipe, lora_model_repos):
     else:
         merger.merge(adapters, scales)
     pipe.unet.invalidate_caches()
-    if getattr(pipe, "text_encoder", None) is None and "TheLastBen/Filmic" in lora_model_repos:
-        print("patch_on_lora: no text encoders on this pipe; the text-encoder LoRA of TheLastBen/Filmic is not applied")
+    for repo, lora_state_dict in zip(lora_model_repos, dicts):
+        pipe.patch_text_encoders(lora_state_dict, repo)

@@ -309,3 +309,37 @@ def _scale_param(name, shape, t):
 
 
 _bias_fan_in = {}
+
+
+# The two SDXL text encoders as far as a LoRA sees them: (layers, width, mlp width)
+TEXT_ENCODER_DIMS = {"text_encoder": (12, 768, 3072), "text_encoder_2": (32, 1280, 5120)}
+
+
+def text_encoder_lora_key_map(which, layers=None):
+    """The reference's key map for a text encoder's LoRA layers (lora_info_shm/*_key_match_text_encoder[_2].json):
+    {state-dict key: {"lora_down_key", "lora_up_key"}} over q/k/v/out projections and the two MLP linears of every
+    layer, in the reference's order, and {state-dict key: (out, in)}."""
+    from collections import OrderedDict
+    n, d, f = TEXT_ENCODER_DIMS[which]
+    km, shapes = OrderedDict(), OrderedDict()
+    for i in range(n if layers is None else layers):
+        base = "text_model.encoder.layers.%d." % i
+        for proj in ("k", "v", "q", "out"):
+            key = base + "self_attn.%s_proj.weight" % proj
+            stem = "%s.%sself_attn.to_%s_lora." % (which, base, proj)
+            km[key] = {"lora_down_key": stem + "down.weight", "lora_up_key": stem + "up.weight"}
+            shapes[key] = (d, d)
+        for fc, shp in (("fc1", (f, d)), ("fc2", (d, f))):
+            key = base + "mlp.%s.weight" % fc
+            stem = "%s.%smlp.%s.lora_linear_layer." % (which, base, fc)
+            km[key] = {"lora_down_key": stem + "down.weight", "lora_up_key": stem + "up.weight"}
+            shapes[key] = shp
+    return km, shapes
+
+
+def key_map_digest(key_map, shapes, rank):
+    """sha256 over the sorted lines `key down_key up_key down_shape up_shape` (what tests/golden pins)."""
+    import hashlib
+    lines = sorted("%s %s %s %s %s" % (k, m["lora_down_key"], m["lora_up_key"], (rank, shapes[k][1]), (shapes[k][0], rank))
+                   for k, m in key_map.items())
+    return hashlib.sha256("\n".join(lines).encode()).hexdigest()

@@ -128,9 +128,79 @@ def kohya_fixture(out_dir):
         json.dump({"keys": mapping, "alphas": alphas}, fw, indent=0, sort_keys=True)
 
 
+def cache_fixture(ref_root, out_dir):
+    """cache_counts.json: the loads the reference's own analysis (trace/adapter_loading_analysis.py:48-200) counts on a
+    seeded synthetic trace (katz_b200.adapter_cache.zipf_trace; the production trace is not distributed), for LRU and
+    LFU and cache sizes 1..10. The analysis plots its result; a do-nothing stand-in for the plotting library is put
+    in its way, and the counts are read from what it prints."""
+    import contextlib
+    import importlib.util
+    import io
+    import re
+    import types
+    sys.path.insert(0, os.path.normpath(os.path.join(HERE, "..", "..")))
+    from katz_b200.adapter_cache import zipf_trace
+    trace = zipf_trace(600, n_loras=24, n_controlnets=6, alpha=1.1, instances=3, seed=7, scene_id="A")
+
+    class _Quiet(types.ModuleType):
+        def __getattr__(self, name):
+            return lambda *a, **k: None
+    mpl, plt = _Quiet("matplotlib"), _Quiet("matplotlib.pyplot")
+    mpl.rcParams = {}
+    mpl.pyplot = plt
+    saved = {k: sys.modules.get(k) for k in ("matplotlib", "matplotlib.pyplot")}
+    sys.modules["matplotlib"], sys.modules["matplotlib.pyplot"] = mpl, plt
+    work = tempfile.mkdtemp(prefix="katz_trace_")
+    cwd = os.getcwd()
+    counts = {}
+    try:
+        os.chdir(work)
+        with open("trace.json", "w") as fw:
+            json.dump(trace, fw)
+        spec = importlib.util.spec_from_file_location("ref_adapter_loading", os.path.join(ref_root, "trace", "adapter_loading_analysis.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        for policy in ("LRU", "LFU"):
+            buf = io.StringIO()
+            with contextlib.redirect_stdout(buf):
+                mod.adapter_loading_analysis("trace.json", "A", policy)
+            counts[policy] = {"loras": {}, "controlnets": {}}
+            for size, kind, n in re.findall(r"Cache size: (\d+), overall switch (controlnet|lora) times: (\d+)", buf.getvalue()):
+                counts[policy][kind + "s"][size] = int(n)
+            assert len(counts[policy]["loras"]) == 10 and len(counts[policy]["controlnets"]) == 10
+    finally:
+        os.chdir(cwd)
+        for k, v in saved.items():
+            if v is None:
+                sys.modules.pop(k, None)
+            else:
+                sys.modules[k] = v
+    with open(os.path.join(out_dir, "cache_counts.json"), "w") as fw:
+        json.dump({"trace": trace, "loads": counts}, fw, sort_keys=True)
+
+
+def text_encoder_key_map_fixture(ref_root, out_dir):
+    """text_encoder_key_maps.json: digest and size of the reference's two text-encoder key maps together with the adapter
+    tensor shapes its shape inventory lists for them (lora_info_shm/TheLastBen_Filmic*.json)."""
+    info = os.path.join(ref_root, "lora_info_shm")
+    with open(os.path.join(info, "TheLastBen_Filmic.json")) as fr:
+        inventory = json.load(fr)
+    out = {}
+    for which in ("text_encoder", "text_encoder_2"):
+        with open(os.path.join(info, "TheLastBen_Filmic_key_match_%s.json" % which)) as fr:
+            km = json.load(fr)
+        lines = sorted("%s %s %s %s %s" % (k, m["lora_down_key"], m["lora_up_key"], tuple(inventory[m["lora_down_key"]]["shape"]),
+                                           tuple(inventory[m["lora_up_key"]]["shape"])) for k, m in km.items())
+        out[which] = {"entries": len(km), "order": list(km)[:6], "digest": hashlib.sha256("\n".join(lines).encode()).hexdigest()}
+    with open(os.path.join(out_dir, "text_encoder_key_maps.json"), "w") as fw:
+        json.dump(out, fw, indent=1, sort_keys=True)
+
+
 def main(ref_root):
     diffusers = _import_reference(ref_root)
     kohya_fixture(HERE)
+    cache_fixture(ref_root, HERE)
+    text_encoder_key_map_fixture(ref_root, HERE)
     from diffusers import ControlNetModel, EulerDiscreteScheduler, UNet2DConditionModel
     from diffusers.models.lora import LoRACompatibleLinear, LoRALinearLayer
     from katz_b200.params import (SDXL_UNET_CONFIG, TINY_UNET_CONFIG, controlnet_param_shapes, init_state_dict,

@@ -97,3 +97,17 @@ def test_file_to_adapter_through_the_key_map_and_the_shm_source(tmp_path):
     from katz_b200 import KatzError
     with pytest.raises(KatzError):
         src(2)
+
+
+def test_text_encoder_key_maps_equal_the_reference(golden_dir):
+    """The text encoders' LoRA key maps (names, order, adapter shapes) against the digest of the reference's own files."""
+    import json
+    import os
+    from katz_b200.params import key_map_digest, text_encoder_lora_key_map
+    with open(os.path.join(golden_dir, "text_encoder_key_maps.json")) as fr:
+        gold = json.load(fr)
+    for which in ("text_encoder", "text_encoder_2"):
+        km, shapes = text_encoder_lora_key_map(which)
+        assert len(km) == gold[which]["entries"] and list(km)[:6] == gold[which]["order"]
+        assert key_map_digest(km, shapes, 64) == gold[which]["digest"]
+    assert len(text_encoder_lora_key_map("text_encoder_2", layers=3)[0]) == 18

@@ -105,3 +105,52 @@ def test_residual_shapes_match_the_sdxl_list():
     a = build_arg_parser("unet").parse_args(["--world-size", "8", "--controlnet-parallel", "--controlnet-parallel-rank", "3", "5", "7",
                                              "--lora-mode", "sync", "--load-lora-mode", "async", "--max-lora-num", "2"])
     assert a.controlnet_parallel_rank == [3, 5, 7] and a.lora_mode == "sync"
+
+
+def test_reference_flags_select_the_lora_hooks():
+    """What main() hands to unet_server_loop for each combination of the reference's LoRA flags (sdxl_unet_server.py:24-38)."""
+    from katz_b200 import servers
+
+    class FakePipe:
+        lora_info_dir = "."
+
+        def __init__(self):
+            self.calls = []
+
+        def patch_on_lora(self, sd, repos, default):
+            self.calls.append((sorted(sd), list(repos), default))
+
+        def restore_unet(self):
+            self.calls.append("restore")
+
+    class FakeClient:
+        def gather(self, i, device):
+            return {"a": torch.full((2,), float(i + 1)), "b": torch.ones(2)}
+
+    def parse(*flags):
+        return servers.build_arg_parser("unet").parse_args(list(flags))
+
+    a = parse()
+    assert a.lora_mode == "without" and a.load_lora_mode == "default" and a.max_lora_num == 0
+    repos = servers.REFERENCE_LORA_REPOS
+    assert repos[0] == [] and len(repos[1]) == 1 and len(repos[2]) == 2
+
+    pipe = FakePipe()
+    req, lora, restore = servers.make_lora_hooks(pipe, "without", "default", [], "cpu")
+    assert req is None and lora is None and restore == pipe.restore_unet
+
+    req, lora, restore = servers.make_lora_hooks(pipe, "full", "default", repos[1], "cpu")
+    assert req is not None and lora is None
+
+    # sync + async: nothing happens until the loader's status says every adapter is in shared memory; then the adapters
+    # are summed element-wise and merged once through the pipeline entry point
+    req, lora, restore = servers.make_lora_hooks(pipe, "sync", "async", repos[2], "cpu", shm_client=FakeClient())
+    assert req is None and lora is not None
+    assert lora(0) is False and lora(10) is False and pipe.calls == []
+    assert lora(20) is True
+    keys, got_repos, default = pipe.calls[0]
+    assert keys == ["a", "b"] and got_repos == repos[2] and default is None
+    restore()
+    assert pipe.calls[-1] == "restore"
+    # a mode that names adapters but has none to load needs no hook
+    assert servers.make_lora_hooks(pipe, "sync", "async", [], "cpu")[:2] == (None, None)

@@ -142,6 +142,13 @@ def test_fast_gelu_mul(cuda_device):
     diff = (out.float() - ref.float()).abs()
     # same rounding sequence; the only freedom is tanh's last bit
     assert float(diff.max()) <= 4e-3 and float((diff > 0).float().mean()) < 0.02
+    # 16-byte packs, the ragged tail after them and a start that is only 4-byte aligned give the same bits
+    from katz_b200 import ops
+    xs, ms = x.cuda().reshape(-1)[:4102], m.cuda().reshape(-1)[:4102]
+    whole = out.cuda().reshape(-1)
+    assert torch.equal(ops.fast_gelu_mul(xs.clone(), ms.clone()), whole[:4102])
+    xo, mo = x.cuda().reshape(-1)[2:4100], m.cuda().reshape(-1)[2:4100]        # views: 4 bytes past a 16-byte boundary
+    assert torch.equal(ops.fast_gelu_mul(xo, mo), whole[2:4100])
 
 
 def test_layer_norm_and_geglu(cuda_device):
@@ -292,7 +299,8 @@ def test_feed_forward_geglu_fused(cuda_device, M, F, K, monkeypatch):
 
 
 @pytest.mark.parametrize("B,H,Sq,Sk", [(2, 2, 256, 256), (2, 5, 1024, 77), (1, 3, 200, 130), (2, 10, 4096, 4096),
-                                       (2, 20, 1024, 1024), (1, 1, 128, 128)])
+                                       (2, 20, 1024, 1024), (1, 1, 128, 128),
+                                       (1, 10, 16384, 16384)])      # the last: one image of the 2048x2048-pixel step
 def test_attention_tcgen05(cuda_device, B, H, Sq, Sk, monkeypatch):
     from katz_b200 import ops
     g = torch.Generator().manual_seed(14)

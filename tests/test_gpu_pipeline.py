@@ -77,3 +77,52 @@ def test_request_stream_switches_loras(cuda_device):
     merger.restore()
     for k, w in targets.items():
         assert torch.equal(w.cpu(), sd[k])
+
+
+def test_cached_stream_loads_adapters_from_pinned_host_copies(cuda_device):
+    """Requests name adapter ids; the adapters live in pinned host memory and reach the GPU through the cache: the
+    results equal those of the stream whose whole pool is resident, and the loads are what the policy predicts."""
+    from katz_b200.adapter_cache import CachedLoraStream, replay_loads
+    from katz_b200.lora import LoraMerger
+    from katz_b200.pipeline import KatzDenoiser, LoraRequestStream
+    from katz_b200.unet import KatzUNet
+    cfg = TINY_UNET_CONFIG
+    sd = init_state_dict(unet_param_shapes(cfg), seed=0, dtype=torch.float16)
+    unet = KatzUNet(cfg, cuda_device, sd)
+    targets = unet.lora_targets(lora_target_keys(cfg, include_proj=True))
+    merger = LoraMerger(targets, on_change=unet.invalidate_caches)
+    g = torch.Generator().manual_seed(4)
+    host = []
+    for _ in range(4):
+        host.append(OrderedDict((k, ((torch.randn(w.shape[0], 8, generator=g) * 0.02).half().pin_memory(),
+                                     (torch.randn(8, w.shape[1], generator=g) / 8).half().pin_memory())) for k, w in targets.items()))
+    loads = []
+
+    def loader(i):
+        loads.append(i)
+        return OrderedDict((k, (u.to(cuda_device, non_blocking=True), d.to(cuda_device, non_blocking=True))) for k, (u, d) in host[i].items())
+
+    _, ctx, te, ti, _ = (t.half().cuda() for t in tiny_inputs(cfg))
+    den = KatzDenoiser(unet, 16, 16)
+    inputs = lambda i: dict(prompt_embeds=ctx, text_embeds=te, time_ids=ti)   # noqa: E731
+    ids = [0, 1, 0, 2, 3, 0, 1, 1]
+    cached = CachedLoraStream(den, merger, loader, capacity=2, policy="LRU")
+    got = cached.run([(i,) for i in ids], inputs, num_inference_steps=2, seed=0)
+    # consecutive equal requests do not look the adapter up again
+    lookups = [i for n, i in enumerate(ids) if n == 0 or ids[n - 1] != i]
+    assert loads == [0, 1, 2, 3, 0, 1] and cached.cache.loads == replay_loads(lookups, 2, "LRU")
+    st = cached.cache.stats()
+    assert st["resident"] == 2 and st["hits"] == 1 and st["bytes_loaded"] == 6 * st["resident_bytes"] // 2
+    resident = LoraRequestStream(den, merger, [loader(i) for i in range(4)])
+    want = resident.run(ids, inputs, num_inference_steps=2, seed=0)
+    for (a, _), (b, _) in zip(got, want):
+        assert torch.equal(a, b)
+    # a request with no adapter runs on the pristine weights; two adapters in one request are summed by the merge
+    more = cached.run([(), (2, 3)], inputs, num_inference_steps=2, seed=0)
+    merger.restore()
+    plain = den.denoise(den.prepare_latents(seed=0), num_inference_steps=2, **inputs(0))
+    assert torch.equal(more[0][0], plain)
+    merger.merge([loader(2), loader(3)], [1.0, 1.0])
+    both = den.denoise(den.prepare_latents(seed=1), num_inference_steps=2, **inputs(0))
+    assert torch.equal(more[1][0], both)
+    merger.restore()

@@ -219,6 +219,76 @@ def test_patch_on_lora_entry_points_with_the_reference_signatures(cuda_device, t
         patch_on_lora(KatzPipe(unet, lora_info_dir=str(tmp_path / "lora_info_shm")), [REPO])      # no lora_source: fails loudly
 
 
+def test_text_encoder_lora_layers_through_both_entry_points(cuda_device, tmp_path):
+    """The text-encoder part of the reference's two patch functions (lora_utils.py:36-54, ...katz.py:1749-1767):
+    `state_dict[key] += up @ down` over the reference's text-encoder key maps, into a module and into a plain dict."""
+    from katz_b200.lora_utils import KatzPipe, patch_on_lora
+    from katz_b200.params import text_encoder_lora_key_map
+    from oracle import lora_oracle
+    info_dir = str(tmp_path / "lora_info_shm")
+    info, km = _fixture_files(info_dir)
+    cfg, unet, _ = _models(cuda_device)
+    tensors = _lora_tensors(info)
+    g = torch.Generator().manual_seed(9)
+    te_maps, te_w = {}, {}
+    for which, layers in (("text_encoder", None), ("text_encoder_2", 3)):       # all 72 layers of the first, 18 of the second
+        kmt, shapes = text_encoder_lora_key_map(which, layers)
+        te_maps[which] = kmt
+        with open(os.path.join(info_dir, REPO.replace("/", "_") + "_key_match_%s.json" % which), "w") as fw:
+            json.dump(kmt, fw)
+        te_w[which] = {k: (torch.randn(shp, generator=g) * 0.02).half() for k, shp in shapes.items()}
+        for k, m in kmt.items():
+            o, n = shapes[k]
+            tensors[m["lora_down_key"]] = (torch.randn(RANK, n, generator=g) / RANK).half()
+            tensors[m["lora_up_key"]] = (torch.randn(o, RANK, generator=g) * 0.02).half()
+
+    class Encoder(torch.nn.Module):                                              # weights addressed by the reference's key names
+        def __init__(self, weights):
+            super().__init__()
+            self.w = torch.nn.ParameterDict({k.replace(".", "/"): torch.nn.Parameter(v.clone().cuda(), requires_grad=False) for k, v in weights.items()})
+
+        def state_dict(self):
+            return {k.replace("/", "."): v.data for k, v in self.w.items()}
+
+    te1 = Encoder(te_w["text_encoder"])
+    te2 = {k: v.clone().cuda() for k, v in te_w["text_encoder_2"].items()}
+    pipe = KatzPipe(unet, lora_source=lambda repo: (tensors, None), lora_info_dir=info_dir, text_encoder=te1, text_encoder_2=te2)
+
+    def expected(which, times):
+        kmt = te_maps[which]
+        ad = {k: (tensors[m["lora_up_key"]], tensors[m["lora_down_key"]]) for k, m in kmt.items()}
+        w = {k: te_w[which][k] for k in kmt}
+        for _ in range(times):
+            w = lora_oracle.merge_set(w, [ad], [1.0])
+        return w
+
+    def check(times):
+        for which, live in (("text_encoder", te1.state_dict()), ("text_encoder_2", te2)):
+            ref = expected(which, times)
+            for k in te_maps[which]:
+                d = (live[k].cpu().float() - ref[k].float()).abs()
+                assert float(d.max()) <= 2 ** -9 * float(ref[k].float().abs().max()), (which, k)
+                assert not torch.equal(live[k].cpu(), te_w[which][k])
+
+    patch_on_lora(pipe, [REPO])                                    # lora_utils.py:9
+    check(1)
+    pipe.patch_on_lora(tensors, [REPO], None)                      # ...katz.py:1730: adds into the text encoders again
+    check(2)
+    pipe.restore_unet()                                            # the reference restores the UNet only
+    assert not torch.equal(te2[next(iter(te2))].cpu(), te_w["text_encoder_2"][next(iter(te2))])
+    pipe.restore_text_encoders()
+    for k, v in te1.state_dict().items():
+        assert torch.equal(v.cpu(), te_w["text_encoder"][k]), k
+    for k, v in te2.items():
+        assert torch.equal(v.cpu(), te_w["text_encoder_2"][k]), k
+    # a pipe without text encoders says so and still merges the UNet
+    plain = KatzPipe(unet, lora_source=lambda repo: (tensors, None), lora_info_dir=info_dir)
+    patch_on_lora(plain, [REPO])
+    plain.restore_unet()
+    with pytest.raises(Exception):
+        KatzPipe(unet, lora_source=lambda repo: (tensors, None), lora_info_dir=info_dir, text_encoder={}).patch_text_encoders(tensors, REPO)
+
+
 def test_hoisted_text_kv_and_cond_embedding_give_identical_steps(cuda_device):
     """Step-invariant hoisting: with `cache_text_kv` / `cache_cond_embedding` the cross-attention K/V projection and the
     ControlNet conditioning embedding are computed once per request; every step must be bit-identical to the un-hoisted
