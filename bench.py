@@ -421,7 +421,7 @@ def main():
                               "oracle at this size by tests/test_gpu_sdxl_size.py)"})
 
     flops = unet_step_flops(cfg, B, HW, HW)
-    roof = tgb = cn_leg = merge32 = None
+    roof = tgb = cn_leg = merge32 = vae_leg = None
     if rank == 0 and not args.no_extras:
         # ---- dominant kernel alone: the feed-forward projection GEMM (2048 x 10240 x 1280), burst conditions
         M, N, K = B * (HW // 4) * (HW // 4), 10240, 1280
@@ -481,6 +481,27 @@ def main():
             tc05 = max(tc05, ops.tc05_status())
             del gcn, both, cn, cond
             torch.cuda.empty_cache()
+            # ---- the VAE decode that follows the last step (one image): 10.47 TFLOP at 1024x1024 pixels
+            if HW <= 128:
+                from katz_b200.params import SDXL_VAE_CONFIG, vae_decode_flops, vae_decoder_param_shapes
+                from katz_b200.vae import KatzVaeDecoder
+                dec = KatzVaeDecoder(SDXL_VAE_CONFIG, dev, init_state_dict(vae_decoder_param_shapes(SDXL_VAE_CONFIG), seed=5,
+                                                                           dtype=torch.float16, device=dev, generator_device=dev))
+                zlat = (torch.randn(1, 4, HW, HW, generator=torch.Generator().manual_seed(6)) * SDXL_VAE_CONFIG["scaling_factor"]).half().to(dev)
+                eager_img = dec.decode_latents(zlat).clone()
+                dec.use_cuda_graph = True
+                for _ in range(2):
+                    img = dec.decode_latents(zlat)
+                vae_ms = time_events(lambda: dec.decode_latents(zlat), max(3, args.steps // 4))
+                vfl = vae_decode_flops(SDXL_VAE_CONFIG, 1, HW, HW)
+                ach = vfl / (vae_ms * 1e-3) / 1e12
+                vae_leg = {"workload": "SDXL VAE decode of one %dx%d latent to %dx%d pixels, fp16 (AutoencoderKL.decode)" % (HW, HW, 8 * HW, 8 * HW),
+                           "ms": vae_ms, "flop": vfl, "achieved": ach, "unit": "TFLOP/s", "peak": peaks["bf16_tflops_sustained"],
+                           "frac": ach / peaks["bf16_tflops_sustained"], "graph_equals_eager": bool(torch.equal(img, eager_img)),
+                           "finite": bool(torch.isfinite(img).all())}
+                tc05 = max(tc05, ops.tc05_status())
+                del dec, zlat, img, eager_img
+                torch.cuda.empty_cache()
             # ---- configuration 1: the 700-layer set with fp32 weights and fp32 adapters
             shapes = unet_param_shapes(cfg)
             keys32 = lora_target_keys(cfg)
@@ -557,7 +578,7 @@ def main():
                               "frac_of_burst": step_tflops / peaks["bf16_tflops"],
                               "peak_source": peaks["_source"] + " sustained", "flop_per_step": flops["total"],
                               "note": "per-GPU algorithmic FLOPs of the whole step / step time"},
-            "lora_merge": merge1, "lora_merge_2adapters": merge2, "lora_merge_fp32": merge32,
+            "lora_merge": merge1, "lora_merge_2adapters": merge2, "lora_merge_fp32": merge32, "vae_decode": vae_leg,
             "controlnet_step": cn_leg, "torch_gpu_baseline": tgb, "request_stream": stream_leg,
         }
         if world == 1 and not args.no_cpu_baseline:

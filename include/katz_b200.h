@@ -270,6 +270,11 @@ int katz_peer_clear_status(void* arena);
 /* get_timestep_embedding (diffusers/models/embeddings.py:26-66), flip_sin_to_cos, shift 0: out[rows, dim] fp16. */
 int katz_timestep_embedding_f16(const float* t, void* out, int rows, int dim, int ld_out, void* stream);
 int katz_silu_f16(const void* x, void* y, long long n, void* stream);
+/* y[r, 0..cols) = softmax(x[r, 0..cols)) in fp32 arithmetic, fp16 in and out, rows `ld_x` / `ld_y` elements apart; y may be
+ * x. The probabilities of an attention whose scores come from a GEMM: the VAE decoder's one-head attention over all
+ * pixels (diffusers/models/attention_processor.py:1276 with a 512-channel head; unet_2d_blocks.py:681-694).
+ * cols: a multiple of 8, at most 16384; ld_x, ld_y: multiples of 8; x, y 16-byte aligned. */
+int katz_softmax_rows_f16(const void* x, void* y, int rows, int cols, long long ld_x, long long ld_y, void* stream);
 int katz_add_f16(const void* a, const void* b, void* y, long long n, void* stream);
 /* y[rows, C1+C2] = x1[rows, C1] ++ x2[rows, C2]: torch.cat([hidden, skip], dim=1) of the up blocks
  * (diffusers/models/unets/unet_2d_blocks.py:2473,2608) in NHWC. */

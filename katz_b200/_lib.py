@@ -92,6 +92,7 @@ SIGNATURES = {
     "katz_residual_intake_f16": (_I, [_V, _V, POINTER(c_void_p), POINTER(c_float), _I, _L, _V]),
     "katz_timestep_embedding_f16": (_I, [_V, _V, _I, _I, _I, _V]),
     "katz_silu_f16": (_I, [_V, _V, _L, _V]),
+    "katz_softmax_rows_f16": (_I, [_V, _V, _I, _I, _L, _L, _V]),
     "katz_halo_assemble_f16": (_I, [_V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _V]),
     "katz_peer_ctrl_bytes": (_I, []),
     "katz_peer_arena_alloc": (_I, [_L, POINTER(c_void_p)]),

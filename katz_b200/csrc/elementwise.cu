@@ -232,6 +232,77 @@ __global__ void upsample2x_kernel(const uint4* __restrict__ x, uint4* __restrict
     }
 }
 
+// y[r, :] = softmax(x[r, :]) over `cols` fp16 logits, fp32 arithmetic: the probabilities of the VAE's one-head attention
+// (attention_processor.py:1276 for a head of 512 channels, which the 64-channel flash kernels do not cover; its scores
+// come from a GEMM). One CTA per row; a row of up to 256 * 8 * SM_MAXV logits stays in registers between the passes.
+constexpr int SM_THREADS = 256, SM_MAXV = 8;
+__global__ void __launch_bounds__(SM_THREADS) softmax_rows_kernel(const __half* __restrict__ x, __half* __restrict__ y, int cols,
+                                                                  long long ld_x, long long ld_y) {
+    pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
+    pdl_launch_dependents();
+    __shared__ float red[SM_THREADS / 32];
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (long long)blockIdx.x * ld_x);
+    uint4* yr = reinterpret_cast<uint4*>(y + (long long)blockIdx.x * ld_y);
+    const int packs = cols >> 3;
+    uint4 v[SM_MAXV];
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < SM_MAXV; ++i) {
+        const int p = tid + i * SM_THREADS;
+        if (p < packs) {
+            v[i] = xr[p];
+            const __half2* h = reinterpret_cast<const __half2*>(&v[i]);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float2 f = __half22float2(h[k]);
+                m = fmaxf(m, fmaxf(f.x, f.y));
+            }
+        }
+    }
+    m = warp_max(m);
+    if (lane == 0) red[wid] = m;
+    __syncthreads();
+    m = red[0];
+#pragma unroll
+    for (int w = 1; w < SM_THREADS / 32; ++w) m = fmaxf(m, red[w]);
+    __syncthreads();
+    const float L2E = 1.4426950408889634f, ml = m * L2E;
+    float e[SM_MAXV][8];
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < SM_MAXV; ++i) {
+        if (tid + i * SM_THREADS < packs) {
+            const __half2* h = reinterpret_cast<const __half2*>(&v[i]);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float2 f = __half22float2(h[k]);
+                e[i][2 * k] = exp2f(fmaf(f.x, L2E, -ml));
+                e[i][2 * k + 1] = exp2f(fmaf(f.y, L2E, -ml));
+                sum += e[i][2 * k] + e[i][2 * k + 1];
+            }
+        }
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) red[wid] = sum;
+    __syncthreads();
+    sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < SM_THREADS / 32; ++w) sum += red[w];       // fixed order: every thread gets the same bits
+    const float inv = 1.0f / sum;
+#pragma unroll
+    for (int i = 0; i < SM_MAXV; ++i) {
+        const int p = tid + i * SM_THREADS;
+        if (p < packs) {
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) oh[k] = __floats2half2_rn(e[i][2 * k] * inv, e[i][2 * k + 1] * inv);
+            yr[p] = o;
+        }
+    }
+}
+
 static inline int ew_grid(long long n, int threads) {
     long long g = (n + threads - 1) / threads;
     long long cap = 148ll * 16;
@@ -331,6 +402,15 @@ extern "C" int katz_halo_assemble_f16(const void* x, const void* edges, void* ou
     const long long total = (long long)B * Ho * Wo * (C / 8);
     launch_k(halo_assemble_kernel, ew_grid(total, 256), 256, 0, (cudaStream_t)stream, (const uint4*)x, (const uint4*)edges,
              (uint4*)out, B, h, W, C / 8, Ho, Wo, top, upsample, rank, world, total);
+    KATZ_LAUNCH_RET();
+}
+
+extern "C" int katz_softmax_rows_f16(const void* x, void* y, int rows, int cols, long long ld_x, long long ld_y, void* stream) {
+    KATZ_CHECK_ARG(x && y, KATZ_EINVAL);
+    KATZ_CHECK_ARG(rows > 0 && cols > 0 && cols % 8 == 0 && cols <= SM_THREADS * 8 * SM_MAXV, KATZ_ESIZE);
+    KATZ_CHECK_ARG(ld_x >= cols && ld_y >= cols && ld_x % 8 == 0 && ld_y % 8 == 0, KATZ_ESIZE);
+    KATZ_CHECK_ARG((((uintptr_t)x | (uintptr_t)y) & 15) == 0, KATZ_EALIGN);
+    launch_k(softmax_rows_kernel, rows, SM_THREADS, 0, (cudaStream_t)stream, (const __half*)x, (__half*)y, cols, ld_x, ld_y);
     KATZ_LAUNCH_RET();
 }
 

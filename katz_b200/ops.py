@@ -337,6 +337,19 @@ def fast_gelu_mul(x, m, out=None):
     return out
 
 
+def softmax_rows(x, out=None):
+    """Row softmax of a 2-D fp16 matrix of logits (fp32 arithmetic); `out` may be `x`. Rows may be strided."""
+    _f16(x, "x")
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise KatzError("softmax_rows: x must be 2-D with unit column stride")
+    if out is None:
+        out = torch.empty_like(x)
+    if out.shape != x.shape or out.stride(1) != 1 or out.dtype != torch.float16:
+        raise KatzError("softmax_rows: bad out")
+    call("katz_softmax_rows_f16", _p(x), _p(out), x.shape[0], x.shape[1], x.stride(0), out.stride(0), _stream())
+    return out
+
+
 def attention(q, k, v, heads, out=None, scale=None, kv_chunks=None):
     """q: [B,Sq,>=H*64] view, k/v: [B,Sk,...] views (unit last stride, any row/batch stride); returns [B,Sq,H*64].
     kv_chunks=(n_chunks, chunk_rows, chunk_stride): k/v describe the FIRST chunk ([B, chunk_rows, ...]); chunk c of the

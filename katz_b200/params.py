@@ -298,7 +298,7 @@ def init_state_dict(shapes, seed=0, dtype=torch.float16, device="cpu", generator
 
 
 def _scale_param(name, shape, t):
-    is_norm = (".norm" in name or name.startswith("conv_norm")) and len(shape) == 1
+    is_norm = (".norm" in name or "_norm" in name or name.startswith("conv_norm")) and len(shape) == 1
     if is_norm:
         return 1.0 + 0.1 * t if name.endswith(".weight") else 0.1 * t
     if name.endswith(".weight"):
@@ -343,3 +343,82 @@ def key_map_digest(key_map, shapes, rank):
     lines = sorted("%s %s %s %s %s" % (k, m["lora_down_key"], m["lora_up_key"], (rank, shapes[k][1]), (shapes[k][0], rank))
                    for k, m in key_map.items())
     return hashlib.sha256("\n".join(lines).encode()).hexdigest()
+
+
+# ---- the VAE decoder that follows the denoising loop (AutoencoderKL.decode; models/autoencoders/vae.py:185-347)
+SDXL_VAE_CONFIG = dict(latent_channels=4, out_channels=3, block_out_channels=(128, 256, 512, 512), layers_per_block=2,
+                       norm_num_groups=32, scaling_factor=0.13025)
+TINY_VAE_CONFIG = dict(latent_channels=4, out_channels=3, block_out_channels=(64, 128, 128), layers_per_block=2,
+                       norm_num_groups=32, scaling_factor=0.13025)
+
+
+def vae_decoder_param_shapes(cfg):
+    """Decoder-side parameter inventory of AutoencoderKL in the reference fork's state-dict naming, module order."""
+    from collections import OrderedDict
+    out = OrderedDict()
+    boc = cfg["block_out_channels"]
+    lc = cfg["latent_channels"]
+
+    def conv(p, cout, cin, k):
+        out[p + ".weight"] = (cout, cin, k, k)
+        out[p + ".bias"] = (cout,)
+
+    def norm(p, c):
+        out[p + ".weight"] = (c,)
+        out[p + ".bias"] = (c,)
+
+    def resnet(p, cin, cout):
+        norm(p + ".norm_silu1.0", cin)
+        conv(p + ".conv1", cout, cin, 3)
+        norm(p + ".norm_silu2.0", cout)
+        conv(p + ".conv2", cout, cout, 3)
+        if cin != cout:
+            conv(p + ".conv_shortcut", cout, cin, 1)
+
+    top = boc[-1]
+    conv("decoder.conv_in", top, lc, 3)
+    rev = list(reversed(boc))
+    prev = rev[0]
+    for i, c in enumerate(rev):
+        for j in range(cfg["layers_per_block"] + 1):
+            resnet("decoder.up_blocks.%d.resnets.%d" % (i, j), prev if j == 0 else c, c)
+        if i != len(rev) - 1:
+            conv("decoder.up_blocks.%d.upsamplers.0.conv" % i, c, c, 3)
+        prev = c
+    a = "decoder.mid_block.attentions.0"
+    norm(a + ".group_norm", top)
+    for n in ("to_q", "to_k", "to_v", "to_out.0"):
+        out[a + ".%s.weight" % n] = (top, top)
+        out[a + ".%s.bias" % n] = (top,)
+    resnet("decoder.mid_block.resnets.0", top, top)
+    resnet("decoder.mid_block.resnets.1", top, top)
+    norm("decoder.conv_norm_out", boc[0])
+    conv("decoder.conv_out", cfg["out_channels"], boc[0], 3)
+    conv("post_quant_conv", lc, lc, 1)
+    return out
+
+
+def vae_decode_flops(cfg, batch, h, w):
+    """Algorithmic FLOPs of one decode of a [batch, latent_channels, h, w] latent: 2*M*N*K per convolution / linear,
+    4*S*S*C for the one-head attention."""
+    shapes = vae_decoder_param_shapes(cfg)
+    boc = cfg["block_out_channels"]
+    n = len(boc)
+    total = 0.0
+
+    def res_of(key):
+        if key.startswith("decoder.up_blocks."):
+            i = int(key.split(".")[2])
+            lvl = i + 1 if ".upsamplers." in key else i
+            return h << lvl, w << lvl
+        if key.startswith("decoder.conv_out"):
+            return h << (n - 1), w << (n - 1)
+        return h, w
+    for k, shp in shapes.items():
+        if k.endswith(".weight") and len(shp) == 4:
+            hh, ww = res_of(k)
+            total += 2.0 * batch * hh * ww * shp[0] * shp[1] * shp[2] * shp[3]
+        elif k.endswith(".weight") and len(shp) == 2:
+            total += 2.0 * batch * h * w * shp[0] * shp[1]
+    total += 4.0 * batch * float(h * w) ** 2 * boc[-1]
+    return total

@@ -25,3 +25,15 @@ def cuda_device():
     from katz_b200 import load_library
     load_library()   # a missing library is a failure, not a skip
     return torch.device("cuda:0")
+
+
+@pytest.fixture(autouse=True, scope="module")
+def _release_cached_device_memory():
+    """The SDXL-size tests peak at tens of GB; hand the caching allocator's blocks back after every test module so that
+    tests which start other processes on the same GPU find room."""
+    yield
+    import gc
+    import torch
+    if torch.cuda.is_available() and torch.cuda.is_initialized():
+        gc.collect()
+        torch.cuda.empty_cache()

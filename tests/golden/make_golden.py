@@ -196,9 +196,35 @@ def text_encoder_key_map_fixture(ref_root, out_dir):
         json.dump(out, fw, indent=1, sort_keys=True)
 
 
+def vae_fixture(out_dir):
+    """tiny_vae_decode.npz: what the reference's AutoencoderKL.decode (models/autoencoders/autoencoder_kl.py) returns for a
+    tiny three-level decoder with seeded weights (katz_b200.params.init_state_dict, seed 3) on a seeded latent, fp32."""
+    from diffusers import AutoencoderKL
+    from katz_b200.params import TINY_VAE_CONFIG, init_state_dict, vae_decoder_param_shapes
+    cfg = TINY_VAE_CONFIG
+    n = len(cfg["block_out_channels"])
+    vae = AutoencoderKL(in_channels=3, out_channels=cfg["out_channels"], down_block_types=("DownEncoderBlock2D",) * n,
+                        up_block_types=("UpDecoderBlock2D",) * n, block_out_channels=cfg["block_out_channels"],
+                        layers_per_block=cfg["layers_per_block"], latent_channels=cfg["latent_channels"],
+                        norm_num_groups=cfg["norm_num_groups"], sample_size=32, scaling_factor=cfg["scaling_factor"]).eval()
+    shapes = vae_decoder_param_shapes(cfg)
+    ref_shapes = {k: tuple(v.shape) for k, v in vae.state_dict().items() if k.startswith("decoder.") or k.startswith("post_quant_conv.")}
+    assert ref_shapes == {k: tuple(v) for k, v in shapes.items()}, "decoder parameter inventory differs from the reference's"
+    sd = init_state_dict(shapes, seed=3, dtype=torch.float32)
+    missing, unexpected = vae.load_state_dict(sd, strict=False)
+    assert not unexpected and all(k.startswith("encoder.") or k.startswith("quant_conv.") for k in missing)
+    rng = np.random.default_rng(11)
+    z = torch.from_numpy(rng.standard_normal((2, cfg["latent_channels"], 8, 8), dtype=np.float32))
+    with torch.no_grad():
+        img = vae.decode(z, return_dict=False)[0]
+    np.savez_compressed(os.path.join(out_dir, "tiny_vae_decode.npz"), z=z.numpy(), image=img.numpy())
+    return _shape_digest(ref_shapes)
+
+
 def main(ref_root):
     diffusers = _import_reference(ref_root)
     kohya_fixture(HERE)
+    vae_fixture(HERE)
     cache_fixture(ref_root, HERE)
     text_encoder_key_map_fixture(ref_root, HERE)
     from diffusers import ControlNetModel, EulerDiscreteScheduler, UNet2DConditionModel
@@ -221,6 +247,16 @@ def main(ref_root):
     meta["sdxl_unet_params"] = int(sum(int(np.prod(s)) for s in ref_shapes.values()))
     meta["sdxl_controlnet_shape_digest"] = _shape_digest(ref_cn_shapes)
     meta["sdxl_controlnet_params"] = int(sum(int(np.prod(s)) for s in ref_cn_shapes.values()))
+    from diffusers import AutoencoderKL
+    from katz_b200.params import SDXL_VAE_CONFIG, vae_decoder_param_shapes
+    with torch.device("meta"):
+        ref_vae = AutoencoderKL(in_channels=3, out_channels=3, down_block_types=("DownEncoderBlock2D",) * 4,
+                                up_block_types=("UpDecoderBlock2D",) * 4, block_out_channels=SDXL_VAE_CONFIG["block_out_channels"],
+                                layers_per_block=2, latent_channels=4, norm_num_groups=32, sample_size=1024)
+    ref_vae_shapes = {k: tuple(v.shape) for k, v in ref_vae.state_dict().items() if k.startswith("decoder.") or k.startswith("post_quant_conv.")}
+    assert ref_vae_shapes == {k: tuple(v) for k, v in vae_decoder_param_shapes(SDXL_VAE_CONFIG).items()}
+    meta["sdxl_vae_decoder_shape_digest"] = _shape_digest(ref_vae_shapes)
+    meta["sdxl_vae_decoder_params"] = int(sum(int(np.prod(s)) for s in ref_vae_shapes.values()))
     # the 722-entry LoRA target set of the reference's key-map fixture
     with open(os.path.join(ref_root, "lora_info_shm", "TheLastBen_Papercut_SDXL_key_match_unet.json")) as fr:
         km = json.load(fr)

@@ -164,6 +164,9 @@ def _worker(rank, port, tmp, prefix, q):
 
 def test_servers_with_real_models_async_lora_over_shm(cuda_device, tmp_path):
     _fixture_files(str(tmp_path / "lora_info_shm"))
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()              # the three child processes share this GPU with whatever this process still caches
     prefix = "katzsrv%d_" % os.getpid()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()

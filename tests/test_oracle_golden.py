@@ -97,3 +97,24 @@ def test_lora_oracle_matches_reference(golden_dir):
     assert torch.equal(merged, torch.from_numpy(g["W16_merged"]))
     # copy restore is bit-exact
     assert torch.equal(lora_oracle.restore({"w": W16})["w"], W16)
+
+
+def test_vae_oracle_equals_reference_autoencoder(golden_dir):
+    """oracle.vae_oracle.vae_decode against the reference's AutoencoderKL.decode on the tiny seeded decoder."""
+    import os
+    import numpy as np
+    import torch
+    from katz_b200.params import (SDXL_VAE_CONFIG, TINY_VAE_CONFIG, init_state_dict, vae_decode_flops,
+                                  vae_decoder_param_shapes)
+    from oracle import vae_oracle
+    gold = np.load(os.path.join(golden_dir, "tiny_vae_decode.npz"))
+    sd = init_state_dict(vae_decoder_param_shapes(TINY_VAE_CONFIG), seed=3, dtype=torch.float32)
+    out = vae_oracle.vae_decode(sd, TINY_VAE_CONFIG, torch.from_numpy(gold["z"]))
+    assert float((out - torch.from_numpy(gold["image"])).abs().max()) <= 1e-5
+    import json
+    with open(os.path.join(golden_dir, "meta.json")) as fr:
+        meta = json.load(fr)
+    shapes = vae_decoder_param_shapes(SDXL_VAE_CONFIG)
+    assert sum(int(np.prod(s)) for s in shapes.values()) == meta["sdxl_vae_decoder_params"] == 49490199
+    assert abs(vae_decode_flops(SDXL_VAE_CONFIG, 1, 128, 128) / 1e12 - 10.47) < 0.01
+    assert vae_oracle.SDXL_VAE_CONFIG == SDXL_VAE_CONFIG
