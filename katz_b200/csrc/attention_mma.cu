@@ -127,12 +127,12 @@ __global__ void __launch_bounds__(ATHREADS) attention_d64_kernel(const __half* _
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             float m_new = fmaxf(m_run[hr], mx);
-            float corr = exp2f(m_run[hr] - m_new);
+            float corr = ex2_fast(m_run[hr] - m_new);
             float rs = 0.f;
 #pragma unroll
             for (int nf = 0; nf < 8; ++nf) {
-                float p0 = exp2f(s[nf][hr * 2] - m_new);
-                float p1 = exp2f(s[nf][hr * 2 + 1] - m_new);
+                float p0 = ex2_fast(s[nf][hr * 2] - m_new);
+                float p1 = ex2_fast(s[nf][hr * 2 + 1] - m_new);
                 s[nf][hr * 2] = p0;
                 s[nf][hr * 2 + 1] = p1;
                 rs += p0 + p1;

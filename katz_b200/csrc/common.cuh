@@ -168,6 +168,14 @@ __device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + _
 // exact (erf) GELU, the form torch.nn.functional.gelu computes by default
 __device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
 
+// 2^x as ONE special-function instruction (about 2 ulp, subnormal results flushed to zero); exp2f() is a short sequence
+// around the same instruction
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -277,8 +277,8 @@ __global__ void __launch_bounds__(SM_THREADS) softmax_rows_kernel(const __half* 
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 float2 f = __half22float2(h[k]);
-                e[i][2 * k] = exp2f(fmaf(f.x, L2E, -ml));
-                e[i][2 * k + 1] = exp2f(fmaf(f.y, L2E, -ml));
+                e[i][2 * k] = ex2_fast(fmaf(f.x, L2E, -ml));
+                e[i][2 * k + 1] = ex2_fast(fmaf(f.y, L2E, -ml));
                 sum += e[i][2 * k] + e[i][2 * k + 1];
             }
         }

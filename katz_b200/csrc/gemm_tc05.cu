@@ -87,16 +87,29 @@ __device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t* r) {
 // rounding that follows): 1 - erf(z) = (a1 t + ... + a5 t^5) exp(-z^2), t = 1 / (1 + p z), z = |x| / sqrt(2).
 // Two values at a time: ten packed instructions, four special-function ones (two reciprocals, two exp2) and four
 // scalar ones for the pair, against erff's thirty per value.
+__device__ __forceinline__ float rcp_approx(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ float2 gelu_erf_fast2(float2 x) {
     const float2 ax = make_float2(fabsf(x.x), fabsf(x.y));
     const float2 den = fma2(ax, make_float2(0.3275911f * 0.70710678f, 0.3275911f * 0.70710678f), make_float2(1.0f, 1.0f));
-    const float2 t = make_float2(__frcp_rn(den.x), __frcp_rn(den.y));
+    // approximate reciprocal and exp2 (one special-function instruction each, about 1 ulp): the rounded forms are short
+    // instruction sequences with a slow-path branch, and eight of them per thread and 16-column group were most of
+    // this epilogue's time
+    const float2 t = make_float2(rcp_approx(den.x), rcp_approx(den.y));
     float2 h = fma2(t, make_float2(0.5f * 1.061405429f, 0.5f * 1.061405429f), make_float2(0.5f * -1.453152027f, 0.5f * -1.453152027f));
     h = fma2(t, h, make_float2(0.5f * 1.421413741f, 0.5f * 1.421413741f));
     h = fma2(t, h, make_float2(0.5f * -0.284496736f, 0.5f * -0.284496736f));
     h = fma2(t, h, make_float2(0.5f * 0.254829592f, 0.5f * 0.254829592f));
     const float2 xx = mul2(mul2(x, x), make_float2(-0.5f * 1.4426950408889634f, -0.5f * 1.4426950408889634f));
-    const float2 e = make_float2(exp2f(xx.x), exp2f(xx.y));
+    const float2 e = make_float2(ex2_approx(xx.x), ex2_approx(xx.y));
     const float2 r = mul2(x, mul2(mul2(h, t), e));          // x * Phi(-|x|): the sign of x
     // x >= 0: x - r (r >= 0); x < 0: r (r < 0)  ==  max(x, 0) - |r|
     return make_float2(fmaxf(x.x, 0.f) - fabsf(r.x), fmaxf(x.y, 0.f) - fabsf(r.y));
@@ -463,13 +476,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                     }
                 }
             }
-            uint4 nb4[4], nv4[4];               // bias / aux values of the warp's next chunk
+            uint4 nb4[4], nv4[4];               // bias / aux values of the warp's next chunk (GEGLU: of its next 16-column group)
             if (!GEGLU) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     nb4[k] = load_vec(bias_p, half * 32 + k * 8);
                     nv4[k] = load_vec(aux_p, half * 32 + k * 8);
                 }
+            } else if (!LN) {
+                // GEGLU: value and gate bias of the warp's first 16-column group (nb4[0..1], nv4[0..1]); every group below
+                // requests the next group's before it starts, so that no group waits for a global load
+                nb4[0] = load_vec(bias_p, half * 32);
+                nb4[1] = load_vec(bias_p, half * 32 + 8);
+                nv4[0] = load_vec(aux_p, half * 32);
+                nv4[1] = load_vec(aux_p, half * 32 + 8);
             }
             ok = mbar_wait(tfull0 + 8 * buf, (t >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-collective: decide as a warp
@@ -522,8 +542,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                         uint32_t v16[16], g16[16];
                         tmem_ld_32x16(tacc + col, v16);
                         tmem_ld_32x16(tacc + BN / 2 + col, g16);
-                        const uint4 bA = load_vec(bias_p, col), bB = load_vec(bias_p, col + 8);
-                        const uint4 gA = load_vec(aux_p, col), gB = load_vec(aux_p, col + 8);
+                        const uint4 bA = nb4[0], bB = nb4[1], gA = nv4[0], gB = nv4[1];
+                        if constexpr (!LN) {
+                            // the next group of this warp: the other half of this chunk, else the first half of its next chunk
+                            const int ncol = k2 == 0 ? col + 16 : (c + EPI_PER_Q) * 32;
+                            if (ncol < BN_OUT) {
+                                nb4[0] = load_vec(bias_p, ncol);
+                                nb4[1] = load_vec(bias_p, ncol + 8);
+                                nv4[0] = load_vec(aux_p, ncol);
+                                nv4[1] = load_vec(aux_p, ncol + 8);
+                            }
+                        }
                         const uint32_t bw[8] = {bA.x, bA.y, bA.z, bA.w, bB.x, bB.y, bB.z, bB.w};
                         const uint32_t gw[8] = {gA.x, gA.y, gA.z, gA.w, gB.x, gB.y, gB.z, gB.w};
                         tmem_ld_wait();
@@ -752,14 +781,17 @@ static int* status_ptr() {
 int* tc05_status_device_ptr() { return status_ptr(); }
 
 // Tile width by wave efficiency: tiles of width bn cost ~bn per wave; pick the width with the least total cost.
-static int pick_bn(int m_tiles, int n_out, bool geglu) {
+static int pick_bn(int m_tiles, int n_out, bool geglu, bool pair) {
     const int sms = sm_count();
-    const int cand[4] = {256, 160, 128, 96};     // 96: small M (batch 1, row shards), where wider tiles leave SMs idle
+    // 96: small M (batch 1, row shards), where wider tiles leave SMs idle. 192: GEGLU on CTA pairs only, for the shapes
+    // whose 256-wide tiles end a little over a whole number of waves (2048 x 10240: 4.3 waves of 256, 5.8 of 192)
+    const int cand[5] = {256, 192, 160, 128, 96};
     int best = 128;
     double best_cost = 1e30;
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 5; ++i) {
         const int bn = cand[i];
         if (geglu && (bn == 160 || bn == 96)) continue;      // half of it is not a whole number of 32-column boxes
+        if (bn == 192 && !(geglu && pair)) continue;
         const int out_w = geglu ? bn / 2 : bn;
         const long long tiles = (long long)m_tiles * ceil_div(n_out, out_w);
         const long long waves = (tiles + sms - 1) / sms;
@@ -798,6 +830,9 @@ static int dispatch(const CUtensorMap& a, const CUtensorMap& b, Tc05Params& p, i
     if (pair) {
         // stage counts: what fits beside the epilogue boxes (8 KB to 64 KB) in 227 KB
         if (bn == 256) return launch_tc05<256, GEGLU ? 5 : 4, GEGLU, true, LN>(a, b, c, r, p, st);
+        if constexpr (GEGLU) {
+            if (bn == 192) return launch_tc05<192, 7, true, true, LN>(a, b, c, r, p, st);
+        }
         if constexpr (!GEGLU) {
             if (bn == 160) return launch_tc05<160, 6, false, true, LN>(a, b, c, r, p, st);
             if (bn == 96) return launch_tc05<96, 8, false, true, LN>(a, b, c, r, p, st);
@@ -895,11 +930,11 @@ static int linear_common(const void* A, int lda, const void* W, void* C, int ldc
     p.rows_img = M;
     KATZ_CHECK_ARG((long long)p.m_tiles * ceil_div(N_out, 64) < (1ll << 30), KATZ_ESIZE);
     const bool geglu = geglu_F > 0;
-    const int bn = pick_bn(p.m_tiles, N_out, geglu);
+    const bool pair = use_pairs(p, geglu);
+    const int bn = pick_bn(p.m_tiles, N_out, geglu, pair);
     const int out_w = geglu ? bn / 2 : bn;
     p.n_tiles = ceil_div(N_out, out_w);
     const uint64_t w_rows = geglu ? 2ull * geglu_F : (uint64_t)N_out;
-    const bool pair = use_pairs(p, geglu);
     rc = encode_2d(&tb, W, K, w_rows, (uint64_t)K * 2, TBK, (geglu || pair) ? bn / 2 : bn);      // box rows: what one load brings
     if (rc) return rc;
     bool ln = false;
@@ -982,9 +1017,9 @@ extern "C" int katz_conv3x3_nhwc_f16(const void* X, const void* W, void* Y, int 
     p.cin_chunks = Cin / TBK; p.ksize = 3; p.pad_h = pad_h; p.pad_w = 1; p.stride = stride;
     p.m_tiles = B * p.tiles_w * p.tiles_h;
     p.rows_img = H * Wd;
-    const int bn = pick_bn(p.m_tiles, Cout, false);
-    p.n_tiles = ceil_div(Cout, bn);
     const bool pair = use_pairs(p, false);
+    const int bn = pick_bn(p.m_tiles, Cout, false, pair);
+    p.n_tiles = ceil_div(Cout, bn);
     rc = encode_2d(&tb, W, (uint64_t)9 * Cin, Cout, (uint64_t)9 * Cin * 2, TBK, pair ? bn / 2 : bn);
     if (rc) return rc;
     return dispatch<false>(ta, tb, p, bn, pair, H * Wd, B, (cudaStream_t)stream);
