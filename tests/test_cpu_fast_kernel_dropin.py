@@ -1,6 +1,6 @@
 """CPU: the drop-in `fast_kernel` package registers the two operators with the schemas torch infers from the reference's
 C++ signatures (fast_kernel/csrc/group_norm.cuh:7-15, gelu.cuh:44, registered in bind.cu:13-14), and — where a checkout
-of the reference is present (REFERENCE_ROOT, default /root/reference) — the reference fork's own
+of the reference is present (the REFERENCE_ROOT variable, or the default location below) — the reference fork's own
 diffusers/models/normalization.py and activations.py import against THIS package and reach its operators
 (normalization.py:23,91; activations.py:21,145). Nothing is computed: there is no GPU here, and the operators refuse CPU
 tensors instead of falling back."""
