@@ -232,6 +232,20 @@ int katz_attention_f16(const void* Q, const void* K, const void* V, void* O, int
                        int ldq, int ldk, int ldv, int ldo, long long bsq, long long bsk, long long bsv, long long bso,
                        float scale, int kv_chunk_rows, long long kv_chunk_stride, void* stream);
 
+/* The same kernel with the wave tail cut (same reference call, attention_processor.py:1276): an SM holds two CTAs of
+ * this kernel, and the query tiles beyond a whole number of rounds of 2 x SMs CTAs make a last round that costs as
+ * much as a full one. With scratch memory, query tiles of 16 or more key tiles (2048 keys) that fall into that last
+ * round are cut along the key axis into short CTAs that are dispatched first; each leaves its unnormalised result in
+ * `scratch` and the last one of a tile to finish adds the parts in index order (bit-reproducible). Shorter tiles are
+ * launched exactly as katz_attention_f16 launches them. `scratch` (16-byte aligned;
+ * katz_attention_split_scratch_bytes() bytes are always enough) must be zero when first used; every launch leaves its
+ * first 4096 bytes (the tickets) zero again. Launches that share a scratch buffer must be ordered on one stream. */
+long long katz_attention_split_scratch_bytes(void);
+int katz_attention_split_f16(const void* Q, const void* K, const void* V, void* O, int B, int H, int Sq, int Sk,
+                             int head_dim, int ldq, int ldk, int ldv, int ldo, long long bsq, long long bsk, long long bsv,
+                             long long bso, float scale, int kv_chunk_rows, long long kv_chunk_stride, void* scratch,
+                             long long scratch_bytes, void* stream);
+
 /* dst = src + half(sum_i scales[i] * residuals[i]) — ControlNet residual intake (unet_2d_condition.py:1281-1292; the
  * sum / mean over nets of :1418-1439). `h_residuals` and `h_scales` are HOST arrays of n_res entries (device pointers
  * inside). */

@@ -17,6 +17,12 @@
 //     P = exp2(S*scale - m) as fp16 into swizzled shared memory for the second MMA, and at the end normalises O.
 // S[j+1] = Q K[j+1]^T is issued before the softmax of tile j has finished, so the two MMAs and the softmax overlap.
 // Every mbarrier wait is bounded; a time-out records a status word (shared with the GEMM kernels) and the CTA unwinds.
+//
+// Wave tail (katz_attention_split_f16): an SM holds two CTAs, so a launch fills 2 x SMs slots at a time and the query
+// tiles beyond a whole number of rounds (640 tiles on 296 slots: 48) run as a last round that costs as much as a full
+// one. With scratch memory, long tiles (16 key tiles or more) are cut along the KEY axis into `parts` short CTAs, dispatched first;
+// each writes its unnormalised O (fp32), its reference maximum and its row sum to scratch, and the last part of a tile
+// to arrive (a ticket, no waiting) adds the parts in index order, so the result does not depend on which one that was.
 #include "tc05.cuh"
 #include "katz_b200.h"
 
@@ -51,6 +57,13 @@ struct FaParams {
     float scale_log2e;
     int kv_chunk_rows;
     int* status;
+    // work decoding: blockIdx.x -> (query tile, key-tile range). Query tiles are numbered x fastest, then head, then batch.
+    int tiles_x, H;
+    int n_full;                 // query tiles [0, n_full) are whole CTAs
+    int n_small, parts;         // query tiles [n_full, n_full + n_small / parts) are cut into `parts` CTAs each
+    int* counters;              // one ticket per cut query tile, zero between launches
+    float2* part_ml;            // [cut tile][part][row]: (reference maximum in log2 units, row sum)
+    float4* part_o;             // [cut tile][part][16 column quads][128 rows]: unnormalised O
 };
 
 __device__ __forceinline__ void tma_load_4d_fa(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
@@ -96,10 +109,24 @@ __global__ void __launch_bounds__(FA_THREADS, FA_CTAS_PER_SM) attention_tc05_ker
                    v_empty = v_full + 8 * FA_ST, s_full = v_empty + 8 * FA_ST, s_free = s_full + 8, p_full = s_free + 8,
                    p_free = p_full + 8;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1 + 4 * FA_ST + 4);
+    volatile int* ticket_slot = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int q0 = blockIdx.x * FA_BM, h = blockIdx.y, b = blockIdx.z;
-    const int NT = (p.Sk + FA_BN - 1) / FA_BN;
+    const int NT_ALL = (p.Sk + FA_BN - 1) / FA_BN;
+    // the short CTAs come first in the grid: they are dispatched first and the whole-tile CTAs fill in behind them
+    int qt, j0 = 0, j1 = NT_ALL, part = 0, cut = -1;
+    if ((int)blockIdx.x < p.n_small) {
+        cut = (int)blockIdx.x / p.parts;
+        part = (int)blockIdx.x - cut * p.parts;
+        qt = p.n_full + cut;
+        j0 = (int)((long long)part * NT_ALL / p.parts);
+        j1 = (int)((long long)(part + 1) * NT_ALL / p.parts);
+    } else {
+        qt = (int)blockIdx.x - p.n_small;
+    }
+    const int qx = qt % p.tiles_x, hb = qt / p.tiles_x;
+    const int q0 = qx * FA_BM, h = hb % p.H, b = hb / p.H;
+    const int NT = j1 - j0;      // key tiles of this CTA: j0 .. j1-1
 
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmQ);
@@ -141,7 +168,7 @@ __global__ void __launch_bounds__(FA_THREADS, FA_CTAS_PER_SM) attention_tc05_ker
             for (int j = 0; j < NT && ok; ++j) {
                 const int s = j % FA_ST;
                 const uint32_t ph = (j / FA_ST) & 1;
-                const int key0 = j * FA_BN;
+                const int key0 = (j0 + j) * FA_BN;
                 const int chunk = key0 / p.kv_chunk_rows, row = key0 - chunk * p.kv_chunk_rows;
                 if (!mbar_wait(k_empty + 8 * s, ph ^ 1)) { ok = false; break; }
                 mbar_expect_tx(k_full + 8 * s, FA_KV_TILE);
@@ -209,7 +236,7 @@ __global__ void __launch_bounds__(FA_THREADS, FA_CTAS_PER_SM) attention_tc05_ker
             if (!ok) break;
             fence_after_sync();
             const uint32_t tS = tS0 + lane_base;
-            const int kbase = j * FA_BN;
+            const int kbase = (j0 + j) * FA_BN;
             const bool tail = kbase + FA_BN > p.Sk;
             // the whole S row (128 fp32) comes into registers with ONE wait: four TMEM loads in flight together
             uint32_t r[FA_BN];
@@ -294,27 +321,93 @@ __global__ void __launch_bounds__(FA_THREADS, FA_CTAS_PER_SM) attention_tc05_ker
             ok = mbar_wait(p_free, (NT - 1) & 1);     // the last O += P V has landed
             ok = __all_sync(0xffffffffu, ok);
         }
-        if (!ok) {
-            if (lane == 0) atomicExch(p.status, 13);
-        } else {
-            fence_after_sync();
-            const float inv = 1.0f / l_sum;
-            const int qrow = q0 + row;
-            __half* op = p.O + (size_t)b * p.bso + (size_t)qrow * p.ldo + h * FA_D;
+        if (!ok && lane == 0) atomicExch(p.status, 13);
+        const int qrow = q0 + row;
+        __half* op = p.O + (size_t)b * p.bso + (size_t)qrow * p.ldo + h * FA_D;
+        if (cut < 0) {
+            if (ok) {
+                fence_after_sync();
+                const float inv = 1.0f / l_sum;
 #pragma unroll 1
-            for (int c = 0; c < FA_D; c += 32) {
-                uint32_t r[32];
-                tmem_ld_32x32(tO + lane_base + c, r);
-                tmem_ld_wait();
-                if (qrow < p.Sq) {
+                for (int c = 0; c < FA_D; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tO + lane_base + c, r);
+                    tmem_ld_wait();
+                    if (qrow < p.Sq) {
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; ++k4) {
-                        uint4 o;
-                        o.x = pack_half2(__uint_as_float(r[8 * k4]) * inv, __uint_as_float(r[8 * k4 + 1]) * inv);
-                        o.y = pack_half2(__uint_as_float(r[8 * k4 + 2]) * inv, __uint_as_float(r[8 * k4 + 3]) * inv);
-                        o.z = pack_half2(__uint_as_float(r[8 * k4 + 4]) * inv, __uint_as_float(r[8 * k4 + 5]) * inv);
-                        o.w = pack_half2(__uint_as_float(r[8 * k4 + 6]) * inv, __uint_as_float(r[8 * k4 + 7]) * inv);
-                        *reinterpret_cast<uint4*>(op + c + 8 * k4) = o;
+                        for (int k4 = 0; k4 < 4; ++k4) {
+                            uint4 o;
+                            o.x = pack_half2(__uint_as_float(r[8 * k4]) * inv, __uint_as_float(r[8 * k4 + 1]) * inv);
+                            o.y = pack_half2(__uint_as_float(r[8 * k4 + 2]) * inv, __uint_as_float(r[8 * k4 + 3]) * inv);
+                            o.z = pack_half2(__uint_as_float(r[8 * k4 + 4]) * inv, __uint_as_float(r[8 * k4 + 5]) * inv);
+                            o.w = pack_half2(__uint_as_float(r[8 * k4 + 6]) * inv, __uint_as_float(r[8 * k4 + 7]) * inv);
+                            *reinterpret_cast<uint4*>(op + c + 8 * k4) = o;
+                        }
+                    }
+                }
+            }
+        } else {
+            // One part of a cut query tile: leave (m, l, unnormalised O) in scratch, take a ticket, and if every other part
+            // has arrived, add them up in index order. A part that timed out still takes its ticket (the status word
+            // already says the result is void), so the counter returns to zero whatever happened.
+            const size_t slot = (size_t)cut * p.parts;
+            if (ok) {
+                fence_after_sync();
+                float4* so = p.part_o + (slot + part) * (16 * FA_BM);
+#pragma unroll 1
+                for (int c = 0; c < FA_D; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tO + lane_base + c, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int k4 = 0; k4 < 8; ++k4)      // quad-major: the 32 rows of a warp write 512 contiguous bytes
+                        so[(c / 4 + k4) * FA_BM + row] = make_float4(__uint_as_float(r[4 * k4]), __uint_as_float(r[4 * k4 + 1]),
+                                                                    __uint_as_float(r[4 * k4 + 2]), __uint_as_float(r[4 * k4 + 3]));
+                }
+                p.part_ml[(slot + part) * FA_BM + row] = make_float2(m_used, l_sum);
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");      // the four softmax warps
+            if (threadIdx.x == 64) *ticket_slot = atomicAdd(p.counters + cut, 1);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (*ticket_slot == p.parts - 1) {
+                __threadfence();
+                if (threadIdx.x == 64) p.counters[cut] = 0;      // every part has its ticket: ready for the next launch
+                float M = -INFINITY;
+                for (int pp = 0; pp < p.parts; ++pp) M = fmaxf(M, __ldcg(p.part_ml + (slot + pp) * FA_BM + row).x);
+                float L = 0.f;
+                for (int pp = 0; pp < p.parts; ++pp) {
+                    const float2 ml = __ldcg(p.part_ml + (slot + pp) * FA_BM + row);
+                    L = fmaf(exp2f(ml.x - M), ml.y, L);
+                }
+                const float inv = 1.0f / L;
+#pragma unroll 1
+                for (int c4 = 0; c4 < 16; c4 += 4) {
+                    float4 acc[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int pp = 0; pp < p.parts; ++pp) {
+                        const float w = exp2f(__ldcg(p.part_ml + (slot + pp) * FA_BM + row).x - M);
+                        const float4* so = p.part_o + (slot + pp) * (16 * FA_BM);
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const float4 v = __ldcg(so + (c4 + u) * FA_BM + row);
+                            acc[u].x = fmaf(w, v.x, acc[u].x);
+                            acc[u].y = fmaf(w, v.y, acc[u].y);
+                            acc[u].z = fmaf(w, v.z, acc[u].z);
+                            acc[u].w = fmaf(w, v.w, acc[u].w);
+                        }
+                    }
+                    if (qrow < p.Sq) {
+#pragma unroll
+                        for (int u = 0; u < 4; u += 2) {
+                            uint4 o;
+                            o.x = pack_half2(acc[u].x * inv, acc[u].y * inv);
+                            o.y = pack_half2(acc[u].z * inv, acc[u].w * inv);
+                            o.z = pack_half2(acc[u + 1].x * inv, acc[u + 1].y * inv);
+                            o.w = pack_half2(acc[u + 1].z * inv, acc[u + 1].w * inv);
+                            *reinterpret_cast<uint4*>(op + 4 * (c4 + u)) = o;
+                        }
                     }
                 }
             }
@@ -366,10 +459,47 @@ static int fa_encode(CUtensorMap* map, const void* base, int cols, long long row
 
 using namespace katz;
 
-extern "C" int katz_attention_f16(const void* Q, const void* K, const void* V, void* O, int B, int H, int Sq, int Sk,
-                                  int head_dim, int ldq, int ldk, int ldv, int ldo, long long bsq, long long bsk,
-                                  long long bsv, long long bso, float scale, int kv_chunk_rows, long long kv_chunk_stride,
-                                  void* stream) {
+// Slots of one dispatch round: two CTAs per SM.
+static int fa_slots() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+        n = FA_CTAS_PER_SM * sms;
+    }
+    return n;
+}
+constexpr long long FA_COUNTER_BYTES = 4096;                                   // tickets of up to 1024 cut query tiles
+constexpr long long FA_PART_BYTES = FA_BM * FA_D * 4 + FA_BM * 8;              // one part: O (fp32) + (m, l) per row
+
+// Which query tiles are cut and into how many parts. Only the tiles beyond a whole number of dispatch rounds are cut
+// (all of them when there is less than one round), into as many parts as fit the slots of one round. A part costs
+// about as much as two or three key tiles beyond its own (its set-up, its partial result, its share of the final sum),
+// so it must be at least four key tiles long, and query tiles of fewer than sixteen key tiles are never cut: measured at 8
+// key tiles (2 x 20 heads x 1024 tokens), every cut was slower than the second round it replaced.
+static void fa_plan(int n_q, int key_tiles, long long scratch_bytes, int* n_full, int* cut_tiles, int* parts) {
+    *n_full = n_q;
+    *cut_tiles = 0;
+    *parts = 1;
+    const int slots = fa_slots();
+    const int rest = n_q % slots;
+    if (rest == 0 || key_tiles < 16 || rest > 1024) return;
+    int pt = slots / rest;
+    if (pt > key_tiles / 4) pt = key_tiles / 4;
+    if (pt > 16) pt = 16;
+    if (pt < 2) return;
+    if (FA_COUNTER_BYTES + (long long)rest * pt * FA_PART_BYTES > scratch_bytes) return;
+    *n_full = n_q - rest;
+    *cut_tiles = rest;
+    *parts = pt;
+}
+
+static int attention_launch(const void* Q, const void* K, const void* V, void* O, int B, int H, int Sq, int Sk, int head_dim,
+                            int ldq, int ldk, int ldv, int ldo, long long bsq, long long bsk, long long bsv, long long bso,
+                            float scale, int kv_chunk_rows, long long kv_chunk_stride, void* scratch, long long scratch_bytes,
+                            void* stream) {
+
     KATZ_CHECK_ARG(Q && K && V && O, KATZ_EINVAL);
     KATZ_CHECK_ARG(head_dim == 64, KATZ_ESIZE);
     KATZ_CHECK_ARG(B > 0 && H > 0 && Sq > 0 && Sk > 0 && B <= 65535 && H <= 65535, KATZ_ESIZE);
@@ -414,7 +544,42 @@ extern "C" int katz_attention_f16(const void* Q, const void* K, const void* V, v
         if (e != cudaSuccess) return (int)e;
         attr = true;
     }
-    dim3 grid((Sq + FA_BM - 1) / FA_BM, H, B);
+    p.tiles_x = (Sq + FA_BM - 1) / FA_BM;
+    p.H = H;
+    const long long n_q = (long long)p.tiles_x * H * B;
+    KATZ_CHECK_ARG(n_q < (1ll << 30), KATZ_ESIZE);
+    int cut_tiles = 0;
+    fa_plan((int)n_q, (Sk + FA_BN - 1) / FA_BN, scratch ? scratch_bytes : 0, &p.n_full, &cut_tiles, &p.parts);
+    p.n_small = cut_tiles * p.parts;
+    if (cut_tiles) {
+        unsigned char* sc = (unsigned char*)scratch;
+        p.counters = (int*)sc;
+        p.part_ml = (float2*)(sc + FA_COUNTER_BYTES);
+        p.part_o = (float4*)(sc + FA_COUNTER_BYTES + (long long)cut_tiles * p.parts * FA_BM * 8);
+    }
+    dim3 grid((unsigned)(p.n_small + p.n_full));
     launch_k(attention_tc05_kernel, grid, FA_THREADS, FA_SMEM, (cudaStream_t)stream, tq, tk, tv, p);
     KATZ_LAUNCH_RET();
+}
+
+extern "C" long long katz_attention_split_scratch_bytes(void) {
+    // parts x cut tiles never exceeds one dispatch round
+    return FA_COUNTER_BYTES + (long long)fa_slots() * FA_PART_BYTES;
+}
+
+extern "C" int katz_attention_split_f16(const void* Q, const void* K, const void* V, void* O, int B, int H, int Sq, int Sk,
+                                        int head_dim, int ldq, int ldk, int ldv, int ldo, long long bsq, long long bsk,
+                                        long long bsv, long long bso, float scale, int kv_chunk_rows,
+                                        long long kv_chunk_stride, void* scratch, long long scratch_bytes, void* stream) {
+    KATZ_CHECK_ARG(scratch && aligned16(scratch) && scratch_bytes >= FA_COUNTER_BYTES, KATZ_EINVAL);
+    return attention_launch(Q, K, V, O, B, H, Sq, Sk, head_dim, ldq, ldk, ldv, ldo, bsq, bsk, bsv, bso, scale, kv_chunk_rows,
+                            kv_chunk_stride, scratch, scratch_bytes, stream);
+}
+
+extern "C" int katz_attention_f16(const void* Q, const void* K, const void* V, void* O, int B, int H, int Sq, int Sk,
+                                  int head_dim, int ldq, int ldk, int ldv, int ldo, long long bsq, long long bsk,
+                                  long long bsv, long long bso, float scale, int kv_chunk_rows, long long kv_chunk_stride,
+                                  void* stream) {
+    return attention_launch(Q, K, V, O, B, H, Sq, Sk, head_dim, ldq, ldk, ldv, ldo, bsq, bsk, bsv, bso, scale, kv_chunk_rows,
+                            kv_chunk_stride, nullptr, 0, stream);
 }

@@ -350,6 +350,19 @@ def softmax_rows(x, out=None):
     return out
 
 
+_attn_scratch = {}
+
+
+def _attention_scratch(device):
+    """Scratch of the attention kernel's cut query tiles: one zero-filled buffer per device, of the size that is enough
+    for every shape, allocated once (a captured graph keeps pointing at it)."""
+    buf = _attn_scratch.get(device)
+    if buf is None:
+        buf = torch.zeros(int(_lib.load().katz_attention_split_scratch_bytes()), dtype=torch.uint8, device=device)
+        _attn_scratch[device] = buf
+    return buf
+
+
 def attention(q, k, v, heads, out=None, scale=None, kv_chunks=None):
     """q: [B,Sq,>=H*64] view, k/v: [B,Sk,...] views (unit last stride, any row/batch stride); returns [B,Sq,H*64].
     kv_chunks=(n_chunks, chunk_rows, chunk_stride): k/v describe the FIRST chunk ([B, chunk_rows, ...]); chunk c of the
@@ -377,7 +390,11 @@ def attention(q, k, v, heads, out=None, scale=None, kv_chunks=None):
     mode = os.environ.get("KATZ_ATTN", "auto")
     if (_use_tc05() and (mode == "tc05" or (mode == "auto" and Sk > 128)) and strides_ok
             and (chunk_rows == 0 or (chunk_rows % 128 == 0 and chunk_stride % 8 == 0))):
-        call("katz_attention_f16", *args)
+        if os.environ.get("KATZ_ATTN_SPLIT", "1") != "0":
+            scratch = _attention_scratch(q.device)
+            call("katz_attention_split_f16", *args[:-1], _p(scratch), scratch.numel(), args[-1])
+        else:
+            call("katz_attention_f16", *args)
     else:
         call("katz_attention_f16_mma", *args)
     return out

@@ -7,6 +7,9 @@
     python -m katz_b200.profiling step [--batch B] [--latent HW]   # ONE eager UNet step
     python -m katz_b200.profiling norms          # LayerNorm / GroupNorm launches of the step's shapes
     python -m katz_b200.profiling compare-cublas # katz_linear_f16 against torch.addmm on the step's shapes (no profiler)
+    python -m katz_b200.profiling compare-cudnn  # katz_conv3x3_nhwc_f16 against F.conv2d (channels-last) on the step's shapes
+    python -m katz_b200.profiling ablate [--batch B] [--latent HW]     # CUDA-graph replay of the step with one entry point's
+                                                 # launches left out at a time: what each family costs INSIDE the graph
     python -m katz_b200.profiling families [--batch B] [--latent HW]   # time share per kernel family of one eager step, CUDA
                                                  # events around every op (also under torchrun: the row-split step, rank 0 reports)
 
@@ -64,7 +67,7 @@ def gemm(dev, args):
 
 def attention(dev, args):
     from . import ops
-    shapes = [(2, 20, 1024), (2, 10, 4096)]
+    shapes = [(2, 20, 1024), (2, 10, 4096), (1, 20, 1024), (1, 10, 4096)]
     bufs = []
     for (B, H, S) in shapes:
         bufs.append((torch.randn(B, S, 3 * H * 64, device=dev).half(), H, torch.empty(B, S, H * 64, dtype=torch.float16, device=dev)))
@@ -76,7 +79,11 @@ def attention(dev, args):
                 ops.attention(qkv[:, :, :C], qkv[:, :, C:2 * C], qkv[:, :, 2 * C:], H, out=o)
     run(1)
     _bracket(lambda: run(2))
-    return {"profiled": "self-attention, 2 launches each", "shapes": shapes, "tc05_status": ops.tc05_status()}
+    times = []
+    for qkv, H, o in bufs:        # CUDA-graph time of 10 launches per shape (no profiler)
+        C = H * 64
+        times.append(round(_graph_time(lambda i: ops.attention(qkv[:, :, :C], qkv[:, :, C:2 * C], qkv[:, :, 2 * C:], H, out=o), n=10), 2))
+    return {"profiled": "self-attention, 2 launches each", "shapes": shapes, "graph_us_per_launch": times, "tc05_status": ops.tc05_status()}
 
 
 def _subset_merger(dev, dtype):
@@ -164,16 +171,130 @@ def compare_cublas(dev, args):
     rows = []
     for (M, N, K) in STEP_LINEAR_SHAPES:
         nw = 6 if N * K < 3e7 else 2
+        if args.cold:      # as in the step: more distinct weights than the 126 MB L2 holds, every launch reads its weights from HBM
+            nw = min(96, max(2, int(3e8 // (N * K * 2)) + 1))
         x = torch.randn(M, K, device=dev).half()
         ws = [(torch.randn(N, K, device=dev) * 0.03).half() for _ in range(nw)]
         b = torch.randn(N, device=dev).half()
         o = torch.empty(M, N, dtype=torch.float16, device=dev)
-        tk = graph_time(lambda i: ops.linear(x, ws[i % nw], b, out=o))
-        tc = graph_time(lambda i: torch.addmm(b, x, ws[i % nw].t(), out=o))
+        n = max(20, nw) if args.cold else 20
+        tk = graph_time(lambda i: ops.linear(x, ws[i % nw], b, out=o), n)
+        tc = graph_time(lambda i: torch.addmm(b, x, ws[i % nw].t(), out=o), n)
         fl = 2.0 * M * N * K
         rows.append({"shape": [M, N, K], "katz_us": round(tk, 1), "katz_tflops": round(fl / tk / 1e6),
                      "cublas_us": round(tc, 1), "cublas_tflops": round(fl / tc / 1e6), "cublas_over_katz": round(tc / tk, 2)})
-    return {"compared": "linear + bias, fp16, CUDA graph of 20 launches", "rows": rows, "tc05_status": ops.tc05_status()}
+    return {"compared": "linear + bias, fp16, CUDA graph of 20 launches", "cold_weights": bool(args.cold), "rows": rows, "tc05_status": ops.tc05_status()}
+
+
+# (H = W of the input, Cin, Cout, stride, launches per step) of the SDXL UNet's 3x3 convolutions at batch 2, latent 128 x 128
+STEP_CONV_SHAPES = [(128, 320, 320, 1, 7), (128, 960, 320, 1, 1), (128, 640, 320, 1, 2), (128, 320, 320, 2, 1),
+                    (64, 320, 640, 1, 1), (64, 640, 640, 1, 6), (64, 1920, 640, 1, 1), (64, 1280, 640, 1, 1), (64, 960, 640, 1, 1),
+                    (64, 640, 640, 2, 1), (128, 640, 640, 1, 1),
+                    (32, 640, 1280, 1, 1), (32, 1280, 1280, 1, 10), (32, 2560, 1280, 1, 2), (32, 1920, 1280, 1, 1), (64, 1280, 1280, 1, 1)]
+
+
+def _graph_time(fn, n=20, reps=5):
+    for _ in range(3):
+        fn(0)
+    torch.cuda.synchronize()
+    gr, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        fn(0)
+        with torch.cuda.graph(gr, stream=st):
+            for i in range(n):
+                fn(i)
+    torch.cuda.synchronize()
+    gr.replay()
+    return _time_events(gr.replay, reps) * 1e3 / n
+
+
+def compare_cudnn(dev, args):
+    """The step's 3x3 convolutions (bias in the epilogue), CUDA graphs of 10 launches cycling through distinct weights."""
+    import torch.nn.functional as F
+    from . import ops
+    rows, tot_k, tot_c = [], 0.0, 0.0
+    B = args.batch
+    for (H, Cin, Cout, stride, count) in STEP_CONV_SHAPES:
+        nw = 4
+        x = torch.randn(B, H, H, Cin, device=dev).half()
+        ws = [(torch.randn(Cout, 3, 3, Cin, device=dev) * 0.02).half() for _ in range(nw)]
+        b = torch.randn(Cout, device=dev).half()
+        Ho = H // stride
+        o = torch.empty(B, Ho, Ho, Cout, dtype=torch.float16, device=dev)
+        tk = _graph_time(lambda i: ops.conv2d(x, ws[i % nw], b, stride=stride, out=o), n=10)
+        xc = x.permute(0, 3, 1, 2)                      # NCHW view of channels-last memory
+        wc = [w.permute(0, 3, 1, 2) for w in ws]
+        tc = _graph_time(lambda i: F.conv2d(xc, wc[i % nw], b, stride=stride, padding=1), n=10)
+        fl = 2.0 * B * Ho * Ho * Cout * 9 * Cin
+        tot_k += tk * count
+        tot_c += tc * count
+        rows.append({"shape": [H, Cin, Cout, stride], "per_step": count, "katz_us": round(tk, 1), "katz_tflops": round(fl / tk / 1e6),
+                     "cudnn_us": round(tc, 1), "cudnn_tflops": round(fl / tc / 1e6), "cudnn_over_katz": round(tc / tk, 2)})
+    return {"compared": "3x3 conv + bias, fp16 NHWC, CUDA graph of 10 launches", "rows": rows, "katz_step_total_us": round(tot_k, 1),
+            "cudnn_step_total_us": round(tot_c, 1), "tc05_status": ops.tc05_status()}
+
+
+def ablate(dev, args):
+    """What each kernel family costs inside the CUDA-graph replay of the step: the step is captured once whole and once per
+    family with that family's entry points skipped (their outputs keep whatever the buffers held, so the results are
+    meaningless; only the replay time is read). The difference includes the launch boundaries the family adds, which a list
+    of isolated kernel times does not show."""
+    from . import _lib, ops
+    from .params import SDXL_UNET_CONFIG, init_state_dict, unet_param_shapes
+    from .unet import KatzUNet
+    cfg = SDXL_UNET_CONFIG
+    unet = KatzUNet(cfg, dev, init_state_dict(unet_param_shapes(cfg), seed=0, dtype=torch.float16, device=dev, generator_device=dev))
+    B, HW = args.batch, args.latent
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(B, 4, HW, HW, generator=g).half().to(dev)
+    ctx = torch.randn(B, 77, 2048, generator=g).half().to(dev)
+    added = {"text_embeds": torch.randn(B, 1280, generator=g).half().to(dev),
+             "time_ids": torch.tensor([[1024., 1024., 0., 0., 1024., 1024.]] * B).half().to(dev)}
+    t = torch.tensor([500.0], device=dev)
+    real_call = ops.call
+    skipped = set()
+    counts = {}
+
+    def call(name, *a):
+        if name in skipped:
+            counts[name] = counts.get(name, 0) + 1
+            return
+        real_call(name, *a)
+    ops.call = call
+
+    def replay_ms():
+        for _ in range(2):
+            unet(x, t, encoder_hidden_states=ctx, added_cond_kwargs=added)
+        torch.cuda.synchronize()
+        gr, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            with torch.cuda.graph(gr, stream=st):
+                unet(x, t, encoder_hidden_states=ctx, added_cond_kwargs=added)
+        torch.cuda.synchronize()
+        for _ in range(3):
+            gr.replay()
+        return _time_events(gr.replay, 10)
+    families_ = [("nothing", ()), ("LayerNorm", ("katz_layer_norm_f16",)),
+                 ("GroupNorm", ("katz_group_norm_nhwc_f16",)),
+                 ("self- and cross-attention", ("katz_attention_f16", "katz_attention_f16_mma")),
+                 ("self-attention (tcgen05)", ("katz_attention_f16",)),
+                 ("cross-attention (mma.sync)", ("katz_attention_f16_mma",)),
+                 ("GEGLU GEMM", ("katz_linear_geglu_f16", "katz_linear_geglu_ex_f16")),
+                 ("3x3 convolution (tcgen05)", ("katz_conv3x3_nhwc_f16",)),
+                 ("linear GEMM", ("katz_linear_f16", "katz_linear_ex_f16")),
+                 ("concat / upsample / layout", ("katz_concat_channels_f16", "katz_upsample_nearest2x_nhwc_f16"))]
+    rows, base = [], None
+    for name, eps in families_:
+        skipped.clear()
+        skipped.update(eps)
+        counts.clear()
+        ms = replay_ms()
+        if base is None:
+            base = ms
+        rows.append({"skipped": name, "replay_ms": round(ms, 3), "family_ms": round(base - ms, 3),
+                     "calls_skipped_per_step": sum(counts.values()) // 3 if counts else 0})
+    ops.call = real_call
+    return {"profiled": "CUDA-graph replay with one family skipped at a time", "batch": B, "latent": HW, "rows": rows}
 
 
 def families(dev, args):
@@ -257,7 +378,7 @@ def families(dev, args):
 
 
 MODES = {"families": families, "gemm": gemm, "attention": attention, "merge": merge, "merge-fp32": merge_fp32, "step": step, "norms": norms,
-         "compare-cublas": compare_cublas}
+         "compare-cublas": compare_cublas, "compare-cudnn": compare_cudnn, "ablate": ablate}
 
 
 def main(argv=None):
@@ -265,6 +386,7 @@ def main(argv=None):
     ap.add_argument("mode", choices=sorted(MODES))
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--latent", type=int, default=128)
+    ap.add_argument("--cold", action="store_true", help="compare-cublas: weights cycle through more memory than L2 holds")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("katz_b200.profiling needs a CUDA device")

@@ -322,6 +322,38 @@ def test_attention_tcgen05(cuda_device, B, H, Sq, Sk, monkeypatch):
     assert float((out.float() - out2.float()).abs().max()) < 4e-3
 
 
+@pytest.mark.parametrize("B,H,Sq,Sk", [(2, 20, 1024, 1024),      # 8 key tiles per query tile: too short to cut (same launch)
+                                       (1, 2, 1024, 2048),       # 16 query tiles, less than one round: every tile cut into 4
+                                       (1, 5, 1000, 2500),       # ragged query and key counts, every tile cut into 5
+                                       (1, 37, 1024, 2048),      # exactly one round of 296 tiles: nothing is cut
+                                       (2, 10, 4096, 4096),      # 640 tiles: 48 cut into 6 parts of 5 or 6 key tiles
+                                       (1, 10, 4096, 4096)])     # 320 tiles: 24 cut into 8 parts of 4 key tiles
+def test_attention_tcgen05_cut_wave_tail(cuda_device, B, H, Sq, Sk, monkeypatch):
+    """The launch that cuts the query tiles of the last, partly filled dispatch round along the key axis against the launch
+    that does not, and against fp32 SDPA; twice in a row, since the tickets in the scratch buffer must return to zero."""
+    from katz_b200 import ops
+    g = torch.Generator().manual_seed(21)
+    C = H * 64
+    q = (torch.randn(B, Sq, C, generator=g) * 1.5).half().cuda()
+    kv = torch.randn(B, Sk, 2 * C, generator=g).half().cuda()
+    k, v = kv[:, :, :C], kv[:, :, C:]
+
+    def heads(t):
+        return t.float().reshape(B, -1, H, 64).transpose(1, 2)
+    ref = F.scaled_dot_product_attention(heads(q), heads(k), heads(v)).transpose(1, 2).reshape(B, Sq, C)
+    monkeypatch.setenv("KATZ_ATTN", "tc05")
+    monkeypatch.setenv("KATZ_ATTN_SPLIT", "0")
+    whole = ops.attention(q, k, v, H)
+    monkeypatch.setenv("KATZ_ATTN_SPLIT", "1")
+    cut1 = ops.attention(q, k, v, H)
+    cut2 = ops.attention(q, k, v, H)
+    assert ops.tc05_status() == 0
+    assert torch.equal(cut1, cut2)                       # parts are added in index order whichever arrives last
+    assert float((cut1.float() - ref).abs().max()) < 4e-3
+    assert float((cut1.float() - whole.float()).abs().max()) < 2e-3
+    assert int(ops._attention_scratch(q.device)[:4096].view(torch.int32).abs().sum()) == 0
+
+
 def test_attention_tcgen05_large_logits_rescale(cuda_device, monkeypatch):
     """Logits that grow along the key axis force the reference maximum (and the O accumulator) to be raised often."""
     from katz_b200 import ops
