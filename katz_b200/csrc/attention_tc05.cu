@@ -3,18 +3,20 @@
 // (diffusers/models/attention_processor.py:1276): softmax(Q K^T / sqrt(64)) V per (batch, head).
 //
 // One CTA owns 128 query rows of one (batch, head) and walks the keys in tiles of 128. The softmax is bound by the
-// special-function unit (one exp2 per score), and a single CTA leaves that unit idle while its four softmax warps wait
-// for TMEM loads, barriers and the row maximum; so the CTA is sized for TWO per SM (113 KB of shared memory, 256 TMEM
-// columns, 168 registers) and the hardware interleaves the two:
+// special-function unit (one exp2 per score) and by the softmax warps' own instruction stream, and a single CTA leaves
+// both idle while its four softmax warps wait for TMEM loads, barriers and the row maximum; so the CTA is sized for TWO
+// per SM (80 KB of shared memory, 256 TMEM columns, 168 registers) and the hardware interleaves the two:
 //   * warp 0, one elected thread: TMA loads of Q (once) and of the K and V tiles into 2-stage rings (128-byte swizzle;
 //     Q/K/V are read in place from the [B, S, ld] projection outputs, head h = columns [64h, 64h+64));
 //   * warp 1, one elected thread: S = Q K^T (tcgen05.mma, 128x128x64, K-major operands) into a TMEM accumulator that
-//     the softmax frees as soon as the scores sit in registers, then O += P V (128x64x128; V is the MN-major operand,
-//     P comes from shared memory) into a second accumulator;
+//     the softmax frees as soon as the scores sit in registers, then O += P V (128x64x128; V is the MN-major operand
+//     in shared memory, P is the A operand read from TENSOR MEMORY: it never crosses shared memory, whose bandwidth the
+//     two MMAs' K, V and Q reads and the TMA fills already use) into a second accumulator;
 //   * warps 2-5: softmax. A thread owns one query row (= one TMEM lane), so row maxima and sums need no shuffles. It
 //     reads S with tcgen05.ld, keeps a running reference maximum that is only raised when the tile maximum exceeds it
 //     by more than 2^8 (so the O accumulator is rescaled rarely: tcgen05.ld / scale / tcgen05.st), writes
-//     P = exp2(S*scale - m) as fp16 into swizzled shared memory for the second MMA, and at the end normalises O.
+//     P = exp2(S*scale - m) as fp16 pairs into its lane of the P columns of tensor memory (tcgen05.st) for the second
+//     MMA, and at the end normalises O.
 // S[j+1] = Q K[j+1]^T is issued before the softmax of tile j has finished, so the two MMAs and the softmax overlap.
 // Every mbarrier wait is bounded; a time-out records a status word (shared with the GEMM kernels) and the CTA unwinds.
 //
@@ -30,20 +32,13 @@ namespace katz {
 
 using namespace tc05;
 
-// Key tile: 128 keys with two CTAs per SM. (64 keys with three CTAs per SM compiles too, -DKATZ_FA_BN=64, and measured
-// 25-40% slower: the per-tile barrier round trips do not shrink with the tile.)
-#ifndef KATZ_FA_BN
-#define KATZ_FA_BN 128
-#endif
-constexpr int FA_BM = 128, FA_BN = KATZ_FA_BN, FA_D = 64, FA_ST = 2;
-static_assert(FA_BN == 64 || FA_BN == 128, "key tile");
-constexpr int FA_CTAS_PER_SM = FA_BN == 64 ? 3 : 2;
+constexpr int FA_BM = 128, FA_BN = 128, FA_D = 64, FA_ST = 3;
+constexpr int FA_CTAS_PER_SM = 2;
 constexpr int FA_THREADS = 192;
 constexpr int FA_TILE = 128 * 128;                     // bytes of a 128-row x 64-half tile (Q; one 64-key sub-tile of P)
 constexpr int FA_KV_TILE = FA_BN * 128;                // bytes of a key or value tile
-constexpr int FA_P_BYTES = FA_BM * FA_BN * 2;          // P: FA_BN / 64 sub-tiles of 128 rows x 64 keys
-constexpr int FA_TMEM_COLS = FA_BN == 64 ? 128 : 256;  // S at columns 0..FA_BN-1, O in the 64 columns after it
-constexpr int FA_SMEM = FA_TILE + 2 * FA_ST * FA_KV_TILE + FA_P_BYTES + 256;     // Q, K ring, V ring, P, barriers
+constexpr int FA_TMEM_COLS = 256;                      // S at columns 0..127, O at 128..191, P (fp16 pairs) at 192..255
+constexpr int FA_SMEM = FA_TILE + 2 * FA_ST * FA_KV_TILE + 256;     // Q, K ring, V ring, barriers
 static_assert(FA_CTAS_PER_SM * (FA_SMEM + 1024) <= 228 * 1024, "the CTAs of one SM must fit its shared memory");
 static_assert(FA_CTAS_PER_SM * FA_TMEM_COLS <= 512, "and its tensor memory");
 constexpr float FA_RESCALE_THRESHOLD = 8.0f;           // log2 units
@@ -84,6 +79,24 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (here P, fp16, two consecutive keys per 32-bit column, lane = row) is read
+// from tensor memory, so it never crosses shared memory.
+__device__ __forceinline__ void umma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // kind::f16 instruction descriptor with an MN-major B operand (bit 16)
@@ -100,9 +113,8 @@ __global__ void __launch_bounds__(FA_THREADS, FA_CTAS_PER_SM) attention_tc05_ker
         return;
     }
     const uint32_t sQ = smem_u32(smem);
-    const uint32_t sK0 = sQ + FA_TILE, sV0 = sK0 + FA_ST * FA_KV_TILE, sP0 = sV0 + FA_ST * FA_KV_TILE;
-    unsigned char* sP_gen = smem + FA_TILE + 2 * FA_ST * FA_KV_TILE;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP_gen + FA_P_BYTES);
+    const uint32_t sK0 = sQ + FA_TILE, sV0 = sK0 + FA_ST * FA_KV_TILE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FA_TILE + 2 * FA_ST * FA_KV_TILE);
     // barrier map
     const uint32_t b0 = smem_u32(bars);
     const uint32_t q_full = b0, k_full = b0 + 8, k_empty = k_full + 8 * FA_ST, v_full = k_empty + 8 * FA_ST,
@@ -155,7 +167,7 @@ __global__ void __launch_bounds__(FA_THREADS, FA_CTAS_PER_SM) attention_tc05_ker
     const uint32_t tmem_base = *tmem_slot;
     // Everything above (barriers, TMEM, descriptor prefetch) may overlap the previous kernel's tail: the producer and the
     // softmax warps call pdl_wait() themselves before their first global-memory access (the MMA thread touches none).
-    const uint32_t tS0 = tmem_base, tO = tmem_base + FA_BN;      // S at columns 0..FA_BN-1, O right after it
+    const uint32_t tS0 = tmem_base, tO = tmem_base + FA_BN, tP = tO + FA_D;      // S | O | P
 
     if (warp == 0) {
         // ------------------------------------------------------------------------------------ TMA producer
@@ -208,14 +220,13 @@ __global__ void __launch_bounds__(FA_THREADS, FA_CTAS_PER_SM) attention_tc05_ker
                 if (!mbar_wait(p_full, j & 1)) { ok = false; break; }
                 if (!mbar_wait(v_full + 8 * s, (j / FA_ST) & 1)) { ok = false; break; }
                 fence_after_sync();
-                const uint32_t pa = sP0, va = sV0 + s * FA_KV_TILE;
+                const uint32_t va = sV0 + s * FA_KV_TILE;
 #pragma unroll
                 for (int k = 0; k < FA_BN / 16; ++k) {
-                    // A = P: two 64-key sub-tiles, +32 B per 16-key step inside a sub-tile.
+                    // A = P from tensor memory: 16 keys per step = 8 columns of fp16 pairs.
                     // B = V (MN-major): 16 key rows per step = two 8-row swizzle groups = 2048 B.
-                    const uint64_t ad = smem_desc_sw128(pa + (k >> 2) * FA_TILE) + 2 * (k & 3);
                     const uint64_t bd = smem_desc_sw128(va + k * 2048);
-                    umma_f16(tO, ad, bd, idesc_pv, (j | k) != 0);
+                    umma_f16_ta(tO, tP + 8 * k, bd, idesc_pv, (j | k) != 0);
                 }
                 umma_commit(v_empty + 8 * s);
                 umma_commit(p_free);
@@ -291,8 +302,8 @@ __global__ void __launch_bounds__(FA_THREADS, FA_CTAS_PER_SM) attention_tc05_ker
             ok = mbar_wait(p_free, (j & 1) ^ 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            // P = exp2(S*scale - m) (masked keys hold -inf -> 0), row sum on four chains, fp16 into swizzled shared memory
-            unsigned char* prow = sP_gen + row * 128;
+            // P = exp2(S*scale - m) (masked keys hold -inf -> 0), row sum on four chains, fp16 pairs into this row's lane of the
+            // P columns of tensor memory (keys 2c, 2c+1 in column c)
             float ls4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < FA_BN; c += 32) {
@@ -304,16 +315,12 @@ __global__ void __launch_bounds__(FA_THREADS, FA_CTAS_PER_SM) attention_tc05_ker
                     ls4[(e >> 1) & 3] += p0 + p1;
                     pk[e >> 1] = pack_half2(p0, p1);
                 }
-                unsigned char* dst = prow + (c >> 6) * FA_TILE;
-                const int ch0 = (c & 63) >> 3;                 // first 16-byte chunk of these 32 keys inside the sub-tile row
-#pragma unroll
-                for (int k4 = 0; k4 < 4; ++k4)
-                    *reinterpret_cast<uint4*>(dst + (((ch0 + k4) ^ (row & 7)) << 4)) =
-                        make_uint4(pk[4 * k4], pk[4 * k4 + 1], pk[4 * k4 + 2], pk[4 * k4 + 3]);
+                tmem_st_32x16(tP + lane_base + (c >> 1), pk);
             }
             l_sum += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
-            // P visible to the tensor core (generic -> async proxy), then signal
-            fence_proxy_async();
+            // P has landed in tensor memory; then signal
+            tmem_st_wait();
+            fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
         }
