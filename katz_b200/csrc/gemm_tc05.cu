@@ -269,6 +269,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                     cw0 = (r - ty * p.tiles_w) * p.TW;
                 }
                 const int n0 = nt * BN_OUT;
+                // the convolution's k-steps walk (tap row, tap column, channel chunk) with counters: two integer divisions
+                // per k-step in this one thread took longer than the tensor pipe needs for the k-step
+                int cc = 0, kx = 0, ky = 0;
                 for (int kt = 0; kt < KT; ++kt, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -279,9 +282,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                         const uint32_t fb = mapa_shared(full0 + 8 * s, 0);
                         if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
                         if (p.conv) {
-                            const int tap = kt / p.cin_chunks;
-                            const int cc = kt - tap * p.cin_chunks;
-                            const int ky = tap / p.ksize, kx = tap - ky * p.ksize;
                             tma_load_4d_pair(sa, &tmA, cc * TBK, cw0 * p.stride + kx - p.pad_w, ch0 * p.stride + ky - p.pad_h, cb, fb);
                         } else {
                             tma_load_2d_pair(sa, &tmA, kt * TBK, m0, fb);
@@ -293,9 +293,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                         const uint32_t fb = full0 + 8 * s;
                         mbar_expect_tx(fb, STAGE_BYTES);
                         if (p.conv) {
-                            const int tap = kt / p.cin_chunks;
-                            const int cc = kt - tap * p.cin_chunks;
-                            const int ky = tap / p.ksize, kx = tap - ky * p.ksize;
                             // the tensor map walks the input with the convolution's stride: TW x TH pixels per box
                             tma_load_4d(sa, &tmA, cc * TBK, cw0 * p.stride + kx - p.pad_w, ch0 * p.stride + ky - p.pad_h, cb, fb);
                         } else {
@@ -309,6 +306,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc05_gemm_kernel(const __grid_c
                         }
                     }
                     issued = it + 1;
+                    if (++cc == p.cin_chunks) {
+                        cc = 0;
+                        if (++kx == p.ksize) {
+                            kx = 0;
+                            ++ky;
+                        }
+                    }
                 }
             }
             if (!ok) {

@@ -225,11 +225,14 @@ _gn_scratch = {}
 
 
 def _scratch(device, nbytes):
-    buf = _gn_scratch.get(device)
+    # one buffer per (device, stream): launches that share a scratch buffer must be ordered, and two branches of a CUDA
+    # graph (the two halves of a CFG batch on two streams) are not
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    buf = _gn_scratch.get(key)
     if buf is None or buf.numel() < nbytes:
         # zero-filled: the head of the scratch holds the GroupNorm ticket counters, which the kernels return to zero
         buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _gn_scratch[device] = buf
+        _gn_scratch[key] = buf
     return buf
 
 
@@ -356,10 +359,11 @@ _attn_scratch = {}
 def _attention_scratch(device):
     """Scratch of the attention kernel's cut query tiles: one zero-filled buffer per device, of the size that is enough
     for every shape, allocated once (a captured graph keeps pointing at it)."""
-    buf = _attn_scratch.get(device)
+    key = (device, torch.cuda.current_stream(device).cuda_stream)      # per stream, as the GroupNorm scratch
+    buf = _attn_scratch.get(key)
     if buf is None:
         buf = torch.zeros(int(_lib.load().katz_attention_split_scratch_bytes()), dtype=torch.uint8, device=device)
-        _attn_scratch[device] = buf
+        _attn_scratch[key] = buf
     return buf
 
 
