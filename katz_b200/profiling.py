@@ -276,8 +276,8 @@ def ablate(dev, args):
         return _time_events(gr.replay, 10)
     families_ = [("nothing", ()), ("LayerNorm", ("katz_layer_norm_f16",)),
                  ("GroupNorm", ("katz_group_norm_nhwc_f16",)),
-                 ("self- and cross-attention", ("katz_attention_f16", "katz_attention_f16_mma")),
-                 ("self-attention (tcgen05)", ("katz_attention_f16",)),
+                 ("self- and cross-attention", ("katz_attention_f16", "katz_attention_split_f16", "katz_attention_f16_mma")),
+                 ("self-attention (tcgen05)", ("katz_attention_f16", "katz_attention_split_f16")),
                  ("cross-attention (mma.sync)", ("katz_attention_f16_mma",)),
                  ("GEGLU GEMM", ("katz_linear_geglu_f16", "katz_linear_geglu_ex_f16")),
                  ("3x3 convolution (tcgen05)", ("katz_conv3x3_nhwc_f16",)),
