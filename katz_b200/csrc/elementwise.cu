@@ -203,31 +203,35 @@ __global__ void euler_cfg_step_kernel(__half* __restrict__ x, const __half* __re
 }
 
 // y[r, :] = x1[r, :C1] ++ x2[r, :C2], 16-byte chunks (C1, C2 multiples of 8)
+// The index type is 32-bit whenever the element count allows: these kernels move 16 bytes per index, and the 64-bit
+// divisions that split a flat index cost more instructions than the copy itself.
+template <typename I>
 __global__ void concat_channels_kernel(const uint4* __restrict__ x1, const uint4* __restrict__ x2, uint4* __restrict__ y,
                                        long long rows, int ch1, int ch2) {
     pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
     pdl_launch_dependents();
-    const int ch = ch1 + ch2;
-    const long long total = rows * ch;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        long long r = i / ch;
-        int c = (int)(i - r * ch);
-        y[i] = c < ch1 ? x1[r * ch1 + c] : x2[r * ch2 + (c - ch1)];
+    const I ch = (I)(ch1 + ch2);
+    const I total = (I)(rows * (ch1 + ch2));
+    for (I i = (I)blockIdx.x * (I)blockDim.x + threadIdx.x; i < total; i += (I)gridDim.x * (I)blockDim.x) {
+        const I r = i / ch;
+        const int c = (int)(i - r * ch);
+        y[i] = c < ch1 ? x1[(size_t)r * ch1 + c] : x2[(size_t)r * ch2 + (c - ch1)];
     }
 }
 
 // Nearest-neighbour 2x upsample of an NHWC tensor (Upsample2D's F.interpolate, upsampling.py:165-172), 16-byte chunks.
+template <typename I>
 __global__ void upsample2x_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int B, int H, int W, int ch) {
     pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
     pdl_launch_dependents();
-    const long long total = (long long)B * (2 * H) * (2 * W) * ch;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        int c = (int)(i % ch);
-        long long p = i / ch;
-        int ox = (int)(p % (2 * W));
-        p /= (2 * W);
-        int oy = (int)(p % (2 * H));
-        int b = (int)(p / (2 * H));
+    const I total = (I)((long long)B * (2 * H) * (2 * W) * ch);
+    for (I i = (I)blockIdx.x * (I)blockDim.x + threadIdx.x; i < total; i += (I)gridDim.x * (I)blockDim.x) {
+        I p = i / (I)ch;
+        const int c = (int)(i - p * (I)ch);
+        const I q = p / (I)(2 * W);
+        const int ox = (int)(p - q * (I)(2 * W));
+        const I b = q / (I)(2 * H);
+        const int oy = (int)(q - b * (I)(2 * H));
         y[i] = x[(((size_t)b * H + (oy >> 1)) * W + (ox >> 1)) * ch + c];
     }
 }
@@ -365,18 +369,20 @@ extern "C" int katz_timestep_embedding_f16(const float* t, void* out, int rows, 
 // image edge) attached above and / or below, optionally seen through a nearest 2x upsample (then rows [1, 2h+3) of the
 // upsampled padded shard, 2W wide: exactly what the 2h output rows read). One pass instead of an allocation, three
 // copies, an upsample and a slice copy. `edges` is the all-gather of every rank's first and last row, [P][2][B][W][C].
+template <typename I>
 __global__ void halo_assemble_kernel(const uint4* __restrict__ x, const uint4* __restrict__ edges, uint4* __restrict__ out,
                                      int B, int h, int W, int ch, int Ho, int Wo, int top, int upsample, int rank, int world,
-                                     long long total) {
+                                     long long total_) {
     pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
     pdl_launch_dependents();
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const int c = (int)(i % ch);
-        long long r = i / ch;
-        const int w = (int)(r % Wo);
-        r /= Wo;
-        const int j = (int)(r % Ho);
-        const int b = (int)(r / Ho);
+    const I total = (I)total_;
+    for (I i = (I)blockIdx.x * (I)blockDim.x + threadIdx.x; i < total; i += (I)gridDim.x * (I)blockDim.x) {
+        I r = i / (I)ch;
+        const int c = (int)(i - r * (I)ch);
+        const I r2 = r / (I)Wo;
+        const int w = (int)(r - r2 * (I)Wo);
+        const int b = (int)(r2 / (I)Ho);
+        const int j = (int)(r2 - (I)b * (I)Ho);
         const int sr = upsample ? (j + 1) / 2 - 1 : j - top;
         const int sw = upsample ? w >> 1 : w;
         uint4 v = make_uint4(0, 0, 0, 0);
@@ -400,8 +406,12 @@ extern "C" int katz_halo_assemble_f16(const void* x, const void* edges, void* ou
     KATZ_CHECK_ARG(aligned16(x) && aligned16(out) && (!edges || aligned16(edges)), KATZ_EALIGN);
     const int Ho = upsample ? 2 * h + 2 : h + top + bottom, Wo = upsample ? 2 * W : W;
     const long long total = (long long)B * Ho * Wo * (C / 8);
-    launch_k(halo_assemble_kernel, ew_grid(total, 256), 256, 0, (cudaStream_t)stream, (const uint4*)x, (const uint4*)edges,
-             (uint4*)out, B, h, W, C / 8, Ho, Wo, top, upsample, rank, world, total);
+    if (total < (1ll << 31))
+        launch_k(halo_assemble_kernel<unsigned int>, ew_grid(total, 256), 256, 0, (cudaStream_t)stream, (const uint4*)x,
+                 (const uint4*)edges, (uint4*)out, B, h, W, C / 8, Ho, Wo, top, upsample, rank, world, total);
+    else
+        launch_k(halo_assemble_kernel<long long>, ew_grid(total, 256), 256, 0, (cudaStream_t)stream, (const uint4*)x,
+                 (const uint4*)edges, (uint4*)out, B, h, W, C / 8, Ho, Wo, top, upsample, rank, world, total);
     KATZ_LAUNCH_RET();
 }
 
@@ -434,8 +444,12 @@ extern "C" int katz_concat_channels_f16(const void* x1, const void* x2, void* y,
     KATZ_CHECK_ARG(rows > 0 && C1 > 0 && C2 > 0 && C1 % 8 == 0 && C2 % 8 == 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(aligned16(x1) && aligned16(x2) && aligned16(y), KATZ_EALIGN);
     long long n = rows * ((C1 + C2) / 8);
-    launch_k(concat_channels_kernel, ew_grid(n, 256), 256, 0, (cudaStream_t)stream, (const uint4*)x1, (const uint4*)x2, (uint4*)y,
-                                                                            rows, C1 / 8, C2 / 8);
+    if (n < (1ll << 31))
+        launch_k(concat_channels_kernel<unsigned int>, ew_grid(n, 256), 256, 0, (cudaStream_t)stream, (const uint4*)x1,
+                 (const uint4*)x2, (uint4*)y, rows, C1 / 8, C2 / 8);
+    else
+        launch_k(concat_channels_kernel<long long>, ew_grid(n, 256), 256, 0, (cudaStream_t)stream, (const uint4*)x1,
+                 (const uint4*)x2, (uint4*)y, rows, C1 / 8, C2 / 8);
     KATZ_LAUNCH_RET();
 }
 
@@ -444,7 +458,10 @@ extern "C" int katz_upsample_nearest2x_nhwc_f16(const void* x, void* y, int B, i
     KATZ_CHECK_ARG(B > 0 && H > 0 && W > 0 && C > 0 && C % 8 == 0, KATZ_ESIZE);
     KATZ_CHECK_ARG(aligned16(x) && aligned16(y), KATZ_EALIGN);
     long long n = (long long)B * 4 * H * W * (C / 8);
-    launch_k(upsample2x_kernel, ew_grid(n, 256), 256, 0, (cudaStream_t)stream, (const uint4*)x, (uint4*)y, B, H, W, C / 8);
+    if (n < (1ll << 31))
+        launch_k(upsample2x_kernel<unsigned int>, ew_grid(n, 256), 256, 0, (cudaStream_t)stream, (const uint4*)x, (uint4*)y, B, H, W, C / 8);
+    else
+        launch_k(upsample2x_kernel<long long>, ew_grid(n, 256), 256, 0, (cudaStream_t)stream, (const uint4*)x, (uint4*)y, B, H, W, C / 8);
     KATZ_LAUNCH_RET();
 }
 

@@ -33,11 +33,23 @@ __global__ void __launch_bounds__(256) peer_allgather_kernel(const uint4* __rest
     pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
     pdl_launch_dependents();
     const long long slot = dst_off + (long long)a.rank * n16 * 16;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) {
-        const long long r = i / row16;
-        const uint4 v = src[r * pitch16 + (i - r * row16)];
+    // (row, column) of the source walk along with i: no division per 16-byte vector
+    const long long step = (long long)gridDim.x * blockDim.x;
+    const long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long step_r = step / row16;
+    const int step_c = (int)(step - step_r * row16);
+    long long r = i0 / row16;
+    int c = (int)(i0 - r * row16);
+    for (long long i = i0; i < n16; i += step) {
+        const uint4 v = src[r * pitch16 + c];
 #pragma unroll 1
         for (int p = 0; p < a.world; ++p) reinterpret_cast<uint4*>(a.base[p] + slot)[i] = v;
+        r += step_r;
+        c += step_c;
+        if (c >= row16) {
+            c -= row16;
+            ++r;
+        }
     }
     __threadfence_system();
     __syncthreads();
