@@ -215,6 +215,14 @@ int katz_conv2d_nhwc_f16_mma(const void* X, const void* X2, const void* W, void*
                              const void* rowvec, int ld_rowvec, const void* residual, int act, float out_scale,
                              void* stream);
 
+/* 3x3 convolution, padding 1 (vertical padding `pad_h`: 0 for a row shard that carries its halo rows), stride 1 or 2, for
+ * NHWC tensors with Cin in {8, 16, 32} and Cout a multiple of 8: the first five layers of
+ * ControlNetConditioningEmbedding (controlnet.py:113-127), which the reference runs through nn.Conv2d. W is [Cout, 3, 3, Cin]; bias (optional) and
+ * SiLU (act = 1) in the epilogue. A direct convolution from a shared-memory patch: these layers move a 1024 x 1024
+ * image and have too few channels to fill the implicit-GEMM tiles. */
+int katz_conv3x3_small_nhwc_f16(const void* X, const void* W, void* Y, int B, int Hin, int Win, int Cin, int Cout,
+                                int stride, int pad_h, const void* bias, int act, void* stream);
+
 /* softmax(Q K^T * scale) V per (batch, head), head_dim 64, no mask (F.scaled_dot_product_attention as called at
  * attention_processor.py:1276). Q/K/V/O are [B, S, ld*] token-major with head h at columns [64h, 64h+64);
  * bs* are batch strides in elements. With 0 < kv_chunk_rows < Sk (a multiple of 64) key/value row j is read from

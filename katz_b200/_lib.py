@@ -88,6 +88,7 @@ SIGNATURES = {
     "katz_upsample_nearest2x_nhwc_f16": (_I, [_V, _V, _I, _I, _I, _I, _V]),
     "katz_conv2d_nhwc_f16_mma": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _V, _V, _I, _V, _I, _F, _V]),
     "katz_attention_f16": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _L, _V]),
+    "katz_conv3x3_small_nhwc_f16": (_I, [_V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _V, _I, _V]),
     "katz_attention_split_scratch_bytes": (_L, []),
     "katz_attention_split_f16": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _L, _V, _L, _V]),
     "katz_attention_f16_mma": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _L, _V]),

@@ -215,6 +215,12 @@ def conv2d(x, w, bias=None, ksize=3, stride=1, pad=1, upsample=False, x2=None, r
         call("katz_conv3x3_nhwc_f16", _p(src), _p(w), _p(out), B, Hin, Win, C1, Cout, stride, ph, _p(bias), _p(rowvec),
              rowvec.stride(0) if rowvec is not None else 0, _p(residual), act, float(out_scale), _stream())
         return out
+    if (ksize == 3 and stride in (1, 2) and pad == 1 and ph in (0, 1) and x2 is None and not upsample and rowvec is None
+            and residual is None and out_scale == 1.0 and C1 in (8, 16, 32) and Cout % 8 == 0 and Cout <= 1024
+            and _al16(x) and _al16(w) and _al16(out) and _al16(bias) and os.environ.get("KATZ_CONV_SMALL", "1") != "0"):
+        # few input channels (the ControlNet conditioning embedding): direct convolution from a shared-memory patch
+        call("katz_conv3x3_small_nhwc_f16", _p(x), _p(w), _p(out), B, Hin, Win, C1, Cout, stride, ph, _p(bias), act, _stream())
+        return out
     call("katz_conv2d_nhwc_f16_mma", _p(x), _p(x2), _p(w), _p(out), B, Hin, Win, C1, C2, Cout, ksize, stride, ph, pad,
          1 if upsample else 0, _p(bias), _p(rowvec), rowvec.stride(0) if rowvec is not None else 0, _p(residual), act,
          float(out_scale), _stream())

@@ -95,14 +95,21 @@ class _Weights:
             self.temb_offset[b] = (off, c)
             off += c
         # --- everything else
+        # The ControlNet conditioning embedding's 96-channel layers are stored with 128 channels (zero weights, zero bias:
+        # the extra channels stay zero through SiLU), so that the convolutions that read them have a channel count the
+        # tcgen05 implicit GEMM takes (a multiple of 64) instead of falling to the mma.sync kernel.
+        def widen(k, c):
+            return 128 if c == 96 and k.startswith("controlnet_cond_embedding.blocks.") else c
         for k, shp in shapes.items():
             if k in self.t:
                 continue
             if len(shp) == 4:
                 cout, cin, kh, kw = shp
-                cin_pad = (cin + 7) // 8 * 8
+                cin_pad = widen(k, (cin + 7) // 8 * 8)
                 self.conv_cin_pad[k] = cin_pad
-                self.t[k] = torch.zeros((cout, kh, kw, cin_pad), dtype=torch.float16, device=dev)
+                self.t[k] = torch.zeros((widen(k, cout), kh, kw, cin_pad), dtype=torch.float16, device=dev)
+            elif len(shp) == 1:
+                self.t[k] = torch.zeros((widen(k, shp[0]),), dtype=torch.float16, device=dev)
             else:
                 self.t[k] = torch.zeros(shp, dtype=torch.float16, device=dev)
 
@@ -130,11 +137,14 @@ class _Weights:
                 cin = self.shapes[ck][1]
                 if tuple(src.shape) != tuple(self.shapes[ck]):
                     raise KatzError("shape mismatch for %s: %s vs %s" % (k, tuple(src.shape), self.shapes[ck]))
-                dst[..., :cin].copy_(src.permute(0, 2, 3, 1))
+                dst[:src.shape[0], :, :, :cin].copy_(src.permute(0, 2, 3, 1))
             else:
-                if tuple(src.shape) != tuple(dst.shape):
-                    raise KatzError("shape mismatch for %s: %s vs %s" % (k, tuple(src.shape), tuple(dst.shape)))
-                dst.copy_(src)
+                if tuple(src.shape) != tuple(self.shapes[ck]):
+                    raise KatzError("shape mismatch for %s: %s vs %s" % (k, tuple(src.shape), tuple(self.shapes[ck])))
+                if dst.shape == src.shape:
+                    dst.copy_(src)
+                else:
+                    dst[:src.shape[0]].copy_(src)      # a widened bias vector: the padding stays zero
             seen.add(ck)
         if strict:
             missing = [k for k in self.shapes if k not in seen]
@@ -148,7 +158,9 @@ class _Weights:
         for k, shp in self.shapes.items():
             t = self.t[k]
             if len(shp) == 4:
-                out[k] = t[..., :shp[1]].permute(0, 3, 1, 2).contiguous()
+                out[k] = t[:shp[0], :, :, :shp[1]].permute(0, 3, 1, 2).contiguous()
+            elif len(shp) == 1:
+                out[k] = t[:shp[0]].clone()
             else:
                 out[k] = t.clone()
         return out

@@ -278,6 +278,38 @@ def test_conv3x3_tcgen05(cuda_device, B, H, W, Cin, Cout, up, stride, monkeypatc
     assert _rel(out.permute(0, 3, 1, 2), ref) < 2e-3
 
 
+@pytest.mark.parametrize("B,H,W,Cin,Cout,stride,act", [(2, 64, 64, 8, 16, 1, 1), (1, 128, 96, 16, 16, 1, 1), (2, 64, 64, 16, 32, 2, 1),
+                                                        (1, 70, 50, 32, 32, 1, 1), (2, 64, 64, 32, 96, 2, 1), (1, 40, 72, 32, 96, 1, 1),
+                                                        (2, 64, 64, 16, 256, 2, 1), (1, 9, 33, 32, 72, 1, 0), (1, 11, 35, 16, 8, 2, 0),
+                                                        (1, 1024, 1024, 8, 16, 1, 1)])      # the last: the embedding's first layer at size
+def test_conv3x3_few_channels(cuda_device, B, H, W, Cin, Cout, stride, act, monkeypatch):
+    """The direct convolution of the ControlNet conditioning embedding's layers (few channels, large images) against fp32
+    F.conv2d (+ SiLU) and against the implicit-GEMM kernel it replaces for these shapes; ragged tile edges included."""
+    from katz_b200 import ops
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(B, Cin, H, W, generator=g).half().cuda()
+    w = (torch.randn(Cout, Cin, 3, 3, generator=g) / (9 * Cin) ** 0.5).half().cuda()
+    bias = torch.randn(Cout, generator=g).half().cuda()
+    ref = F.conv2d(x.float(), w.float(), bias.float(), padding=1, stride=stride)
+    if act:
+        ref = F.silu(ref)
+    xn, wn = x.permute(0, 2, 3, 1).contiguous(), w.permute(0, 2, 3, 1).contiguous()
+    n0 = ops._lib.launch_count()
+    out = ops.conv2d(xn, wn, bias, stride=stride, act=ops.ACT_SILU if act else ops.ACT_NONE)
+    assert ops._lib.launch_count() == n0 + 1
+    assert _rel(out.permute(0, 3, 1, 2), ref) < 2e-3
+    assert float((out.permute(0, 3, 1, 2).float() - ref).abs().max()) < 2e-2
+    monkeypatch.setenv("KATZ_CONV_SMALL", "0")
+    old = ops.conv2d(xn, wn, bias, stride=stride, act=ops.ACT_SILU if act else ops.ACT_NONE)
+    assert _rel(out, old) < 1e-3
+    # a row shard that carries its halo rows: no vertical padding
+    monkeypatch.setenv("KATZ_CONV_SMALL", "1")
+    if stride == 1 and H <= 128:
+        xp = F.pad(xn, (0, 0, 0, 0, 1, 1))
+        out2 = ops.conv2d(xp, wn, bias, stride=1, act=ops.ACT_SILU if act else ops.ACT_NONE, pad_h=0)
+        assert torch.equal(out2, out)
+
+
 @pytest.mark.parametrize("M,F,K", [(2048, 5120, 1280), (8192, 2560, 640), (300, 64, 64), (256, 80, 128)])
 def test_feed_forward_geglu_fused(cuda_device, M, F, K, monkeypatch):
     monkeypatch.setenv("KATZ_GEMM", "tc05")
