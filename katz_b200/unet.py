@@ -98,8 +98,14 @@ class _Weights:
         # The ControlNet conditioning embedding's 96-channel layers are stored with 128 channels (zero weights, zero bias:
         # the extra channels stay zero through SiLU), so that the convolutions that read them have a channel count the
         # tcgen05 implicit GEMM takes (a multiple of 64) instead of falling to the mma.sync kernel.
+        # Likewise the UNet's last convolution (320 -> 4 channels) is stored with 8 output channels: the tcgen05 convolution
+        # wants a multiple of 8, and the layout kernel that follows keeps the first 4.
         def widen(k, c):
-            return 128 if c == 96 and k.startswith("controlnet_cond_embedding.blocks.") else c
+            if c == 96 and k.startswith("controlnet_cond_embedding.blocks."):
+                return 128
+            if c == 4 and k in ("conv_out.weight", "conv_out.bias"):
+                return 8
+            return c
         for k, shp in shapes.items():
             if k in self.t:
                 continue
