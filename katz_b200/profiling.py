@@ -2,6 +2,7 @@
 
     python -m katz_b200.profiling gemm           # the step's dominant linear shapes, 3 launches each
     python -m katz_b200.profiling attention      # the step's two self-attention shapes, 2 launches each
+    python -m katz_b200.profiling conv           # two of the step's 3x3 convolutions, 2 launches each
     python -m katz_b200.profiling merge          # one LoRA merge over a 102-layer subset (0.7 GB of weights)
     python -m katz_b200.profiling merge-fp32     # the same subset with fp32 weights and adapters
     python -m katz_b200.profiling step [--batch B] [--latent HW]   # ONE eager UNet step
@@ -84,6 +85,25 @@ def attention(dev, args):
         C = H * 64
         times.append(round(_graph_time(lambda i: ops.attention(qkv[:, :, :C], qkv[:, :, C:2 * C], qkv[:, :, 2 * C:], H, out=o), n=10), 2))
     return {"profiled": "self-attention, 2 launches each", "shapes": shapes, "graph_us_per_launch": times, "tc05_status": ops.tc05_status()}
+
+
+def conv(dev, args):
+    from . import ops
+    shapes = [(32, 1280, 1280), (64, 640, 640)]      # (H = W, Cin, Cout) at batch 2: 10 and 6 launches per step
+    bufs = []
+    for (H, Cin, Cout) in shapes:
+        bufs.append((torch.randn(2, H, H, Cin, device=dev).half(), (torch.randn(Cout, 3, 3, Cin, device=dev) * 0.02).half(),
+                     torch.randn(Cout, device=dev).half(), torch.empty(2, H, H, Cout, dtype=torch.float16, device=dev)))
+
+    def run(n):
+        for x, w, b, o in bufs:
+            for _ in range(n):
+                ops.conv2d(x, w, b, out=o)
+    run(1)
+    _bracket(lambda: run(2))
+    times = [round(_graph_time(lambda i: ops.conv2d(x, w, b, out=o), n=10), 2) for x, w, b, o in bufs]
+    return {"profiled": "3x3 convolutions, 2 launches each", "shapes": shapes, "graph_us_per_launch": times,
+            "kernel": ops.gemm_kernel_name(), "tc05_status": ops.tc05_status()}
 
 
 def _subset_merger(dev, dtype):
@@ -377,7 +397,7 @@ def families(dev, args):
     return out
 
 
-MODES = {"families": families, "gemm": gemm, "attention": attention, "merge": merge, "merge-fp32": merge_fp32, "step": step, "norms": norms,
+MODES = {"families": families, "gemm": gemm, "attention": attention, "conv": conv, "merge": merge, "merge-fp32": merge_fp32, "step": step, "norms": norms,
          "compare-cublas": compare_cublas, "compare-cudnn": compare_cudnn, "ablate": ablate}
 
 
