@@ -254,6 +254,17 @@ int katz_attention_split_f16(const void* Q, const void* K, const void* V, void* 
                              long long bso, float scale, int kv_chunk_rows, long long kv_chunk_stride, void* scratch,
                              long long scratch_bytes, void* stream);
 
+/* The same kernel for a row shard whose K/V chunks are pushed by peers (katz_peer_push) into this GPU's arena: chunk
+ * `self_chunk` is this rank's own shard and is walked first; before its first tile of any other chunk r the kernel waits
+ * (bounded: about a second, then a non-zero katz_tc05_status() and no valid output) until peer_ctrl[64 + r] has reached
+ * peer_ctrl[0], the number of the exchange that delivered the chunks. `peer_ctrl` points at the control words of this
+ * rank's arena; the kernel must follow the katz_peer_push of the same K/V on the same stream. `scratch` may be NULL.
+ * No reference counterpart (the reference has no row split). */
+int katz_attention_peer_f16(const void* Q, const void* K, const void* V, void* O, int B, int H, int Sq, int Sk,
+                            int head_dim, int ldq, int ldk, int ldv, int ldo, long long bsq, long long bsk, long long bsv,
+                            long long bso, float scale, int kv_chunk_rows, long long kv_chunk_stride, void* scratch,
+                            long long scratch_bytes, const void* peer_ctrl, int self_chunk, void* stream);
+
 /* dst = src + half(sum_i scales[i] * residuals[i]) — ControlNet residual intake (unet_2d_condition.py:1281-1292; the
  * sum / mean over nets of :1418-1439). `h_residuals` and `h_scales` are HOST arrays of n_res entries (device pointers
  * inside). */
@@ -286,6 +297,10 @@ int katz_peer_ipc_open(const void* handle, void** ptr);
 int katz_peer_ipc_close(void* ptr);
 int katz_peer_allgather(const void* src, long long rows, long long row_bytes, long long src_pitch_bytes, long long dst_off,
                         const unsigned long long* h_bases, int rank, int world, void* stream);
+/* The same push without the wait: the block goes to slot `rank` of every arena and the flags are raised; a consumer
+ * that waits for the flags itself (katz_attention_peer_f16) follows on the same stream. */
+int katz_peer_push(const void* src, long long rows, long long row_bytes, long long src_pitch_bytes, long long dst_off,
+                   const unsigned long long* h_bases, int rank, int world, void* stream);
 int katz_peer_status(const void* arena);
 /* Put the status word back to zero (for instance after a warm-up during which the ranks were not yet in step). */
 int katz_peer_clear_status(void* arena);

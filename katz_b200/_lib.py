@@ -91,6 +91,7 @@ SIGNATURES = {
     "katz_conv3x3_small_nhwc_f16": (_I, [_V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _V, _I, _V]),
     "katz_attention_split_scratch_bytes": (_L, []),
     "katz_attention_split_f16": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _L, _V, _L, _V]),
+    "katz_attention_peer_f16": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _L, _V, _L, _V, _I, _V]),
     "katz_attention_f16_mma": (_I, [_V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _L, _V]),
     "katz_residual_intake_f16": (_I, [_V, _V, POINTER(c_void_p), POINTER(c_float), _I, _L, _V]),
     "katz_timestep_embedding_f16": (_I, [_V, _V, _I, _I, _I, _V]),
@@ -105,6 +106,7 @@ SIGNATURES = {
     "katz_peer_ipc_open": (_I, [_V, POINTER(c_void_p)]),
     "katz_peer_ipc_close": (_I, [_V]),
     "katz_peer_allgather": (_I, [_V, _L, _L, _L, _L, POINTER(ctypes.c_ulonglong), _I, _I, _V]),
+    "katz_peer_push": (_I, [_V, _L, _L, _L, _L, POINTER(ctypes.c_ulonglong), _I, _I, _V]),
     "katz_peer_status": (_I, [_V]),
     "katz_peer_clear_status": (_I, [_V]),
     "katz_add_f16": (_I, [_V, _V, _V, _L, _V]),

@@ -42,6 +42,7 @@ constexpr int FA_SMEM = FA_TILE + 2 * FA_ST * FA_KV_TILE + 256;     // Q, K ring
 static_assert(FA_CTAS_PER_SM * (FA_SMEM + 1024) <= 228 * 1024, "the CTAs of one SM must fit its shared memory");
 static_assert(FA_CTAS_PER_SM * FA_TMEM_COLS <= 512, "and its tensor memory");
 constexpr float FA_RESCALE_THRESHOLD = 8.0f;           // log2 units
+constexpr uint32_t FA_PEER_WAIT_LIMIT = 1u << 19;      // polls of about two microseconds: a second or so
 
 int* tc05_status_device_ptr();   // defined next to the status word (gemm_tc05.cu)
 
@@ -59,6 +60,11 @@ struct FaParams {
     int* counters;              // one ticket per cut query tile, zero between launches
     float2* part_ml;            // [cut tile][part][row]: (reference maximum in log2 units, row sum)
     float4* part_o;             // [cut tile][part][16 column quads][128 rows]: unnormalised O
+    // K/V chunks that peers push into this GPU's memory (latent-row split): the control words of this rank's peer arena
+    // ([0]: number of the exchange that delivered them, [64 + r]: the last exchange whose block from rank r has landed),
+    // this rank's own chunk, and the number of chunks. NULL: every chunk is there when the kernel starts.
+    const unsigned int* peer_ctrl;
+    int self_chunk, n_chunks;
 };
 
 __device__ __forceinline__ void tma_load_4d_fa(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
@@ -177,11 +183,39 @@ __global__ void __launch_bounds__(FA_THREADS, FA_CTAS_PER_SM) attention_tc05_ker
             pdl_launch_dependents();
             mbar_expect_tx(q_full, FA_TILE);
             tma_load_4d_fa(sQ, &tmQ, h * FA_D, q0, b, 0, q_full);
+            // Peer mode: the chunks are walked starting with this rank's own shard, and the first tile of every other chunk
+            // waits (bounded) for that rank's flag: its K/V cross NVLink while the tiles before it are being worked on.
+            unsigned int epoch = 0;
+            int landed = p.self_chunk;
+            if (p.peer_ctrl) epoch = *reinterpret_cast<const volatile unsigned int*>(p.peer_ctrl);
             for (int j = 0; j < NT && ok; ++j) {
                 const int s = j % FA_ST;
                 const uint32_t ph = (j / FA_ST) & 1;
                 const int key0 = (j0 + j) * FA_BN;
-                const int chunk = key0 / p.kv_chunk_rows, row = key0 - chunk * p.kv_chunk_rows;
+                int chunk = key0 / p.kv_chunk_rows;
+                const int row = key0 - chunk * p.kv_chunk_rows;
+                if (p.peer_ctrl) {
+                    chunk += p.self_chunk;
+                    if (chunk >= p.n_chunks) chunk -= p.n_chunks;
+                    if (chunk != landed) {
+                        const unsigned int* flag = p.peer_ctrl + 64 + chunk;
+                        bool there = false;
+                        for (uint32_t polls = 0; polls < FA_PEER_WAIT_LIMIT; ++polls) {
+                            unsigned int v;
+                            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+                            if ((int)(v - epoch) >= 0) {
+                                there = true;
+                                break;
+                            }
+                            __nanosleep(64);
+                        }
+                        // a chunk that never came: the status word voids the result, and the loads go ahead on whatever the
+                        // buffer holds, so that the other roles finish at once instead of running out their own waits
+                        if (!there) atomicExch(p.status, 14);
+                        asm volatile("fence.proxy.async;" ::: "memory");      // the TMA loads below read what the peer wrote
+                        landed = chunk;
+                    }
+                }
                 if (!mbar_wait(k_empty + 8 * s, ph ^ 1)) { ok = false; break; }
                 mbar_expect_tx(k_full + 8 * s, FA_KV_TILE);
                 tma_load_4d_fa(sK0 + s * FA_KV_TILE, &tmK, h * FA_D, row, b, chunk, k_full + 8 * s);
@@ -189,7 +223,7 @@ __global__ void __launch_bounds__(FA_THREADS, FA_CTAS_PER_SM) attention_tc05_ker
                 mbar_expect_tx(v_full + 8 * s, FA_KV_TILE);
                 tma_load_4d_fa(sV0 + s * FA_KV_TILE, &tmV, h * FA_D, row, b, chunk, v_full + 8 * s);
             }
-            if (!ok) atomicExch(p.status, 11);
+            if (!ok) atomicCAS(p.status, 0, 11);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------------------------ MMA issuer
@@ -505,7 +539,7 @@ static void fa_plan(int n_q, int key_tiles, long long scratch_bytes, int* n_full
 static int attention_launch(const void* Q, const void* K, const void* V, void* O, int B, int H, int Sq, int Sk, int head_dim,
                             int ldq, int ldk, int ldv, int ldo, long long bsq, long long bsk, long long bsv, long long bso,
                             float scale, int kv_chunk_rows, long long kv_chunk_stride, void* scratch, long long scratch_bytes,
-                            void* stream) {
+                            const void* peer_ctrl, int self_chunk, void* stream) {
 
     KATZ_CHECK_ARG(Q && K && V && O, KATZ_EINVAL);
     KATZ_CHECK_ARG(head_dim == 64, KATZ_ESIZE);
@@ -553,6 +587,12 @@ static int attention_launch(const void* Q, const void* K, const void* V, void* O
     }
     p.tiles_x = (Sq + FA_BM - 1) / FA_BM;
     p.H = H;
+    if (peer_ctrl) {
+        KATZ_CHECK_ARG(chunks > 1 && self_chunk >= 0 && self_chunk < chunks && chunks <= 8 && ((uintptr_t)peer_ctrl & 3) == 0, KATZ_EINVAL);
+        p.peer_ctrl = (const unsigned int*)peer_ctrl;
+        p.self_chunk = self_chunk;
+        p.n_chunks = chunks;
+    }
     const long long n_q = (long long)p.tiles_x * H * B;
     KATZ_CHECK_ARG(n_q < (1ll << 30), KATZ_ESIZE);
     int cut_tiles = 0;
@@ -580,7 +620,18 @@ extern "C" int katz_attention_split_f16(const void* Q, const void* K, const void
                                         long long kv_chunk_stride, void* scratch, long long scratch_bytes, void* stream) {
     KATZ_CHECK_ARG(scratch && aligned16(scratch) && scratch_bytes >= FA_COUNTER_BYTES, KATZ_EINVAL);
     return attention_launch(Q, K, V, O, B, H, Sq, Sk, head_dim, ldq, ldk, ldv, ldo, bsq, bsk, bsv, bso, scale, kv_chunk_rows,
-                            kv_chunk_stride, scratch, scratch_bytes, stream);
+                            kv_chunk_stride, scratch, scratch_bytes, nullptr, 0, stream);
+}
+
+extern "C" int katz_attention_peer_f16(const void* Q, const void* K, const void* V, void* O, int B, int H, int Sq, int Sk,
+                                       int head_dim, int ldq, int ldk, int ldv, int ldo, long long bsq, long long bsk,
+                                       long long bsv, long long bso, float scale, int kv_chunk_rows,
+                                       long long kv_chunk_stride, void* scratch, long long scratch_bytes, const void* peer_ctrl,
+                                       int self_chunk, void* stream) {
+    KATZ_CHECK_ARG(peer_ctrl, KATZ_EINVAL);
+    KATZ_CHECK_ARG(!scratch || (aligned16(scratch) && scratch_bytes >= FA_COUNTER_BYTES), KATZ_EINVAL);
+    return attention_launch(Q, K, V, O, B, H, Sq, Sk, head_dim, ldq, ldk, ldv, ldo, bsq, bsk, bsv, bso, scale, kv_chunk_rows,
+                            kv_chunk_stride, scratch, scratch_bytes, peer_ctrl, self_chunk, stream);
 }
 
 extern "C" int katz_attention_f16(const void* Q, const void* K, const void* V, void* O, int B, int H, int Sq, int Sk,
@@ -588,5 +639,5 @@ extern "C" int katz_attention_f16(const void* Q, const void* K, const void* V, v
                                   long long bsv, long long bso, float scale, int kv_chunk_rows, long long kv_chunk_stride,
                                   void* stream) {
     return attention_launch(Q, K, V, O, B, H, Sq, Sk, head_dim, ldq, ldk, ldv, ldo, bsq, bsk, bsv, bso, scale, kv_chunk_rows,
-                            kv_chunk_stride, nullptr, 0, stream);
+                            kv_chunk_stride, nullptr, 0, nullptr, 0, stream);
 }

@@ -28,8 +28,10 @@ struct PeerArgs {
 
 // The block is `rows` rows of `row16` 16-byte vectors, `pitch16` vectors apart in the source (a column slice of a wider
 // tensor is pushed without being made contiguous first); it lands packed.
+// wait = 0: push and raise the flags only; whoever consumes the gathered buffer waits for the peers' flags itself (the
+// attention kernel does, chunk by chunk, so that the transfer of the remote K/V shards overlaps its work on the local one).
 __global__ void __launch_bounds__(256) peer_allgather_kernel(const uint4* __restrict__ src, long long n16, int row16,
-                                                             long long pitch16, long long dst_off, PeerArgs a) {
+                                                             long long pitch16, long long dst_off, PeerArgs a, int wait) {
     pdl_wait();      // nothing below may touch global memory before the kernels this launch depends on are done
     pdl_launch_dependents();
     const long long slot = dst_off + (long long)a.rank * n16 * 16;
@@ -64,6 +66,7 @@ __global__ void __launch_bounds__(256) peer_allgather_kernel(const uint4* __rest
         unsigned int* flag = reinterpret_cast<unsigned int*>(a.base[p]) + 64 + a.rank;
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
     }
+    if (!wait) return;
     for (int s = 0; s < a.world; ++s) {
         const unsigned int* flag = ctrl + 64 + s;
         unsigned int polls = 0;
@@ -141,8 +144,9 @@ extern "C" int katz_peer_ipc_close(void* ptr) {
     return e == cudaSuccess ? KATZ_OK : (int)e;
 }
 
-extern "C" int katz_peer_allgather(const void* src, long long rows, long long row_bytes, long long src_pitch_bytes,
-                                   long long dst_off, const unsigned long long* h_bases, int rank, int world, void* stream) {
+static int peer_allgather_launch(const void* src, long long rows, long long row_bytes, long long src_pitch_bytes,
+                                 long long dst_off, const unsigned long long* h_bases, int rank, int world, int wait,
+                                 void* stream) {
     KATZ_CHECK_ARG(src && h_bases, KATZ_EINVAL);
     KATZ_CHECK_ARG(world >= 1 && world <= PEER_MAX_RANKS && rank >= 0 && rank < world, KATZ_ESIZE);
     KATZ_CHECK_ARG(rows > 0 && row_bytes > 0 && row_bytes % 16 == 0 && row_bytes < (1ll << 34) && src_pitch_bytes >= row_bytes &&
@@ -163,8 +167,18 @@ extern "C" int katz_peer_allgather(const void* src, long long rows, long long ro
     if (ctas > 64) ctas = 64;
     if (ctas < 1) ctas = 1;
     launch_k(peer_allgather_kernel, dim3((unsigned)ctas), dim3(256), 0, (cudaStream_t)stream, (const uint4*)src, n16,
-             (int)(row_bytes / 16), src_pitch_bytes / 16, dst_off, a);
+             (int)(row_bytes / 16), src_pitch_bytes / 16, dst_off, a, wait);
     KATZ_LAUNCH_RET();
+}
+
+extern "C" int katz_peer_allgather(const void* src, long long rows, long long row_bytes, long long src_pitch_bytes,
+                                   long long dst_off, const unsigned long long* h_bases, int rank, int world, void* stream) {
+    return peer_allgather_launch(src, rows, row_bytes, src_pitch_bytes, dst_off, h_bases, rank, world, 1, stream);
+}
+
+extern "C" int katz_peer_push(const void* src, long long rows, long long row_bytes, long long src_pitch_bytes, long long dst_off,
+                              const unsigned long long* h_bases, int rank, int world, void* stream) {
+    return peer_allgather_launch(src, rows, row_bytes, src_pitch_bytes, dst_off, h_bases, rank, world, 0, stream);
 }
 
 // Back to zero (after a warm-up in which the ranks were not yet in step, say). Synchronous.

@@ -159,7 +159,18 @@ class RowParallel:
         place by the attention kernel as P chunks."""
         from . import ops
         B, s, _ = qkv.shape
-        g = self.gather_shards(qkv[:, :, C:])                               # [P, B, s, 2C]
+        kv_local = qkv[:, :, C:]
+        if (self.peer is not None and self.world > 1 and s % 128 == 0 and (2 * C * qkv.element_size()) % 16 == 0
+                and os.environ.get("KATZ_PEER_OVERLAP", "1") != "0"):
+            # The shards are pushed without waiting for the peers: the attention kernel starts on this rank's own shard and
+            # waits for each peer's flag only before it first touches that peer's chunk, so the NVLink transfer of the
+            # remote shards overlaps the work on the local one.
+            k = self._exchange
+            self._exchange += 1
+            g = self.peer.allgather(kv_local, k, wait=False)                # [P, B, s, 2C], chunks still arriving
+            return ops.attention(qkv[:, :, :C], g[0][:, :, :C], g[0][:, :, C:], heads, kv_chunks=(self.world, s, B * s * 2 * C),
+                                 peer=(self.peer.ctrl_address(), self.rank))
+        g = self.gather_shards(kv_local)                                    # [P, B, s, 2C]
         if s % 64 == 0:
             return ops.attention(qkv[:, :, :C], g[0][:, :, :C], g[0][:, :, C:], heads,
                                  kv_chunks=(self.world, s, B * s * 2 * C))
@@ -191,6 +202,11 @@ def peer_arena_bytes(cfg, batch, height, width):
     return int(total * 1.25) + (64 << 20)
 
 
+def _lib_clear_tc05_status():
+    from . import _lib
+    _lib.check(_lib.load().katz_tc05_clear_status(), "katz_tc05_clear_status")
+
+
 class RowParallelStep:
     """CUDA-graph step of a row-split UNet: same interface as engine.GraphedStep. Every rank passes the same inputs
     and receives the whole prediction."""
@@ -219,6 +235,7 @@ class RowParallelStep:
             torch.cuda.synchronize()
             dist.barrier(group=group)
             rp.peer.clear_status()
+            _lib_clear_tc05_status()      # the attention kernel's own wait for a peer's K/V reports through the tcgen05 status word
             dist.barrier(group=group)
         self.graph = self._inner.graph
         self.launches_per_step = self._inner.launches_per_step

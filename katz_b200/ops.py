@@ -373,10 +373,12 @@ def _attention_scratch(device):
     return buf
 
 
-def attention(q, k, v, heads, out=None, scale=None, kv_chunks=None):
+def attention(q, k, v, heads, out=None, scale=None, kv_chunks=None, peer=None):
     """q: [B,Sq,>=H*64] view, k/v: [B,Sk,...] views (unit last stride, any row/batch stride); returns [B,Sq,H*64].
     kv_chunks=(n_chunks, chunk_rows, chunk_stride): k/v describe the FIRST chunk ([B, chunk_rows, ...]); chunk c of the
-    keys/values starts `c * chunk_stride` elements later (the [P, B, s, C] result of an all-gather of row shards)."""
+    keys/values starts `c * chunk_stride` elements later (the [P, B, s, C] result of an all-gather of row shards).
+    peer=(address of this rank's arena control words, this rank's chunk): the chunks were pushed WITHOUT waiting
+    (PeerArena.allgather(wait=False)) and the kernel waits for each peer's flag before it first touches that peer's chunk."""
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _f16(t, n)
         if t.dim() != 3 or t.stride(2) != 1:
@@ -400,12 +402,18 @@ def attention(q, k, v, heads, out=None, scale=None, kv_chunks=None):
     mode = os.environ.get("KATZ_ATTN", "auto")
     if (_use_tc05() and (mode == "tc05" or (mode == "auto" and Sk > 128)) and strides_ok
             and (chunk_rows == 0 or (chunk_rows % 128 == 0 and chunk_stride % 8 == 0))):
-        if os.environ.get("KATZ_ATTN_SPLIT", "1") != "0":
+        if peer is not None:
+            scratch = _attention_scratch(q.device)
+            call("katz_attention_peer_f16", *args[:-1], _p(scratch), scratch.numel(), ctypes.c_void_p(int(peer[0])), int(peer[1]),
+                 args[-1])
+        elif os.environ.get("KATZ_ATTN_SPLIT", "1") != "0":
             scratch = _attention_scratch(q.device)
             call("katz_attention_split_f16", *args[:-1], _p(scratch), scratch.numel(), args[-1])
         else:
             call("katz_attention_f16", *args)
     else:
+        if peer is not None:
+            raise KatzError("attention: chunks that are still in flight need the tcgen05 kernel (128-row chunks, aligned strides)")
         call("katz_attention_f16_mma", *args)
     return out
 

@@ -85,9 +85,10 @@ class PeerArena:
         self._slots.append((off, nbytes))
         return off
 
-    def allgather(self, src, index):
+    def allgather(self, src, index, wait=True):
         """src: CUDA tensor, contiguous or a column slice [..., c0:c1] of a contiguous tensor, whose rows are multiples of
-        16 bytes -> [world, *src.shape] view of the arena (packed)."""
+        16 bytes -> [world, *src.shape] view of the arena (packed). wait=False: push and raise the flags only; the consumer
+        (ops.attention(peer=...)) waits for each peer's flag itself, so the transfer overlaps its work on the local block."""
         es = src.element_size()
         if src.is_contiguous():
             rows, row_bytes, pitch = 1, src.numel() * es, src.numel() * es
@@ -104,9 +105,13 @@ class PeerArena:
         nb = rows * row_bytes
         off = self.slot(index, self.world * nb)
         st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        _lib.call("katz_peer_allgather", ctypes.c_void_p(src.data_ptr()), rows, row_bytes, pitch, off, self.bases, self.rank,
-                  self.world, st)
+        _lib.call("katz_peer_allgather" if wait else "katz_peer_push", ctypes.c_void_p(src.data_ptr()), rows, row_bytes, pitch,
+                  off, self.bases, self.rank, self.world, st)
         return self.local[off:off + self.world * nb].view(src.dtype).view((self.world,) + tuple(src.shape))
+
+    def ctrl_address(self):
+        """Device address of this rank's control words (exchange counter, flags): what a consumer that waits itself reads."""
+        return self._ptr
 
     def close(self):
         """Unmap the peers' arenas and free this rank's. Collective in effect: call it on every rank, after a

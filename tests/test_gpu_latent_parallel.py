@@ -44,6 +44,35 @@ def test_attention_reads_gathered_kv_chunks(cuda_device, B, H, s, P):
         assert float((out.float() - ref.float()).abs().max()) < 4e-3
 
 
+def test_attention_waits_for_pushed_kv_chunks(cuda_device):
+    """The attention entry point for K/V chunks that peers push while the kernel already works on the local chunk, on one
+    GPU: with every flag raised it must give the chunked result (the chunks are only walked in another order); with one
+    flag missing its bounded wait must run out, leave a status word and return."""
+    from katz_b200 import _lib, ops
+    g = torch.Generator().manual_seed(3)
+    B, H, s, P, me = 2, 10, 512, 4, 2
+    C = H * 64
+    q = torch.randn(B, s, C, generator=g).half().cuda()
+    kv = torch.randn(B, P * s, 2 * C, generator=g).half().cuda()
+    gathered = kv.view(B, P, s, 2 * C).permute(1, 0, 2, 3).contiguous()      # [P, B, s, 2C]
+    chunks = (P, s, B * s * 2 * C)
+    ref = ops.attention(q, gathered[0][:, :, :C], gathered[0][:, :, C:], H, kv_chunks=chunks)
+    ctrl = torch.zeros(1024, dtype=torch.int32, device="cuda")      # control words as a peer arena holds them
+    ctrl[0] = 7                                                      # the exchange that delivered the chunks
+    ctrl[64:64 + P] = 7
+    out = ops.attention(q, gathered[0][:, :, :C], gathered[0][:, :, C:], H, kv_chunks=chunks, peer=(ctrl.data_ptr(), me))
+    assert ops.tc05_status() == 0
+    assert float((out.float() - ref.float()).abs().max()) < 2e-3
+    ctrl[64 + 1] = 6                                                 # rank 1's block of exchange 7 never arrives
+    ops.attention(q, gathered[0][:, :, :C], gathered[0][:, :, C:], H, kv_chunks=chunks, peer=(ctrl.data_ptr(), me))
+    assert ops.tc05_status() != 0
+    _lib.check(_lib.load().katz_tc05_clear_status(), "katz_tc05_clear_status")
+    ctrl[64 + 1] = 7
+    out2 = ops.attention(q, gathered[0][:, :, :C], gathered[0][:, :, C:], H, kv_chunks=chunks, peer=(ctrl.data_ptr(), me))
+    assert ops.tc05_status() == 0
+    assert torch.equal(out2, out)
+
+
 @pytest.mark.parametrize("gemm", ["tc05", "mma"])
 def test_halo_padded_convolutions(cuda_device, gemm, monkeypatch):
     monkeypatch.setenv("KATZ_GEMM", gemm)
