@@ -86,6 +86,9 @@ __global__ void __launch_bounds__(ATHREADS) attention_d64_kernel(const __half* _
         const unsigned char* k_s = sK[t & 1];
         const unsigned char* v_s = sV[t & 1];
 
+        // 16-key groups of this tile that hold at least one key (the 77 text tokens fill 4 + 1 of the 8 groups of two tiles):
+        // the others are skipped in both MMAs and stay masked
+        const int kgroups = min(4, (Sk - t * ABN + 15) >> 4);
         float s[8][4];
 #pragma unroll
         for (int i = 0; i < 8; ++i)
@@ -95,6 +98,7 @@ __global__ void __launch_bounds__(ATHREADS) attention_d64_kernel(const __half* _
         for (int ks = 0; ks < 4; ++ks) {
 #pragma unroll
             for (int np = 0; np < 4; ++np) {
+                if (np >= kgroups) continue;
                 uint32_t bfr[4];
                 int r = np * 16 + (lane & 7) + ((lane >> 4) << 3);
                 int ch = ks * 2 + ((lane >> 3) & 1);
@@ -150,6 +154,7 @@ __global__ void __launch_bounds__(ATHREADS) attention_d64_kernel(const __half* _
         // O += P V
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {  // 16 keys per step
+            if (kk >= kgroups) continue;
             uint32_t pf[4];
             pf[0] = pack_half2(s[kk * 2][0], s[kk * 2][1]);
             pf[1] = pack_half2(s[kk * 2][2], s[kk * 2][3]);

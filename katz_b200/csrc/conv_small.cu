@@ -23,6 +23,7 @@ struct ConvSmallParams {
     const __half* bias;
     __half* Y;
     int B, Hin, Win, Cin, Cout, Hout, Wout, pad_h, act;
+    int n_split;      // output-channel passes spread over grid.z (1: one CTA runs all passes over its patch)
 };
 
 // CIN: input channels as held in shared memory (a multiple of 16; 8 real channels are padded with zeros). S: stride.
@@ -42,7 +43,7 @@ __global__ void __launch_bounds__(CS_THREADS) conv3x3_small_kernel(const ConvSma
     unsigned char* s_patch = smem;
     unsigned char* s_w = smem + ((PH * PW * PS + 127) / 128) * 128;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int ox0 = blockIdx.x * CS_TW, oy0 = blockIdx.y * TH, b = blockIdx.z;
+    const int ox0 = blockIdx.x * CS_TW, oy0 = blockIdx.y * TH, b = blockIdx.z / p.n_split, pass = blockIdx.z - b * p.n_split;
     const int iy0 = oy0 * S - p.pad_h, ix0 = ox0 * S - 1;
     const int cin_chunks = p.Cin / 8;                      // 16-byte chunks that exist in global memory per pixel
 
@@ -61,7 +62,8 @@ __global__ void __launch_bounds__(CS_THREADS) conv3x3_small_kernel(const ConvSma
     const int my_row = S == 1 ? warp : warp >> 1;          // output row of this warp inside the tile
     const int my_x0 = S == 1 ? 0 : (warp & 1) * 16;        // first output column of its first 16-pixel block
 
-    for (int n0 = 0; n0 < p.Cout; n0 += NC) {
+    const int n_first = p.n_split > 1 ? pass * NC : 0, n_end = p.n_split > 1 ? min(p.Cout, n_first + NC) : p.Cout;
+    for (int n0 = n_first; n0 < n_end; n0 += NC) {
         const int nc = min(NC, p.Cout - n0);            // output channels of this pass (a multiple of 8)
         __syncthreads();                                   // the previous pass has finished reading s_w
         // ---- weights of this pass: rows n0 .. n0+nc-1, [tap][CIN] with zero padding of missing input channels
@@ -160,9 +162,15 @@ static int launch_conv_small(const ConvSmallParams& p, cudaStream_t st) {
         if (e != cudaSuccess) return (int)e;
         attr = true;
     }
-    dim3 grid(ceil_div(p.Wout, CS_TW), ceil_div(p.Hout, TH), p.B);
+    // a layer with many output channels on a small image (the UNet's conv_in: 8 -> 320 channels at 128 x 128) has few
+    // tiles and many passes: with a patch this cheap to reload, the passes go on the grid as well
+    ConvSmallParams q = p;
+    const int passes = ceil_div(p.Cout, NC);
+    const long long tiles = (long long)ceil_div(p.Wout, CS_TW) * ceil_div(p.Hout, TH) * p.B;
+    q.n_split = (CIN <= 16 && passes > 1 && tiles < 592) ? passes : 1;
+    dim3 grid(ceil_div(p.Wout, CS_TW), ceil_div(p.Hout, TH), p.B * q.n_split);
     if (grid.y > 65535 || grid.z > 65535) return KATZ_ESIZE;
-    launch_k(conv3x3_small_kernel<CIN, S, NC>, grid, CS_THREADS, smem, st, p);
+    launch_k(conv3x3_small_kernel<CIN, S, NC>, grid, CS_THREADS, smem, st, q);
     KATZ_LAUNCH_RET();
 }
 

@@ -799,9 +799,12 @@ static int pick_bn(int m_tiles, int n_out, bool geglu, bool pair) {
         const int out_w = geglu ? bn / 2 : bn;
         const long long tiles = (long long)m_tiles * ceil_div(n_out, out_w);
         const long long waves = (tiles + sms - 1) / sms;
-        // per-tile time ~ MMA time (prop. to bn) + fixed overhead per tile (epilogue drain, barrier round trips)
-        // (the GEGLU epilogue is several times heavier per tile: 72 fits the measured 128- and 256-wide launches)
-        const double cost = (double)waves * (bn + (geglu ? 72.0 : 24.0));
+        // per-tile time: a k-step of a CTA pair is bound by shared-memory bandwidth, (128 + bn/2) x 128 B in and the same
+        // out at 128 B/clk = 256 + bn cycles (2 bn of tcgen05.mma fit under it up to bn = 256), plus the tile's fixed
+        // overhead (epilogue drain, barrier round trips). Measured against forced widths on the step's shapes: the model
+        // picks the fastest or a width within 1 % of it everywhere.
+        // (GEGLU: the epilogue is several times heavier per tile and hides less: 72 fits the measured 128- and 256-wide launches)
+        const double cost = (double)waves * (bn + (geglu ? 72.0 : 280.0));
         if (cost < best_cost) {
             best_cost = cost;
             best = bn;
