@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(F32_THREADS, 1) lora_merge_f32_ws_kernel(const
     if (warp < 4) {
         // ------------------------------------------------------------------------------------ fold + write-back (128 threads)
         const int row = tid;
-        for (int j = 0, tile; (tile = tile_of(j)) >= 0; ++j) {
+        for (int j = 0; tile_of(j) >= 0; ++j) {
             const int s = j % F32_NW, b = j & 1;
             ok = mbar_wait(wfull0 + 8 * s, (j / F32_NW) & 1) && mbar_wait(dfull0 + 8 * b, (j >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);
@@ -253,7 +253,7 @@ __global__ void __launch_bounds__(F32_THREADS, 1) lora_merge_f32_ws_kernel(const
         // ------------------------------------------------------------------------------------ MMA issuer (one thread)
         if (elect_one()) {
             int bands = 0;
-            for (int j = 0, tile; (tile = tile_of(j)) >= 0; ++j) {
+            for (int j = 0; tile_of(j) >= 0; ++j) {
                 const int s = j % F32_NA, b = j & 1;
                 if (!mbar_wait(afull0 + 8 * s, (j / F32_NA) & 1)) { ok = false; break; }
                 if (!mbar_wait(dempty0 + 8 * b, ((j >> 1) & 1) ^ 1)) { ok = false; break; }
